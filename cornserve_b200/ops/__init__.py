@@ -1,0 +1,397 @@
+"""Operator front-end.
+
+Every function takes torch tensors.  CUDA bf16 tensors go to the hand-written sm_100a kernels in
+``libcornserve_b200.so`` (tcgen05 GEMM and attention, fused norms / rotary / gather kernels);
+CPU tensors go to the fp32 restatements in :mod:`cornserve_b200.ops.reference`.  There is no
+PyTorch-kernel fallback for CUDA tensors: a missing library raises.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib, reference
+from .reference import ACTS
+
+__all__ = [
+    "linear", "swiglu_linear", "rms_norm", "layer_norm", "rope_", "mrope_table", "rope_kv_write_",
+    "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
+    "flow_step_", "pcm16", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
+]
+
+_launches = 0
+
+
+def kernel_launches() -> int:
+    """Number of launches of this library's kernels issued through this module so far."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _chk(rc: int, name: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+
+
+def check_error(where: str = "") -> None:
+    _lib.check_error(where)
+
+
+def _as2d(x: torch.Tensor) -> torch.Tensor:
+    if x.dim() == 2:
+        return x
+    return x.reshape(-1, x.shape[-1])
+
+
+def _rowmajor(x: torch.Tensor) -> torch.Tensor:
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    return x
+
+
+# --------------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------------
+def linear(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    *,
+    act: str | None = None,
+    residual: torch.Tensor | None = None,
+    gate: torch.Tensor | None = None,
+    gate_rows_per_batch: int = 1,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    bn: int = 0,
+    stages: int = 0,
+) -> torch.Tensor:
+    """``act(x @ w.T + bias) * gate + residual`` with w in the nn.Linear layout ``[N, K]``.
+
+    ``gate`` is ``[rows / gate_rows_per_batch, N]`` (one gate row per batch element, as in AdaLN).
+    """
+    shape = x.shape
+    x2 = _rowmajor(_as2d(x))
+    if not x2.is_cuda:
+        r2 = None if residual is None else _as2d(residual)
+        y = reference.linear(x2, w, bias, act, r2, gate, gate_rows_per_batch, out_dtype)
+        if out is not None:
+            out.copy_(y.view(out.shape))
+            return out
+        return y.view(*shape[:-1], w.shape[0])
+    assert x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "CUDA GEMM is bf16"
+    M, K = x2.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and w.stride(1) == 1
+    fp32 = out_dtype == torch.float32
+    if out is None:
+        out = torch.empty((M, N), device=x.device, dtype=torch.float32 if fp32 else torch.bfloat16)
+    o2 = _as2d(out)
+    r2 = None if residual is None else _rowmajor(_as2d(residual))
+    lib = _lib.load()
+    rc = lib.cs_gemm_bf16(
+        x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), o2.data_ptr(), o2.stride(0),
+        _ptr(bias), _ptr(r2), 0 if r2 is None else r2.stride(0),
+        _ptr(gate), 0 if gate is None else gate.stride(0), gate_rows_per_batch,
+        M, N, K, ACTS[act or "none"], 0, 1 if fp32 else 0, bn, stages, _stream(),
+    )
+    _chk(rc, "cs_gemm_bf16")
+    _count()
+    return out.view(*shape[:-1], N) if out.dim() == 2 and len(shape) != 2 else out
+
+
+def swiglu_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, act: str = "silu",
+                  bn: int = 0, stages: int = 0) -> torch.Tensor:
+    """``act(x @ Wg.T) * (x @ Wu.T)`` with ``w = cat([Wg, Wu])`` of shape ``[2I, K]``; one kernel."""
+    shape = x.shape
+    x2 = _rowmajor(_as2d(x))
+    n = w.shape[0] // 2
+    if not x2.is_cuda:
+        return reference.swiglu_linear(x2, w, bias, act).view(*shape[:-1], n)
+    M, K = x2.shape
+    out = torch.empty((M, n), device=x.device, dtype=torch.bfloat16)
+    lib = _lib.load()
+    rc = lib.cs_gemm_bf16(
+        x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+        _ptr(bias), None, 0, None, 0, 1, M, n, K, ACTS[act], 1, 0, bn, stages, _stream(),
+    )
+    _chk(rc, "cs_gemm_bf16(swiglu)")
+    _count()
+    return out.view(*shape[:-1], n)
+
+
+# --------------------------------------------------------------------------------------------
+# norms
+# --------------------------------------------------------------------------------------------
+def _norm(x, w, b, eps, mode, residual, scale, shift, rows_per_batch):
+    shape = x.shape
+    x2 = _rowmajor(_as2d(x))
+    rows, H = x2.shape
+    y = torch.empty((rows, H), device=x.device, dtype=x.dtype)
+    r2 = None if residual is None else _rowmajor(_as2d(residual))
+    new_res = torch.empty_like(y) if residual is not None else None
+    lib = _lib.load()
+    rc = lib.cs_norm(
+        x2.data_ptr(), x2.stride(0), _ptr(r2), 0 if r2 is None else r2.stride(0),
+        _ptr(new_res), H, _ptr(w), _ptr(b), _ptr(scale), _ptr(shift),
+        0 if scale is None else scale.stride(0), rows_per_batch,
+        y.data_ptr(), H, rows, H, float(eps), mode, _stream(),
+    )
+    _chk(rc, "cs_norm")
+    _count()
+    y = y.view(shape)
+    if residual is not None:
+        return y, new_res.view(shape)
+    return y
+
+
+def rms_norm(x, w, eps: float = 1e-6, residual=None, gemma: bool = False):
+    """RMSNorm in fp32.  With ``residual`` returns ``(norm(x + residual), x + residual)``."""
+    if not x.is_cuda:
+        return reference.rms_norm(x, w, eps, residual, gemma)
+    return _norm(x, w, None, eps, 1 if gemma else 0, residual, None, None, 1)
+
+
+def layer_norm(x, w, b, eps: float = 1e-5, scale=None, shift=None, rows_per_batch: int = 1, residual=None):
+    """LayerNorm; optional AdaLN modulation ``y * (1 + scale[b]) + shift[b]`` with one row per batch."""
+    if not x.is_cuda:
+        return reference.layer_norm(x, w, b, eps, scale, shift, rows_per_batch, residual)
+    return _norm(x, w, b, eps, 2, residual, scale, shift, rows_per_batch)
+
+
+# --------------------------------------------------------------------------------------------
+# rotary
+# --------------------------------------------------------------------------------------------
+def rope_(x: torch.Tensor, cs: torch.Tensor, rot: int | None = None) -> torch.Tensor:
+    """In-place rotate-half RoPE on ``x`` = ``[T, heads, d]`` (a view with token stride is fine)."""
+    T, heads, d = x.shape
+    rot = rot or d
+    if not x.is_cuda:
+        x.copy_(reference.rope(x, cs, rot))
+        return x
+    assert x.stride(2) == 1 and x.stride(1) == d and cs.dtype == torch.float32 and cs.is_contiguous()
+    lib = _lib.load()
+    _chk(lib.cs_rope(x.data_ptr(), x.stride(0), T, heads, d, rot, cs.data_ptr(), _stream()), "cs_rope")
+    _count()
+    return x
+
+
+def mrope_table(positions: torch.Tensor, half: int, theta: float, sections=None) -> torch.Tensor:
+    """cos/sin table ``[T, 2, half]`` from ``positions`` ``[3, T]`` (int32) with M-RoPE sections."""
+    sections = sections or [half, 0, 0]
+    if not positions.is_cuda:
+        return reference.mrope_table(positions, half, theta, sections)
+    positions = positions.to(torch.int32).contiguous()
+    T = positions.shape[1]
+    cs = torch.empty((T, 2, half), device=positions.device, dtype=torch.float32)
+    lib = _lib.load()
+    _chk(lib.cs_mrope_table(positions.data_ptr(), T, half, float(theta), sections[0], sections[1],
+                            cs.data_ptr(), _stream()), "cs_mrope_table")
+    _count()
+    return cs
+
+
+def rope_kv_write_(qkv: torch.Tensor, Hq: int, Hkv: int, d: int, cs: torch.Tensor, cache: torch.Tensor,
+                   slot: torch.Tensor) -> torch.Tensor:
+    """Rotate q (in place) and k, and append k, v to the paged cache ``[pages, 2, Hkv, page, d]``.
+
+    Returns the query view ``[T, Hq, d]`` into ``qkv``.
+    """
+    T = qkv.shape[0]
+    page = cache.shape[3]
+    if not qkv.is_cuda:
+        q = reference.rope_kv_write(qkv, Hq, Hkv, d, cs, cache, slot, page)
+        return q
+    assert qkv.stride(1) == 1 and slot.dtype == torch.int32
+    lib = _lib.load()
+    _chk(lib.cs_rope_kv_write(qkv.data_ptr(), qkv.stride(0), T, Hq, Hkv, d, cs.data_ptr(), cache.data_ptr(),
+                              slot.data_ptr(), page, _stream()), "cs_rope_kv_write")
+    _count()
+    return qkv[:, : Hq * d].view(T, Hq, d)
+
+
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = None, causal: bool = False,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """Packed variable-length attention.  q ``[Tq, Hq, d]``, k/v ``[Tk, Hkv, d]`` (strided views are
+    fine as long as heads are ``d`` apart); ``cu_*`` are int32 prefix sums.  Returns ``[Tq, Hq, d]``."""
+    Tq, Hq, d = q.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        o = reference.attention_varlen(q, k, v, cu_q, cu_k, scale, causal)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    Tk, Hkv, _ = k.shape
+    for t in (q, k, v):
+        assert t.stride(2) == 1 and t.stride(1) == d and t.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty((Tq, Hq, d), device=q.device, dtype=torch.bfloat16)
+    B = cu_q.numel() - 1
+    lib = _lib.load()
+    rc = lib.cs_attention(
+        q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+        out.data_ptr(), out.stride(0), cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
+        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, _stream(),
+    )
+    _chk(rc, "cs_attention")
+    _count()
+    return out
+
+
+def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: float | None = None,
+                    causal: bool = True, pack_gqa: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of packed queries over a paged KV cache ``[pages, 2, Hkv, 128, d]``.
+
+    ``kv_len[s]`` counts the keys of sequence ``s`` *including* the ones just appended for these
+    queries.  ``pack_gqa`` packs the query heads of one KV head into one tile (decode)."""
+    Tq, Hq, d = q.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        o = reference.attention_paged(q, cache, block_table, kv_len, cu_q, scale, causal)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    pages, _, Hkv, page, _ = cache.shape
+    assert page == 128, "the paged kernel uses 128-token pages"
+    assert q.stride(2) == 1 and q.stride(1) == d and cache.is_contiguous()
+    if out is None:
+        out = torch.empty((Tq, Hq, d), device=q.device, dtype=torch.bfloat16)
+    B = cu_q.numel() - 1
+    lib = _lib.load()
+    rc = lib.cs_attention(
+        q.data_ptr(), q.stride(0), cache.data_ptr(), 0, None, 0, out.data_ptr(), out.stride(0),
+        cu_q.data_ptr(), None, kv_len.data_ptr(), block_table.data_ptr(), block_table.stride(0), pages,
+        B, Tq, 0, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 1 if pack_gqa else 0, _stream(),
+    )
+    _chk(rc, "cs_attention(paged)")
+    _count()
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# misc
+# --------------------------------------------------------------------------------------------
+def act_mul(gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(gu[..., :I]) * gu[..., I:]``."""
+    if not gu.is_cuda:
+        return reference.act_mul(gu, act)
+    g2 = _rowmajor(_as2d(gu))
+    rows, two_i = g2.shape
+    n = two_i // 2
+    y = torch.empty((rows, n), device=gu.device, dtype=gu.dtype)
+    lib = _lib.load()
+    _chk(lib.cs_act_mul(g2.data_ptr(), g2.stride(0), y.data_ptr(), n, rows, n, ACTS[act], _stream()), "cs_act_mul")
+    _count()
+    return y.view(*gu.shape[:-1], n)
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[i] = src[idx[i]]`` for 2-D ``src`` (rows of a multiple of 16 bytes)."""
+    if not src.is_cuda:
+        r = src[idx.long()]
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    n = idx.numel()
+    row_bytes = src.shape[1] * src.element_size()
+    if out is None:
+        out = torch.empty((n, src.shape[1]), device=src.device, dtype=src.dtype)
+    idx = idx.to(torch.int32)
+    lib = _lib.load()
+    _chk(lib.cs_gather_rows(src.data_ptr(), src.stride(0) * src.element_size(), out.data_ptr(),
+                            out.stride(0) * out.element_size(), idx.data_ptr(), n, row_bytes, 0, _stream()),
+         "cs_gather_rows")
+    _count()
+    return out
+
+
+def scatter_rows_(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """``dst[idx[i]] = src[i]`` (negative indices are skipped)."""
+    if not dst.is_cuda:
+        ok = idx >= 0
+        dst[idx[ok].long()] = src[ok]
+        return dst
+    n = idx.numel()
+    row_bytes = src.shape[1] * src.element_size()
+    idx = idx.to(torch.int32)
+    lib = _lib.load()
+    _chk(lib.cs_gather_rows(src.data_ptr(), src.stride(0) * src.element_size(), dst.data_ptr(),
+                            dst.stride(0) * dst.element_size(), idx.data_ptr(), n, row_bytes, 1, _stream()),
+         "cs_gather_rows(scatter)")
+    _count()
+    return dst
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Greedy sampling: int32 arg-max of each row (lowest index wins ties)."""
+    if not logits.is_cuda:
+        return reference.argmax(logits)
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty((rows,), device=logits.device, dtype=torch.int32)
+    lib = _lib.load()
+    _chk(lib.cs_argmax(logits.data_ptr(), logits.stride(0), rows, V, 1 if logits.dtype == torch.float32 else 0,
+                       out.data_ptr(), _stream()), "cs_argmax")
+    _count()
+    return out
+
+
+def flow_step_(x: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor | None, cfg: float, dt: float,
+               norm_rescale: bool = False) -> torch.Tensor:
+    """In-place flow-matching Euler step with classifier-free guidance on fp32 latents ``[rows, C]``."""
+    if not x.is_cuda:
+        x.copy_(reference.flow_step(x, cond, uncond, cfg, dt, norm_rescale))
+        return x
+    rows, C = x.shape
+    assert x.dtype == torch.float32 and cond.dtype == torch.bfloat16 and cond.is_contiguous()
+    lib = _lib.load()
+    _chk(lib.cs_flow_step(x.data_ptr(), cond.data_ptr(), _ptr(uncond), rows, C, float(cfg), float(dt),
+                          1 if norm_rescale else 0, _stream()), "cs_flow_step")
+    _count()
+    return x
+
+
+def pcm16(x: torch.Tensor) -> torch.Tensor:
+    """fp32 waveform in [-1, 1] -> int16 PCM."""
+    if not x.is_cuda:
+        return reference.pcm16(x)
+    xf = x.float().contiguous()
+    y = torch.empty(xf.shape, device=x.device, dtype=torch.int16)
+    lib = _lib.load()
+    _chk(lib.cs_pcm16(xf.data_ptr(), y.data_ptr(), xf.numel(), _stream()), "cs_pcm16")
+    _count()
+    return y
+
+
+def l2_flush(buf: torch.Tensor, value: int = 0) -> None:
+    """Overwrite ``buf`` (should be larger than L2) to evict cached lines between timed iterations."""
+    if not buf.is_cuda:
+        return
+    lib = _lib.load()
+    _chk(lib.cs_l2_flush(buf.data_ptr(), buf.numel() * buf.element_size(), value, _stream()), "cs_l2_flush")
+    _count()

@@ -1,0 +1,386 @@
+// bf16 GEMM for sm_100a:  C[M,N] = epilogue(A[M,K] * W[N,K]^T)
+//
+// Persistent, warp-specialised kernel.  One CTA per SM walks a list of 128 x BN output tiles:
+//   warp 0 (one lane)  : TMA producer, fills a ring of (A,B) K-blocks of 64 columns
+//   warp 1 (one lane)  : issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
+//                        accumulators, releases ring slots with tcgen05.commit
+//   warps 2..5         : epilogue; each warp owns 32 TMEM lanes (= 32 output rows), reads the
+//                        accumulator with tcgen05.ld and applies bias / activation / gate /
+//                        residual / SwiGLU before storing bf16 (or fp32)
+// While the epilogue drains accumulator i, the MMA warp already fills accumulator i^1.
+//
+// Operands are K-major (A row-major [M,K]; W is the nn.Linear layout [N,K]), staged by TMA with
+// the 128-byte swizzle; edges in M, N and K are handled by TMA zero fill plus masked stores.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int MAX_STAGES = 16;
+constexpr int GROUP_M = 16;
+
+enum Act : int { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_QUICK_GELU = 4, ACT_RELU = 5 };
+
+struct GemmParams {
+  int M, N, K;            // N = number of output columns
+  void* C;                // bf16 or fp32 [M, ldc]
+  long long ldc;
+  const __nv_bfloat16* bias;      // [N] (or [2N] for SwiGLU), may be null
+  const __nv_bfloat16* residual;  // [M, ldr], may be null
+  long long ldr;
+  const __nv_bfloat16* gate;      // [M / gate_rpb, ldg] multiplicative gate applied before the residual
+  long long ldg;
+  int gate_rpb;
+  int act;
+  int out_fp32;
+  int stages;
+  int a_rows;             // rows of the A box actually fetched (<= 128)
+  int up_row_offset;      // SwiGLU: row of W where the "up" half starts
+  uint32_t idesc;
+  int* err;
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case ACT_GELU_TANH: {
+      float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case ACT_SILU: return x / (1.0f + __expf(-x));
+    case ACT_QUICK_GELU: return x / (1.0f + __expf(-1.702f * x));
+    case ACT_RELU: return fmaxf(x, 0.0f);
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  int per_band = GROUP_M * tiles_n;
+  int band = t / per_band;
+  int r = t - band * per_band;
+  int m_first = band * GROUP_M;
+  int gm = min(GROUP_M, tiles_m - m_first);
+  tm = m_first + (r % gm);
+  tn = r / gm;
+}
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[MAX_STAGES];
+  __shared__ uint64_t empty_bar[MAX_STAGES];
+  __shared__ uint64_t acc_full[2];
+  __shared__ uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN_OUT - 1) / BN_OUT;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = static_cast<uint32_t>(p.a_rows * BK * 2 + B_BYTES);
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN_OUT;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp, p.err, CS_ERR_TIMEOUT_SLOT)) { ok = false; break; }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], tx_bytes);
+          tma_load_2d(sA, &tmA, kb * BK, m0, &full_bar[stage]);
+          if (SWIGLU) {
+            tma_load_2d(sB, &tmB, kb * BK, n0, &full_bar[stage]);
+            tma_load_2d(sB + B_BYTES / 2, &tmB, kb * BK, p.up_row_offset + n0, &full_bar[stage]);
+          } else {
+            tma_load_2d(sB, &tmB, kb * BK, n0, &full_bar[stage]);
+          }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------ MMA issuer --------------------------------
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abortp, p.err, CS_ERR_TIMEOUT_EPI)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abortp, p.err, CS_ERR_TIMEOUT_TMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = umma_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = umma_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // -------------------------------- epilogue ----------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may touch
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN_OUT;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abortp, p.err, CS_ERR_TIMEOUT_MMA)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const bool row_ok = row < p.M;
+      const __nv_bfloat16* gate_row =
+          (p.gate != nullptr && row_ok) ? p.gate + static_cast<long long>(row / p.gate_rpb) * p.ldg : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN_OUT / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t v[32];
+        float f[32];
+        tmem_ld32(t_row + c * 32, v);
+        if (SWIGLU) {
+          uint32_t u[32];
+          tmem_ld32(t_row + BN_OUT + c * 32, u);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float g = __uint_as_float(v[j]);
+            float up = __uint_as_float(u[j]);
+            if (p.bias != nullptr && col0 + j < p.N) {
+              g += __bfloat162float(p.bias[col0 + j]);
+              up += __bfloat162float(p.bias[p.N + col0 + j]);
+            }
+            f[j] = apply_act(g, p.act) * up;
+          }
+        } else {
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(v[j]);
+            if (p.bias != nullptr && col0 + j < p.N) x += __bfloat162float(p.bias[col0 + j]);
+            f[j] = apply_act(x, p.act);
+          }
+        }
+        if (row_ok) {
+          const bool full = (col0 + 32 <= p.N);
+          if (gate_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) f[j] *= __bfloat162float(gate_row[col0 + j]);
+          }
+          if (p.residual != nullptr) {
+            const __nv_bfloat16* rr = p.residual + static_cast<long long>(row) * p.ldr + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(rr) & 15) == 0)) {
+              const uint4* r4 = reinterpret_cast<const uint4*>(rr);
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4) {
+                uint4 w = r4[j4];
+                f[j4 * 8 + 0] += bf16lo(w.x); f[j4 * 8 + 1] += bf16hi(w.x);
+                f[j4 * 8 + 2] += bf16lo(w.y); f[j4 * 8 + 3] += bf16hi(w.y);
+                f[j4 * 8 + 4] += bf16lo(w.z); f[j4 * 8 + 5] += bf16hi(w.z);
+                f[j4 * 8 + 6] += bf16lo(w.w); f[j4 * 8 + 7] += bf16hi(w.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) f[j] += __bfloat162float(rr[j]);
+            }
+          }
+          if (p.out_fp32) {
+            float* out = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+              float4* o4 = reinterpret_cast<float4*>(out);
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4)
+                o4[j4] = make_float4(f[j4 * 4], f[j4 * 4 + 1], f[j4 * 4 + 2], f[j4 * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) out[j] = f[j];
+            }
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+              uint4* o4 = reinterpret_cast<uint4*>(out);
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4) {
+                uint4 w;
+                w.x = pack_bf16x2(f[j4 * 8 + 0], f[j4 * 8 + 1]);
+                w.y = pack_bf16x2(f[j4 * 8 + 2], f[j4 * 8 + 3]);
+                w.z = pack_bf16x2(f[j4 * 8 + 4], f[j4 * 8 + 5]);
+                w.w = pack_bf16x2(f[j4 * 8 + 6], f[j4 * 8 + 7]);
+                o4[j4] = w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) out[j] = __float2bfloat16(f[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, bool SWIGLU>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
+  constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
+  const int stage_bytes = BM * BK * 2 + BN * BK * 2;
+  int stages = p.stages;
+  const int max_smem = 220 * 1024;
+  if (stages <= 0) stages = 8;
+  while (stages > 2 && stages * stage_bytes + 1024 > max_smem) --stages;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  p.stages = stages;
+  const int smem = stages * stage_bytes + 1024;
+  static bool attr_done[64] = {false};
+  auto kern = gemm_bf16_kernel<BN, SWIGLU>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!attr_done[dev]) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    attr_done[dev] = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN_OUT - 1) / BN_OUT);
+  int grid = tiles < cs_num_sms() ? tiles : cs_num_sms();
+  if (grid < 1) return 0;
+  p.idesc = umma_idesc_bf16(128, BN, 0, 0);
+  kern<<<grid, 192, smem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+}  // namespace
+
+// C[M,N] = act(A[M,K] W[N,K]^T + bias) * gate + residual         (swiglu == 0)
+// C[M,N] = act(A Wg^T + bg) * (A Wu^T + bu), W = [Wg; Wu] ([2N,K]) (swiglu == 1)
+// All matrices bf16 row-major with the given leading dimensions (elements); lda/ldw must be
+// multiples of 8.  `bn` picks the tile width (0 = choose from the problem size).
+CS_API int cs_gemm_bf16(const void* A, long long lda, const void* W, long long ldw, void* C,
+                        long long ldc, const void* bias, const void* residual, long long ldr,
+                        const void* gate, long long ldg, int gate_rpb, int M, int N, int K, int act,
+                        int swiglu, int out_fp32, int bn, int stages, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (lda & 7) || (ldw & 7)) return -1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
+  p.ldg = ldg;
+  p.gate_rpb = gate_rpb > 0 ? gate_rpb : 1;
+  p.act = act;
+  p.out_fp32 = out_fp32;
+  p.stages = stages;
+  p.up_row_offset = N;
+  p.err = cs_error_word();
+  p.a_rows = M >= BM ? BM : ((M + 7) & ~7);
+
+  const int sms = cs_num_sms();
+  const int tiles_m = (M + BM - 1) / BM;
+  if (bn == 0) {
+    if (swiglu) {
+      bn = (tiles_m * ((N + 127) / 128) >= sms) ? 256 : 128;
+    } else {
+      bn = 256;
+      while (bn > 32 && tiles_m * ((N + bn - 1) / bn) < sms) bn >>= 1;
+      if (M > 2048 && bn < 128) bn = 128;
+    }
+  }
+  const int w_rows = swiglu ? 2 * N : N;
+  CUtensorMap tmA, tmB;
+  if (cs_encode_tmap_2d(&tmA, A, K, M, lda * 2, BK, p.a_rows, 2, 1) != 0) return -2;
+  const int b_box = swiglu ? bn / 2 : bn;
+  if (cs_encode_tmap_2d(&tmB, W, K, w_rows, ldw * 2, BK, b_box, 2, 1) != 0) return -3;
+
+  if (swiglu) {
+    switch (bn) {
+      case 256: return launch<256, true>(tmA, tmB, p, stream);
+      case 128: return launch<128, true>(tmA, tmB, p, stream);
+      case 64: return launch<64, true>(tmA, tmB, p, stream);
+      default: return -4;
+    }
+  }
+  switch (bn) {
+    case 256: return launch<256, false>(tmA, tmB, p, stream);
+    case 128: return launch<128, false>(tmA, tmB, p, stream);
+    case 64: return launch<64, false>(tmA, tmB, p, stream);
+    case 32: return launch<32, false>(tmA, tmB, p, stream);
+    default: return -4;
+  }
+}

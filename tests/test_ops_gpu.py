@@ -1,0 +1,184 @@
+"""Numerics of the sm_100a kernels against the fp32 PyTorch restatements (GPU only)."""
+
+import math
+
+import pytest
+import torch
+
+from cornserve_b200 import ops
+from cornserve_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(a, b, atol, rtol, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).float().mean().item()
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    assert bad < 1e-3 and cos > 0.999, f"{name}: max err {err.max().item():.4g}, frac bad {bad:.4g}, cos {cos:.6f}"
+
+
+@pytest.fixture(autouse=True)
+def _no_kernel_error():
+    yield
+    torch.cuda.synchronize()
+    ops.check_error("after test")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 200, 136), (4784, 3840, 1280),
+                                   (1000, 1280, 1712), (8, 4608, 3584), (64, 3584, 18944)])
+@pytest.mark.parametrize("bn", [0, 32, 64, 128, 256])
+def test_gemm_plain(M, N, K, bn):
+    torch.manual_seed(0)
+    x, w = _rand(M, K), _rand(N, K, scale=K ** -0.5)
+    y = ops.linear(x, w, bn=bn)
+    _close(y, ref.linear(x, w, out_dtype=torch.float32), 2e-2, 2e-2, f"gemm {M}x{N}x{K} bn={bn}")
+
+
+@pytest.mark.parametrize("act", ["none", "gelu", "gelu_tanh", "silu", "quick_gelu"])
+def test_gemm_epilogues(act):
+    torch.manual_seed(1)
+    M, N, K = 515, 1280, 320
+    x, w, b, r = _rand(M, K), _rand(N, K, scale=K ** -0.5), _rand(N), _rand(M, N)
+    y = ops.linear(x, w, b, act=act, residual=r)
+    _close(y, ref.linear(x, w, b, act, r, out_dtype=torch.float32), 3e-2, 2e-2, f"epilogue {act}")
+    g = _rand(5, N)
+    y = ops.linear(x, w, b, act=act, residual=r, gate=g, gate_rows_per_batch=103)
+    _close(y, ref.linear(x, w, b, act, r, g, 103, out_dtype=torch.float32), 3e-2, 2e-2, f"gated {act}")
+    y32 = ops.linear(x, w, b, out_dtype=torch.float32)
+    assert y32.dtype == torch.float32
+    _close(y32, ref.linear(x, w, b, out_dtype=torch.float32), 1e-2, 1e-2, "fp32 out")
+
+
+@pytest.mark.parametrize("M,I,K,bn", [(700, 1712, 1280, 0), (64, 512, 256, 128), (4784, 3424, 1280, 256), (9, 96, 64, 64)])
+def test_gemm_swiglu(M, I, K, bn):
+    torch.manual_seed(2)
+    x, w, b = _rand(M, K), _rand(2 * I, K, scale=K ** -0.5), _rand(2 * I, scale=0.1)
+    y = ops.swiglu_linear(x, w, b, bn=bn)
+    _close(y, ref.swiglu_linear(x.float(), w.float(), b.float()), 3e-2, 2e-2, "swiglu")
+
+
+@pytest.mark.parametrize("H", [1280, 3584, 5120, 128])
+def test_norms(H):
+    torch.manual_seed(3)
+    x, r, w, b = _rand(77, H), _rand(77, H), _rand(H), _rand(H)
+    _close(ops.rms_norm(x, w, 1e-6), ref.rms_norm(x.float(), w, 1e-6), 2e-2, 1e-2, "rms")
+    y, nr = ops.rms_norm(x, w, 1e-6, residual=r)
+    y0, nr0 = ref.rms_norm(x, w, 1e-6, residual=r)
+    _close(y, y0, 3e-2, 2e-2, "rms+res")
+    _close(nr, nr0, 1e-2, 1e-2, "res out")
+    _close(ops.rms_norm(x, w, 1e-6, gemma=True), ref.rms_norm(x.float(), w, 1e-6, gemma=True), 3e-2, 1e-2, "gemma")
+    _close(ops.layer_norm(x, w, b, 1e-5), ref.layer_norm(x.float(), w, b, 1e-5), 3e-2, 1e-2, "ln")
+    sc, sh = _rand(7, H, scale=0.2), _rand(7, H, scale=0.2)
+    _close(ops.layer_norm(x, None, None, 1e-6, sc, sh, 11), ref.layer_norm(x.float(), None, None, 1e-6, sc, sh, 11),
+           3e-2, 1e-2, "adaln")
+
+
+def test_rope_and_tables():
+    torch.manual_seed(4)
+    T, H, d = 333, 16, 80
+    qkv = _rand(T, 3 * H * d)
+    cs = torch.stack([torch.randn(T, d // 2, device=DEV).cos(), torch.randn(T, d // 2, device=DEV).sin()], 1).contiguous()
+    q = qkv[:, : H * d].view(T, H, d)
+    want = ref.rope(q.clone(), cs)
+    ops.rope_(q, cs)
+    _close(q, want, 1e-2, 1e-2, "rope")
+    pos = torch.randint(0, 4000, (3, T), device=DEV, dtype=torch.int32)
+    t = ops.mrope_table(pos, 64, 1e6, [16, 24, 24])
+    _close(t, ref.mrope_table(pos.cpu(), 64, 1e6, [16, 24, 24]).to(DEV), 2e-3, 0, "mrope table")
+
+
+@pytest.mark.parametrize("H,d,lens,causal", [
+    (16, 80, [64, 64, 48, 64, 17], False),
+    (16, 80, [1000, 300], False),
+    (4, 128, [257, 128, 5], True),
+    (2, 64, [130], False),
+    (3, 72, [200, 9], False),
+])
+def test_attention_varlen(H, d, lens, causal):
+    torch.manual_seed(5)
+    T = sum(lens)
+    qkv = _rand(T, 3 * H * d)
+    q, k, v = (qkv[:, i * H * d: (i + 1) * H * d].view(T, H, d) for i in range(3))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    o = ops.attention_varlen(q, k, v, cu, cu, max(lens), causal=causal)
+    want = ref.attention_varlen(q.float(), k.float(), v.float(), cu.cpu(), cu.cpu(), 1 / math.sqrt(d), causal)
+    _close(o, want, 2e-2, 2e-2, f"attn H={H} d={d}")
+
+
+@pytest.mark.parametrize("q_lens,ctx", [([1, 1, 1], [300, 128, 1]), ([200, 77], [200, 500]), ([1] * 9, [1000] * 9)])
+@pytest.mark.parametrize("pack", [False, True])
+def test_attention_paged(q_lens, ctx, pack):
+    torch.manual_seed(6)
+    Hq, Hkv, d, page = 28, 4, 128, 128
+    B = len(q_lens)
+    nblk = [(c + page - 1) // page for c in ctx]
+    pages = sum(nblk) + 2
+    cache = torch.zeros(pages, 2, Hkv, page, d, device=DEV, dtype=torch.bfloat16)
+    perm = torch.randperm(pages - 1)[: sum(nblk)] + 1
+    bt = torch.zeros(B, max(nblk), dtype=torch.int32)
+    p = 0
+    for s in range(B):
+        bt[s, : nblk[s]] = perm[p: p + nblk[s]].int()
+        p += nblk[s]
+    bt = bt.to(DEV)
+    for s in range(B):
+        n = ctx[s]
+        kv = _rand(2, n, Hkv, d)
+        for j in range(nblk[s]):
+            m = min(page, n - j * page)
+            cache[bt[s, j], :, :, :m] = kv[:, j * page: j * page + m].permute(0, 2, 1, 3)
+    Tq = sum(q_lens)
+    q = _rand(Tq, Hq, d)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    kv_len = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    o = ops.attention_paged(q, cache, bt, kv_len, cu, max(q_lens), causal=True, pack_gqa=pack)
+    want = ref.attention_paged(q.cpu().float(), cache.cpu().float(), bt.cpu(), kv_len.cpu(), cu.cpu(),
+                               1 / math.sqrt(d), True)
+    _close(o, want.to(DEV), 2e-2, 2e-2, "paged attn")
+
+
+def test_rope_kv_write():
+    torch.manual_seed(7)
+    T, Hq, Hkv, d, page = 150, 28, 4, 128, 128
+    qkv = _rand(T, (Hq + 2 * Hkv) * d)
+    pos = torch.arange(T, device=DEV, dtype=torch.int32)[None].expand(3, -1).contiguous()
+    cs = ops.mrope_table(pos, d // 2, 1e6, [16, 24, 24])
+    cache = torch.zeros(4, 2, Hkv, page, d, device=DEV, dtype=torch.bfloat16)
+    slot = (torch.arange(T, device=DEV, dtype=torch.int32) + 128)
+    slot[3] = -1
+    cache_ref = cache.clone().cpu()
+    q_ref = ref.rope_kv_write(qkv.clone().cpu(), Hq, Hkv, d, cs.cpu(), cache_ref, slot.cpu(), page)
+    q = ops.rope_kv_write_(qkv, Hq, Hkv, d, cs, cache, slot)
+    _close(q, q_ref.to(DEV), 2e-2, 1e-2, "q rope")
+    _close(cache, cache_ref.to(DEV), 2e-2, 1e-2, "cache")
+
+
+def test_misc_kernels():
+    torch.manual_seed(8)
+    gu = _rand(33, 2 * 3424)
+    _close(ops.act_mul(gu), ref.act_mul(gu.float()), 2e-2, 1e-2, "act_mul")
+    src = _rand(100, 1280)
+    idx = torch.randperm(100, device=DEV)[:60].int()
+    assert torch.equal(ops.gather_rows(src, idx), src[idx.long()])
+    dst = torch.zeros(100, 1280, device=DEV, dtype=torch.bfloat16)
+    ops.scatter_rows_(dst, idx, src[:60])
+    assert torch.equal(dst[idx.long()], src[:60])
+    logits = _rand(7, 152064)
+    assert torch.equal(ops.argmax(logits).long(), logits.float().argmax(-1))
+    lf = logits.float()
+    assert torch.equal(ops.argmax(lf).long(), lf.argmax(-1))
+    x = torch.randn(64, 64, device=DEV)
+    c, u = _rand(64, 64), _rand(64, 64)
+    want = ref.flow_step(x.clone(), c, u, 4.0, -0.02, True)
+    ops.flow_step_(x, c, u, 4.0, -0.02, True)
+    _close(x, want, 1e-4, 1e-4, "flow step")
+    w = torch.rand(1000, device=DEV) * 2.4 - 1.2
+    assert (ops.pcm16(w).int() - ref.pcm16(w).int()).abs().max() <= 1
