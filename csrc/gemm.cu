@@ -36,22 +36,60 @@ struct GemmParams {
   int out_fp32;
   int stages;
   int a_rows;             // rows of the A box actually fetched (<= 128)
+  int a_bytes;            // shared-memory bytes reserved per stage for the A tile (multiple of 1024)
   int up_row_offset;      // SwiGLU: row of W where the "up" half starts
   uint32_t idesc;
   int* err;
 };
 
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-    case ACT_GELU_TANH: {
-      float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.0f + tanhf(u));
+// f[j] += bias[j] for the first n (<= 32) columns; bias + 0 is 16-byte aligned when col0 is.
+__device__ __forceinline__ void add_bias32(float (&f)[32], const __nv_bfloat16* b, int n) {
+  if (n == 32 && (reinterpret_cast<uintptr_t>(b) & 15) == 0) {
+    const uint4* b4 = reinterpret_cast<const uint4*>(b);
+#pragma unroll
+    for (int j4 = 0; j4 < 4; ++j4) {
+      const uint4 w = __ldg(b4 + j4);
+      f[j4 * 8 + 0] += bf16lo(w.x); f[j4 * 8 + 1] += bf16hi(w.x);
+      f[j4 * 8 + 2] += bf16lo(w.y); f[j4 * 8 + 3] += bf16hi(w.y);
+      f[j4 * 8 + 4] += bf16lo(w.z); f[j4 * 8 + 5] += bf16hi(w.z);
+      f[j4 * 8 + 6] += bf16lo(w.w); f[j4 * 8 + 7] += bf16hi(w.w);
     }
-    case ACT_SILU: return x / (1.0f + __expf(-x));
-    case ACT_QUICK_GELU: return x / (1.0f + __expf(-1.702f * x));
-    case ACT_RELU: return fmaxf(x, 0.0f);
-    default: return x;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < n) f[j] += __bfloat162float(b[j]);
+  }
+}
+
+// The activation is chosen once per 32 columns (uniform branch), then applied in a straight loop.
+__device__ __forceinline__ void apply_act32(float (&f)[32], int act) {
+  switch (act) {
+    case ACT_GELU_ERF:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = 0.5f * f[j] * (1.0f + erff(f[j] * 0.70710678118654752f));
+      break;
+    case ACT_GELU_TANH:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float u = 0.7978845608028654f * (f[j] + 0.044715f * f[j] * f[j] * f[j]);
+        // tanh(u) = 1 - 2 / (exp(2u) + 1)
+        f[j] = 0.5f * f[j] * (2.0f - 2.0f / (__expf(2.0f * u) + 1.0f));
+      }
+      break;
+    case ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = f[j] / (1.0f + __expf(-f[j]));
+      break;
+    case ACT_QUICK_GELU:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = f[j] / (1.0f + __expf(-1.702f * f[j]));
+      break;
+    case ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.0f);
+      break;
+    default:
+      break;
   }
 }
 
@@ -70,9 +108,9 @@ __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
-  constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  const int A_BYTES = p.a_bytes;
+  const int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
 
   extern __shared__ uint8_t smem_raw[];
@@ -195,6 +233,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int c = 0; c < BN_OUT / 32; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
+        const bool full = (col0 + 32 <= p.N);
         uint32_t v[32];
         float f[32];
         tmem_ld32(t_row + c * 32, v);
@@ -203,30 +242,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld32(t_row + BN_OUT + c * 32, u);
           tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float g = __uint_as_float(v[j]);
-            float up = __uint_as_float(u[j]);
-            if (p.bias != nullptr && col0 + j < p.N) {
-              g += __bfloat162float(p.bias[col0 + j]);
-              up += __bfloat162float(p.bias[p.N + col0 + j]);
-            }
-            f[j] = apply_act(g, p.act) * up;
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (p.bias != nullptr) {
+            add_bias32(f, p.bias + col0, full ? 32 : p.N - col0);
+            float fu[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) fu[j] = __uint_as_float(u[j]);
+            add_bias32(fu, p.bias + p.N + col0, full ? 32 : p.N - col0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(fu[j]);
           }
+          apply_act32(f, p.act);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(u[j]);
         } else {
           tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(v[j]);
-            if (p.bias != nullptr && col0 + j < p.N) x += __bfloat162float(p.bias[col0 + j]);
-            f[j] = apply_act(x, p.act);
-          }
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (p.bias != nullptr) add_bias32(f, p.bias + col0, full ? 32 : p.N - col0);
+          apply_act32(f, p.act);
         }
         if (row_ok) {
-          const bool full = (col0 + 32 <= p.N);
           if (gate_row != nullptr) {
+            const __nv_bfloat16* gr = gate_row + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(gr) & 15) == 0)) {
+              const uint4* g4 = reinterpret_cast<const uint4*>(gr);
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < p.N) f[j] *= __bfloat162float(gate_row[col0 + j]);
+              for (int j4 = 0; j4 < 4; ++j4) {
+                const uint4 w = g4[j4];
+                f[j4 * 8 + 0] *= bf16lo(w.x); f[j4 * 8 + 1] *= bf16hi(w.x);
+                f[j4 * 8 + 2] *= bf16lo(w.y); f[j4 * 8 + 3] *= bf16hi(w.y);
+                f[j4 * 8 + 4] *= bf16lo(w.z); f[j4 * 8 + 5] *= bf16hi(w.z);
+                f[j4 * 8 + 6] *= bf16lo(w.w); f[j4 * 8 + 7] *= bf16hi(w.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) f[j] *= __bfloat162float(gr[j]);
+            }
           }
           if (p.residual != nullptr) {
             const __nv_bfloat16* rr = p.residual + static_cast<long long>(row) * p.ldr + col0;
@@ -297,10 +350,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <int BN, bool SWIGLU>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
-  const int stage_bytes = BM * BK * 2 + BN * BK * 2;
+  const int stage_bytes = p.a_bytes + BN * BK * 2;
   int stages = p.stages;
   const int max_smem = 220 * 1024;
-  if (stages <= 0) stages = 8;
+  if (stages <= 0) stages = MAX_STAGES;
   while (stages > 2 && stages * stage_bytes + 1024 > max_smem) --stages;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   p.stages = stages;
@@ -350,6 +403,7 @@ CS_API int cs_gemm_bf16(const void* A, long long lda, const void* W, long long l
   p.up_row_offset = N;
   p.err = cs_error_word();
   p.a_rows = M >= BM ? BM : ((M + 7) & ~7);
+  p.a_bytes = p.a_rows * BK * 2;
 
   const int sms = cs_num_sms();
   const int tiles_m = (M + BM - 1) / BM;
