@@ -1,0 +1,1 @@
+"""Eric: the multimodal encoder executor (router -> engine -> tensor-parallel workers)."""

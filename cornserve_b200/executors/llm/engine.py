@@ -1,0 +1,380 @@
+"""LLM engine: request queue, paged-KV scheduling, batch construction, CUDA-graph decode.
+
+This is the in-process core of the LLM executor (the reference uses an external vLLM fork for this
+role; its contract is in tasklib/cornserve_tasklib/task_executors/descriptor/llm.py:68-210).
+
+Scheduling: first-come-first-served.  A step is either a *prefill* step (waiting prompts, possibly
+chunked, packed up to ``max_batched_tokens`` tokens) or a *decode burst* (``decode_burst`` tokens for
+every running sequence).  During a burst the sampled token, the positions, the key counts and the
+cache slots are advanced on the device, the whole step is replayed from a CUDA graph, and the host
+reads the produced tokens once per burst.
+"""
+
+from __future__ import annotations
+
+import enum
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Iterable
+
+import numpy as np
+import torch
+
+from ... import ops
+from ...models.qwen_llm import PAGE_SIZE, BatchMeta, LLMConfig, QwenLLM
+from .block_manager import BlockManager
+from .mrope import mrope_positions
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 256
+    ignore_eos: bool = False
+    stop_token_ids: tuple[int, ...] = ()
+
+
+@dataclass
+class MMItem:
+    """Encoder output for one image/video/audio: ``embeds`` rows replace the placeholder run that starts
+    at prompt index ``offset``."""
+
+    embeds: torch.Tensor
+    offset: int
+    grid_thw: tuple[int, int, int] | None = None
+
+
+class SeqStatus(enum.Enum):
+    WAITING = 0
+    RUNNING = 1
+    FINISHED = 2
+
+
+@dataclass
+class Sequence:
+    seq_id: str
+    prompt_ids: np.ndarray
+    params: SamplingParams = field(default_factory=SamplingParams)
+    mm_items: list[MMItem] = field(default_factory=list)
+    return_hidden: bool = False
+    positions: np.ndarray | None = None     # [3, T]
+    next_pos: int = 0
+    status: SeqStatus = SeqStatus.WAITING
+    num_computed: int = 0                   # prompt tokens already in the KV cache
+    output_ids: list[int] = field(default_factory=list)
+    hidden_chunks: list[torch.Tensor] = field(default_factory=list)
+    arrival: float = field(default_factory=time.monotonic)
+    first_token_time: float | None = None
+    finish_reason: str | None = None
+
+    @property
+    def prompt_len(self) -> int:
+        return int(self.prompt_ids.shape[0])
+
+
+@dataclass
+class EngineConfig:
+    num_pages: int = 2048
+    max_batched_tokens: int = 16384
+    max_num_seqs: int = 256
+    decode_burst: int = 8
+    use_cuda_graph: bool = True
+    graph_batch_sizes: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    max_model_len: int = 32768
+
+
+@dataclass
+class StepOutput:
+    seq_id: str
+    new_token_ids: list[int]
+    finished: bool
+    finish_reason: str | None = None
+    hidden: torch.Tensor | None = None
+
+
+class _DecodeState:
+    """Static device buffers (and the captured graph) for one decode batch-size bucket."""
+
+    def __init__(self, B: int, max_blocks: int, burst: int, device: torch.device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.B = B
+        self.input_ids = torch.zeros(B, **i32)
+        self.positions = torch.zeros(3, B, **i32)
+        self.slot = torch.zeros(B, **i32)
+        self.kv_len = torch.ones(B, **i32)
+        self.block_table = torch.zeros(B, max_blocks, **i32)
+        self.active = torch.zeros(B, **i32)
+        self.cu_q = torch.arange(B + 1, **i32)
+        self.logits_idx = torch.arange(B, **i32)
+        self.out_log = torch.zeros(max(burst, 1), B, **i32)
+        self.step_counter = torch.zeros(1, **i32)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.launches_per_replay = 0
+
+    def meta(self) -> BatchMeta:
+        return BatchMeta(self.input_ids, self.positions, self.slot, self.cu_q, self.kv_len, self.block_table,
+                         self.logits_idx, 1, True)
+
+
+class LLMEngine:
+    """Synchronous engine core.  ``add_request`` + ``step`` drive it; ``generate`` is the batch helper."""
+
+    def __init__(self, model: QwenLLM, cfg: EngineConfig | None = None):
+        self.model = model
+        self.mcfg: LLMConfig = model.cfg
+        self.cfg = cfg or EngineConfig()
+        self.device = model.device
+        self.on_gpu = self.device.type == "cuda"
+        self.blocks = BlockManager(self.cfg.num_pages)
+        self.kv_caches = model.alloc_kv_cache(self.cfg.num_pages)
+        self.max_blocks = -(-self.cfg.max_model_len // PAGE_SIZE)
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+        self._decode_states: dict[int, _DecodeState] = {}
+        self._copy_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+
+    # ---------------------------------------------------------------------------------------------
+    # requests
+    # ---------------------------------------------------------------------------------------------
+    def add_request(self, seq: Sequence) -> None:
+        if seq.positions is None:
+            grids = [it.grid_thw for it in seq.mm_items if it.grid_thw is not None]
+            if grids:
+                seq.positions, seq.next_pos = mrope_positions(
+                    seq.prompt_ids, grids, self.mcfg.image_token_id, self.mcfg.video_token_id,
+                    self.mcfg.spatial_merge_size)
+            else:
+                T = seq.prompt_len
+                seq.positions = np.broadcast_to(np.arange(T, dtype=np.int32)[None], (3, T)).copy()
+                seq.next_pos = T
+        if seq.prompt_len + seq.params.max_tokens > self.cfg.max_model_len:
+            raise ValueError("request exceeds max_model_len")
+        self.waiting.append(seq)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def abort(self, seq_id: str) -> None:
+        for q in (self.waiting, self.running):
+            for s in list(q):
+                if s.seq_id == seq_id:
+                    q.remove(s)
+                    self.blocks.free(seq_id)
+
+    # ---------------------------------------------------------------------------------------------
+    # one engine step
+    # ---------------------------------------------------------------------------------------------
+    def step(self) -> list[StepOutput]:
+        self.stats["steps"] += 1
+        batch = self._schedule_prefill()
+        if batch:
+            return self._run_prefill(batch)
+        if self.running:
+            return self._run_decode_burst()
+        return []
+
+    def _schedule_prefill(self) -> list[tuple[Sequence, int]]:
+        """Pick prompt chunks for one prefill step: unfinished chunked prefills first, then new arrivals
+        while the token budget, the sequence limit and the page pool allow.  A sequence is admitted only
+        if its whole lifetime (prompt + max_tokens) fits in free pages, so decode never runs out."""
+        budget = self.cfg.max_batched_tokens
+        batch: list[tuple[Sequence, int]] = []
+        for s in self.running:
+            if s.num_computed < s.prompt_len and budget > 0:
+                n = min(s.prompt_len - s.num_computed, budget)
+                batch.append((s, n))
+                budget -= n
+        while self.waiting and budget > 0 and len(self.running) + len(batch) < self.cfg.max_num_seqs:
+            s = self.waiting[0]
+            total = s.prompt_len + s.params.max_tokens + 1
+            if not self.blocks.can_allocate(total, s.seq_id):
+                break
+            self.waiting.popleft()
+            self.blocks.ensure(s.seq_id, total)
+            n = min(s.prompt_len, budget)
+            batch.append((s, n))
+            budget -= n
+        return batch
+
+    def _run_prefill(self, batch: list[tuple[Sequence, int]]) -> list[StepOutput]:
+        dev = self.device
+        ids, pos, slots, cu, kvl, last = [], [], [], [0], [], []
+        mm_rows, mm_idx = [], []
+        bt = np.zeros((len(batch), self.max_blocks), dtype=np.int32)
+        tok = 0
+        for b, (s, n) in enumerate(batch):
+            lo, hi = s.num_computed, s.num_computed + n
+            pages = self.blocks.ensure(s.seq_id, hi + 1)
+            bt[b, : len(pages)] = pages
+            ids.append(s.prompt_ids[lo:hi])
+            pos.append(s.positions[:, lo:hi])
+            ar = np.arange(lo, hi)
+            slots.append(np.asarray(pages, dtype=np.int64)[ar // PAGE_SIZE] * PAGE_SIZE + ar % PAGE_SIZE)
+            for it in s.mm_items:
+                a, e = max(it.offset, lo), min(it.offset + it.embeds.shape[0], hi)
+                if a < e:
+                    mm_rows.append(it.embeds[a - it.offset: e - it.offset])
+                    mm_idx.append(np.arange(a, e) - lo + tok)
+            tok += n
+            cu.append(tok)
+            kvl.append(hi)
+            last.append(tok - 1)
+        max_blk = max(1, max(-(-k // PAGE_SIZE) for k in kvl) + 1)
+        f = lambda a, dt=np.int32: self._to_dev(np.ascontiguousarray(np.asarray(a).astype(dt)))  # noqa: E731
+        m = BatchMeta(
+            input_ids=f(np.concatenate(ids)), positions=f(np.concatenate(pos, axis=1)),
+            slot_mapping=f(np.concatenate(slots)), cu_q=f(cu), kv_len=f(kvl), block_table=f(bt[:, :max_blk]),
+            logits_idx=f(last), max_q_len=max(n for _, n in batch), is_decode=False,
+        )
+        if mm_rows:
+            m.mm_embeds = torch.cat([r.to(dev, non_blocking=True) for r in mm_rows], dim=0)
+            m.mm_index = f(np.concatenate(mm_idx))
+        want_hidden = any(s.return_hidden for s, _ in batch)
+        with torch.inference_mode():
+            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden)
+        toks = next_tok.tolist()
+        self.stats["prefill_tokens"] += tok
+        outs: list[StepOutput] = []
+        now = time.monotonic()
+        for b, (s, n) in enumerate(batch):
+            s.num_computed += n
+            if s not in self.running:
+                self.running.append(s)
+            if s.return_hidden and hidden is not None:
+                s.hidden_chunks.append(hidden[cu[b]: cu[b + 1]])
+            if s.num_computed < s.prompt_len:
+                continue
+            s.status = SeqStatus.RUNNING
+            s.first_token_time = now
+            s.output_ids.append(int(toks[b]))
+            outs.append(self._emit(s, [int(toks[b])]))
+        self._reap()
+        return outs
+
+    # ---------------------------------------------------------------------------------------------
+    # decode
+    # ---------------------------------------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in self.cfg.graph_batch_sizes:
+            if b >= n:
+                return b
+        return n
+
+    def _run_decode_burst(self) -> list[StepOutput]:
+        seqs = [s for s in self.running if s.status is SeqStatus.RUNNING]
+        if not seqs:
+            return []
+        burst = max(1, min(self.cfg.decode_burst, min(s.params.max_tokens - len(s.output_ids) for s in seqs)))
+        n = len(seqs)
+        B = self._bucket(n) if (self.on_gpu and self.cfg.use_cuda_graph) else n
+        st = self._decode_states.get(B)
+        if st is None:
+            st = self._decode_states[B] = _DecodeState(B, self.max_blocks, self.cfg.decode_burst, self.device)
+        # host-side batch state
+        ids = np.zeros(B, np.int32); pos = np.zeros((3, B), np.int32); slot = np.zeros(B, np.int32)
+        kvl = np.ones(B, np.int32); act = np.zeros(B, np.int32)
+        bt = np.zeros((B, self.max_blocks), np.int32)
+        for b, s in enumerate(seqs):
+            cur = s.prompt_len + len(s.output_ids) - 1  # index of the token being fed = keys already cached
+            pages = self.blocks.ensure(s.seq_id, cur + burst + 1)
+            bt[b, : len(pages)] = pages
+            ids[b] = s.output_ids[-1]
+            pos[:, b] = s.next_pos + len(s.output_ids) - 1
+            slot[b] = pages[cur // PAGE_SIZE] * PAGE_SIZE + cur % PAGE_SIZE
+            kvl[b] = cur + 1
+            act[b] = 1
+        for t, a in ((st.input_ids, ids), (st.positions, pos), (st.slot, slot), (st.kv_len, kvl), (st.active, act),
+                     (st.block_table, bt)):
+            t.copy_(self._pin(a), non_blocking=True)
+        st.step_counter.zero_()
+        with torch.inference_mode():
+            for _ in range(burst):
+                self._decode_once(st)
+        log = st.out_log[:burst].cpu().numpy()  # one sync per burst
+        self.stats["decode_tokens"] += burst * n
+        outs = []
+        for b, s in enumerate(seqs):
+            new = []
+            for t in log[:, b].tolist():
+                s.output_ids.append(int(t))
+                new.append(int(t))
+                if self._should_stop(s):
+                    break
+            outs.append(self._emit(s, new))
+        self._reap()
+        return outs
+
+    def _decode_once(self, st: _DecodeState) -> None:
+        def body():
+            tok, _ = self.model(st.meta(), self.kv_caches)
+            ops.decode_advance_(tok, st.input_ids, st.positions, st.kv_len, st.slot, st.block_table, st.active,
+                                st.out_log, st.step_counter)
+
+        if not (self.on_gpu and self.cfg.use_cuda_graph):
+            body()
+            return
+        if st.graph is None:
+            # warm-up run outside the graph (sets kernel attributes, fills allocator pools), then capture;
+            # the state is restored afterwards so the warm-up leaves no trace
+            snap = [t.clone() for t in (st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter)]
+            body()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = ops.kernel_launches()
+            with torch.cuda.graph(g):
+                body()
+            st.launches_per_replay = ops.kernel_launches() - before
+            st.graph = g
+            for t, v in zip((st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter), snap):
+                t.copy_(v)
+        st.graph.replay()
+        ops._count(st.launches_per_replay)
+
+    # ---------------------------------------------------------------------------------------------
+    # helpers
+    # ---------------------------------------------------------------------------------------------
+    def _pin(self, a: np.ndarray) -> torch.Tensor:
+        t = torch.from_numpy(a)
+        return t.pin_memory() if self.on_gpu else t
+
+    def _to_dev(self, a: np.ndarray) -> torch.Tensor:
+        return self._pin(a).to(self.device, non_blocking=True)
+
+    def _should_stop(self, s: Sequence) -> bool:
+        if len(s.output_ids) >= s.params.max_tokens:
+            s.finish_reason = "length"
+            return True
+        last = s.output_ids[-1]
+        if not s.params.ignore_eos and (last == self.mcfg.eos_token_id or last in s.params.stop_token_ids):
+            s.finish_reason = "stop"
+            return True
+        return False
+
+    def _emit(self, s: Sequence, new: list[int]) -> StepOutput:
+        done = s.finish_reason is not None or self._should_stop(s)
+        hidden = None
+        if done:
+            s.status = SeqStatus.FINISHED
+            if s.return_hidden and s.hidden_chunks:
+                hidden = torch.cat(s.hidden_chunks, dim=0)
+        return StepOutput(s.seq_id, new, done, s.finish_reason, hidden)
+
+    def _reap(self) -> None:
+        for s in [s for s in self.running if s.status is SeqStatus.FINISHED]:
+            self.running.remove(s)
+            self.blocks.free(s.seq_id)
+
+    # ---------------------------------------------------------------------------------------------
+    # batch helper
+    # ---------------------------------------------------------------------------------------------
+    def generate(self, seqs: Iterable[Sequence]) -> dict[str, list[int]]:
+        """Run the given requests to completion; returns ``seq_id -> generated token ids``."""
+        out: dict[str, list[int]] = {}
+        for s in seqs:
+            out[s.seq_id] = []
+            self.add_request(s)
+        while self.has_work():
+            for o in self.step():
+                out[o.seq_id].extend(o.new_token_ids)
+        return out

@@ -1,0 +1,319 @@
+"""Decoder-only LLM used by the own LLM executor: Qwen2 / Qwen2.5-VL / Qwen3 (dense and MoE) text models.
+
+The reference delegates this part to a vLLM fork that is not in its tree (only the contract is:
+tasklib/cornserve_tasklib/task_executors/descriptor/llm.py:68-210).  This is a from-scratch decoder
+over a paged KV cache (128-token pages) driven by flattened, mixed prefill/decode batches:
+
+  embed (+ scatter of encoder embeddings) -> L x [RMSNorm(+residual) -> qkv GEMM -> fused RoPE +
+  KV-cache append -> paged tcgen05 attention -> o_proj GEMM -> RMSNorm(+residual) -> SwiGLU GEMM ->
+  down GEMM] -> final norm -> lm_head GEMM on the last token of each sequence -> greedy arg-max.
+
+M-RoPE (3-row position ids with sections) covers Qwen2.5-VL; plain RoPE is the special case of
+three identical rows.  Tensor parallelism shards heads / MLP columns; row-parallel outputs are
+reduced over the group.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Iterable
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..parallel.state import ParallelGroup, single_group
+from .layers import (ColumnParallelLinear, Embedding, Linear, MergedColumnParallelLinear, QKVParallelLinear,
+                     RMSNorm, RowParallelLinear)
+
+PAGE_SIZE = 128
+
+
+@dataclass
+class LLMConfig:
+    hidden_size: int = 3584
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 28
+    num_key_value_heads: int = 4
+    head_dim: int | None = None
+    intermediate_size: int = 18944
+    vocab_size: int = 152064
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    mrope_section: list[int] | None = field(default_factory=lambda: [16, 24, 24])
+    attention_bias: bool = True
+    qk_norm: bool = False
+    tie_word_embeddings: bool = False
+    # mixture of experts (0 experts = dense)
+    num_experts: int = 0
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    norm_topk_prob: bool = True
+    # multimodal placeholder token ids (used by the executor to place encoder embeddings)
+    image_token_id: int = 151655
+    video_token_id: int = 151656
+    vision_start_token_id: int = 151652
+    eos_token_id: int = 151645
+    spatial_merge_size: int = 2
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    @classmethod
+    def from_hf(cls, cfg: dict) -> "LLMConfig":
+        t = dict(cfg.get("text_config") or cfg)
+        for k in ("image_token_id", "video_token_id", "vision_start_token_id"):
+            if k in cfg:
+                t.setdefault(k, cfg[k])
+        rs = t.get("rope_scaling") or cfg.get("rope_scaling") or t.get("rope_parameters") or {}
+        kw = {k: t[k] for k in cls.__dataclass_fields__.keys() if k in t}
+        if "mrope_section" in rs:
+            kw["mrope_section"] = list(rs["mrope_section"])
+        elif "mrope_section" not in kw:
+            kw["mrope_section"] = None
+        if "rope_theta" in rs:
+            kw["rope_theta"] = rs["rope_theta"]
+        mt = t.get("model_type", cfg.get("model_type", ""))
+        if "qwen3" in mt:
+            kw.setdefault("qk_norm", True)
+            kw.setdefault("attention_bias", t.get("attention_bias", False))
+        if isinstance(kw.get("eos_token_id"), list):
+            kw["eos_token_id"] = kw["eos_token_id"][0]
+        if kw.get("eos_token_id") is None:
+            kw.pop("eos_token_id", None)
+        return cls(**kw)
+
+
+@dataclass
+class BatchMeta:
+    """One engine step over a flattened batch of ``T`` tokens from ``B`` sequences."""
+
+    input_ids: torch.Tensor        # [T] int32
+    positions: torch.Tensor        # [3, T] int32
+    slot_mapping: torch.Tensor     # [T] int32 (page * 128 + offset; -1 = do not cache)
+    cu_q: torch.Tensor             # [B + 1] int32
+    kv_len: torch.Tensor           # [B] int32, keys per sequence including this step's tokens
+    block_table: torch.Tensor      # [B, max_blocks] int32
+    logits_idx: torch.Tensor       # [B] int32, flattened index of each sequence's last token
+    max_q_len: int = 1
+    is_decode: bool = False
+    mm_embeds: torch.Tensor | None = None   # [n, H] encoder rows to place into the input embeddings
+    mm_index: torch.Tensor | None = None    # [n] int32 destination rows (-1 = skip)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: LLMConfig, group: ParallelGroup, device):
+        super().__init__()
+        self.cfg, self.group = cfg, group
+        d = cfg.head_dim
+        self.qkv = QKVParallelLinear(cfg.hidden_size, d, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                     bias=cfg.attention_bias, group=group, device=device)
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * d, cfg.hidden_size, bias=False, group=group,
+                                        device=device)
+        self.hq, self.hkv = self.qkv.heads_local, self.qkv.kv_heads_local
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(d, cfg.rms_norm_eps, device=device)
+            self.k_norm = RMSNorm(d, cfg.rms_norm_eps, device=device)
+
+    def forward(self, h: torch.Tensor, cs: torch.Tensor, cache: torch.Tensor, m: BatchMeta) -> torch.Tensor:
+        d = self.cfg.head_dim
+        T = h.shape[0]
+        qkv = self.qkv(h)
+        if self.cfg.qk_norm:
+            qk = qkv[:, : (self.hq + self.hkv) * d]
+            normed_q = self.q_norm(qkv[:, : self.hq * d].reshape(-1, d)).view(T, self.hq * d)
+            normed_k = self.k_norm(qkv[:, self.hq * d: (self.hq + self.hkv) * d].reshape(-1, d)).view(T, self.hkv * d)
+            qk[:, : self.hq * d] = normed_q
+            qk[:, self.hq * d:] = normed_k
+        q = ops.rope_kv_write_(qkv, self.hq, self.hkv, d, cs, cache, m.slot_mapping)
+        o = ops.attention_paged(q, cache, m.block_table, m.kv_len, m.cu_q, m.max_q_len, causal=True,
+                                pack_gqa=m.is_decode and self.hq > self.hkv)
+        return self.o_proj(o.view(T, self.hq * d))
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: LLMConfig, group: ParallelGroup, device, intermediate: int | None = None):
+        super().__init__()
+        inter = intermediate or cfg.intermediate_size
+        self.gate_up = MergedColumnParallelLinear(cfg.hidden_size, inter, bias=False, group=group, device=device)
+        self.down = RowParallelLinear(inter, cfg.hidden_size, bias=False, group=group,
+                                      in_padded=self.gate_up.inter_padded, device=device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down(self.gate_up(x))
+
+
+class SparseMoE(nn.Module):
+    """Top-k routed experts.  Expert weights are stacked ``[E_local, ...]``; with expert parallelism each
+    rank owns ``E / ep`` experts and tokens travel by all-to-all (see ``parallel.moe``)."""
+
+    def __init__(self, cfg: LLMConfig, group: ParallelGroup, device):
+        super().__init__()
+        self.cfg, self.group = cfg, group
+        E, H, inter = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        assert E % group.size == 0
+        self.e_local = E // group.size
+        self.router = Linear(H, E, bias=False, device=device)
+        self.w_gate_up = nn.Parameter(torch.empty(self.e_local, 2 * inter, H, device=device, dtype=torch.bfloat16)
+                                      .normal_(0, 0.02), requires_grad=False)
+        self.w_down = nn.Parameter(torch.empty(self.e_local, H, inter, device=device, dtype=torch.bfloat16)
+                                   .normal_(0, 0.02), requires_grad=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from ..parallel import moe
+
+        logits = self.router(x, out_dtype=torch.float32)
+        return moe.moe_forward(x, logits, self.w_gate_up, self.w_down, self.cfg.num_experts_per_tok,
+                               self.cfg.norm_topk_prob, self.group)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: LLMConfig, group: ParallelGroup, device, ep_group: ParallelGroup | None = None):
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+        self.self_attn = Attention(cfg, group, device)
+        self.mlp = SparseMoE(cfg, ep_group or group, device) if cfg.num_experts > 0 else MLP(cfg, group, device)
+
+    def forward(self, x, residual, cs, cache, m: BatchMeta):
+        if residual is None:
+            residual = x
+            h = self.input_layernorm(x)
+        else:
+            h, residual = self.input_layernorm(x, residual=residual)
+        x = self.self_attn(h, cs, cache, m)
+        h, residual = self.post_attention_layernorm(x, residual=residual)
+        x = self.mlp(h)
+        return x, residual
+
+
+class QwenLLM(nn.Module):
+    def __init__(self, cfg: LLMConfig, group: ParallelGroup | None = None, device="cpu",
+                 ep_group: ParallelGroup | None = None):
+        super().__init__()
+        self.cfg = cfg
+        self.group = group or single_group(device)
+        self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, device=device)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, self.group, device, ep_group) for _ in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+        if cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = ColumnParallelLinear(cfg.hidden_size, cfg.vocab_size, bias=False, group=self.group,
+                                                pad_multiple=64, device=device)
+
+    @property
+    def device(self) -> torch.device:
+        return self.embed_tokens.weight.device
+
+    @property
+    def kv_heads_local(self) -> int:
+        return self.layers[0].self_attn.hkv
+
+    def alloc_kv_cache(self, num_pages: int) -> list[torch.Tensor]:
+        """One zero-initialised cache ``[pages, 2, Hkv_local, 128, d]`` per layer."""
+        shape = (num_pages, 2, self.kv_heads_local, PAGE_SIZE, self.cfg.head_dim)
+        return [torch.zeros(shape, device=self.device, dtype=self.embed_tokens.weight.dtype)
+                for _ in range(self.cfg.num_hidden_layers)]
+
+    def kv_bytes_per_page(self) -> int:
+        return 2 * self.kv_heads_local * PAGE_SIZE * self.cfg.head_dim * 2 * self.cfg.num_hidden_layers
+
+    def embed(self, m: BatchMeta) -> torch.Tensor:
+        x = self.embed_tokens(m.input_ids)
+        if m.mm_embeds is not None and m.mm_embeds.shape[0] > 0:
+            ops.scatter_rows_(x, m.mm_index, m.mm_embeds.to(x.dtype))
+        return x
+
+    def forward_hidden(self, m: BatchMeta, kv_caches: list[torch.Tensor]) -> torch.Tensor:
+        """Final-norm hidden states of every token ``[T, H]``."""
+        cfg = self.cfg
+        x = self.embed(m)
+        half = cfg.head_dim // 2
+        sections = cfg.mrope_section or [half, 0, 0]
+        cs = ops.mrope_table(m.positions, half, cfg.rope_theta, sections)
+        residual = None
+        for layer, cache in zip(self.layers, kv_caches):
+            x, residual = layer(x, residual, cs, cache, m)
+        h, _ = self.norm(x, residual=residual)
+        return h
+
+    def compute_logits(self, h_last: torch.Tensor) -> torch.Tensor:
+        if self.lm_head is None:
+            return ops.linear(h_last, self.embed_tokens.weight, out_dtype=torch.float32)
+        logits = ops.linear(h_last, self.lm_head.weight, out_dtype=torch.float32)
+        if self.group.size > 1:
+            logits = self.group.all_gather(logits, dim=-1)
+        return logits[:, : self.cfg.vocab_size]
+
+    def forward(self, m: BatchMeta, kv_caches: list[torch.Tensor], return_hidden: bool = False):
+        """Returns ``(next_token_ids [B] int32, hidden [T, H] or None)`` (greedy)."""
+        h = self.forward_hidden(m, kv_caches)
+        h_last = ops.gather_rows(h, m.logits_idx)
+        logits = self.compute_logits(h_last)
+        return ops.argmax(logits), (h if return_hidden else None)
+
+    # -- checkpoint loading -------------------------------------------------------------------------
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        """Accepts HF names with or without the ``model.`` / ``model.language_model.`` prefixes."""
+        loaded: set[str] = set()
+        for name, t in weights:
+            n = name
+            for pre in ("model.language_model.", "language_model.model.", "language_model.", "model.", "thinker.model."):
+                if n.startswith(pre):
+                    n = n[len(pre):]
+                    break
+            p = n.split(".")
+            leaf = p[-1]
+            if n == "embed_tokens.weight":
+                self.embed_tokens.weight.data.copy_(t)
+            elif n == "norm.weight":
+                self.norm.weight.data.copy_(t)
+            elif n in ("lm_head.weight", "head.weight") or name == "lm_head.weight":
+                if self.lm_head is not None:
+                    self.lm_head.load(weight=t)
+            elif p[0] == "layers":
+                layer: DecoderLayer = self.layers[int(p[1])]
+                sub = ".".join(p[2:-1])
+                kw = {leaf: t}
+                if sub == "input_layernorm":
+                    layer.input_layernorm.weight.data.copy_(t)
+                elif sub == "post_attention_layernorm":
+                    layer.post_attention_layernorm.weight.data.copy_(t)
+                elif sub in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"):
+                    layer.self_attn.qkv.load(sub[-6], **kw)
+                elif sub == "self_attn.o_proj":
+                    layer.self_attn.o_proj.load(**kw)
+                elif sub == "self_attn.q_norm":
+                    layer.self_attn.q_norm.weight.data.copy_(t)
+                elif sub == "self_attn.k_norm":
+                    layer.self_attn.k_norm.weight.data.copy_(t)
+                elif sub == "mlp.gate_proj":
+                    layer.mlp.gate_up.load("gate", **kw)
+                elif sub == "mlp.up_proj":
+                    layer.mlp.gate_up.load("up", **kw)
+                elif sub == "mlp.down_proj":
+                    layer.mlp.down.load(**kw)
+                elif sub == "mlp.gate":
+                    layer.mlp.router.load(weight=t)
+                elif sub.startswith("mlp.experts."):
+                    e = int(p[4])
+                    moe: SparseMoE = layer.mlp
+                    lo = moe.group.rank * moe.e_local
+                    if not (lo <= e < lo + moe.e_local):
+                        continue
+                    inter = self.cfg.moe_intermediate_size
+                    which = p[5]
+                    if which == "gate_proj":
+                        moe.w_gate_up.data[e - lo, :inter].copy_(t)
+                    elif which == "up_proj":
+                        moe.w_gate_up.data[e - lo, inter:].copy_(t)
+                    elif which == "down_proj":
+                        moe.w_down.data[e - lo].copy_(t)
+                else:
+                    continue
+            else:
+                continue
+            loaded.add(name)
+        return loaded

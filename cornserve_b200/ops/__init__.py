@@ -18,7 +18,7 @@ from .reference import ACTS
 __all__ = [
     "linear", "swiglu_linear", "rms_norm", "layer_norm", "rope_", "mrope_table", "rope_kv_write_",
     "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
-    "flow_step_", "pcm16", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
+    "flow_step_", "pcm16", "decode_advance_", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
 ]
 
 _launches = 0
@@ -386,6 +386,32 @@ def pcm16(x: torch.Tensor) -> torch.Tensor:
     _chk(lib.cs_pcm16(xf.data_ptr(), y.data_ptr(), xf.numel(), _stream()), "cs_pcm16")
     _count()
     return y
+
+
+def decode_advance_(sampled, input_ids, positions, kv_len, slot, block_table, active, out_log, step_counter,
+                    page: int = 128) -> None:
+    """Feed sampled tokens back as next inputs and advance positions / key counts / cache slots of the
+    active sequences on the device (keeps multi-step decode free of host round trips)."""
+    B = sampled.numel()
+    if not sampled.is_cuda:
+        step = int(step_counter.item())
+        step_counter += 1
+        input_ids.copy_(sampled)
+        if step < out_log.shape[0]:
+            out_log[step] = sampled
+        act = active.bool()
+        positions[:, act] += 1
+        kv_len[act] += 1
+        kv = kv_len.long()
+        new_slot = block_table[torch.arange(B), (kv - 1) // page].long() * page + (kv - 1) % page
+        slot[act] = new_slot[act].to(slot.dtype)
+        return
+    lib = _lib.load()
+    _chk(lib.cs_decode_advance(sampled.data_ptr(), input_ids.data_ptr(), positions.data_ptr(), kv_len.data_ptr(),
+                               slot.data_ptr(), block_table.data_ptr(), block_table.stride(0), active.data_ptr(),
+                               out_log.data_ptr(), out_log.shape[0], step_counter.data_ptr(), B, page, _stream()),
+         "cs_decode_advance")
+    _count()
 
 
 def l2_flush(buf: torch.Tensor, value: int = 0) -> None:

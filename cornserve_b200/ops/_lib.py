@@ -43,6 +43,7 @@ _SIGNATURES = {
     "cs_flow_step": ([P, P, P, I, I, F, F, I, P], I),
     "cs_pcm16": ([P, P, L, P], I),
     "cs_l2_flush": ([P, L, U, P], I),
+    "cs_decode_advance": ([P, P, P, P, P, P, I, P, P, I, P, I, I, P], I),
     "cs_attention": ([P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P], I),
 }
 

@@ -363,6 +363,28 @@ __global__ void l2_flush_kernel(uint4* buf, long long n, unsigned v) {
   for (; i < n; i += stride) buf[i] = make_uint4(v, v, v, v);
 }
 
+// After a decode step: feed the sampled token back as the next input, log it, advance positions,
+// key counts and cache slots of every active sequence.  One block, B <= 1024.
+__global__ void decode_advance_kernel(const int* sampled, int* input_ids, int* positions, int* kv_len, int* slot,
+                                      const int* block_table, int bt_stride, const int* active, int* out_log,
+                                      int log_cap, int* step_counter, int B, int page) {
+  const int b = threadIdx.x;
+  const int step = *step_counter;
+  __syncthreads();
+  if (b == 0) *step_counter = step + 1;
+  if (b >= B) return;
+  const int tok = sampled[b];
+  input_ids[b] = tok;
+  if (step < log_cap) out_log[step * B + b] = tok;
+  if (!active[b]) return;
+  positions[b] += 1;
+  positions[B + b] += 1;
+  positions[2 * B + b] += 1;
+  const int kv = kv_len[b] + 1;
+  kv_len[b] = kv;
+  slot[b] = block_table[(long long)b * bt_stride + (kv - 1) / page] * page + (kv - 1) % page;
+}
+
 inline int ceil_div_ll(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
 
 }  // namespace
@@ -463,5 +485,16 @@ CS_API int cs_pcm16(const void* x, void* y, long long n, void* stream) {
 CS_API int cs_l2_flush(void* buf, long long bytes, unsigned v, void* stream) {
   if (bytes < 16) return 0;
   l2_flush_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((uint4*)buf, bytes >> 4, v);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+CS_API int cs_decode_advance(const void* sampled, void* input_ids, void* positions, void* kv_len, void* slot,
+                             const void* block_table, int bt_stride, const void* active, void* out_log, int log_cap,
+                             void* step_counter, int B, int page, void* stream) {
+  if (B <= 0) return 0;
+  if (B > 1024) return -1;
+  decode_advance_kernel<<<1, ((B + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(
+      (const int*)sampled, (int*)input_ids, (int*)positions, (int*)kv_len, (int*)slot, (const int*)block_table,
+      bt_stride, (const int*)active, (int*)out_log, log_cap, (int*)step_counter, B, page);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }

@@ -354,10 +354,13 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaSt
   int stages = p.stages;
   const int max_smem = 220 * 1024;
   if (stages <= 0) stages = MAX_STAGES;
-  while (stages > 2 && stages * stage_bytes + 1024 > max_smem) --stages;
+  // The MMA always reads 128 rows of A; when fewer rows are fetched the read runs past the A slot,
+  // so keep a tail pad that makes the last stage's read stay inside the allocation.
+  const int tail_pad = BM * BK * 2 - p.a_bytes;
+  while (stages > 2 && stages * stage_bytes + 1024 + tail_pad > max_smem) --stages;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   p.stages = stages;
-  const int smem = stages * stage_bytes + 1024;
+  const int smem = stages * stage_bytes + 1024 + tail_pad;
   static bool attr_done[64] = {false};
   auto kern = gemm_bf16_kernel<BN, SWIGLU>;
   int dev = 0;

@@ -1,0 +1,97 @@
+"""LLM engine on CPU: continuous batching, chunked prefill, decode bursts and encoder-embedding
+injection must reproduce a plain full-sequence forward (same model, fp32)."""
+
+import numpy as np
+import torch
+
+from cornserve_b200.executors.llm.block_manager import BlockManager, OutOfPages
+from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, MMItem, SamplingParams, Sequence
+from cornserve_b200.executors.llm.mrope import mrope_positions
+from cornserve_b200.models.qwen_llm import BatchMeta, LLMConfig, QwenLLM
+
+
+def _model():
+    torch.manual_seed(0)
+    cfg = LLMConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                    intermediate_size=256, vocab_size=512, mrope_section=[4, 6, 6], rope_theta=10000.0,
+                    image_token_id=500, eos_token_id=511)
+    m = QwenLLM(cfg, device="cpu").float()
+    for p in m.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.1)
+    return m
+
+
+def _greedy_reference(model, ids, positions, n_new, mm=None):
+    """Recompute the whole sequence every step (no cache reuse), greedy."""
+    ids = list(ids)
+    pos = positions.copy()
+    out = []
+    for _ in range(n_new):
+        T = len(ids)
+        caches = model.alloc_kv_cache(2 + T // 128 + 1)
+        nblk = T // 128 + 1
+        bt = torch.arange(1, 1 + nblk, dtype=torch.int32)[None]
+        meta = BatchMeta(torch.tensor(ids, dtype=torch.int32), torch.from_numpy(pos).int(),
+                         (128 + torch.arange(T)).int(), torch.tensor([0, T], dtype=torch.int32),
+                         torch.tensor([T], dtype=torch.int32), bt, torch.tensor([T - 1], dtype=torch.int32), T)
+        if mm is not None:
+            meta.mm_embeds, meta.mm_index = mm
+        tok, _ = model(meta, caches)
+        t = int(tok[0])
+        out.append(t)
+        ids.append(t)
+        pos = np.concatenate([pos, np.full((3, 1), pos.max() + 1 if len(out) == 1 else pos[0, -1] + 1, np.int32)], 1)
+    return out
+
+
+def test_engine_matches_full_recompute_with_chunked_prefill_and_bursts():
+    model = _model()
+    prompts = [np.arange(3, 40, dtype=np.int32), np.arange(50, 57, dtype=np.int32), np.arange(100, 250, dtype=np.int32)]
+    eng = LLMEngine(model, EngineConfig(num_pages=32, max_batched_tokens=64, decode_burst=3, max_model_len=512))
+    seqs = [Sequence(f"s{i}", p, SamplingParams(max_tokens=7, ignore_eos=True)) for i, p in enumerate(prompts)]
+    got = eng.generate(seqs)
+    for i, p in enumerate(prompts):
+        pos = np.broadcast_to(np.arange(len(p), dtype=np.int32)[None], (3, len(p))).copy()
+        assert got[f"s{i}"] == _greedy_reference(model, p, pos, 7), f"sequence {i}"
+    assert eng.blocks.num_free == 31 and not eng.has_work()
+
+
+def test_engine_injects_encoder_embeddings_with_mrope():
+    model = _model()
+    grid = (1, 4, 6)  # -> 6 merged tokens
+    ids = np.array([1, 2, 3] + [500] * 6 + [7, 8], dtype=np.int32)
+    emb = torch.randn(6, 128)
+    pos, nxt = mrope_positions(ids, [grid], 500)
+    assert pos[:, :3].tolist() == [[0, 1, 2]] * 3 and pos[1, 3:9].tolist() == [3, 3, 3, 4, 4, 4]
+    assert pos[2, 3:9].tolist() == [3, 4, 5, 3, 4, 5] and pos[0, 9] == 6 and nxt == 8
+    eng = LLMEngine(model, EngineConfig(num_pages=8, decode_burst=2, max_model_len=256))
+    got = eng.generate([Sequence("a", ids, SamplingParams(max_tokens=4, ignore_eos=True),
+                                 mm_items=[MMItem(emb, 3, grid)], return_hidden=True)])
+    want = _greedy_reference(model, ids, pos, 4, mm=(emb, torch.arange(3, 9, dtype=torch.int32)))
+    assert got["a"] == want
+
+
+def test_eos_stops_generation():
+    model = _model()
+    eng = LLMEngine(model, EngineConfig(num_pages=8, decode_burst=4, max_model_len=256))
+    p = np.arange(10, 30, dtype=np.int32)
+    free_run = eng.generate([Sequence("x", p, SamplingParams(max_tokens=12, ignore_eos=True))])["x"]
+    stop_tok = free_run[5]
+    first = free_run.index(stop_tok)
+    out = eng.generate([Sequence("y", p, SamplingParams(max_tokens=12, stop_token_ids=(stop_tok,)))])["y"]
+    assert out == free_run[: first + 1]
+
+
+def test_block_manager():
+    bm = BlockManager(5)
+    assert bm.ensure("a", 129) == [1, 2] and bm.num_free == 2
+    assert bm.ensure("a", 200) == [1, 2]
+    assert not bm.can_allocate(400, "b")
+    try:
+        bm.ensure("b", 400)
+        raise AssertionError
+    except OutOfPages:
+        pass
+    bm.free("a")
+    assert bm.num_free == 4
