@@ -71,6 +71,48 @@ def _rowmajor(x: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # GEMM
 # --------------------------------------------------------------------------------------------
+SKINNY_MAX_M = 128          # largest row count the weight-streaming split-K kernel is considered for
+
+
+def _use_skinny(M: int, N: int, K: int) -> bool:
+    """Measured crossover on B200: the split-K kernel wins whenever K is long (down projections) and
+    for very few rows; otherwise the persistent tiled kernel already streams W at full width."""
+    if M > SKINNY_MAX_M:
+        return False
+    return K >= 8192 or M <= 32
+_SKINNY_WS_BYTES = 64 << 20
+_SKINNY_COUNTERS = 8192
+_skinny_ws: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _skinny_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Split-K scratch (fp32 partials + per-tile counters) of the current stream of ``device``.
+
+    Kernels on one stream run in order, so they can share one scratch area; different streams get
+    their own.  The buffers are created on first use (before any graph capture: engines warm up first).
+    """
+    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
+    w = _skinny_ws.get(key)
+    if w is None:
+        w = (torch.empty(_SKINNY_WS_BYTES, device=device, dtype=torch.uint8),
+             torch.zeros(_SKINNY_COUNTERS, device=device, dtype=torch.int32))
+        _skinny_ws[key] = w
+    return w
+
+
+def _skinny(x2, w, bias, act, r2, out2, M, N, K, swiglu, fp32, splits):
+    lib = _lib.load()
+    ws, counters = _skinny_workspace(x2.device)
+    rc = lib.cs_gemm_skinny(
+        x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), out2.data_ptr(), out2.stride(0),
+        _ptr(bias), _ptr(r2), 0 if r2 is None else r2.stride(0), M, N, K, ACTS[act or "none"],
+        1 if swiglu else 0, 1 if fp32 else 0, splits, ws.data_ptr(), ws.numel(), counters.data_ptr(),
+        counters.numel(), _stream(),
+    )
+    _chk(rc, "cs_gemm_skinny")
+    _count()
+
+
 def linear(
     x: torch.Tensor,
     w: torch.Tensor,
@@ -84,8 +126,13 @@ def linear(
     out_dtype: torch.dtype | None = None,
     bn: int = 0,
     stages: int = 0,
+    skinny: bool | None = None,
+    splits: int = 0,
 ) -> torch.Tensor:
     """``act(x @ w.T + bias) * gate + residual`` with w in the nn.Linear layout ``[N, K]``.
+
+    Up to ``SKINNY_MAX_M`` rows the weight-streaming split-K kernel is used (``skinny=False`` or an
+    explicit ``bn`` forces the tiled kernel).
 
     ``gate`` is ``[rows / gate_rows_per_batch, N]`` (one gate row per batch element, as in AdaLN).
     """
@@ -107,6 +154,9 @@ def linear(
         out = torch.empty((M, N), device=x.device, dtype=torch.float32 if fp32 else torch.bfloat16)
     o2 = _as2d(out)
     r2 = None if residual is None else _rowmajor(_as2d(residual))
+    if gate is None and bn == 0 and M <= 256 and (skinny or (skinny is None and _use_skinny(M, N, K))):
+        _skinny(x2, w, bias, act, r2, o2, M, N, K, False, fp32, splits)
+        return out.view(*shape[:-1], N) if out.dim() == 2 and len(shape) != 2 else out
     lib = _lib.load()
     rc = lib.cs_gemm_bf16(
         x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), o2.data_ptr(), o2.stride(0),
@@ -120,7 +170,7 @@ def linear(
 
 
 def swiglu_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, act: str = "silu",
-                  bn: int = 0, stages: int = 0) -> torch.Tensor:
+                  bn: int = 0, stages: int = 0, skinny: bool | None = None, splits: int = 0) -> torch.Tensor:
     """``act(x @ Wg.T) * (x @ Wu.T)`` with ``w = cat([Wg, Wu])`` of shape ``[2I, K]``; one kernel."""
     shape = x.shape
     x2 = _rowmajor(_as2d(x))
@@ -129,6 +179,9 @@ def swiglu_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = 
         return reference.swiglu_linear(x2, w, bias, act).view(*shape[:-1], n)
     M, K = x2.shape
     out = torch.empty((M, n), device=x.device, dtype=torch.bfloat16)
+    if bn == 0 and M <= 256 and (skinny or (skinny is None and _use_skinny(M, n, K))):
+        _skinny(x2, w, bias, act, None, out, M, n, K, True, False, splits)
+        return out.view(*shape[:-1], n)
     lib = _lib.load()
     rc = lib.cs_gemm_bf16(
         x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),

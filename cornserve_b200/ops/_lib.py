@@ -33,6 +33,9 @@ _SIGNATURES = {
     "cs_sm_count": ([], I),
     "cs_abi_version": ([], I),
     "cs_gemm_bf16": ([P, L, P, L, P, L, P, P, L, P, L, I, I, I, I, I, I, I, I, I, P], I),
+    "cs_gemm_skinny": ([P, L, P, L, P, L, P, P, L, I, I, I, I, I, I, I, P, L, P, I, P], I),
+    "cs_gemm_skinny_ws_bytes": ([I, I, I, I], L),
+    "cs_gemm_skinny_auto_splits": ([I, I, I], I),
     "cs_norm": ([P, L, P, L, P, L, P, P, P, P, L, I, P, L, I, I, F, I, P], I),
     "cs_rope": ([P, L, I, I, I, I, P, P], I),
     "cs_mrope_table": ([P, I, I, F, I, I, P, P], I),

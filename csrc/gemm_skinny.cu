@@ -1,0 +1,359 @@
+// Weight-streaming bf16 GEMM for small M (decode):  C[M,N] = epilogue(X[M,K] * W[N,K]^T),  M <= 256.
+//
+// The operands are swapped relative to gemm.cu: 128 rows of W form the M side of the tcgen05.mma tile
+// and the (padded) token rows of X form the N side, so one CTA streams a 128-row slab of W exactly
+// once and the tensor core is fed full-width tiles however few tokens there are.  K is split across
+// CTAs (split-K) so that every SM streams weights; partial sums go to an fp32 workspace and the last
+// CTA to finish a tile reduces them and applies the epilogue (bias, activation, residual, SwiGLU).
+//
+//   warp 0 (one lane)  TMA producer: ring of stages, each = 2 swizzle atoms (128 K columns) of W and X
+//   warp 1 (one lane)  tcgen05.mma issuer, accumulator [128 W rows x M_pad tokens] fp32 in TMEM
+//   warps 2..5         epilogue: thread r owns W row r of the tile = output column n0 + r, so for a
+//                      fixed token the 32 lanes of a warp write 32 consecutive output columns
+//
+// Scratch: `ws` holds splits x N x M_pad fp32 partials, `counters` one int per tile (zero before the
+// first call; the reducing CTA resets its counter, so back-to-back calls on one stream can share them).
+#include "common.cuh"
+
+namespace {
+
+constexpr int BK = 64;
+constexpr int KATOMS = 2;          // swizzle atoms per stage
+constexpr int W_ATOM = 128 * 128;  // 128 rows x 128 bytes
+constexpr int MAX_STAGES = 8;
+
+enum Act : int { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_QUICK_GELU = 4, ACT_RELU = 5 };
+
+// The activation is selected once per 16 values (uniform branch), then applied in a straight loop.
+__device__ __forceinline__ void act16(float (&f)[16], int act) {
+  switch (act) {
+    case ACT_GELU_ERF:
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = 0.5f * f[i] * (1.0f + erff(f[i] * 0.70710678118654752f));
+      break;
+    case ACT_GELU_TANH:
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float u = 0.7978845608028654f * (f[i] + 0.044715f * f[i] * f[i] * f[i]);
+        f[i] = 0.5f * f[i] * (2.0f - 2.0f / (__expf(2.0f * u) + 1.0f));
+      }
+      break;
+    case ACT_SILU:
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = f[i] / (1.0f + __expf(-f[i]));
+      break;
+    case ACT_QUICK_GELU:
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = f[i] / (1.0f + __expf(-1.702f * f[i]));
+      break;
+    case ACT_RELU:
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = fmaxf(f[i], 0.0f);
+      break;
+    default:
+      break;
+  }
+}
+
+struct SkinnyParams {
+  int M, N, K;          // N = output columns
+  int m_pad;            // tokens padded to a multiple of 16
+  int splits, stages;
+  int swiglu;           // tile = 64 gate rows + 64 up rows, 64 output columns per tile
+  int up_row_offset;    // row of W where the "up" half starts
+  void* C; long long ldc; int out_fp32;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual; long long ldr;
+  int act;
+  float* ws; int* counters;
+  uint32_t idesc;
+  uint32_t tmem_cols;
+  int* err;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                   const SkinnyParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag, is_last;
+  __shared__ float xchg[64 * 17];  // SwiGLU: up values of 64 columns x 16 tokens
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / p.splits, split = blockIdx.x % p.splits;
+  const int cols_per_tile = p.swiglu ? 64 : 128;
+  const int n0 = tile * cols_per_tile;
+  const int x_atom = p.m_pad * 128;
+  const int stage_bytes = KATOMS * (W_ATOM + x_atom);
+  const int total_it = (p.K + BK * KATOMS - 1) / (BK * KATOMS);
+  const int it_lo = static_cast<int>((static_cast<long long>(split) * total_it) / p.splits);
+  const int it_hi = static_cast<int>((static_cast<long long>(split + 1) * total_it) / p.splits);
+  const int n_it = it_hi - it_lo;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    is_last = 0;
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_full, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(&tmem_slot, p.tmem_cols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      const uint32_t tx = static_cast<uint32_t>(stage_bytes);
+      for (int it = 0; it < n_it; ++it) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp, p.err, CS_ERR_TIMEOUT_SLOT)) break;
+        uint8_t* sW = smem + stage * stage_bytes;
+        uint8_t* sX = sW + KATOMS * W_ATOM;
+        mbar_arrive_expect_tx(&full_bar[stage], tx);
+        const int k0 = (it_lo + it) * BK * KATOMS;
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a) {
+          if (p.swiglu) {
+            tma_load_2d(sW + a * W_ATOM, &tmW, k0 + a * BK, n0, &full_bar[stage]);
+            tma_load_2d(sW + a * W_ATOM + W_ATOM / 2, &tmW, k0 + a * BK, p.up_row_offset + n0, &full_bar[stage]);
+          } else {
+            tma_load_2d(sW + a * W_ATOM, &tmW, k0 + a * BK, n0, &full_bar[stage]);
+          }
+          tma_load_2d(sX + a * x_atom, &tmX, k0 + a * BK, 0, &full_bar[stage]);
+        }
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int it = 0; it < n_it; ++it) {
+        if (!mbar_wait(&full_bar[stage], phase, abortp, p.err, CS_ERR_TIMEOUT_TMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t w_addr = smem_u32(smem + stage * stage_bytes);
+        const uint32_t x_addr = w_addr + KATOMS * W_ATOM;
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a) {
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_f16_ss(tmem, umma_smem_desc(w_addr + a * W_ATOM + k * 32, 16, 1024),
+                        umma_smem_desc(x_addr + a * x_atom + k * 32, 16, 1024), p.idesc,
+                        (it | a | k) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(&empty_bar[stage]);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(&acc_full);
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // W row of the tile
+    const uint32_t t_row = tmem + (static_cast<uint32_t>(q * 32) << 16);
+    bool ok = true;
+    if (n_it > 0) ok = mbar_wait(&acc_full, 0, abortp, p.err, CS_ERR_TIMEOUT_MMA);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    const int chunks = p.m_pad / 16;
+    // For the fused SwiGLU tile rows 0..63 are gate columns and rows 64..127 the matching up columns.
+    const int w_row = p.swiglu ? (r < 64 ? n0 + r : p.up_row_offset + n0 + (r - 64)) : n0 + r;
+    const bool row_valid = p.swiglu ? (n0 + (r & 63) < p.N) : (n0 + r < p.N);
+    if (p.splits > 1) {
+      // 1) publish this split's partial sums
+      float* wsrow = p.ws + (static_cast<long long>(split) * (p.swiglu ? 2 * p.N : p.N) + (p.swiglu ? (r < 64 ? n0 + r : p.N + n0 + r - 64) : n0 + r)) * p.m_pad;
+      for (int c = 0; c < chunks; ++c) {
+        uint32_t v[16];
+        if (ok && n_it > 0) { tmem_ld16(t_row + c * 16, v); tmem_wait_ld(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0;
+        }
+        if (row_valid) {
+          float4* dst = reinterpret_cast<float4*>(wsrow + c * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int prev = atomicAdd(&p.counters[tile], 1);
+        if (prev == p.splits - 1) { p.counters[tile] = 0; is_last = 1; }
+        __threadfence();
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const bool reducer = (p.splits == 1) || (*reinterpret_cast<volatile int*>(&is_last) != 0);
+    if (reducer) {
+      const float bias = (p.bias != nullptr && row_valid) ? __bfloat162float(p.bias[p.swiglu ? (r < 64 ? n0 + r : p.N + n0 + r - 64) : n0 + r]) : 0.f;
+      (void)w_row;
+      for (int c = 0; c < chunks; ++c) {
+        float f[16];
+        if (p.splits == 1) {
+          uint32_t v[16];
+          if (ok && n_it > 0) { tmem_ld16(t_row + c * 16, v); tmem_wait_ld(); }
+          else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = 0.f;
+          if (row_valid) {
+            const long long rows_total = p.swiglu ? 2 * p.N : p.N;
+            const long long myrow = p.swiglu ? (r < 64 ? n0 + r : p.N + n0 + r - 64) : n0 + r;
+            for (int s = 0; s < p.splits; ++s) {
+              const float4* src = reinterpret_cast<const float4*>(p.ws + (s * rows_total + myrow) * p.m_pad + c * 16);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float4 t = __ldcg(src + i);
+                f[4 * i] += t.x; f[4 * i + 1] += t.y; f[4 * i + 2] += t.z; f[4 * i + 3] += t.w;
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) f[i] += bias;
+        if (p.swiglu) {
+          // hand the up values (rows 64..127) to the threads that hold the matching gate columns
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (r >= 64) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) xchg[(r - 64) * 17 + i] = f[i];
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (r < 64) {
+            act16(f, p.act);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[i] *= xchg[r * 17 + i];
+          }
+        } else {
+          act16(f, p.act);
+        }
+        const bool writer = row_valid && (!p.swiglu || r < 64);
+        if (writer) {
+          const int n = n0 + r;
+          const int mmax = min(16, p.M - c * 16);
+          if (p.residual != nullptr) {
+            const __nv_bfloat16* rp = p.residual + static_cast<long long>(c * 16) * p.ldr + n;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (i < mmax) f[i] += __bfloat162float(rp[static_cast<long long>(i) * p.ldr]);
+          }
+          if (p.out_fp32) {
+            float* op = reinterpret_cast<float*>(p.C) + static_cast<long long>(c * 16) * p.ldc + n;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (i < mmax) op[static_cast<long long>(i) * p.ldc] = f[i];
+          } else {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(c * 16) * p.ldc + n;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (i < mmax) op[static_cast<long long>(i) * p.ldc] = __float2bfloat16(f[i]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, p.tmem_cols); }
+}
+
+}  // namespace
+
+// Workspace sizes for cs_gemm_skinny: bytes of fp32 partials and number of int counters.
+CS_API long long cs_gemm_skinny_ws_bytes(int M, int N, int splits, int swiglu) {
+  const long long m_pad = (M + 15) & ~15;
+  return splits > 1 ? static_cast<long long>(splits) * (swiglu ? 2 * N : N) * m_pad * 4 : 0;
+}
+
+// Picks the split count used when `splits` is passed as 0.
+CS_API int cs_gemm_skinny_auto_splits(int N, int K, int swiglu) {
+  const int tiles = (N + (swiglu ? 64 : 128) - 1) / (swiglu ? 64 : 128);
+  const int sms = cs_num_sms();
+  const int total_it = (K + BK * KATOMS - 1) / (BK * KATOMS);
+  int splits = 1;
+  if (tiles < sms) {
+    splits = sms / tiles;
+    if (splits > total_it) splits = total_it;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  return splits;
+}
+
+// C[M,N] = act(X W^T + bias) + residual   (swiglu == 0),  W: [N,K]
+// C[M,N] = act(X Wg^T + bg) * (X Wu^T + bu), W = [Wg; Wu] ([2N,K])   (swiglu == 1)
+// M <= 256.  `ws` / `counters` as described at the top of this file (`counters` needs one int per tile).
+CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc,
+                          const void* bias, const void* residual, long long ldr, int M, int N, int K, int act,
+                          int swiglu, int out_fp32, int splits, void* ws, long long ws_bytes, void* counters,
+                          int num_counters, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 256 || K <= 0 || (ldx & 7) || (ldw & 7)) return -1;
+  SkinnyParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.m_pad = (M + 15) & ~15;
+  p.swiglu = swiglu;
+  p.up_row_offset = N;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.act = act;
+  p.err = cs_error_word();
+  const int cols_per_tile = swiglu ? 64 : 128;
+  const int tiles = (N + cols_per_tile - 1) / cols_per_tile;
+  if (splits <= 0) splits = cs_gemm_skinny_auto_splits(N, K, swiglu);
+  const int total_it = (K + BK * KATOMS - 1) / (BK * KATOMS);
+  if (splits > total_it) splits = total_it;
+  if (splits > 1) {
+    if (ws == nullptr || counters == nullptr || tiles > num_counters ||
+        cs_gemm_skinny_ws_bytes(M, N, splits, swiglu) > ws_bytes)
+      return -5;
+  }
+  p.splits = splits;
+  p.ws = reinterpret_cast<float*>(ws);
+  p.counters = reinterpret_cast<int*>(counters);
+  const int stage_bytes = KATOMS * (W_ATOM + p.m_pad * 128);
+  int stages = MAX_STAGES;
+  const int max_smem = 220 * 1024;
+  while (stages > 2 && stages * stage_bytes + 1024 > max_smem) --stages;
+  p.stages = stages;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.m_pad)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.idesc = umma_idesc_bf16(128, p.m_pad, 0, 0);
+
+  CUtensorMap tmW, tmX;
+  const int w_rows = swiglu ? 2 * N : N;
+  if (cs_encode_tmap_2d(&tmW, W, K, w_rows, ldw * 2, BK, swiglu ? 64 : 128, 2, 1) != 0) return -2;
+  if (cs_encode_tmap_2d(&tmX, X, K, M, ldx * 2, BK, p.m_pad, 2, 1) != 0) return -3;
+  const int smem = stages * stage_bytes + 1024;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!attr_done[dev]) {
+    cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    attr_done[dev] = true;
+  }
+  gemm_skinny_kernel<<<tiles * splits, 192, smem, stream>>>(tmW, tmX, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}

@@ -182,3 +182,27 @@ def test_misc_kernels():
     _close(x, want, 1e-4, 1e-4, "flow step")
     w = torch.rand(1000, device=DEV) * 2.4 - 1.2
     assert (ops.pcm16(w).int() - ref.pcm16(w).int()).abs().max() <= 1
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (16, 3584, 3584), (64, 3584, 18944), (7, 4608, 3584), (128, 1000, 1352),
+                                   (100, 152064, 512)])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_gemm_skinny(M, N, K, splits):
+    if N > 100000 and splits > 1:
+        pytest.skip("split-K scratch is sized for decoder projections, not for a forced split of the vocabulary")
+    torch.manual_seed(9)
+    x, w, b, r = _rand(M, K), _rand(N, K, scale=K ** -0.5), _rand(N), _rand(M, N)
+    for _ in range(2):  # twice: the split-K counters must be back at zero after a call
+        y = ops.linear(x, w, b, act="gelu", residual=r, skinny=True, splits=splits)
+        _close(y, ref.linear(x, w, b, "gelu", r, out_dtype=torch.float32), 3e-2, 2e-2, f"skinny {M}x{N}x{K}")
+    y32 = ops.linear(x, w, out_dtype=torch.float32, splits=splits)
+    _close(y32, ref.linear(x, w, out_dtype=torch.float32), 1e-2, 1e-2, "skinny fp32")
+
+
+@pytest.mark.parametrize("M,I,K", [(16, 18944, 3584), (3, 96, 64), (128, 1712, 1280)])
+@pytest.mark.parametrize("splits", [0, 1, 2])
+def test_gemm_skinny_swiglu(M, I, K, splits):
+    torch.manual_seed(10)
+    x, w, b = _rand(M, K), _rand(2 * I, K, scale=K ** -0.5), _rand(2 * I, scale=0.1)
+    y = ops.swiglu_linear(x, w, b, skinny=True, splits=splits)
+    _close(y, ref.swiglu_linear(x.float(), w.float(), b.float()), 3e-2, 2e-2, "skinny swiglu")
