@@ -307,7 +307,7 @@ def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = 
     rc = lib.cs_attention(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
         out.data_ptr(), out.stride(0), cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
-        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, _stream(),
+        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, 1, None, 0, _stream(),
     )
     _chk(rc, "cs_attention")
     _count()
@@ -315,7 +315,8 @@ def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = 
 
 
 def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: float | None = None,
-                    causal: bool = True, pack_gqa: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+                    causal: bool = True, pack_gqa: bool = False, out: torch.Tensor | None = None,
+                    kv_splits: int = 0) -> torch.Tensor:
     """Attention of packed queries over a paged KV cache ``[pages, 2, Hkv, 128, d]``.
 
     ``kv_len[s]`` counts the keys of sequence ``s`` *including* the ones just appended for these
@@ -335,13 +336,27 @@ def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: 
         out = torch.empty((Tq, Hq, d), device=q.device, dtype=torch.bfloat16)
     B = cu_q.numel() - 1
     lib = _lib.load()
+    if kv_splits == 0:
+        # decode (one query token per sequence): spread the keys of each sequence over idle SMs
+        items = B * (Hkv if pack_gqa else Hq)
+        sms = lib.cs_sm_count()
+        kv_splits = max(1, min(16, sms // max(items, 1))) if max_q_len == 1 else 1
+    ws_ptr, ws_bytes = None, 0
+    if kv_splits > 1:
+        ws, _ = _skinny_workspace(q.device)
+        need = Tq * Hq * kv_splits * (d + 2) * 4
+        if need > ws.numel():
+            kv_splits = 1
+        else:
+            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     rc = lib.cs_attention(
         q.data_ptr(), q.stride(0), cache.data_ptr(), 0, None, 0, out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), None, kv_len.data_ptr(), block_table.data_ptr(), block_table.stride(0), pages,
-        B, Tq, 0, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 1 if pack_gqa else 0, _stream(),
+        B, Tq, 0, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 1 if pack_gqa else 0,
+        kv_splits, ws_ptr, ws_bytes, _stream(),
     )
     _chk(rc, "cs_attention(paged)")
-    _count()
+    _count(2 if kv_splits > 1 else 1)
     return out
 
 
@@ -407,10 +422,11 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     rows, V = logits.shape
     if out is None:
         out = torch.empty((rows,), device=logits.device, dtype=torch.int32)
+    scratch = torch.empty(rows * 128, device=logits.device, dtype=torch.float32)
     lib = _lib.load()
     _chk(lib.cs_argmax(logits.data_ptr(), logits.stride(0), rows, V, 1 if logits.dtype == torch.float32 else 0,
-                       out.data_ptr(), _stream()), "cs_argmax")
-    _count()
+                       out.data_ptr(), scratch.data_ptr(), _stream()), "cs_argmax")
+    _count(2)
     return out
 
 

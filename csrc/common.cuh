@@ -92,6 +92,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // the CTA gives up, the other roles stop waiting too and fall through to the tear-down.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* err, int err_code) {
+  if (*abort_flag) return false;  // the CTA already gave up: do not spin again
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {

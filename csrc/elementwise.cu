@@ -140,6 +140,86 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_kernel(const NormParams p) 
   }
 }
 
+// Same math with one warp per row (no block-wide synchronisation); used when H <= 2048.
+constexpr int WNORM_MAXV = 8;
+__global__ void __launch_bounds__(256) norm_warp_kernel(const NormParams p) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const int nvec = p.H >> 3;
+  float v[WNORM_MAXV][8];
+  const uint4* xr = reinterpret_cast<const uint4*>(p.x + (long long)row * p.ldx);
+  const uint4* rr = p.residual ? reinterpret_cast<const uint4*>(p.residual + (long long)row * p.ldres) : nullptr;
+  uint4* ro = p.res_out ? reinterpret_cast<uint4*>(p.res_out + (long long)row * p.ldro) : nullptr;
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < WNORM_MAXV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) {
+      unpack8(xr[c], v[i]);
+      if (rr) {
+        float r[8];
+        unpack8(rr[c], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+      }
+      if (ro) {
+        uint4 w = pack8(v[i]);
+        ro[c] = w;
+        unpack8(w, v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
+    }
+  }
+  float mean = 0.f, rstd;
+  if (p.mode == 2) {
+    mean = warp_sum(s) / p.H;
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < WNORM_MAXV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; var += d * d; }
+      }
+    }
+    rstd = rsqrtf(warp_sum(var) / p.H + p.eps);
+  } else {
+    rstd = rsqrtf(warp_sum(ss) / p.H + p.eps);
+  }
+  const uint4* w4 = p.w ? reinterpret_cast<const uint4*>(p.w) : nullptr;
+  const uint4* b4 = p.b ? reinterpret_cast<const uint4*>(p.b) : nullptr;
+  const long long mrow = p.scale ? (long long)(row / p.rpb) * p.ldmod : 0;
+  const uint4* sc4 = p.scale ? reinterpret_cast<const uint4*>(p.scale + mrow) : nullptr;
+  const uint4* sh4 = p.shift ? reinterpret_cast<const uint4*>(p.shift + mrow) : nullptr;
+  uint4* yr = reinterpret_cast<uint4*>(p.y + (long long)row * p.ldy);
+#pragma unroll
+  for (int i = 0; i < WNORM_MAXV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) {
+      float o[8], w[8], b[8];
+      if (w4) unpack8(__ldg(w4 + c), w);
+      if (b4) unpack8(__ldg(b4 + c), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = (v[i][j] - mean) * rstd;
+        if (w4) t *= (p.mode == 1 ? 1.0f + w[j] : w[j]);
+        if (b4) t += b[j];
+        o[j] = t;
+      }
+      if (sc4) {
+        float sc[8], sh[8];
+        unpack8(sc4[c], sc);
+        unpack8(sh4[c], sh);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = o[j] * (1.0f + sc[j]) + sh[j];
+      }
+      yr[c] = pack8(o);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Rotary embeddings, rotate-half convention: for i < d/2
 //   out[i]       = x[i]*cos[i] - x[i+d/2]*sin[i]
@@ -281,38 +361,64 @@ __global__ void gather_rows_kernel(const uint4* src, long long src_ld16, uint4* 
 // ---------------------------------------------------------------------------------------
 // Greedy sampling: arg-max over a [rows, V] logits matrix (bf16 or fp32).  One CTA per row.
 // ---------------------------------------------------------------------------------------
+// Two-stage so that few rows still fill the GPU: stage 1 scans a slice of the vocabulary per CTA and
+// leaves (value, index) candidates, stage 2 (one warp per row) picks the winner.
 template <typename T>
-__global__ void __launch_bounds__(1024) argmax_kernel(const T* logits, long long ld, int V, int* out) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+__global__ void __launch_bounds__(256) argmax_stage1_kernel(const T* logits, long long ld, int V, int slices,
+                                                            float* cand_v, int* cand_i) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
   const long long row = blockIdx.x;
+  const int slice = blockIdx.y;
+  const int per = (V + slices - 1) / slices;
+  const int lo = slice * per, hi = min(V, lo + per);
   const T* p = logits + row * ld;
   float best = -INFINITY;
-  int bi = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = static_cast<float>(p[i]);
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = static_cast<float>(p[i]);
     if (v > best) { best = v; bi = i; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
   }
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   if (l == 0) { sv[w] = best; si[w] = bi; }
   __syncthreads();
   if (w == 0) {
-    best = l < (blockDim.x >> 5) ? sv[l] : -INFINITY;
-    bi = l < (blockDim.x >> 5) ? si[l] : 0x7fffffff;
+    best = l < 8 ? sv[l] : -INFINITY;
+    bi = l < 8 ? si[l] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    for (int o = 4; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (l == 0) out[row] = bi;
+    if (l == 0) { cand_v[row * slices + slice] = best; cand_i[row * slices + slice] = bi; }
   }
+}
+
+__global__ void argmax_stage2_kernel(const float* cand_v, const int* cand_i, int slices, int rows, int* out) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int l = threadIdx.x & 31;
+  if (row >= rows) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int s = l; s < slices; s += 32) {
+    const float v = cand_v[(long long)row * slices + s];
+    const int i = cand_i[(long long)row * slices + s];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (l == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -404,7 +510,10 @@ CS_API int cs_norm(const void* x, long long ldx, const void* residual, long long
   p.ldmod = ldmod; p.rpb = rpb > 0 ? rpb : 1;
   p.y = (__nv_bfloat16*)y; p.ldy = ldy;
   p.rows = rows; p.H = H; p.eps = eps; p.mode = mode;
-  norm_kernel<<<rows, NORM_THREADS, 0, (cudaStream_t)stream>>>(p);
+  if (H <= 32 * 8 * WNORM_MAXV && rows >= 64)
+    norm_warp_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(p);
+  else
+    norm_kernel<<<rows, NORM_THREADS, 0, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 
@@ -458,13 +567,22 @@ CS_API int cs_gather_rows(const void* src, long long src_ld_bytes, void* dst, lo
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 
-CS_API int cs_argmax(const void* logits, long long ld, int rows, int V, int is_fp32, void* out, void* stream) {
+// `scratch` must hold rows * 64 floats followed by rows * 64 ints (candidates of stage 1).
+CS_API int cs_argmax(const void* logits, long long ld, int rows, int V, int is_fp32, void* out, void* scratch,
+                     void* stream) {
   if (rows <= 0) return 0;
+  int slices = (148 * 4 + rows - 1) / rows;
+  if (slices > 64) slices = 64;
+  if (slices < 1) slices = 1;
+  float* cv = reinterpret_cast<float*>(scratch);
+  int* ci = reinterpret_cast<int*>(cv + static_cast<long long>(rows) * 64);
+  dim3 grid(rows, slices);
   if (is_fp32)
-    argmax_kernel<float><<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, ld, V, (int*)out);
+    argmax_stage1_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)logits, ld, V, slices, cv, ci);
   else
-    argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ld, V,
-                                                                           (int*)out);
+    argmax_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ld, V,
+                                                                                slices, cv, ci);
+  argmax_stage2_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(cv, ci, slices, rows, (int*)out);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 

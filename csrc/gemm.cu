@@ -73,16 +73,16 @@ __device__ __forceinline__ void apply_act32(float (&f)[32], int act) {
       for (int j = 0; j < 32; ++j) {
         const float u = 0.7978845608028654f * (f[j] + 0.044715f * f[j] * f[j] * f[j]);
         // tanh(u) = 1 - 2 / (exp(2u) + 1)
-        f[j] = 0.5f * f[j] * (2.0f - 2.0f / (__expf(2.0f * u) + 1.0f));
+        f[j] = 0.5f * f[j] * (2.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f));
       }
       break;
     case ACT_SILU:
 #pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] = f[j] / (1.0f + __expf(-f[j]));
+      for (int j = 0; j < 32; ++j) f[j] = __fdividef(f[j], 1.0f + __expf(-f[j]));
       break;
     case ACT_QUICK_GELU:
 #pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] = f[j] / (1.0f + __expf(-1.702f * f[j]));
+      for (int j = 0; j < 32; ++j) f[j] = __fdividef(f[j], 1.0f + __expf(-1.702f * f[j]));
       break;
     case ACT_RELU:
 #pragma unroll

@@ -40,11 +40,11 @@ __device__ __forceinline__ void act16(float (&f)[16], int act) {
       break;
     case ACT_SILU:
 #pragma unroll
-      for (int i = 0; i < 16; ++i) f[i] = f[i] / (1.0f + __expf(-f[i]));
+      for (int i = 0; i < 16; ++i) f[i] = __fdividef(f[i], 1.0f + __expf(-f[i]));
       break;
     case ACT_QUICK_GELU:
 #pragma unroll
-      for (int i = 0; i < 16; ++i) f[i] = f[i] / (1.0f + __expf(-1.702f * f[i]));
+      for (int i = 0; i < 16; ++i) f[i] = __fdividef(f[i], 1.0f + __expf(-1.702f * f[i]));
       break;
     case ACT_RELU:
 #pragma unroll

@@ -115,7 +115,8 @@ def test_attention_varlen(H, d, lens, causal):
 
 @pytest.mark.parametrize("q_lens,ctx", [([1, 1, 1], [300, 128, 1]), ([200, 77], [200, 500]), ([1] * 9, [1000] * 9)])
 @pytest.mark.parametrize("pack", [False, True])
-def test_attention_paged(q_lens, ctx, pack):
+@pytest.mark.parametrize("kv_splits", [1, 0, 3])
+def test_attention_paged(q_lens, ctx, pack, kv_splits):
     torch.manual_seed(6)
     Hq, Hkv, d, page = 28, 4, 128, 128
     B = len(q_lens)
@@ -139,7 +140,7 @@ def test_attention_paged(q_lens, ctx, pack):
     q = _rand(Tq, Hq, d)
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=DEV, dtype=torch.int32)
     kv_len = torch.tensor(ctx, device=DEV, dtype=torch.int32)
-    o = ops.attention_paged(q, cache, bt, kv_len, cu, max(q_lens), causal=True, pack_gqa=pack)
+    o = ops.attention_paged(q, cache, bt, kv_len, cu, max(q_lens), causal=True, pack_gqa=pack, kv_splits=kv_splits)
     want = ref.attention_paged(q.cpu().float(), cache.cpu().float(), bt.cpu(), kv_len.cpu(), cu.cpu(),
                                1 / math.sqrt(d), True)
     _close(o, want.to(DEV), 2e-2, 2e-2, "paged attn")
