@@ -1,0 +1,1 @@
+from .base import LaunchSpec, TaskExecutionDescriptor  # noqa: F401

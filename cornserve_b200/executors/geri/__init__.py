@@ -1,0 +1,1 @@
+"""Geri: the multimodal generator executor (images in batches, audio as a stream)."""
