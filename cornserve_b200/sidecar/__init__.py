@@ -1,0 +1,1 @@
+from .schema import SidecarConfig  # noqa: F401
