@@ -1,0 +1,142 @@
+"""Encoder worker: one per GPU of the executor's tensor-parallel group.
+
+Loads the model shard, turns decoded inputs into model tensors on the device, runs the forward pass and
+hands every item's embeddings to the sidecar (reference: python/cornserve/task_executors/eric/executor/
+worker.py:59-405).  Rank 0 lives in the executor's main process next to the engine; ranks > 0 are
+separate processes that replay the batches rank 0 broadcasts.
+"""
+
+from __future__ import annotations
+
+import os
+from pathlib import Path
+
+import torch
+
+from ...logging import get_logger
+from ...parallel.state import ParallelGroup, init_distributed, set_tp_group
+from ...sidecar.api import Sidecar
+from ...sidecar.schema import SidecarConfig
+from ...tracing import extract, get_tracer
+from ...utils.hub import load_config, load_model_weights
+from .config import EricConfig
+from .preprocess import patchify_frames
+from .registry import MODEL_REGISTRY
+from .schema import Batch
+
+logger = get_logger(__name__)
+tracer = get_tracer(__name__)
+
+
+def pick_device(local_index: int) -> torch.device:
+    if not torch.cuda.is_available() or os.environ.get("CORNSERVE_DEVICE") == "cpu":
+        return torch.device("cpu")
+    ids = [int(x) for x in os.environ.get("CORNSERVE_LOCAL_GPUS", "").split(",") if x.strip() != ""]
+    return torch.device("cuda", ids[local_index] if ids else local_index)
+
+
+class Worker:
+    def __init__(self, config: EricConfig, tp_rank: int = 0, group: ParallelGroup | None = None):
+        self.config = config
+        self.tp_rank = tp_rank
+        self.device = group.device if group is not None else pick_device(tp_rank)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        self.group = group or ParallelGroup(0, 1, None, None, self.device)
+        set_tp_group(self.group)
+        hf_cfg = load_config(config.model.id)
+        model_type = hf_cfg.get("model_type", "")
+        if model_type not in MODEL_REGISTRY:
+            raise ValueError(f"Model type {model_type!r} is not supported by the encoder executor "
+                             f"(supported: {sorted(MODEL_REGISTRY)})")
+        self.entry = MODEL_REGISTRY[model_type]
+        if config.model.modality not in self.entry.modalities:
+            raise ValueError(f"{model_type} does not encode {config.model.modality}")
+        model_cls, cfg_cls = self.entry.load_classes()
+        self.model_cfg = cfg_cls.from_hf(hf_cfg)
+        dtype = torch.float32 if (self.device.type == "cpu" or hf_cfg.get("torch_dtype") == "float32") else torch.bfloat16
+        torch.manual_seed(int(os.environ.get("CORNSERVE_SEED", "0")))  # reproducible random-weight runs
+        self.model = model_cls(self.model_cfg, group=self.group, device=self.device)
+        if dtype == torch.float32:
+            self.model = self.model.float()
+        load_model_weights(self.model, config.model.id, self.entry.weight.required_prefixes,
+                           ignored_prefixes=self.entry.weight.ignored_prefixes)
+        self.model.eval()
+        self.sidecar: Sidecar | None = None
+        if config.sidecar.ranks:
+            self.sidecar = Sidecar(SidecarConfig(
+                sidecar_rank=config.sidecar.ranks[tp_rank], group=list(config.sidecar.ranks),
+                send_tensor_dtype=self.model.dtype, send_tensor_shape=(-1, *self.model.chunk_shape[1:])))
+        self.dump_dir = os.environ.get("CORNSERVE_TEST_DUMP_TENSOR_DIR")
+        self.profiler = None
+        logger.info("Worker %d ready on %s (%s)", tp_rank, self.device, model_type)
+
+    def prepare(self, batch: Batch) -> dict[str, list]:
+        """Decoded uint8 data -> model inputs on the device."""
+        data = dict(batch.data)
+        vc = self.model_cfg
+        if "raw_images" in data or "raw_videos" in data:
+            raw_key = "raw_images" if "raw_images" in data else "raw_videos"
+            pix, grids = [], []
+            for frames in data.pop(raw_key):
+                pv, g = patchify_frames(frames.to(self.device, non_blocking=True), vc.patch_size, vc.temporal_patch_size,
+                                        vc.spatial_merge_size, out_dtype=self.model.dtype)
+                pix.append(pv)
+                grids.append(list(g))
+            if raw_key == "raw_images":
+                data["pixel_values"], data["image_grid_thw"] = pix, grids
+            else:
+                data["pixel_values_videos"], data["video_grid_thw"] = pix, grids
+        return data
+
+    @torch.inference_mode()
+    def execute_model(self, batch: Batch) -> None:
+        ctx = extract(batch.trace_carriers[0]) if batch.trace_carriers else None
+        with tracer.start_as_current_span("Worker.execute_model", context=ctx):
+            outputs = self.model(batch.modality.value, batch.adapter_name, self.prepare(batch))
+            if self.profiler is not None:
+                self.profiler.step()
+            for out, data_id, ranks in zip(outputs, batch.data_ids, batch.receiver_ranks, strict=True):
+                out = out.contiguous()
+                if self.dump_dir and self.tp_rank == 0:
+                    torch.save(out.cpu(), Path(self.dump_dir) / f"{data_id}.pt")
+                if self.sidecar is not None and ranks:
+                    self.sidecar.send(out, id=data_id, dst_sidecar_ranks=ranks)
+            if self.sidecar is not None:
+                # outputs are shared with the sidecar by reference: they must outlive the hand-off
+                self.sidecar.flush()
+
+    def start_profile(self, out_dir: str) -> None:
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if self.device.type == "cuda":
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        Path(out_dir).mkdir(parents=True, exist_ok=True)
+        self.profiler = torch.profiler.profile(
+            activities=acts, record_shapes=True, with_stack=True,
+            on_trace_ready=torch.profiler.tensorboard_trace_handler(out_dir, worker_name=f"eric-rank{self.tp_rank}"))
+        self.profiler.start()
+
+    def stop_profile(self) -> None:
+        if self.profiler is not None:
+            self.profiler.stop()
+            self.profiler = None
+
+    def shutdown(self) -> None:
+        if self.sidecar is not None:
+            self.sidecar.shutdown_sync()
+
+
+def tp_worker_main(config_json: str, tp_rank: int, tp_size: int, master_port: int) -> None:
+    """Entry of a TP worker process (rank > 0): replay what rank 0 broadcasts until told to stop."""
+    config = EricConfig.model_validate_json(config_json)
+    device = pick_device(tp_rank)
+    group = init_distributed(tp_rank, tp_size, master_port=master_port,
+                             local_device=device.index if device.type == "cuda" else None,
+                             backend=None if device.type == "cuda" else "gloo")
+    worker = Worker(config, tp_rank, group)
+    while True:
+        method, arg = group.broadcast_object(None, src=0)
+        if method == "shutdown":
+            break
+        getattr(worker, method)(*arg)
+    worker.shutdown()

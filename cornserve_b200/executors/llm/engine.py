@@ -228,8 +228,8 @@ class LLMEngine:
             logits_idx=f(last), max_q_len=max(n for _, n in batch), is_decode=False,
         )
         if mm_rows:
-            m.mm_embeds = torch.cat([r.to(dev, non_blocking=True) for r in mm_rows], dim=0)
-            m.mm_index = f(np.concatenate(mm_idx))
+            m.mm_embeds = mm_rows  # placed row by row by the scatter kernel, from wherever they live
+            m.mm_index = [f(i) for i in mm_idx]
         want_hidden = any(s.return_hidden for s, _ in batch)
         with torch.inference_mode():
             next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden)

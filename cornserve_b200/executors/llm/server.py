@@ -1,0 +1,408 @@
+"""LLM executor: OpenAI-compatible chat-completions server on top of :class:`LLMEngine`.
+
+This process plays the role the reference gives to its vLLM fork (contract in
+tasklib/cornserve_tasklib/task_executors/descriptor/llm.py:68-563 and docker/vllm.Dockerfile):
+
+* ``POST /v1/chat/completions`` (server-sent events when ``stream`` is true, one JSON otherwise), ``GET /health``.
+* Multimodal parts whose URL is ``data:{modality}/uuid;data_id={id};url={original},`` are not decoded here:
+  the embeddings with that id are received from the sidecar (a view of the producer's GPU slab) and placed
+  into the prompt embeddings by a copy kernel.  Plain URLs are encoded locally by an in-process vision tower
+  (the monolithic, no-fission deployment).
+* ``vllm_xargs`` carries forwarding instructions: ``cornserve_hidden_states_forward_id/_ranks`` sends the
+  prompt's final hidden states to another executor instead of generating text.
+
+The command line accepts the flags the descriptors pass (vLLM-style names); flags that only make sense for
+vLLM are accepted and ignored.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ast
+import asyncio
+import io
+import json
+import os
+import re
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+import torch
+import uvicorn
+from fastapi import FastAPI, Request, Response
+from fastapi.responses import JSONResponse, StreamingResponse
+
+from ...logging import get_logger
+from ...models.qwen_llm import LLMConfig, QwenLLM
+from ...parallel.state import ParallelGroup
+from ...tracing import configure_otel
+from ...utils.hub import load_config, load_model_weights
+from ..eric.preprocess import smart_resize
+from ..eric.processor import fetch_bytes
+from .engine import EngineConfig, LLMEngine, MMItem, SamplingParams, Sequence, StepOutput
+from .tokenizer import load_tokenizer
+
+logger = get_logger(__name__)
+
+_SIDECAR_URI = re.compile(r"^data:(?P<modality>\w+)/uuid;data_id=(?P<id>[0-9a-f]+);url=(?P<url>.*),$", re.S)
+
+
+def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
+    ap = argparse.ArgumentParser("cornserve-b200 LLM executor")
+    ap.add_argument("model")
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--cornserve-sidecar-ranks", type=int, nargs="*", default=[])
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-model-len", type=int, default=32768)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=16384)
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    ap.add_argument("--num-kv-pages", type=int, default=0, help="0 = size the cache from free memory")
+    ap.add_argument("--decode-burst", type=int, default=4)
+    ap.add_argument("--kv-transfer-config", default=None)
+    ap.add_argument("--run-talker", action="store_true")
+    ap.add_argument("--run-vocoder", action="store_true")
+    for flag in ("--trust-remote-code", "--enforce-eager", "--no-enable-prefix-caching", "--disable-mm-preprocessor-cache",
+                 "--no-enable-chunked-prefill", "--disable-chunked-mm-input"):
+        ap.add_argument(flag, action="store_true", help="accepted for compatibility")
+    return ap.parse_args(argv)
+
+
+def pick_device() -> torch.device:
+    if not torch.cuda.is_available() or os.environ.get("CORNSERVE_DEVICE") == "cpu":
+        return torch.device("cpu")
+    ids = [int(x) for x in os.environ.get("CORNSERVE_LOCAL_GPUS", "").split(",") if x.strip() != ""]
+    return torch.device("cuda", ids[0] if ids else 0)
+
+
+@dataclass
+class _Pending:
+    queue: asyncio.Queue
+    loop: asyncio.AbstractEventLoop
+    recv_ids: list[str] = field(default_factory=list)
+
+
+class AsyncLLM:
+    """Runs the synchronous engine on its own thread and fans step outputs out to per-request queues."""
+
+    def __init__(self, engine: LLMEngine):
+        self.engine = engine
+        self.pending: dict[str, _Pending] = {}
+        self.inbox: list[Sequence] = []
+        self.cv = threading.Condition()
+        self.alive = True
+        self.thread = threading.Thread(target=self._run, name="llm-engine", daemon=True)
+        self.thread.start()
+
+    def submit(self, seq: Sequence) -> asyncio.Queue:
+        q: asyncio.Queue = asyncio.Queue()
+        self.pending[seq.seq_id] = _Pending(q, asyncio.get_running_loop())
+        with self.cv:
+            self.inbox.append(seq)
+            self.cv.notify()
+        return q
+
+    def _deliver(self, out: StepOutput) -> None:
+        p = self.pending.get(out.seq_id)
+        if p is None:
+            return
+        if out.finished:
+            self.pending.pop(out.seq_id, None)
+        p.loop.call_soon_threadsafe(p.queue.put_nowait, out)
+
+    def _run(self) -> None:
+        try:
+            while self.alive:
+                with self.cv:
+                    while self.alive and not self.inbox and not self.engine.has_work():
+                        self.cv.wait(timeout=0.5)
+                    new, self.inbox = self.inbox, []
+                for s in new:
+                    try:
+                        self.engine.add_request(s)
+                    except Exception as e:
+                        self._deliver(StepOutput(s.seq_id, [], True, f"error: {e}"))
+                for out in self.engine.step():
+                    self._deliver(out)
+        except Exception:
+            logger.exception("LLM engine thread died")
+        finally:
+            self.alive = False
+            for sid in list(self.pending):
+                self._deliver(StepOutput(sid, [], True, "error: engine stopped"))
+
+    def shutdown(self) -> None:
+        self.alive = False
+        with self.cv:
+            self.cv.notify_all()
+        self.thread.join(timeout=10)
+
+
+def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -> tuple[LLMEngine, dict[str, Any]]:
+    hf_cfg = load_config(args.model)
+    cfg = LLMConfig.from_hf(hf_cfg)
+    device = group.device if group is not None else pick_device()
+    if device.type == "cuda":
+        torch.cuda.set_device(device)
+    torch.manual_seed(int(os.environ.get("CORNSERVE_SEED", "0")))  # reproducible random-weight runs
+    model = QwenLLM(cfg, group=group, device=device)
+    if device.type == "cpu" or hf_cfg.get("torch_dtype") == "float32":
+        model = model.float()
+    load_model_weights(model, args.model, ["model.language_model.", "language_model.", "model.", "lm_head.", ""],
+                       strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower."])
+    model.eval()
+    pages = args.num_kv_pages
+    if pages <= 0:
+        if device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(device)
+            budget = int(free * args.gpu_memory_utilization) - (4 << 30)
+            pages = max(64, budget // model.kv_bytes_per_page())
+        else:
+            pages = 64
+    ecfg = EngineConfig(num_pages=int(pages), max_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
+                        decode_burst=args.decode_burst, max_model_len=args.max_model_len,
+                        use_cuda_graph=device.type == "cuda")
+    return LLMEngine(model, ecfg), hf_cfg
+
+
+class LLMServer:
+    def __init__(self, args: argparse.Namespace):
+        self.args = args
+        self.engine, self.hf_cfg = build_engine(args)
+        self.llm = AsyncLLM(self.engine)
+        self.cfg = self.engine.mcfg
+        self.tokenizer = load_tokenizer(args.model, self.hf_cfg, self.cfg.vocab_size)
+        self.receive_embeddings = os.environ.get("CORNSERVE_VLLM_DISABLE_MULTIMODAL") == "1"
+        self.sidecar = None
+        if args.cornserve_sidecar_ranks:
+            from ...sidecar.api import Sidecar
+            from ...sidecar.schema import SidecarConfig
+
+            dtype = next(self.engine.model.parameters()).dtype
+            self.sidecar = Sidecar(SidecarConfig(sidecar_rank=args.cornserve_sidecar_ranks[0],
+                                                 group=list(args.cornserve_sidecar_ranks),
+                                                 send_tensor_dtype=dtype, send_tensor_shape=(-1, self.cfg.hidden_size),
+                                                 recv_tensor_dtype=dtype, recv_tensor_shape=(-1, self.cfg.hidden_size)))
+        self.vision = None  # built lazily for requests that carry raw URLs
+
+    # -- multimodal inputs ----------------------------------------------------------------------------------
+    def _grid_of(self, modality: str, url: str, n_rows: int) -> tuple[int, int, int] | None:
+        """Patch grid of the item behind ``url`` (needed for M-RoPE): read the image size, not the pixels."""
+        merge = self.cfg.spatial_merge_size
+        try:
+            if url.startswith("synthetic:"):
+                h, w = (int(v) for v in url.split(":")[1].split("x"))
+            else:
+                from PIL import Image
+
+                data, _ = fetch_bytes(url)
+                w, h = Image.open(io.BytesIO(data)).size
+            rh, rw = smart_resize(h, w, 14 * merge)
+            gh, gw = rh // 14, rw // 14
+            per_frame = (gh // merge) * (gw // merge)
+            t = max(1, n_rows // per_frame)
+            if t * per_frame == n_rows:
+                return (t, gh, gw)
+        except Exception as e:
+            logger.warning("Could not determine the grid of %s (%s); using sequential positions", url[:60], e)
+        return None
+
+    async def _local_encode(self, modality: str, url: str) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        if self.vision is None:
+            from ...models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+
+            v = Qwen25VisionTransformer(Qwen25VisionConfig.from_hf(self.hf_cfg), device=self.engine.device)
+            if next(self.engine.model.parameters()).dtype == torch.float32:
+                v = v.float()
+            load_model_weights(v, self.args.model, ["visual.", "model.visual."], strict=False)
+            self.vision = v.eval()
+        from ..eric.preprocess import patchify_frames
+        from ..eric.processor import load_image
+
+        img = torch.from_numpy(await asyncio.to_thread(load_image, url)).to(self.engine.device)
+        vc = self.vision.cfg
+        with torch.inference_mode():
+            pv, grid = patchify_frames(img, vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size,
+                                       out_dtype=self.vision.dtype)
+            (emb,) = self.vision("image", None, {"pixel_values": [pv], "image_grid_thw": [list(grid)]})
+        return emb, grid
+
+    async def build_sequence(self, body: dict[str, Any]) -> tuple[Sequence, list[str]]:
+        messages = body["messages"]
+        ids, marks = self.tokenizer.render_chat(messages)
+        parts = [p for m in messages if not isinstance(m["content"], str) for p in m["content"]
+                 if p.get("type", "text") != "text"]
+        if len(parts) != len(marks):
+            raise ValueError("placeholder count does not match the multimodal parts")
+        embeds: list[tuple[torch.Tensor, tuple[int, int, int] | None]] = []
+        recv_ids: list[str] = []
+        for p in parts:
+            modality = p["type"].split("_")[0]
+            url = p[p["type"]]["url"]
+            m = _SIDECAR_URI.match(url)
+            if m is not None:
+                if self.sidecar is None:
+                    raise ValueError("request refers to forwarded embeddings but this executor has no sidecar")
+                chunks, k = [], 0
+                while True:
+                    t = await self.sidecar.recv(m["id"], k)
+                    if t is None:
+                        break
+                    chunks.append(t)
+                    k += 1
+                rows = chunks[0] if len(chunks) == 1 else torch.cat(chunks, dim=0)
+                recv_ids.extend(f"{m['id']}:{i}" for i in range(k))
+                embeds.append((rows, self._grid_of(modality, m["url"], rows.shape[0])))
+            else:
+                emb, grid = await self._local_encode(modality, url)
+                embeds.append((emb, grid))
+        # expand each single placeholder into as many pad tokens as there are embedding rows
+        out: list[int] = []
+        items: list[MMItem] = []
+        prev = 0
+        for (pos, _), (rows, grid) in zip(marks, embeds):
+            out += ids[prev:pos]
+            items.append(MMItem(rows, len(out), grid))
+            out += [ids[pos]] * rows.shape[0]
+            prev = pos + 1
+        out += ids[prev:]
+        params = SamplingParams(max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
+                                ignore_eos=bool(body.get("ignore_eos", False)))
+        # without grids M-RoPE degrades to sequential positions (text-only layout)
+        if any(it.grid_thw is None for it in items):
+            for it in items:
+                it.grid_thw = None
+        xargs = body.get("vllm_xargs") or {}
+        seq = Sequence(body.get("request_id") or uuid.uuid4().hex, np.asarray(out, dtype=np.int32), params, mm_items=items,
+                       return_hidden="cornserve_hidden_states_forward_id" in xargs)
+        return seq, recv_ids
+
+    async def _release(self, recv_ids: list[str]) -> None:
+        for rid in recv_ids:
+            data_id, chunk = rid.split(":")
+            try:
+                await self.sidecar.mark_done(data_id, int(chunk))
+            except Exception:
+                logger.exception("mark_done failed for %s", rid)
+
+    # -- request handling ---------------------------------------------------------------------------------------
+    async def chat(self, body: dict[str, Any]):
+        try:
+            seq, recv_ids = await self.build_sequence(body)
+        except Exception as e:
+            logger.exception("Bad request")
+            return JSONResponse({"error": {"message": str(e), "type": "invalid_request_error"}}, status_code=400)
+        xargs = body.get("vllm_xargs") or {}
+        created, rid, model = int(time.time()), f"chatcmpl-{seq.seq_id}", body.get("model", self.args.model)
+        queue = self.llm.submit(seq)
+        include_usage = bool((body.get("stream_options") or {}).get("include_usage", False))
+
+        def chunk(delta: dict[str, Any], finish: str | None = None, usage: dict | None = None) -> str:
+            payload = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
+                       "choices": [{"index": 0, "delta": delta, "finish_reason": finish}] if usage is None else []}
+            if usage is not None:
+                payload["usage"] = usage
+            return f"data: {json.dumps(payload)}\n\n"
+
+        async def consume():
+            """Yields (text_delta, finished, finish_reason, hidden) per engine output."""
+            all_ids: list[int] = []
+            emitted = ""
+            first = True
+            while True:
+                out: StepOutput = await queue.get()
+                if first and recv_ids:
+                    first = False
+                    await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
+                all_ids.extend(out.new_token_ids)
+                text = self.tokenizer.decode(all_ids)
+                if text.endswith("�") and not out.finished:
+                    delta = ""  # an incomplete multi-byte character: wait for the next token
+                else:
+                    delta, emitted = text[len(emitted):], text
+                yield delta, out, len(all_ids)
+                if out.finished:
+                    return
+
+        if "cornserve_hidden_states_forward_id" in xargs:
+            hidden = None
+            async for _, out, _ in consume():
+                hidden = out.hidden if out.finished else hidden
+            if hidden is not None and self.sidecar is not None:
+                ranks = ast.literal_eval(xargs.get("cornserve_hidden_states_forward_ranks", "[]")) or []
+                if ranks:
+                    self.sidecar.send(hidden.contiguous(), id=xargs["cornserve_hidden_states_forward_id"],
+                                      dst_sidecar_ranks=ranks)
+                    await asyncio.to_thread(self.sidecar.flush)
+            return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
+                                 "choices": [], "cornserve": {"hidden_states_rows": 0 if hidden is None else hidden.shape[0]}})
+
+        if body.get("stream"):
+            async def sse():
+                yield chunk({"role": "assistant", "content": ""})
+                n = 0
+                async for delta, out, n in consume():
+                    if out.finish_reason and out.finish_reason.startswith("error"):
+                        yield f"data: {json.dumps({'error': out.finish_reason})}\n\n"
+                        break
+                    if delta or out.finished:
+                        yield chunk({"content": delta} if delta else {}, out.finish_reason if out.finished else None)
+                if include_usage:
+                    yield chunk({}, usage={"prompt_tokens": seq.prompt_len, "completion_tokens": n,
+                                           "total_tokens": seq.prompt_len + n})
+                yield "data: [DONE]\n\n"
+
+            return StreamingResponse(sse(), media_type="text/event-stream")
+
+        text, reason, n = "", None, 0
+        async for delta, out, n in consume():
+            text += delta
+            reason = out.finish_reason
+        if reason and reason.startswith("error"):
+            return JSONResponse({"error": {"message": reason}}, status_code=500)
+        return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
+                             "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
+                                          "finish_reason": reason}],
+                             "usage": {"prompt_tokens": seq.prompt_len, "completion_tokens": n,
+                                       "total_tokens": seq.prompt_len + n}})
+
+    def create_app(self) -> FastAPI:
+        app = FastAPI(title="cornserve-b200 LLM executor")
+
+        @app.get("/health")
+        async def health():
+            return Response(status_code=200 if self.llm.alive else 503)
+
+        @app.get("/v1/models")
+        async def models():
+            return {"object": "list", "data": [{"id": self.args.model, "object": "model"}]}
+
+        @app.post("/v1/chat/completions")
+        async def chat(raw: Request):
+            return await self.chat(await raw.json())
+
+        return app
+
+    def shutdown(self) -> None:
+        self.llm.shutdown()
+        if self.sidecar is not None:
+            self.sidecar.shutdown_sync()
+
+
+def main(argv: list[str] | None = None) -> None:
+    args = parse_args(argv)
+    configure_otel("llm")
+    server = LLMServer(args)
+    try:
+        uvicorn.run(server.create_app(), host=args.host, port=args.port, log_level="warning")
+    finally:
+        server.shutdown()
+
+
+if __name__ == "__main__":
+    main()

@@ -98,8 +98,11 @@ class BatchMeta:
     logits_idx: torch.Tensor       # [B] int32, flattened index of each sequence's last token
     max_q_len: int = 1
     is_decode: bool = False
-    mm_embeds: torch.Tensor | None = None   # [n, H] encoder rows to place into the input embeddings
-    mm_index: torch.Tensor | None = None    # [n] int32 destination rows (-1 = skip)
+    # encoder rows to place into the input embeddings: per source tensor [n_i, H] the destination rows
+    # [n_i] int32 (-1 = skip).  A source may live in another GPU's memory (a sidecar slab mapped through
+    # CUDA IPC): the placement kernel then reads it over NVLink and writes the local embedding rows.
+    mm_embeds: list[torch.Tensor] | torch.Tensor | None = None
+    mm_index: list[torch.Tensor] | torch.Tensor | None = None
 
 
 class Attention(nn.Module):
@@ -222,8 +225,16 @@ class QwenLLM(nn.Module):
 
     def embed(self, m: BatchMeta) -> torch.Tensor:
         x = self.embed_tokens(m.input_ids)
-        if m.mm_embeds is not None and m.mm_embeds.shape[0] > 0:
-            ops.scatter_rows_(x, m.mm_index, m.mm_embeds.to(x.dtype))
+        if m.mm_embeds is None:
+            return x
+        embeds = m.mm_embeds if isinstance(m.mm_embeds, (list, tuple)) else [m.mm_embeds]
+        index = m.mm_index if isinstance(m.mm_index, (list, tuple)) else [m.mm_index]
+        for rows, idx in zip(embeds, index, strict=True):
+            if rows.shape[0] == 0:
+                continue
+            if rows.dtype != x.dtype or (x.is_cuda and not rows.is_cuda):
+                rows = rows.to(device=x.device, dtype=x.dtype)
+            ops.scatter_rows_(x, idx, rows)
         return x
 
     def forward_hidden(self, m: BatchMeta, kv_caches: list[torch.Tensor]) -> torch.Tensor:

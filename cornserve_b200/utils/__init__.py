@@ -1,0 +1,1 @@
+"""Utilities: checkpoint resolution and safetensors loading, timing helpers."""
