@@ -55,6 +55,26 @@ __device__ __forceinline__ void act16(float (&f)[16], int act) {
   }
 }
 
+// One-shot all-reduce fused into the epilogue (tensor-parallel row-parallel projections at decode time).
+// Every rank pushes its bf16 partial tile into slot [rank] of every peer's receive buffer, bumps the
+// peer's per-tile arrival counter, waits until its own counter shows all `world` partials, sums them with
+// the residual, and the CTA that finishes last applies RMSNorm to the rows.  Buffers alternate between two
+// halves by call parity (a rank can never run two calls ahead of a peer), counters only ever grow, and the
+// call number lives in device memory so that a CUDA graph can replay the kernel.
+constexpr int AR_MAX_WORLD = 8;
+struct AllReduceParams {
+  int world, rank;
+  __nv_bfloat16* recv[AR_MAX_WORLD];  // per peer: [2][world][m_cap][n_cap]
+  unsigned* flags[AR_MAX_WORLD];      // per peer: [2][tiles_cap]
+  int m_cap, n_cap, tiles_cap;
+  float* ssq;                         // local [m_cap] row sums of squares (zero between calls)
+  int* done;                          // local tile-completion counter (zero between calls)
+  unsigned* epoch;                    // local call counter
+  const __nv_bfloat16* norm_w;        // RMSNorm weight [N] or null (then no norm output)
+  __nv_bfloat16* normed; long long ldn;
+  float eps;
+};
+
 struct SkinnyParams {
   int M, N, K;          // N = output columns
   int m_pad;            // tokens padded to a multiple of 16
@@ -69,6 +89,7 @@ struct SkinnyParams {
   uint32_t idesc;
   uint32_t tmem_cols;
   int* err;
+  AllReduceParams ar;
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -164,6 +185,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     const int chunks = p.m_pad / 16;
+    const unsigned ar_epoch = p.ar.world > 1 ? *reinterpret_cast<volatile unsigned*>(p.ar.epoch) : 0u;
+    const unsigned ar_parity = ar_epoch & 1u;
+    const int num_tiles_total = gridDim.x / p.splits;
     // For the fused SwiGLU tile rows 0..63 are gate columns and rows 64..127 the matching up columns.
     const int w_row = p.swiglu ? (r < 64 ? n0 + r : p.up_row_offset + n0 + (r - 64)) : n0 + r;
     const bool row_valid = p.swiglu ? (n0 + (r & 63) < p.N) : (n0 + r < p.N);
@@ -244,6 +268,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           act16(f, p.act);
         }
         const bool writer = row_valid && (!p.swiglu || r < 64);
+        if (p.ar.world > 1) {
+          // push this rank's partial (bias already applied on rank 0 only by the caller) to every peer
+          if (writer) {
+            const int n = n0 + r;
+            const int mmax = min(16, p.M - c * 16);
+            const long long slot = (static_cast<long long>(ar_parity) * p.ar.world + p.ar.rank) * p.ar.m_cap;
+            for (int peer = 0; peer < p.ar.world; ++peer) {
+              __nv_bfloat16* dst = p.ar.recv[peer] + (slot + c * 16) * p.ar.n_cap + n;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < mmax) dst[static_cast<long long>(i) * p.ar.n_cap] = __float2bfloat16(f[i]);
+            }
+          }
+          continue;
+        }
         if (writer) {
           const int n = n0 + r;
           const int mmax = min(16, p.M - c * 16);
@@ -264,6 +303,104 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             for (int i = 0; i < 16; ++i)
               if (i < mmax) op[static_cast<long long>(i) * p.ldc] = __float2bfloat16(f[i]);
           }
+        }
+      }
+      if (p.ar.world > 1) {
+        // ---- signal: all stores of this CTA are visible system-wide before the counters move ----
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (r < p.ar.world) {
+          unsigned* flag = p.ar.flags[r] + static_cast<long long>(ar_parity) * p.ar.tiles_cap + tile;
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+        }
+        // ---- wait for the partials of all ranks for this tile ----
+        const unsigned target = (ar_epoch / 2 + 1) * static_cast<unsigned>(p.ar.world);
+        const unsigned* mine = p.ar.flags[p.ar.rank] + static_cast<long long>(ar_parity) * p.ar.tiles_cap + tile;
+        if (r == 0) {
+          uint64_t t0 = 0;
+          for (uint32_t spin = 0;; ++spin) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v >= target) break;
+            if ((spin & 0xff) == 0xff) {
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              if (now - t0 > CS_WAIT_LIMIT_NS) { cs_set_error(p.err, CS_ERR_TIMEOUT_PEER); break; }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // ---- reduce: sum the world partials (+ residual), keep the new residual, gather row norms ----
+        const int n = n0 + r;
+        for (int c = 0; c < chunks; ++c) {
+          const int mmax = min(16, p.M - c * 16);
+          float h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) h[i] = 0.f;
+          if (row_valid) {
+            for (int src = 0; src < p.ar.world; ++src) {
+              const __nv_bfloat16* part = p.ar.recv[p.ar.rank] +
+                  ((static_cast<long long>(ar_parity) * p.ar.world + src) * p.ar.m_cap + c * 16) * p.ar.n_cap + n;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < mmax) h[i] += __bfloat162float(__ldcg(part + static_cast<long long>(i) * p.ar.n_cap));
+            }
+            if (p.residual != nullptr) {
+              const __nv_bfloat16* rp = p.residual + static_cast<long long>(c * 16) * p.ldr + n;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < mmax) h[i] += __bfloat162float(rp[static_cast<long long>(i) * p.ldr]);
+            }
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(c * 16) * p.ldc + n;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (i < mmax) {
+                const __nv_bfloat16 hb = __float2bfloat16(h[i]);
+                op[static_cast<long long>(i) * p.ldc] = hb;
+                h[i] = __bfloat162float(hb);  // the norm sees the stored (rounded) value
+              }
+            }
+          }
+          if (p.ar.norm_w != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float sq = (row_valid && i < mmax) ? h[i] * h[i] : 0.f;
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+              if (lane == 0 && i < mmax) atomicAdd(&p.ar.ssq[c * 16 + i], sq);
+            }
+          }
+        }
+        // ---- the CTA that completes the last tile normalises all rows and re-arms the scratch ----
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (r == 0) {
+          const int prev = atomicAdd(p.ar.done, 1);
+          is_last = (prev == num_tiles_total - 1) ? 2 : 0;
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*reinterpret_cast<volatile int*>(&is_last) == 2) {
+          if (p.ar.norm_w != nullptr) {
+            for (int m = 0; m < p.M; ++m) {
+              const float rstd = rsqrtf(__ldcg(&p.ar.ssq[m]) / static_cast<float>(p.N) + p.ar.eps);
+              const __nv_bfloat16* hrow = reinterpret_cast<const __nv_bfloat16*>(p.C) + static_cast<long long>(m) * p.ldc;
+              __nv_bfloat16* orow = p.ar.normed + static_cast<long long>(m) * p.ar.ldn;
+              for (int col = r * 8; col < p.N; col += 128 * 8) {
+                const uint4 hv = __ldcg(reinterpret_cast<const uint4*>(hrow + col));
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.ar.norm_w + col));
+                uint4 o;
+                o.x = pack_bf16x2(bf16lo(hv.x) * rstd * bf16lo(wv.x), bf16hi(hv.x) * rstd * bf16hi(wv.x));
+                o.y = pack_bf16x2(bf16lo(hv.y) * rstd * bf16lo(wv.y), bf16hi(hv.y) * rstd * bf16hi(wv.y));
+                o.z = pack_bf16x2(bf16lo(hv.z) * rstd * bf16lo(wv.z), bf16hi(hv.z) * rstd * bf16hi(wv.z));
+                o.w = pack_bf16x2(bf16lo(hv.w) * rstd * bf16lo(wv.w), bf16hi(hv.w) * rstd * bf16hi(wv.w));
+                *reinterpret_cast<uint4*>(orow + col) = o;
+              }
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int m = r; m < p.ar.m_cap; m += 128) p.ar.ssq[m] = 0.f;
+          if (r == 0) { *p.ar.done = 0; *p.ar.epoch = ar_epoch + 1; }
         }
       }
     }
@@ -344,6 +481,87 @@ CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long
   CUtensorMap tmW, tmX;
   const int w_rows = swiglu ? 2 * N : N;
   if (cs_encode_tmap_2d(&tmW, W, K, w_rows, ldw * 2, BK, swiglu ? 64 : 128, 2, 1) != 0) return -2;
+  if (cs_encode_tmap_2d(&tmX, X, K, M, ldx * 2, BK, p.m_pad, 2, 1) != 0) return -3;
+  const int smem = stages * stage_bytes + 1024;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!attr_done[dev]) {
+    cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    attr_done[dev] = true;
+  }
+  gemm_skinny_kernel<<<tiles * splits, 192, smem, stream>>>(tmW, tmX, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+// Fused row-parallel projection + one-shot all-reduce + residual + RMSNorm over NVLink peer memory:
+//   h      = sum_over_ranks(X_r W_r^T (+ bias on rank 0)) + residual       -> `H`      [M,N] bf16
+//   normed = RMSNorm(h) * norm_w                                           -> `normed` [M,N] bf16 (if norm_w)
+// `recv_ptrs[p]` / `flag_ptrs[p]` are rank p's symmetric receive buffer ([2][world][m_cap][n_cap] bf16) and
+// arrival counters ([2][tiles_cap] u32, zero at start, never reset); `ssq` ([m_cap] f32), `done` (int) and
+// `epoch` (u32) are local scratch, zero before the first call.  Every rank must call with the same shapes,
+// in the same order, on streams that do not run two of these calls concurrently.  M <= 256, N % 8 == 0.
+CS_API int cs_gemm_skinny_allreduce(const void* X, long long ldx, const void* W, long long ldw, void* H, long long ldh,
+                                    const void* bias, const void* residual, long long ldr, const void* norm_w,
+                                    void* normed, long long ldn, float eps, int M, int N, int K, int splits,
+                                    void* ws, long long ws_bytes, void* counters, int num_counters, int world,
+                                    int rank, const void* const* recv_ptrs, const void* const* flag_ptrs, int m_cap,
+                                    int n_cap, int tiles_cap, void* ssq, void* done, void* epoch, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 256 || K <= 0 || (ldx & 7) || (ldw & 7) || (N & 7) || world < 1 || world > AR_MAX_WORLD) return -1;
+  SkinnyParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.m_pad = (M + 15) & ~15;
+  if (p.m_pad > m_cap || N > n_cap) return -6;
+  p.swiglu = 0;
+  p.up_row_offset = N;
+  p.C = H; p.ldc = ldh; p.out_fp32 = 0;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.act = ACT_NONE;
+  p.err = cs_error_word();
+  const int tiles = (N + 127) / 128;
+  if (tiles > tiles_cap) return -6;
+  if (splits <= 0) splits = cs_gemm_skinny_auto_splits(N, K, 0);
+  const int total_it = (K + BK * KATOMS - 1) / (BK * KATOMS);
+  if (splits > total_it) splits = total_it;
+  if (splits > 1 && (ws == nullptr || counters == nullptr || tiles > num_counters ||
+                     cs_gemm_skinny_ws_bytes(M, N, splits, 0) > ws_bytes))
+    return -5;
+  // every CTA of every rank must be resident at once (tile CTAs wait for their peers' tile CTAs)
+  while (splits > 1 && tiles * splits > cs_num_sms()) --splits;
+  if (tiles * splits > cs_num_sms()) return -6;
+  p.splits = splits;
+  p.ws = reinterpret_cast<float*>(ws);
+  p.counters = reinterpret_cast<int*>(counters);
+  p.ar.world = world; p.ar.rank = rank;
+  for (int i = 0; i < world; ++i) {
+    p.ar.recv[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(recv_ptrs[i]));
+    p.ar.flags[i] = reinterpret_cast<unsigned*>(const_cast<void*>(flag_ptrs[i]));
+  }
+  p.ar.m_cap = m_cap; p.ar.n_cap = n_cap; p.ar.tiles_cap = tiles_cap;
+  p.ar.ssq = reinterpret_cast<float*>(ssq);
+  p.ar.done = reinterpret_cast<int*>(done);
+  p.ar.epoch = reinterpret_cast<unsigned*>(epoch);
+  p.ar.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
+  p.ar.normed = reinterpret_cast<__nv_bfloat16*>(normed);
+  p.ar.ldn = ldn;
+  p.ar.eps = eps;
+  if (world == 1) return -7;  // use cs_gemm_skinny + cs_norm on a single GPU
+  const int stage_bytes = KATOMS * (W_ATOM + p.m_pad * 128);
+  int stages = MAX_STAGES;
+  const int max_smem = 220 * 1024;
+  while (stages > 2 && stages * stage_bytes + 1024 > max_smem) --stages;
+  p.stages = stages;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.m_pad)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.idesc = umma_idesc_bf16(128, p.m_pad, 0, 0);
+  CUtensorMap tmW, tmX;
+  if (cs_encode_tmap_2d(&tmW, W, K, N, ldw * 2, BK, 128, 2, 1) != 0) return -2;
   if (cs_encode_tmap_2d(&tmX, X, K, M, ldx * 2, BK, p.m_pad, 2, 1) != 0) return -3;
   const int smem = stages * stage_bytes + 1024;
   static bool attr_done[64] = {false};
