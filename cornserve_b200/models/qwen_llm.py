@@ -119,7 +119,8 @@ class Attention(nn.Module):
             self.q_norm = RMSNorm(d, cfg.rms_norm_eps, device=device)
             self.k_norm = RMSNorm(d, cfg.rms_norm_eps, device=device)
 
-    def forward(self, h: torch.Tensor, cs: torch.Tensor, cache: torch.Tensor, m: BatchMeta) -> torch.Tensor:
+    def attend(self, h: torch.Tensor, cs: torch.Tensor, cache: torch.Tensor, m: BatchMeta) -> torch.Tensor:
+        """Attention context ``[T, heads_local * d]`` (before the output projection)."""
         d = self.cfg.head_dim
         T = h.shape[0]
         qkv = self.qkv(h)
@@ -132,7 +133,10 @@ class Attention(nn.Module):
         q = ops.rope_kv_write_(qkv, self.hq, self.hkv, d, cs, cache, m.slot_mapping)
         o = ops.attention_paged(q, cache, m.block_table, m.kv_len, m.cu_q, m.max_q_len, causal=True,
                                 pack_gqa=m.is_decode and self.hq > self.hkv)
-        return self.o_proj(o.view(T, self.hq * d))
+        return o.view(T, self.hq * d)
+
+    def forward(self, h, cs, cache, m):
+        return self.o_proj(self.attend(h, cs, cache, m))
 
 
 class MLP(nn.Module):
@@ -179,16 +183,36 @@ class DecoderLayer(nn.Module):
         self.self_attn = Attention(cfg, group, device)
         self.mlp = SparseMoE(cfg, ep_group or group, device) if cfg.num_experts > 0 else MLP(cfg, group, device)
 
-    def forward(self, x, residual, cs, cache, m: BatchMeta):
-        if residual is None:
-            residual = x
-            h = self.input_layernorm(x)
-        else:
-            h, residual = self.input_layernorm(x, residual=residual)
-        x = self.self_attn(h, cs, cache, m)
-        h, residual = self.post_attention_layernorm(x, residual=residual)
-        x = self.mlp(h)
-        return x, residual
+    def forward(self, h, residual, cs, cache, m: BatchMeta, next_norm: RMSNorm, fused=None):
+        """``h`` = this layer's normalised input, ``residual`` = the un-normalised stream.  Returns the
+        normalised input of the next layer (through ``next_norm``) and the updated residual stream.
+
+        Each half (attention, MLP) ends in "row-parallel projection -> reduce over the group -> add residual
+        -> RMSNorm".  With tensor parallelism and few tokens that whole tail is one fused kernel
+        (``parallel.fused.FusedRowParallel``: the partial sums travel over NVLink from the GEMM epilogue);
+        otherwise the projection's epilogue adds the residual and a norm kernel follows."""
+        attn = self.self_attn.attend(h, cs, cache, m)
+        h, residual = row_parallel_tail(attn, self.self_attn.o_proj, residual, self.post_attention_layernorm, fused)
+        if isinstance(self.mlp, SparseMoE):
+            y = self.mlp(h)
+            h, residual = next_norm(y, residual=residual)
+            return h, residual
+        act = self.mlp.gate_up(h)
+        return row_parallel_tail(act, self.mlp.down, residual, next_norm, fused)
+
+
+def row_parallel_tail(x: torch.Tensor, proj: RowParallelLinear, residual: torch.Tensor, norm: RMSNorm, fused=None):
+    """``residual' = all_reduce(x @ W^T) + residual`` and ``norm(residual')``; returns ``(normed, residual')``."""
+    g = proj.group
+    if g.size > 1 and fused is not None and x.is_cuda and x.shape[0] <= fused.m_cap:
+        new_res, normed = fused(x, proj.weight, proj.bias, residual, norm.weight, norm.eps)
+        return normed, new_res
+    if g.size == 1:
+        new_res = proj(x, residual=residual)  # residual add in the GEMM epilogue
+        return norm(new_res), new_res
+    y = proj(x)  # partial sums reduced by the library collective
+    normed, new_res = norm(y, residual=residual)
+    return normed, new_res
 
 
 class QwenLLM(nn.Module):
@@ -244,11 +268,22 @@ class QwenLLM(nn.Module):
         half = cfg.head_dim // 2
         sections = cfg.mrope_section or [half, 0, 0]
         cs = ops.mrope_table(m.positions, half, cfg.rope_theta, sections)
-        residual = None
-        for layer, cache in zip(self.layers, kv_caches):
-            x, residual = layer(x, residual, cs, cache, m)
-        h, _ = self.norm(x, residual=residual)
+        residual = x
+        h = self.layers[0].input_layernorm(x)
+        fused = self._fused_tail() if (self.group.size > 1 and x.is_cuda) else None
+        n = len(self.layers)
+        for i, (layer, cache) in enumerate(zip(self.layers, kv_caches)):
+            next_norm = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
+            h, residual = layer(h, residual, cs, cache, m, next_norm, fused)
         return h
+
+    def _fused_tail(self):
+        """Lazily built fused GEMM + all-reduce + residual + RMSNorm kernel context (needs the fabric)."""
+        if getattr(self, "_fused", None) is None and self.group.fabric is not None:
+            from ..parallel.fused import FusedRowParallel
+
+            self._fused = FusedRowParallel(self.group, self.cfg.hidden_size, m_cap=256)
+        return getattr(self, "_fused", None)
 
     def compute_logits(self, h_last: torch.Tensor) -> torch.Tensor:
         if self.lm_head is None:

@@ -35,7 +35,7 @@ class FusedRowParallel:
         self.flags: SymmetricBuffer = fab.alloc(2 * self.tiles_cap, torch.int32)
         dev = group.device
         self.ssq = torch.zeros(m_cap, device=dev, dtype=torch.float32)
-        self.done = torch.zeros(1, device=dev, dtype=torch.int32)
+        self.done = torch.zeros(2, device=dev, dtype=torch.int32)
         self.epoch = torch.zeros(1, device=dev, dtype=torch.int32)
         self._recv_ptrs = self.recv.ptr_array()
         self._flag_ptrs = self.flags.ptr_array()

@@ -68,7 +68,7 @@ struct AllReduceParams {
   unsigned* flags[AR_MAX_WORLD];      // per peer: [2][tiles_cap]
   int m_cap, n_cap, tiles_cap;
   float* ssq;                         // local [m_cap] row sums of squares (zero between calls)
-  int* done;                          // local tile-completion counter (zero between calls)
+  int* done;                          // local int[2]: tiles reduced / tiles normalised (zero between calls)
   unsigned* epoch;                    // local call counter
   const __nv_bfloat16* norm_w;        // RMSNorm weight [N] or null (then no norm output)
   __nv_bfloat16* normed; long long ldn;
@@ -371,36 +371,55 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
           }
         }
-        // ---- the CTA that completes the last tile normalises all rows and re-arms the scratch ----
+        // ---- once every tile of this rank is reduced, each tile CTA normalises its own 128 columns ----
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (r == 0) {
-          const int prev = atomicAdd(p.ar.done, 1);
+          atomicAdd(&p.ar.done[0], 1);
+          if (p.ar.norm_w != nullptr) {
+            // all tile CTAs of the grid are resident (checked by the host), so this wait cannot starve
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0;; ++spin) {
+              if (*reinterpret_cast<volatile int*>(&p.ar.done[0]) >= num_tiles_total) break;
+              if ((spin & 0xff) == 0xff) {
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > CS_WAIT_LIMIT_NS) { cs_set_error(p.err, CS_ERR_TIMEOUT_EPI); break; }
+              }
+            }
+            __threadfence();
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (p.ar.norm_w != nullptr && row_valid) {
+          const float wn = __bfloat162float(p.ar.norm_w[n]);
+          const float inv_n = 1.0f / static_cast<float>(p.N);
+          for (int c = 0; c < chunks; ++c) {
+            const int mmax = min(16, p.M - c * 16);
+            const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(p.C) + static_cast<long long>(c * 16) * p.ldc + n;
+            __nv_bfloat16* op = p.ar.normed + static_cast<long long>(c * 16) * p.ar.ldn + n;
+            float hv[16], sv[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              hv[i] = i < mmax ? __bfloat162float(hp[static_cast<long long>(i) * p.ldc]) : 0.f;
+              sv[i] = i < mmax ? __ldcg(&p.ar.ssq[c * 16 + i]) : 1.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (i < mmax) op[static_cast<long long>(i) * p.ar.ldn] = __float2bfloat16(hv[i] * rsqrtf(sv[i] * inv_n + p.ar.eps) * wn);
+          }
+        }
+        // ---- the CTA that leaves last re-arms the scratch for the next call ----
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (r == 0) {
+          const int prev = atomicAdd(&p.ar.done[1], 1);
           is_last = (prev == num_tiles_total - 1) ? 2 : 0;
-          __threadfence();
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*reinterpret_cast<volatile int*>(&is_last) == 2) {
-          if (p.ar.norm_w != nullptr) {
-            for (int m = 0; m < p.M; ++m) {
-              const float rstd = rsqrtf(__ldcg(&p.ar.ssq[m]) / static_cast<float>(p.N) + p.ar.eps);
-              const __nv_bfloat16* hrow = reinterpret_cast<const __nv_bfloat16*>(p.C) + static_cast<long long>(m) * p.ldc;
-              __nv_bfloat16* orow = p.ar.normed + static_cast<long long>(m) * p.ar.ldn;
-              for (int col = r * 8; col < p.N; col += 128 * 8) {
-                const uint4 hv = __ldcg(reinterpret_cast<const uint4*>(hrow + col));
-                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.ar.norm_w + col));
-                uint4 o;
-                o.x = pack_bf16x2(bf16lo(hv.x) * rstd * bf16lo(wv.x), bf16hi(hv.x) * rstd * bf16hi(wv.x));
-                o.y = pack_bf16x2(bf16lo(hv.y) * rstd * bf16lo(wv.y), bf16hi(hv.y) * rstd * bf16hi(wv.y));
-                o.z = pack_bf16x2(bf16lo(hv.z) * rstd * bf16lo(wv.z), bf16hi(hv.z) * rstd * bf16hi(wv.z));
-                o.w = pack_bf16x2(bf16lo(hv.w) * rstd * bf16lo(wv.w), bf16hi(hv.w) * rstd * bf16hi(wv.w));
-                *reinterpret_cast<uint4*>(orow + col) = o;
-              }
-            }
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
           for (int m = r; m < p.ar.m_cap; m += 128) p.ar.ssq[m] = 0.f;
-          if (r == 0) { *p.ar.done = 0; *p.ar.epoch = ar_epoch + 1; }
+          if (r == 0) { p.ar.done[0] = 0; p.ar.done[1] = 0; *p.ar.epoch = ar_epoch + 1; }
         }
       }
     }
@@ -499,7 +518,7 @@ CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long
 //   h      = sum_over_ranks(X_r W_r^T (+ bias on rank 0)) + residual       -> `H`      [M,N] bf16
 //   normed = RMSNorm(h) * norm_w                                           -> `normed` [M,N] bf16 (if norm_w)
 // `recv_ptrs[p]` / `flag_ptrs[p]` are rank p's symmetric receive buffer ([2][world][m_cap][n_cap] bf16) and
-// arrival counters ([2][tiles_cap] u32, zero at start, never reset); `ssq` ([m_cap] f32), `done` (int) and
+// arrival counters ([2][tiles_cap] u32, zero at start, never reset); `ssq` ([m_cap] f32), `done` (int[2]) and
 // `epoch` (u32) are local scratch, zero before the first call.  Every rank must call with the same shapes,
 // in the same order, on streams that do not run two of these calls concurrently.  M <= 256, N % 8 == 0.
 CS_API int cs_gemm_skinny_allreduce(const void* X, long long ldx, const void* W, long long ldw, void* H, long long ldh,
