@@ -19,6 +19,8 @@ __all__ = [
     "linear", "swiglu_linear", "rms_norm", "layer_norm", "rope_", "mrope_table", "rope_kv_write_",
     "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
     "flow_step_", "pcm16", "decode_advance_", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
+    "head_norm_rope_", "softmax_rows", "im2col3x3", "im2col1d", "dwconv1d", "to_rgb8", "conv3x3", "conv1d_causal",
+    "conv_transpose1d_causal",
 ]
 
 _launches = 0
@@ -286,13 +288,14 @@ def rope_kv_write_(qkv: torch.Tensor, Hq: int, Hkv: int, d: int, cs: torch.Tenso
 # attention
 # --------------------------------------------------------------------------------------------
 def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = None, causal: bool = False,
-                     out: torch.Tensor | None = None) -> torch.Tensor:
+                     out: torch.Tensor | None = None, window: int = 0) -> torch.Tensor:
     """Packed variable-length attention.  q ``[Tq, Hq, d]``, k/v ``[Tk, Hkv, d]`` (strided views are
-    fine as long as heads are ``d`` apart); ``cu_*`` are int32 prefix sums.  Returns ``[Tq, Hq, d]``."""
+    fine as long as heads are ``d`` apart); ``cu_*`` are int32 prefix sums.  Returns ``[Tq, Hq, d]``.
+    ``window > 0`` (causal only): each query sees the last ``window`` keys up to its own position."""
     Tq, Hq, d = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     if not q.is_cuda:
-        o = reference.attention_varlen(q, k, v, cu_q, cu_k, scale, causal)
+        o = reference.attention_varlen(q, k, v, cu_q, cu_k, scale, causal, window)
         if out is not None:
             out.copy_(o)
             return out
@@ -307,11 +310,25 @@ def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = 
     rc = lib.cs_attention(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
         out.data_ptr(), out.stride(0), cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
-        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, 1, None, 0, _stream(),
+        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, 1, None, 0, int(window), _stream(),
     )
     _chk(rc, "cs_attention")
     _count()
     return out
+
+
+def _decode_kv_splits(items: int, sms: int, max_tiles: int) -> int:
+    """Split count for decode attention.  The kernel is persistent with a static round-robin assignment of
+    work items to SMs, so the time is ``ceil(items * s / sms) / s`` item-lengths: take the smallest ``s`` that
+    gets within 3% of the best balance, keeping at least two key tiles per split."""
+    best_s, best = 1, float("inf")
+    for s in range(1, 17):
+        if s > 1 and 2 * s > max_tiles:
+            break
+        cost = -(-items * s // sms) / s
+        if cost < best * 0.97:
+            best, best_s = cost, s
+    return best_s
 
 
 def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: float | None = None,
@@ -339,8 +356,7 @@ def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: 
     if kv_splits == 0:
         # decode (one query token per sequence): spread the keys of each sequence over idle SMs
         items = B * (Hkv if pack_gqa else Hq)
-        sms = lib.cs_sm_count()
-        kv_splits = max(1, min(16, sms // max(items, 1))) if max_q_len == 1 else 1
+        kv_splits = _decode_kv_splits(items, lib.cs_sm_count(), block_table.shape[1]) if max_q_len == 1 else 1
     ws_ptr, ws_bytes = None, 0
     if kv_splits > 1:
         ws, _ = _skinny_workspace(q.device)
@@ -353,7 +369,7 @@ def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: 
         q.data_ptr(), q.stride(0), cache.data_ptr(), 0, None, 0, out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), None, kv_len.data_ptr(), block_table.data_ptr(), block_table.stride(0), pages,
         B, Tq, 0, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 1 if pack_gqa else 0,
-        kv_splits, ws_ptr, ws_bytes, _stream(),
+        kv_splits, ws_ptr, ws_bytes, 0, _stream(),
     )
     _chk(rc, "cs_attention(paged)")
     _count(2 if kv_splits > 1 else 1)
@@ -490,3 +506,125 @@ def l2_flush(buf: torch.Tensor, value: int = 0) -> None:
     lib = _lib.load()
     _chk(lib.cs_l2_flush(buf.data_ptr(), buf.numel() * buf.element_size(), value, _stream()), "cs_l2_flush")
     _count()
+
+
+# --------------------------------------------------------------------------------------------
+# generator models: per-head norm + rotary, soft-max, convolutions as tap gather + tcgen05 GEMM
+# --------------------------------------------------------------------------------------------
+def head_norm_rope_(x: torch.Tensor, w: torch.Tensor | None, eps: float, cs: torch.Tensor | None) -> torch.Tensor:
+    """In place on ``x`` = ``[T, heads, d]`` (token-strided view is fine): RMSNorm over ``d`` with weight
+    ``w`` (skipped when ``None``), then rotate-half RoPE with ``cs`` = ``[T, 2, d/2]`` (skipped when ``None``)."""
+    T, heads, d = x.shape
+    if not x.is_cuda:
+        x.copy_(reference.head_norm_rope(x, w, eps, cs))
+        return x
+    assert x.stride(2) == 1 and x.stride(1) == d and x.dtype == torch.bfloat16
+    assert cs is None or (cs.dtype == torch.float32 and cs.is_contiguous() and cs.shape[-1] * 2 == d)
+    lib = _lib.load()
+    _chk(lib.cs_head_norm_rope(x.data_ptr(), x.stride(0), T, heads, d, _ptr(w), float(eps), _ptr(cs), _stream()),
+         "cs_head_norm_rope")
+    _count()
+    return x
+
+
+def softmax_rows(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Row soft-max of ``scale * x`` for a 2-D bf16 matrix (columns a multiple of 8)."""
+    if not x.is_cuda:
+        return reference.softmax_rows(x, scale)
+    x = _rowmajor(x)
+    rows, cols = x.shape
+    y = torch.empty_like(x)
+    lib = _lib.load()
+    _chk(lib.cs_softmax_rows(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), rows, cols, float(scale),
+                             _stream()), "cs_softmax_rows")
+    _count()
+    return y
+
+
+def im2col3x3(x: torch.Tensor, B: int, H: int, W: int, up: int = 1, silu: bool = False) -> torch.Tensor:
+    """Channels-last image ``[B*H*W, C]`` -> ``[B*(up H)*(up W), 9 C]`` GEMM operand of a 3x3 convolution."""
+    if not x.is_cuda:
+        return reference.im2col3x3(x, B, H, W, up, silu)
+    C = x.shape[-1]
+    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    out = torch.empty((B * H * up * W * up, 9 * C), device=x.device, dtype=x.dtype)
+    lib = _lib.load()
+    _chk(lib.cs_im2col3x3(x.data_ptr(), out.data_ptr(), B, H, W, C, up, 1 if silu else 0, _stream()), "cs_im2col3x3")
+    _count()
+    return out
+
+
+def im2col1d(x: torch.Tensor, B: int, T: int, To: int, taps: int, first: int, dilation: int = 1,
+             alpha: torch.Tensor | None = None, beta: torch.Tensor | None = None) -> torch.Tensor:
+    """Channels-last sequence ``[B*T, C]`` -> ``[B*To, taps*C]``; with ``alpha``/``beta`` (fp32 ``[C]``) SnakeBeta
+    is applied to every gathered value."""
+    if not x.is_cuda:
+        return reference.im2col1d(x, B, T, To, taps, first, dilation, alpha, beta)
+    C = x.shape[-1]
+    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    out = torch.empty((B * To, taps * C), device=x.device, dtype=x.dtype)
+    lib = _lib.load()
+    _chk(lib.cs_im2col1d(x.data_ptr(), out.data_ptr(), B, T, To, C, taps, first, dilation, 0 if alpha is None else 1,
+                         _ptr(alpha), _ptr(beta), _stream()), "cs_im2col1d")
+    _count()
+    return out
+
+
+def dwconv1d(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, B: int, T: int) -> torch.Tensor:
+    """Depth-wise causal 1-D convolution on ``[B*T, C]`` with ``w`` = ``[C, k]``."""
+    if not x.is_cuda:
+        return reference.dwconv1d(x, w, bias, B, T)
+    C, k = w.shape
+    y = torch.empty_like(x)
+    lib = _lib.load()
+    _chk(lib.cs_dwconv1d(x.data_ptr(), y.data_ptr(), w.data_ptr(), _ptr(bias), B, T, C, k, _stream()), "cs_dwconv1d")
+    _count()
+    return y
+
+
+def to_rgb8(x: torch.Tensor) -> torch.Tensor:
+    """Channels-last image rows ``[pixels, >=3]`` in [-1, 1] -> uint8 ``[pixels, 3]``."""
+    if not x.is_cuda:
+        return reference.to_rgb8(x)
+    y = torch.empty((x.shape[0], 3), device=x.device, dtype=torch.uint8)
+    lib = _lib.load()
+    _chk(lib.cs_to_rgb8(x.data_ptr(), x.stride(0), y.data_ptr(), x.shape[0], _stream()), "cs_to_rgb8")
+    _count()
+    return y
+
+
+def conv3x3(x: torch.Tensor, w2d: torch.Tensor, bias: torch.Tensor | None, B: int, H: int, W: int, *, up: int = 1,
+            silu: bool = False, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """3x3 convolution (padding 1) on a channels-last image; ``w2d`` is ``[Cout, 9*Cin]`` in (ky, kx, cin) order.
+    ``silu`` applies SiLU to the input first, ``up=2`` convolves the nearest-neighbour 2x upsampled image."""
+    cols = im2col3x3(x, B, H, W, up, silu)
+    return linear(cols, w2d, bias, residual=residual)
+
+
+def conv1d_causal(x: torch.Tensor, w2d: torch.Tensor, bias: torch.Tensor | None, B: int, T: int, k: int,
+                  dilation: int = 1, *, alpha=None, beta=None, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal dilated 1-D convolution on ``[B*T, Cin]``; ``w2d`` is ``[Cout, k*Cin]`` in (tap, cin) order.  With
+    ``alpha``/``beta`` SnakeBeta is applied to the input on the fly."""
+    if k == 1 and alpha is None:
+        return linear(x, w2d, bias, residual=residual)
+    cols = im2col1d(x, B, T, T, k, -(k - 1) * dilation, dilation, alpha, beta)
+    return linear(cols, w2d, bias, residual=residual)
+
+
+def conv_transpose1d_causal(x: torch.Tensor, w2d: torch.Tensor, bias_rep: torch.Tensor | None, B: int, T: int,
+                            stride: int, kernel: int, *, alpha=None, beta=None) -> tuple[torch.Tensor, int]:
+    """Transposed 1-D convolution with the trimming used by causal vocoders.
+
+    ``kernel == stride``: every input step yields ``stride`` outputs (``w2d`` = ``[stride*Cout, Cin]``).
+    ``kernel == 2*stride``: outputs are trimmed by ``stride`` on both sides, so output ``(t-1)*stride + p`` is
+    ``W[:, :, p] x[t] + W[:, :, p + stride] x[t-1]`` for ``t`` in ``1..T-1`` (``w2d`` = ``[stride*Cout, 2*Cin]``,
+    input taps ordered (x[t], x[t-1])).  Returns ``([B*To, Cout], To)``."""
+    if kernel == stride:
+        xin = x if alpha is None else im2col1d(x, B, T, T, 1, 0, 1, alpha, beta)
+        y = linear(xin, w2d, bias_rep)
+        return y.view(B * T * stride, -1), T * stride
+    assert kernel == 2 * stride
+    # rows t = 1..T-1: taps (x[t], x[t-1])  ->  first = +1 with dilation -1
+    cols = im2col1d(x, B, T, T - 1, 2, 1, -1, alpha, beta)
+    y = linear(cols, w2d, bias_rep)
+    return y.view(B * (T - 1) * stride, -1), (T - 1) * stride

@@ -1,0 +1,138 @@
+"""Times one kernel of the library on one shape (CUDA events, warm-up, L2 flushed between iterations).
+
+  python -m cornserve_b200.ops.microbench gemm 16384 3584 3584
+  python -m cornserve_b200.ops.microbench swiglu 19136 3424 1280
+  python -m cornserve_b200.ops.microbench skinny 64 3584 18944
+  python -m cornserve_b200.ops.microbench attn-window 4            # Qwen2.5-VL windows of 4 1280x720 images
+  python -m cornserve_b200.ops.microbench attn-full 16 80 4784 0   # heads, head_dim, length, causal
+  python -m cornserve_b200.ops.microbench attn-decode 48 3500      # sequences, context
+  python -m cornserve_b200.ops.microbench norm 19136 1280
+
+Each line printed gives the time per launch, the achieved rate and the fraction of the measured peak
+(``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).  The same
+commands, with ``--iters 1 --warmup 1``, are what the ncu summaries under ``profiles/`` were captured on.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from cornserve_b200 import ops
+
+
+def peaks() -> tuple[float, float, str]:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]) * 1e9, float(d["bf16_tflops"]) * 1e12, "of measured"
+    return 6.65e12, 1.59e15, "of fallback"
+
+
+class Timer:
+    def __init__(self, iters: int, warmup: int, flush: bool):
+        self.iters, self.warmup = iters, warmup
+        self.flush_buf = torch.empty(256 << 20, device="cuda", dtype=torch.uint8) if flush else None
+
+    def __call__(self, fn) -> float:
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(self.iters):
+            if self.flush_buf is not None:
+                ops.l2_flush(self.flush_buf)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        ops.check_error("microbench")
+        return total / self.iters * 1e-3
+
+
+def report(name: str, secs: float, flops: float = 0.0, nbytes: float = 0.0) -> None:
+    bw, fl, tag = peaks()
+    parts = [f"{name}: {secs * 1e6:.1f} us"]
+    if flops:
+        parts.append(f"{flops / secs / 1e12:.1f} TFLOP/s ({flops / secs / fl:.2f} {tag} bf16 burst)")
+    if nbytes:
+        parts.append(f"{nbytes / secs / 1e9:.0f} GB/s ({nbytes / secs / bw:.2f} {tag} copy bandwidth)")
+    print("  ".join(parts), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel")
+    ap.add_argument("args", nargs="*", type=int)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--bn", type=int, default=0)
+    a = ap.parse_args()
+    t = Timer(a.iters, a.warmup, not a.no_flush)
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s, std=1.0: (torch.randn(*s, device=dev, generator=g) * std).bfloat16()  # noqa: E731
+    k = a.kernel
+    if k in ("gemm", "swiglu", "skinny"):
+        M, N, K = a.args[:3]
+        x = rnd(M, K)
+        if k == "swiglu":
+            w = rnd(2 * N, K, std=K ** -0.5)
+            secs = t(lambda: ops.swiglu_linear(x, w, bn=a.bn))
+            report(f"swiglu {M}x{N}x{K}", secs, 4.0 * M * N * K, 2.0 * (M * K + 2 * N * K + M * N))
+        else:
+            w = rnd(N, K, std=K ** -0.5)
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            secs = t(lambda: ops.linear(x, w, out=out, bn=a.bn, skinny=(k == "skinny")))
+            report(f"{k} {M}x{N}x{K}", secs, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N))
+    elif k == "attn-window":
+        from cornserve_b200.models.qwen2_5_vl import window_index
+
+        n = a.args[0] if a.args else 4
+        grid = np.array([[1, 52, 92]] * n)
+        _, cu = window_index(grid, 112, 2, 14)
+        T, H, d = 4784 * n, 16, 80
+        qkv = rnd(T, 3 * H * d)
+        q, kk, v = (qkv[:, i * H * d:(i + 1) * H * d].view(T, H, d) for i in range(3))
+        cu_d = torch.from_numpy(cu).cuda()
+        mx = int(np.diff(cu).max())
+        secs = t(lambda: ops.attention_varlen(q, kk, v, cu_d, cu_d, mx))
+        lens = np.diff(cu).astype(np.float64)
+        report(f"attn-window {n} images ({len(lens)} windows)", secs, 4.0 * H * d * float((lens ** 2).sum()),
+               2.0 * 4 * T * H * d)
+    elif k == "attn-full":
+        H, d, L, causal = (a.args + [16, 80, 4784, 0][len(a.args):])[:4]
+        q, kk, v = rnd(L, H, d), rnd(L, H, d), rnd(L, H, d)
+        cu = torch.tensor([0, L], device=dev, dtype=torch.int32)
+        secs = t(lambda: ops.attention_varlen(q, kk, v, cu, cu, L, causal=bool(causal)))
+        report(f"attn-full H={H} d={d} L={L} causal={causal}", secs, 4.0 * H * d * L * L * (0.5 if causal else 1.0))
+    elif k == "attn-decode":
+        B, ctx = (a.args + [48, 3500][len(a.args):])[:2]
+        Hq, Hkv, d = 28, 4, 128
+        blocks = -(-ctx // 128)
+        cache = rnd(B * blocks, 2, Hkv, 128, d)
+        bt = torch.arange(B * blocks, device=dev, dtype=torch.int32).view(B, blocks)
+        kv_len = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+        cu = torch.arange(B + 1, device=dev, dtype=torch.int32)
+        q = rnd(B, Hq, d)
+        secs = t(lambda: ops.attention_paged(q, cache, bt, kv_len, cu, 1, causal=True, pack_gqa=True))
+        report(f"attn-decode B={B} ctx={ctx}", secs, 4.0 * B * Hq * d * ctx, 2.0 * 2 * B * Hkv * ctx * d)
+    elif k == "norm":
+        rows, H = a.args[:2]
+        x, r, w = rnd(rows, H), rnd(rows, H), rnd(H)
+        secs = t(lambda: ops.rms_norm(x, w, 1e-6, residual=r))
+        report(f"rms_norm+residual {rows}x{H}", secs, 0.0, 2.0 * 4 * rows * H)
+    else:
+        raise SystemExit(f"unknown kernel {k}")
+
+
+if __name__ == "__main__":
+    main()

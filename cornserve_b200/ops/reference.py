@@ -108,7 +108,7 @@ def mrope_table(positions, half, theta, sections):
     return torch.stack([ang.cos(), ang.sin()], dim=1).contiguous().view(T, 2, half)
 
 
-def attention_varlen(q, k, v, cu_q, cu_k, scale, causal=False):
+def attention_varlen(q, k, v, cu_q, cu_k, scale, causal=False, window=0):
     """q: [Tq, Hq, d]; k, v: [Tk, Hkv, d]; packed sequences; returns [Tq, Hq, d]."""
     Hq, Hkv = q.shape[1], k.shape[1]
     rep = Hq // Hkv
@@ -129,6 +129,8 @@ def attention_varlen(q, k, v, cu_q, cu_k, scale, causal=False):
             qi = torch.arange(Lq, device=q.device)[:, None] + (Lk - Lq)
             kj = torch.arange(Lk, device=q.device)[None, :]
             sc = sc.masked_fill(kj > qi, float("-inf"))
+            if window > 0:
+                sc = sc.masked_fill(kj <= qi - window, float("-inf"))
         pr = torch.softmax(sc, dim=-1)
         pr = torch.nan_to_num(pr, nan=0.0)
         out[cu_q[s]: cu_q[s + 1]] = (pr @ vs).transpose(0, 1)
@@ -207,3 +209,65 @@ def pcm16(x):
 
 def softmax_scale(d: int) -> float:
     return 1.0 / math.sqrt(d)
+
+
+def head_norm_rope(x, w, eps, cs):
+    """x: [T, heads, d]; per-head RMSNorm with weight ``w`` [d] (or None), then rotate-half RoPE (or None)."""
+    y = x
+    if w is not None:
+        y = rms_norm(y, w, eps)
+    if cs is not None:
+        y = rope(y, cs)
+    return y
+
+
+def softmax_rows(x, scale=1.0):
+    return torch.softmax(x.float() * scale, dim=-1).to(x.dtype)
+
+
+def im2col3x3(x, B, H, W, up=1, silu=False):
+    """x: [B*H*W, C] channels-last -> [B*Ho*Wo, 9*C] (tap-major: ky, kx, c), zero padding 1."""
+    C = x.shape[-1]
+    img = x.float().view(B, H, W, C)
+    if silu:
+        img = F.silu(img)
+    if up == 2:
+        img = img.repeat_interleave(2, dim=1).repeat_interleave(2, dim=2)
+    Ho, Wo = H * up, W * up
+    p = F.pad(img, (0, 0, 1, 1, 1, 1))
+    taps = [p[:, ky: ky + Ho, kx: kx + Wo, :] for ky in range(3) for kx in range(3)]
+    return torch.stack(taps, dim=3).reshape(B * Ho * Wo, 9 * C).to(x.dtype)
+
+
+def snake_beta(x, alpha, beta):
+    a, b = alpha.float().exp(), beta.float().exp()
+    xf = x.float()
+    return xf + torch.sin(xf * a).pow(2) / (b + 1e-9)
+
+
+def im2col1d(x, B, T, To, taps, first, dilation, alpha=None, beta=None):
+    """x: [B*T, C] -> [B*To, taps*C]; row t, tap j reads time ``t + first + j*dilation`` (zero outside)."""
+    C = x.shape[-1]
+    xf = x.float().view(B, T, C)
+    if alpha is not None:
+        xf = snake_beta(xf, alpha, beta)
+    out = torch.zeros(B, To, taps, C, dtype=torch.float32, device=x.device)
+    t = torch.arange(To, device=x.device)
+    for j in range(taps):
+        ts = t + first + j * dilation
+        ok = (ts >= 0) & (ts < T)
+        out[:, ok, j, :] = xf[:, ts[ok], :]
+    return out.reshape(B * To, taps * C).to(x.dtype)
+
+
+def dwconv1d(x, w, bias, B, T):
+    """Depth-wise causal conv: x [B*T, C], w [C, k]."""
+    C, k = w.shape
+    xf = x.float().view(B, T, C).transpose(1, 2)
+    y = F.conv1d(F.pad(xf, (k - 1, 0)), w.float().unsqueeze(1), None if bias is None else bias.float(), groups=C)
+    return y.transpose(1, 2).reshape(B * T, C).to(x.dtype)
+
+
+def to_rgb8(x):
+    v = (x[..., :3].float() * 0.5 + 0.5).clamp(0, 1)
+    return (v * 255.0).round().to(torch.uint8)

@@ -30,6 +30,7 @@ struct AttnParams {
   int bt_stride;
   int Hq, Hkv, d, G;      // G = query heads packed per tile (1, or Hq/Hkv)
   int causal, paged;
+  int window;             // > 0 (with causal): query i only sees the last `window` keys up to its own position
   int max_q_tiles, head_blks, total_items;
   int kv_splits;          // > 1: every item covers 1/kv_splits of the key tiles and writes fp32 partials
   float* ws_o;            // [Tq*Hq, kv_splits, d] unnormalised partial outputs
@@ -227,7 +228,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       if (!it.valid) continue;
       const bool row_ok = tl < it.n_tok;
       const int qi = it.t0 + tl;
-      const int lim = p.causal ? min(it.k_len, qi + it.shift + 1) : it.k_len;  // keys [0, lim) are visible
+      const int lim = p.causal ? min(it.k_len, qi + it.shift + 1) : it.k_len;  // keys [lo, lim) are visible
+      const int lo = (p.causal && p.window > 0) ? max(0, qi + it.shift + 1 - p.window) : 0;
       float m = -INFINITY, l = 0.f;
       for (int j = 0; j < it.n_kv; ++j) {
         if (!mbar_wait(&s_full[n_s & 1], (n_s >> 1) & 1, abortp, p.err, CS_ERR_TIMEOUT_MMA)) ok = false;
@@ -244,12 +246,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           tmem_ld32(tS + c * 32, v);
           tmem_wait_ld();
           const int nvalid = lim - (kbase + c * 32);
+          const int nlow = lo - (kbase + c * 32);
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            if (i < nvalid) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
-            if (i + 1 < nvalid) mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
-            if (i + 2 < nvalid) mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
-            if (i + 3 < nvalid) mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+            if (i < nvalid && i >= nlow) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+            if (i + 1 < nvalid && i + 1 >= nlow) mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+            if (i + 2 < nvalid && i + 2 >= nlow) mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+            if (i + 3 < nvalid && i + 3 >= nlow) mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
@@ -269,10 +272,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             tmem_ld32(tS + c * 32, v);
             tmem_wait_ld();
             const int nvalid = lim - (kbase + c * 32);
+            const int nlow = lo - (kbase + c * 32);
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float e0 = (i < nvalid) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
-              const float e1 = (i + 1 < nvalid) ? exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
+              const float e0 = (i < nvalid && i >= nlow) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
+              const float e1 = (i + 1 < nvalid && i + 1 >= nlow) ? exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
               const uint32_t wv = pack_bf16x2(e0, e1);
               // accumulate the rounded values so that the normaliser matches what the MMA sums
               sum0 += bf16lo(wv);
@@ -439,13 +443,14 @@ int cs_encode_tmap_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t 
 // token strides ldk / ldv and packed offsets cu_k.  Paged mode (block_table != null): `k` is the cache
 // [pages, 2, Hkv, 128, d] (v ignored), kv_len gives the key count per sequence.
 // pack_gqa != 0 packs the Hq/Hkv query heads of one KV head into the rows of a tile (use for decode).
+// window > 0 (causal only) restricts every query to the last `window` keys up to and including its own position.
 // kv_splits > 1 divides the key tiles of every item over that many CTAs (flash-decoding); `ws` must then hold
 // Tq*Hq*kv_splits*(d+2) floats of scratch.  Calls sharing `ws` must be ordered on one stream.
 CS_API int cs_attention(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
                         void* o, long long ldo, const void* cu_q, const void* cu_k, const void* kv_len,
                         const void* block_table, int bt_stride, int num_pages, int B, int Tq, int Tk,
                         int max_q_len, int Hq, int Hkv, int d, float scale, int causal, int pack_gqa,
-                        int kv_splits, void* ws, long long ws_bytes, void* stream_) {
+                        int kv_splits, void* ws, long long ws_bytes, int window, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (B <= 0 || Tq <= 0) return 0;
   if (d > 128 || (d & 7) || Hkv <= 0 || Hq % Hkv != 0) return -1;
@@ -458,6 +463,7 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
   p.cu_q = (const int*)cu_q; p.cu_k = (const int*)cu_k; p.kv_len = (const int*)kv_len;
   p.block_table = (const int*)block_table; p.bt_stride = bt_stride;
   p.Hq = Hq; p.Hkv = Hkv; p.d = d; p.G = G; p.causal = causal; p.paged = paged;
+  p.window = window > 0 ? window : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int dpad = (d + 15) & ~15;
   p.idesc_s = umma_idesc_bf16(128, 128, 0, 0);
