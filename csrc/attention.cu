@@ -78,6 +78,7 @@ __device__ __forceinline__ Item decode_item(const AttnParams& p, int w) {
 // Persistent: every CTA walks work items blockIdx.x, blockIdx.x + gridDim.x, ...; barriers and TMEM
 // are set up once and all pipeline phases are derived from running counters, so the producer already
 // fetches Q/K of the next item while the softmax / PV of the current one are still in flight.
+template <bool kWindow>
 __global__ void __launch_bounds__(320, 1)
 attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
             const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -229,13 +230,24 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const bool row_ok = tl < it.n_tok;
       const int qi = it.t0 + tl;
       const int lim = p.causal ? min(it.k_len, qi + it.shift + 1) : it.k_len;  // keys [lo, lim) are visible
-      const int lo = (p.causal && p.window > 0) ? max(0, qi + it.shift + 1 - p.window) : 0;
+      const int lo = kWindow ? max(0, qi + it.shift + 1 - p.window) : 0;
       float m = -INFINITY, l = 0.f;
+      // A warp whose 32 tile rows all lie beyond the item's tokens (decode: 7 of 128 rows are real) only keeps
+      // the barriers company: it neither reads S nor writes P (rows of the MMA are independent, and the rows
+      // it would have produced are never stored).
+      const bool warp_active = ((warp & 3) * 32) / p.G < it.n_tok;
       for (int j = 0; j < it.n_kv; ++j) {
         if (!mbar_wait(&s_full[n_s & 1], (n_s >> 1) & 1, abortp, p.err, CS_ERR_TIMEOUT_MMA)) ok = false;
         tc_fence_after();
         const uint32_t tS = tS0 + (n_s & 1) * 128 + lane_off + hf * 64;
         ++n_s;
+        if (!warp_active) {
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          if (j > 0) ++n_pv;
+          tc_fence_before();
+          mbar_arrive(&p_full);
+          continue;
+        }
         const int kbase = (it.j0 + j) * KV_TILE + hf * 64;
         // 32-key chunks of this half that hold any visible key of the tile (uniform over the CTA)
         const int n_ch = max(0, min(2, (it.k_end - kbase + 31) / 32));
@@ -247,12 +259,17 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           tmem_wait_ld();
           const int nvalid = lim - (kbase + c * 32);
           const int nlow = lo - (kbase + c * 32);
+          if (kWindow && nlow > 0) {  // sliding window: keys below the window count as -inf
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nlow) v[i] = 0xff800000u;
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            if (i < nvalid && i >= nlow) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
-            if (i + 1 < nvalid && i + 1 >= nlow) mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
-            if (i + 2 < nvalid && i + 2 >= nlow) mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
-            if (i + 3 < nvalid && i + 3 >= nlow) mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+            if (i < nvalid) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+            if (i + 1 < nvalid) mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+            if (i + 2 < nvalid) mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+            if (i + 3 < nvalid) mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
@@ -273,10 +290,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             tmem_wait_ld();
             const int nvalid = lim - (kbase + c * 32);
             const int nlow = lo - (kbase + c * 32);
+            if (kWindow && nlow > 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < nlow) v[i] = 0xff800000u;
+            }
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float e0 = (i < nvalid && i >= nlow) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
-              const float e1 = (i + 1 < nvalid && i + 1 >= nlow) ? exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
+              const float e0 = (i < nvalid) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
+              const float e1 = (i + 1 < nvalid) ? exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
               const uint32_t wv = pack_bf16x2(e0, e1);
               // accumulate the rounded values so that the normaliser matches what the MMA sums
               sum0 += bf16lo(wv);
@@ -463,7 +485,7 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
   p.cu_q = (const int*)cu_q; p.cu_k = (const int*)cu_k; p.kv_len = (const int*)kv_len;
   p.block_table = (const int*)block_table; p.bt_stride = bt_stride;
   p.Hq = Hq; p.Hkv = Hkv; p.d = d; p.G = G; p.causal = causal; p.paged = paged;
-  p.window = window > 0 ? window : 0;
+  p.window = (window > 0 && causal) ? window : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int dpad = (d + 15) & ~15;
   p.idesc_s = umma_idesc_bf16(128, 128, 0, 0);
@@ -486,7 +508,8 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
   cudaGetDevice(&dev);
   dev &= 63;
   if (!attr_done[dev]) {
-    cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev] = true;
   }
   p.max_q_tiles = (max_q_len + tok_per_tile - 1) / tok_per_tile;
@@ -505,7 +528,8 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
   if (total <= 0 || total > 0x7fffffffLL) return -1;
   p.total_items = static_cast<int>(total);
   const int grid = p.total_items < cs_num_sms() ? p.total_items : cs_num_sms();
-  attn_kernel<<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p);
+  if (p.window > 0) attn_kernel<true><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p);
+  else attn_kernel<false><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p);
   if (kv_splits > 1) {
     const int rows = Tq * Hq;
     attn_combine_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(p.ws_o, p.ws_ml, p.O, ldo, rows, Hq, d, kv_splits);

@@ -207,3 +207,94 @@ def test_gemm_skinny_swiglu(M, I, K, splits):
     x, w, b = _rand(M, K), _rand(2 * I, K, scale=K ** -0.5), _rand(2 * I, scale=0.1)
     y = ops.swiglu_linear(x, w, b, skinny=True, splits=splits)
     _close(y, ref.swiglu_linear(x.float(), w.float(), b.float()), 3e-2, 2e-2, "skinny swiglu")
+
+
+# ------------------------------------------------------------------------------------------------
+# generator kernels
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("d,heads", [(64, 5), (128, 24), (256, 2)])
+@pytest.mark.parametrize("with_norm,with_rope", [(True, True), (True, False), (False, True)])
+def test_head_norm_rope(d, heads, with_norm, with_rope):
+    torch.manual_seed(10)
+    T = 77
+    buf = _rand(T, 3 * heads * d)
+    x = buf[:, heads * d: 2 * heads * d].view(T, heads, d)  # a strided view, as q/k inside a fused qkv buffer
+    w = (1 + 0.2 * torch.randn(d, device=DEV)).bfloat16() if with_norm else None
+    ang = torch.rand(T, d // 2, device=DEV) * 6.28
+    cs = torch.stack([ang.cos(), ang.sin()], dim=1).contiguous() if with_rope else None
+    want = ref.head_norm_rope(x.clone(), w, 1e-6, cs)
+    before = buf.clone()
+    ops.head_norm_rope_(x, w, 1e-6, cs)
+    _close(x, want, 2e-2, 2e-2, "head_norm_rope")
+    assert torch.equal(buf[:, : heads * d], before[:, : heads * d]) and torch.equal(buf[:, 2 * heads * d:], before[:, 2 * heads * d:])
+
+
+def test_softmax_rows():
+    torch.manual_seed(11)
+    x = _rand(300, 1032, scale=4.0)
+    _close(ops.softmax_rows(x, 0.37), ref.softmax_rows(x, 0.37), 2e-3, 2e-2, "softmax")
+
+
+@pytest.mark.parametrize("up,silu", [(1, False), (2, True), (1, True)])
+def test_im2col3x3_and_conv(up, silu):
+    torch.manual_seed(12)
+    B, H, W, C, Co = 2, 7, 9, 24, 40
+    x = _rand(B * H * W, C)
+    assert torch.equal(ops.im2col3x3(x, B, H, W, up, silu), ref.im2col3x3(x, B, H, W, up, silu)) or \
+        (ops.im2col3x3(x, B, H, W, up, silu).float() - ref.im2col3x3(x, B, H, W, up, silu).float()).abs().max() < 2e-2
+    w, b = _rand(Co, 9 * C, scale=(9 * C) ** -0.5), _rand(Co)
+    y = ops.conv3x3(x, w, b, B, H, W, up=up, silu=silu)
+    # the same convolution through torch (NCHW)
+    img = x.float().view(B, H, W, C).permute(0, 3, 1, 2)
+    if silu:
+        img = torch.nn.functional.silu(img)
+    if up == 2:
+        img = torch.nn.functional.interpolate(img, scale_factor=2.0, mode="nearest")
+    w4 = w.float().view(Co, 3, 3, C).permute(0, 3, 1, 2)
+    want = torch.nn.functional.conv2d(img, w4, b.float(), padding=1).permute(0, 2, 3, 1).reshape(-1, Co)
+    _close(y, want, 3e-2, 3e-2, "conv3x3")
+
+
+def test_conv1d_family():
+    torch.manual_seed(13)
+    B, T, C, Co = 2, 37, 16, 24
+    x = _rand(B * T, C)
+    alpha, beta = torch.randn(C, device=DEV) * 0.3, torch.randn(C, device=DEV) * 0.3
+    for k, dil in ((7, 1), (7, 3), (1, 1)):
+        w, b = _rand(Co, k * C, scale=(k * C) ** -0.5), _rand(Co)
+        y = ops.conv1d_causal(x, w, b, B, T, k, dil, alpha=alpha, beta=beta)
+        xin = ref.snake_beta(x.float().view(B, T, C), alpha, beta).transpose(1, 2)
+        w3 = w.float().view(Co, k, C).permute(0, 2, 1)
+        want = torch.nn.functional.conv1d(torch.nn.functional.pad(xin, ((k - 1) * dil, 0)), w3, b.float(), dilation=dil)
+        _close(y, want.transpose(1, 2).reshape(B * T, Co), 3e-2, 3e-2, f"conv1d k={k} dil={dil}")
+    # transposed convolutions: kernel == stride, and kernel == 2 * stride with both ends trimmed by stride
+    for s, k in ((2, 2), (3, 6)):
+        wt, bt = _rand(C, Co, k, scale=C ** -0.5), _rand(Co)
+        wk = wt.permute(2, 1, 0)
+        w2d = torch.cat([wk[:s].reshape(s * Co, C)] + ([wk[s:].reshape(s * Co, C)] if k == 2 * s else []), dim=1).contiguous()
+        y, To = ops.conv_transpose1d_causal(x, w2d, bt.repeat(s), B, T, s, k)
+        full = torch.nn.functional.conv_transpose1d(x.float().view(B, T, C).transpose(1, 2), wt.float(), bt.float(), stride=s)
+        pad = k - s
+        want = full[..., pad: full.shape[-1] - pad] if pad else full
+        assert To == want.shape[-1]
+        _close(y, want.transpose(1, 2).reshape(B * To, Co), 3e-2, 3e-2, f"convT s={s} k={k}")
+    wd, bd = _rand(C, 7, scale=0.4), _rand(C)
+    _close(ops.dwconv1d(x, wd, bd, B, T), ref.dwconv1d(x, wd, bd, B, T), 2e-2, 2e-2, "dwconv1d")
+
+
+def test_to_rgb8():
+    x = _rand(1000, 8)
+    got, want = ops.to_rgb8(x), ref.to_rgb8(x)
+    assert got.dtype == torch.uint8 and (got.int() - want.int()).abs().max().item() <= 1
+
+
+@pytest.mark.parametrize("window", [6, 72, 200])
+def test_attention_sliding_window(window):
+    torch.manual_seed(14)
+    H, d, lens = 4, 64, [325, 40]
+    T = sum(lens)
+    q, k, v = _rand(T, H, d), _rand(T, H, d), _rand(T, H, d)
+    cu = torch.tensor([0, lens[0], T], device=DEV, dtype=torch.int32)
+    got = ops.attention_varlen(q, k, v, cu, cu, max(lens), causal=True, window=window)
+    want = ref.attention_varlen(q, k, v, cu, cu, 1 / math.sqrt(d), True, window)
+    _close(got, want, 2e-2, 2e-2, f"sliding window {window}")
