@@ -594,3 +594,145 @@ CS_API int cs_gemm_skinny_allreduce(const void* X, long long ldx, const void* W,
   gemm_skinny_kernel<<<tiles * splits, 192, smem, stream>>>(tmW, tmX, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free entry point (contract and audience: cornserve_noalloc.h).  The split-K scratch and the
+// word that records a bounded wait running out are one static device array of this library; nothing below
+// allocates host or device memory.
+// ---------------------------------------------------------------------------------------------------------
+#include <mutex>
+#include <stdio.h>
+
+#include "cornserve_noalloc.h"
+
+// [partial sums | arrival counters | error word].  In host code this name is only the handle given to
+// cudaGetSymbolAddress; it is never handed to a kernel as if it were a device pointer.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CS_NOALLOC_SCRATCH_BYTES + 256];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_dev[kNoallocMaxDevices] = {nullptr};  // device address of the array, per device
+thread_local char g_noalloc_msg[320] = "ok";
+
+int noalloc_fail(int code, const char* fmt, long long a = 0, long long b = 0) {
+  snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), fmt, a, b);
+  return code;
+}
+
+// Device address of the scratch array on the current device.  The first call on a device looks the address
+// up (cudaGetSymbolAddress with that device current) and raises the kernel's shared-memory limit.
+unsigned char* noalloc_scratch_of_current_device(int* code) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) {
+    *code = noalloc_fail(CS_NOALLOC_SETUP_FAILED, "cs_gemm_skinny_noalloc: no usable current device (%lld)", dev);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_dev[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      *code = noalloc_fail(CS_NOALLOC_SETUP_FAILED,
+                           "cs_gemm_skinny_noalloc: cudaGetSymbolAddress failed with CUDA error %lld on device %lld",
+                           static_cast<long long>(e), dev);
+      return nullptr;
+    }
+    const cudaError_t a = cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (a != cudaSuccess) {
+      *code = noalloc_fail(CS_NOALLOC_SETUP_FAILED, "cs_gemm_skinny_noalloc: cudaFuncSetAttribute failed with CUDA error %lld",
+                           static_cast<long long>(a));
+      return nullptr;
+    }
+    g_noalloc_dev[dev] = ptr;
+  }
+  return g_noalloc_dev[dev];
+}
+
+int noalloc_effective_splits(int N, int K, int swiglu, int splits) {
+  if (splits <= 0) splits = cs_gemm_skinny_auto_splits(N, K, swiglu);
+  const int total_it = (K + BK * KATOMS - 1) / (BK * KATOMS);
+  return splits > total_it ? total_it : splits;
+}
+}  // namespace
+
+CS_API long long cs_gemm_skinny_noalloc_need_bytes(int M, int N, int K, int swiglu, int splits) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return cs_gemm_skinny_ws_bytes(M, N, noalloc_effective_splits(N, K, swiglu, splits), swiglu);
+}
+
+CS_API const char* cs_noalloc_last_message(void) { return g_noalloc_msg; }
+
+// Copies the error word of the current device back (synchronises with the device; no allocation): 0, or the
+// CsError code of a bounded wait that ran out inside a cs_gemm_skinny_noalloc kernel since the last call here.
+CS_API int cs_gemm_skinny_noalloc_kernel_error(void) {
+  int code = 0;
+  unsigned char* base = noalloc_scratch_of_current_device(&code);
+  if (base == nullptr) return code;
+  int word = 0;
+  if (cudaMemcpy(&word, base + CS_NOALLOC_SCRATCH_BYTES, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return CS_NOALLOC_SETUP_FAILED;
+  if (word != 0) cudaMemset(base + CS_NOALLOC_SCRATCH_BYTES, 0, sizeof(int));
+  return word;
+}
+
+CS_API int cs_gemm_skinny_noalloc(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc,
+                                  const void* bias, const void* residual, long long ldr, int M, int N, int K, int act,
+                                  int swiglu, int out_fp32, int splits, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 256 || K <= 0 || (ldx & 7) || (ldw & 7))
+    return noalloc_fail(-1, "cs_gemm_skinny_noalloc: needs 1 <= M <= 256, K > 0 and row strides that are multiples of 8 elements");
+  splits = noalloc_effective_splits(N, K, swiglu, splits);
+  const int cols_per_tile = swiglu ? 64 : 128;
+  const int tiles = (N + cols_per_tile - 1) / cols_per_tile;
+  const long long need = cs_gemm_skinny_ws_bytes(M, N, splits, swiglu);
+  if (need > CS_NOALLOC_PARTIAL_BYTES)
+    return noalloc_fail(CS_NOALLOC_TOO_LARGE,
+                        "cs_gemm_skinny_noalloc: this problem needs %lld bytes of partial sums but the built-in scratch holds "
+                        "%lld; pass a smaller `splits` (1 needs none) or call cs_gemm_skinny with your own workspace",
+                        need, CS_NOALLOC_PARTIAL_BYTES);
+  if (splits > 1 && tiles > CS_NOALLOC_MAX_TILES)
+    return noalloc_fail(CS_NOALLOC_TOO_LARGE, "cs_gemm_skinny_noalloc: %lld output tiles exceed the %lld built-in arrival counters",
+                        tiles, CS_NOALLOC_MAX_TILES);
+  int code = 0;
+  unsigned char* base = noalloc_scratch_of_current_device(&code);
+  if (base == nullptr) return code;
+  int* counters = reinterpret_cast<int*>(base + CS_NOALLOC_PARTIAL_BYTES);
+  if (splits > 1) {
+    // the counters must start at zero; a call that ended in an error may have left some raised
+    if (cudaMemsetAsync(counters, 0, static_cast<size_t>(tiles) * sizeof(int), stream) != cudaSuccess)
+      return noalloc_fail(CS_NOALLOC_SETUP_FAILED, "cs_gemm_skinny_noalloc: clearing the arrival counters failed");
+  }
+  SkinnyParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.m_pad = (M + 15) & ~15;
+  p.swiglu = swiglu;
+  p.up_row_offset = N;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.act = act;
+  p.err = reinterpret_cast<int*>(base + CS_NOALLOC_SCRATCH_BYTES);
+  p.splits = splits;
+  p.ws = reinterpret_cast<float*>(base);
+  p.counters = counters;
+  const int stage_bytes = KATOMS * (W_ATOM + p.m_pad * 128);
+  int stages = MAX_STAGES;
+  while (stages > 2 && stages * stage_bytes + 1024 > 220 * 1024) --stages;
+  p.stages = stages;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.m_pad)) cols <<= 1;
+  p.tmem_cols = cols;
+  p.idesc = umma_idesc_bf16(128, p.m_pad, 0, 0);
+  CUtensorMap tmW, tmX;
+  if (cs_encode_tmap_2d(&tmW, W, K, swiglu ? 2 * N : N, ldw * 2, BK, swiglu ? 64 : 128, 2, 1) != 0)
+    return noalloc_fail(-2, "cs_gemm_skinny_noalloc: W cannot be described to the TMA unit (16-byte aligned base and row stride needed)");
+  if (cs_encode_tmap_2d(&tmX, X, K, M, ldx * 2, BK, p.m_pad, 2, 1) != 0)
+    return noalloc_fail(-3, "cs_gemm_skinny_noalloc: X cannot be described to the TMA unit (16-byte aligned base and row stride needed)");
+  gemm_skinny_kernel<<<tiles * splits, 192, stages * stage_bytes + 1024, stream>>>(tmW, tmX, p);
+  if (cudaGetLastError() != cudaSuccess) return noalloc_fail(-10, "cs_gemm_skinny_noalloc: the kernel launch failed");
+  snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ok");
+  return 0;
+}
