@@ -1,0 +1,176 @@
+"""Failure detection and recovery, with every failure made on the host (no GPU is faulted, trapped or hung):
+
+* an executor process that exits during start-up, one that never reports healthy, one that dies after it was
+  healthy (detected by the health check and replaced on the same GPUs);
+* a rank of a process group that leaves between steps: the survivor's next collective ends with an error
+  within the group's timeout instead of waiting forever (gloo ranks on CPU);
+* on the GPU, a kernel wait that cannot be satisfied (a peer flag that nothing sets) runs into its limit, the
+  kernel returns, the host reads the recorded status and the CUDA context stays usable.
+"""
+
+import asyncio
+import os
+import subprocess
+import sys
+import textwrap
+import time
+
+import pytest
+import torch
+
+from cornserve_b200.services.process import free_port, spawn
+from cornserve_b200.services.resource import GPU
+from cornserve_b200.services.task_manager.manager import TaskManager
+from cornserve_b200.tasklib.task.unit.encoder import EncoderTask, Modality
+
+FAKE_EXECUTOR = textwrap.dedent("""
+    import sys, time
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+    port, mode = int(sys.argv[1]), sys.argv[2]
+    if mode == "exit":
+        print("fatal: model weights are corrupt"); sys.exit(3)
+    class H(BaseHTTPRequestHandler):
+        def do_GET(self):
+            self.send_response(503 if mode == "never_ready" else 200); self.end_headers()
+        def log_message(self, *a): pass
+    HTTPServer(("127.0.0.1", port), H).serve_forever()
+""")
+
+
+def _task():
+    return EncoderTask(modality=Modality.IMAGE, model_ids={"cornserve-b200/tiny-vlm"})
+
+
+def _spawner(mode_of, tmp_path):
+    calls = []
+
+    async def spawn_fn(executor_id, gpus, port, launch_args):
+        mode = mode_of(len(calls))
+        calls.append(mode)
+        proc = spawn(executor_id, [sys.executable, "-c", FAKE_EXECUTOR, str(port), mode], port=port, log_dir=str(tmp_path))
+        return f"http://127.0.0.1:{port}", proc
+
+    return spawn_fn, calls
+
+
+def _gpus(n):
+    return [GPU(node="local", global_rank=i, local_rank=i) for i in range(n)]
+
+
+def test_executor_that_exits_at_startup_is_reported_with_its_log(tmp_path):
+    async def run():
+        spawn_fn, _ = _spawner(lambda i: "exit", tmp_path)
+        tm = TaskManager("tm", _task(), spawn_fn=spawn_fn, health_timeout_s=20)
+        with pytest.raises(RuntimeError) as e:
+            await tm.update_resources(add_gpus=_gpus(1))
+        assert "exited with code 3" in str(e.value) and "weights are corrupt" in str(e.value)
+        assert not tm.executors
+        await tm.shutdown()
+
+    asyncio.run(run())
+
+
+def test_executor_that_never_turns_healthy_times_out(tmp_path):
+    async def run():
+        spawn_fn, _ = _spawner(lambda i: "never_ready", tmp_path)
+        tm = TaskManager("tm", _task(), spawn_fn=spawn_fn, health_timeout_s=1.5)
+        t0 = time.monotonic()
+        with pytest.raises(RuntimeError) as e:
+            await tm.update_resources(add_gpus=_gpus(1))
+        assert "did not become healthy" in str(e.value) and time.monotonic() - t0 < 15
+        assert not tm.executors  # the half-started process was cleaned up
+        await tm.shutdown()
+
+    asyncio.run(run())
+
+
+def test_dead_executor_is_detected_and_replaced(tmp_path):
+    async def run():
+        spawn_fn, calls = _spawner(lambda i: "ok", tmp_path)
+        tm = TaskManager("tm", _task(), spawn_fn=spawn_fn, health_timeout_s=20)
+        await tm.update_resources(add_gpus=_gpus(2))
+        assert len(tm.executors) == 2 and all(ok for ok, _ in (await tm.healthcheck()).values())
+        victim = sorted(tm.executors.values(), key=lambda d: d.executor_id)[0]
+        victim.process.popen.kill()  # the failure: the process is gone (its GPU work is not our concern here)
+        victim.process.popen.wait()
+        health = await tm.healthcheck()
+        assert health[victim.executor_id][0] is False and sum(ok for ok, _ in health.values()) == 1
+        # routing skips the dead executor
+        urls = {(await tm.get_route(f"r{i}"))[0] for i in range(4)}
+        assert urls == {d.url for d in tm.executors.values() if d.healthy}
+        assert await tm.respawn_unhealthy() == [victim.executor_id]
+        assert len(calls) == 3 and all(ok for ok, _ in (await tm.healthcheck()).values())
+        await tm.shutdown()
+
+    asyncio.run(run())
+
+
+RANK_SCRIPT = textwrap.dedent("""
+    import datetime, os, sys, torch, torch.distributed as dist
+    rank = int(sys.argv[1]); port = sys.argv[2]
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=2,
+                            timeout=datetime.timedelta(seconds=4))
+    x = torch.ones(4)
+    dist.all_reduce(x)                       # step 1: both ranks take part
+    assert x[0].item() == 2.0
+    if rank == 1:
+        os._exit(0)                          # leaves between steps, nothing of its own in flight
+    try:
+        dist.all_reduce(x)                   # step 2: the peer is gone
+        print("UNEXPECTED: collective finished")
+    except Exception as e:
+        print("SURVIVOR_SAW_ERROR", type(e).__name__)
+""")
+
+
+def test_rank_that_leaves_between_steps_is_noticed_by_the_survivor():
+    port = str(free_port())
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    procs = [subprocess.Popen([sys.executable, "-c", RANK_SCRIPT, str(r), port], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
+    out0, _ = procs[0].communicate(timeout=120)
+    procs[1].wait(timeout=120)
+    assert "SURVIVOR_SAW_ERROR" in out0, out0[-2000:]
+
+
+@pytest.mark.gpu
+def test_kernel_wait_on_a_flag_nobody_sets_returns_an_error_status():
+    """One GPU plays rank 0 of a two-rank fused GEMM + all-reduce; rank 1 never runs, so its arrival flag never
+    moves.  The kernel's peer wait must give up after its limit, record ``timeout waiting for a peer flag`` and
+    return, leaving the context usable."""
+    import ctypes
+
+    from cornserve_b200 import ops
+    from cornserve_b200.ops import _lib
+    from cornserve_b200.parallel import fused  # noqa: F401  (declares the entry point's signature)
+
+    dev = "cuda"
+    lib = _lib.load()
+    lib.cs_reset_error()
+    M, N, K, world = 8, 256, 512, 2
+    m_cap, n_cap, tiles_cap = 16, 256, 2
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = torch.randn(N, K, device=dev).bfloat16() * K ** -0.5
+    h = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    recv = [torch.zeros(2 * world * m_cap * n_cap, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(2 * tiles_cap, device=dev, dtype=torch.int32) for _ in range(world)]
+    ssq, done, epoch = (torch.zeros(n, device=dev, dtype=t) for n, t in ((m_cap, torch.float32), (2, torch.int32), (1, torch.int32)))
+    ws, counters = ops._skinny_workspace(torch.device(dev, torch.cuda.current_device()))
+    recv_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in recv])
+    flag_ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in flags])
+    t0 = time.monotonic()
+    rc = lib.cs_gemm_skinny_allreduce(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), h.data_ptr(), h.stride(0), None, None, 0, None, None, N,
+        1e-6, M, N, K, 1, ws.data_ptr(), ws.numel(), counters.data_ptr(), counters.numel(), world, 0,
+        ctypes.cast(recv_ptrs, ctypes.c_void_p), ctypes.cast(flag_ptrs, ctypes.c_void_p), m_cap, n_cap, tiles_cap,
+        ssq.data_ptr(), done.data_ptr(), epoch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()  # returns: the wait is bounded
+    assert time.monotonic() - t0 < 30
+    with pytest.raises(RuntimeError, match="peer flag"):
+        ops.check_error("fused all-reduce without a peer")
+    # the context is intact: an ordinary kernel still runs and gives the right answer
+    y = ops.linear(x, w)
+    torch.cuda.synchronize()
+    ops.check_error("after the timed-out kernel")
+    assert torch.allclose(y.float(), x.float() @ w.float().t(), atol=5e-2, rtol=5e-2)
