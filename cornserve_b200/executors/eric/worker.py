@@ -20,7 +20,8 @@ from ...sidecar.schema import SidecarConfig
 from ...tracing import extract, get_tracer
 from ...utils.hub import load_config, load_model_weights
 from .config import EricConfig
-from .preprocess import patchify_frames
+from .preprocess import (HALF, IMAGENET_MEAN, IMAGENET_STD, anyres_tiles, dynamic_tiles, log_mel_spectrogram,
+                         patchify_frames, resize_normalize)
 from .registry import MODEL_REGISTRY
 from .schema import Batch
 
@@ -56,12 +57,21 @@ class Worker:
         self.model_cfg = cfg_cls.from_hf(hf_cfg)
         dtype = torch.float32 if (self.device.type == "cpu" or hf_cfg.get("torch_dtype") == "float32") else torch.bfloat16
         torch.manual_seed(int(os.environ.get("CORNSERVE_SEED", "0")))  # reproducible random-weight runs
-        self.model = model_cls(self.model_cfg, group=self.group, device=self.device)
+        kw = {"model_id": config.model.id} if self.entry.adapter_attr else {}
+        self.model = model_cls(self.model_cfg, group=self.group, device=self.device, **kw)
         if dtype == torch.float32:
             self.model = self.model.float()
         load_model_weights(self.model, config.model.id, self.entry.weight.required_prefixes,
-                           ignored_prefixes=self.entry.weight.ignored_prefixes)
+                           ignored_prefixes=self.entry.weight.ignored_prefixes, strip_prefixes=self.entry.weight.strip_prefixes)
         self.model.eval()
+        if self.entry.adapter_attr and config.model.adapter_model_ids:
+            # other LLM sizes that share this tower: each contributes its own projector
+            add = getattr(self.model, self.entry.adapter_attr)
+            for aid in config.model.adapter_model_ids:
+                from ...utils.hub import has_weights, iter_safetensors
+
+                w = iter_safetensors(aid, self.entry.weight.adapter_prefixes, True) if has_weights(aid) else None
+                add(aid, load_config(aid), w)
         self.sidecar: Sidecar | None = None
         if config.sidecar.ranks:
             self.sidecar = Sidecar(SidecarConfig(
@@ -72,21 +82,50 @@ class Worker:
         logger.info("Worker %d ready on %s (%s)", tp_rank, self.device, model_type)
 
     def prepare(self, batch: Batch) -> dict[str, list]:
-        """Decoded uint8 data -> model inputs on the device."""
+        """Decoded uint8 pixels / float waveforms -> model inputs on the device, by the model's preprocessing recipe."""
         data = dict(batch.data)
-        vc = self.model_cfg
-        if "raw_images" in data or "raw_videos" in data:
-            raw_key = "raw_images" if "raw_images" in data else "raw_videos"
+        recipe, dev, dt = self.entry.processor, self.device, self.model.dtype
+        to_dev = lambda t: t.to(dev, non_blocking=True)  # noqa: E731
+        if "raw_audio" in data:
+            data["input_features"] = [log_mel_spectrogram(to_dev(w)).to(dt) for w in data.pop("raw_audio")]
+            return data
+        raw_key = "raw_images" if "raw_images" in data else ("raw_videos" if "raw_videos" in data else None)
+        if raw_key is None:
+            return data
+        items = data.pop(raw_key)
+        video = raw_key == "raw_videos"
+        if recipe in ("qwen2_vl", "qwen3_vl", "qwen2_5_omni", "qwen3_omni"):
+            vc = self.model_cfg.vision if hasattr(self.model_cfg, "vision") else self.model_cfg
+            half = recipe in ("qwen3_vl", "qwen3_omni")
             pix, grids = [], []
-            for frames in data.pop(raw_key):
-                pv, g = patchify_frames(frames.to(self.device, non_blocking=True), vc.patch_size, vc.temporal_patch_size,
-                                        vc.spatial_merge_size, out_dtype=self.model.dtype)
+            for frames in items:
+                pv, g = patchify_frames(to_dev(frames), vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size, out_dtype=dt,
+                                        **({"mean": HALF, "std": HALF} if half else {}))
                 pix.append(pv)
                 grids.append(list(g))
-            if raw_key == "raw_images":
-                data["pixel_values"], data["image_grid_thw"] = pix, grids
+            k = ("pixel_values_videos", "video_grid_thw") if video else ("pixel_values", "image_grid_thw")
+            data[k[0]], data[k[1]] = pix, grids
+        elif recipe == "gemma3":
+            s = self.model_cfg.vision.image_size
+            data["pixel_values"] = [resize_normalize(to_dev(im), (s, s), out_dtype=dt) for im in items]
+            data["num_crops"] = [torch.zeros(1, dtype=torch.long) for _ in items]
+        elif recipe == "llava_onevision":
+            cfg = self.model_cfg
+            s = cfg.vision.image_size
+            if video:
+                data["pixel_values_videos"] = [resize_normalize(to_dev(v), (s, s), mode="bicubic", out_dtype=dt) for v in items]
             else:
-                data["pixel_values_videos"], data["video_grid_thw"] = pix, grids
+                tiles = [anyres_tiles(to_dev(im), cfg.image_grid_pinpoints, s, out_dtype=dt) for im in items]
+                data["pixel_values"] = [t for t, _ in tiles]
+                data["image_sizes"] = [torch.tensor(sz) for _, sz in tiles]
+        elif recipe == "internvl":
+            s = self.model_cfg.image_size
+            if video:
+                data["pixel_values_videos"] = [resize_normalize(to_dev(v), (s, s), IMAGENET_MEAN, IMAGENET_STD, "bicubic", dt) for v in items]
+            else:
+                data["pixel_values"] = [dynamic_tiles(to_dev(im), s, out_dtype=dt) for im in items]
+        else:
+            raise ValueError(f"unknown preprocessing recipe {recipe}")
         return data
 
     @torch.inference_mode()

@@ -241,6 +241,8 @@ class Qwen25VisionTransformer(nn.Module):
                         blk.norm2.weight.data.copy_(t)
                     elif sub == "attn.qkv":
                         blk.qkv.load_fused(**kw)
+                    elif sub in ("attn.q", "attn.k", "attn.v"):  # Qwen2.5-Omni stores the projections separately
+                        blk.qkv.load(sub[-1], **kw)
                     elif sub == "attn.proj":
                         blk.proj.load(**kw)
                     elif sub == "mlp.gate_proj":

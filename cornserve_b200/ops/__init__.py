@@ -20,7 +20,7 @@ __all__ = [
     "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
     "flow_step_", "pcm16", "decode_advance_", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
     "head_norm_rope_", "softmax_rows", "im2col3x3", "im2col1d", "dwconv1d", "to_rgb8", "conv3x3", "conv1d_causal",
-    "conv_transpose1d_causal",
+    "conv_transpose1d_causal", "bilinear_embed_add_",
 ]
 
 _launches = 0
@@ -541,31 +541,34 @@ def softmax_rows(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     return y
 
 
-def im2col3x3(x: torch.Tensor, B: int, H: int, W: int, up: int = 1, silu: bool = False) -> torch.Tensor:
-    """Channels-last image ``[B*H*W, C]`` -> ``[B*(up H)*(up W), 9 C]`` GEMM operand of a 3x3 convolution."""
+def im2col3x3(x: torch.Tensor, B: int, H: int, W: int, up: int = 1, silu: bool = False, stride: int = 1) -> torch.Tensor:
+    """Channels-last image ``[B*H*W, C]`` -> ``[B*Ho*Wo, 9 C]`` GEMM operand of a 3x3 convolution with padding 1
+    (``Ho = (up*H - 1) // stride + 1``)."""
     if not x.is_cuda:
-        return reference.im2col3x3(x, B, H, W, up, silu)
+        return reference.im2col3x3(x, B, H, W, up, silu, stride)
     C = x.shape[-1]
     assert x.is_contiguous() and x.dtype == torch.bfloat16
-    out = torch.empty((B * H * up * W * up, 9 * C), device=x.device, dtype=x.dtype)
+    Ho, Wo = (H * up - 1) // stride + 1, (W * up - 1) // stride + 1
+    out = torch.empty((B * Ho * Wo, 9 * C), device=x.device, dtype=x.dtype)
     lib = _lib.load()
-    _chk(lib.cs_im2col3x3(x.data_ptr(), out.data_ptr(), B, H, W, C, up, 1 if silu else 0, _stream()), "cs_im2col3x3")
+    _chk(lib.cs_im2col3x3(x.data_ptr(), out.data_ptr(), B, H, W, C, up, 1 if silu else 0, stride, _stream()),
+         "cs_im2col3x3")
     _count()
     return out
 
 
 def im2col1d(x: torch.Tensor, B: int, T: int, To: int, taps: int, first: int, dilation: int = 1,
-             alpha: torch.Tensor | None = None, beta: torch.Tensor | None = None) -> torch.Tensor:
-    """Channels-last sequence ``[B*T, C]`` -> ``[B*To, taps*C]``; with ``alpha``/``beta`` (fp32 ``[C]``) SnakeBeta
-    is applied to every gathered value."""
+             alpha: torch.Tensor | None = None, beta: torch.Tensor | None = None, stride: int = 1) -> torch.Tensor:
+    """Channels-last sequence ``[B*T, C]`` -> ``[B*To, taps*C]``: row ``t``, tap ``j`` reads time
+    ``t*stride + first + j*dilation``; with ``alpha``/``beta`` (fp32 ``[C]``) SnakeBeta is applied on the fly."""
     if not x.is_cuda:
-        return reference.im2col1d(x, B, T, To, taps, first, dilation, alpha, beta)
+        return reference.im2col1d(x, B, T, To, taps, first, dilation, alpha, beta, stride)
     C = x.shape[-1]
     assert x.is_contiguous() and x.dtype == torch.bfloat16
     out = torch.empty((B * To, taps * C), device=x.device, dtype=x.dtype)
     lib = _lib.load()
-    _chk(lib.cs_im2col1d(x.data_ptr(), out.data_ptr(), B, T, To, C, taps, first, dilation, 0 if alpha is None else 1,
-                         _ptr(alpha), _ptr(beta), _stream()), "cs_im2col1d")
+    _chk(lib.cs_im2col1d(x.data_ptr(), out.data_ptr(), B, T, To, C, taps, first, dilation, stride,
+                         0 if alpha is None else 1, _ptr(alpha), _ptr(beta), _stream()), "cs_im2col1d")
     _count()
     return out
 
@@ -594,11 +597,11 @@ def to_rgb8(x: torch.Tensor) -> torch.Tensor:
 
 
 def conv3x3(x: torch.Tensor, w2d: torch.Tensor, bias: torch.Tensor | None, B: int, H: int, W: int, *, up: int = 1,
-            silu: bool = False, residual: torch.Tensor | None = None) -> torch.Tensor:
+            silu: bool = False, residual: torch.Tensor | None = None, stride: int = 1, act: str | None = None) -> torch.Tensor:
     """3x3 convolution (padding 1) on a channels-last image; ``w2d`` is ``[Cout, 9*Cin]`` in (ky, kx, cin) order.
     ``silu`` applies SiLU to the input first, ``up=2`` convolves the nearest-neighbour 2x upsampled image."""
-    cols = im2col3x3(x, B, H, W, up, silu)
-    return linear(cols, w2d, bias, residual=residual)
+    cols = im2col3x3(x, B, H, W, up, silu, stride)
+    return linear(cols, w2d, bias, residual=residual, act=act)
 
 
 def conv1d_causal(x: torch.Tensor, w2d: torch.Tensor, bias: torch.Tensor | None, B: int, T: int, k: int,
@@ -628,3 +631,19 @@ def conv_transpose1d_causal(x: torch.Tensor, w2d: torch.Tensor, bias_rep: torch.
     cols = im2col1d(x, B, T, T - 1, 2, 1, -1, alpha, beta)
     y = linear(cols, w2d, bias_rep)
     return y.view(B * (T - 1) * stride, -1), (T - 1) * stride
+
+
+def bilinear_embed_add_(x: torch.Tensor, table: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor) -> torch.Tensor:
+    """``x[l] += sum_i wgt[i, l] * table[idx[i, l]]`` for ``idx``/``wgt`` of shape ``[4, L]`` (int32 / fp32): the
+    bilinear interpolation of a learned 2-D position table, added in place."""
+    if not x.is_cuda:
+        pos = (table.float()[idx.long()] * wgt.float()[:, :, None]).sum(0)
+        x.copy_((x.float() + pos).to(x.dtype))
+        return x
+    L, H = x.shape
+    assert x.stride(1) == 1 and table.stride(1) == 1 and idx.dtype == torch.int32 and wgt.dtype == torch.float32
+    lib = _lib.load()
+    _chk(lib.cs_bilinear_embed_add(x.data_ptr(), x.stride(0), table.data_ptr(), table.stride(0), idx.contiguous().data_ptr(),
+                                   wgt.contiguous().data_ptr(), L, H, _stream()), "cs_bilinear_embed_add")
+    _count()
+    return x

@@ -49,9 +49,10 @@ _SIGNATURES = {
     "cs_decode_advance": ([P, P, P, P, P, P, I, P, P, I, P, I, I, P], I),
     "cs_head_norm_rope": ([P, L, L, I, I, P, F, P, P], I),
     "cs_softmax_rows": ([P, L, P, L, I, I, F, P], I),
-    "cs_im2col3x3": ([P, P, I, I, I, I, I, I, P], I),
-    "cs_im2col1d": ([P, P, I, I, I, I, I, I, I, I, P, P, P], I),
+    "cs_im2col3x3": ([P, P, I, I, I, I, I, I, I, P], I),
+    "cs_im2col1d": ([P, P, I, I, I, I, I, I, I, I, I, P, P, P], I),
     "cs_dwconv1d": ([P, P, P, P, I, I, I, I, P], I),
+    "cs_bilinear_embed_add": ([P, L, P, L, P, P, L, I, P], I),
     "cs_to_rgb8": ([P, L, P, L, P], I),
     "cs_attention": ([P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, L, I, P], I),
 }

@@ -225,7 +225,7 @@ def softmax_rows(x, scale=1.0):
     return torch.softmax(x.float() * scale, dim=-1).to(x.dtype)
 
 
-def im2col3x3(x, B, H, W, up=1, silu=False):
+def im2col3x3(x, B, H, W, up=1, silu=False, stride=1):
     """x: [B*H*W, C] channels-last -> [B*Ho*Wo, 9*C] (tap-major: ky, kx, c), zero padding 1."""
     C = x.shape[-1]
     img = x.float().view(B, H, W, C)
@@ -233,10 +233,11 @@ def im2col3x3(x, B, H, W, up=1, silu=False):
         img = F.silu(img)
     if up == 2:
         img = img.repeat_interleave(2, dim=1).repeat_interleave(2, dim=2)
-    Ho, Wo = H * up, W * up
+    Hu, Wu = H * up, W * up
     p = F.pad(img, (0, 0, 1, 1, 1, 1))
-    taps = [p[:, ky: ky + Ho, kx: kx + Wo, :] for ky in range(3) for kx in range(3)]
-    return torch.stack(taps, dim=3).reshape(B * Ho * Wo, 9 * C).to(x.dtype)
+    taps = [p[:, ky: ky + Hu: stride, kx: kx + Wu: stride, :] for ky in range(3) for kx in range(3)]
+    out = torch.stack(taps, dim=3)
+    return out.reshape(-1, 9 * C).to(x.dtype)
 
 
 def snake_beta(x, alpha, beta):
@@ -245,7 +246,7 @@ def snake_beta(x, alpha, beta):
     return xf + torch.sin(xf * a).pow(2) / (b + 1e-9)
 
 
-def im2col1d(x, B, T, To, taps, first, dilation, alpha=None, beta=None):
+def im2col1d(x, B, T, To, taps, first, dilation, alpha=None, beta=None, stride=1):
     """x: [B*T, C] -> [B*To, taps*C]; row t, tap j reads time ``t + first + j*dilation`` (zero outside)."""
     C = x.shape[-1]
     xf = x.float().view(B, T, C)
@@ -254,7 +255,7 @@ def im2col1d(x, B, T, To, taps, first, dilation, alpha=None, beta=None):
     out = torch.zeros(B, To, taps, C, dtype=torch.float32, device=x.device)
     t = torch.arange(To, device=x.device)
     for j in range(taps):
-        ts = t + first + j * dilation
+        ts = t * stride + first + j * dilation
         ok = (ts >= 0) & (ts < T)
         out[:, ok, j, :] = xf[:, ts[ok], :]
     return out.reshape(B * To, taps * C).to(x.dtype)

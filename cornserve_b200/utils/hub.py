@@ -53,6 +53,38 @@ BUILTIN_CONFIGS: dict[str, dict[str, Any]] = {
                           "temporal_patch_size": 2, "spatial_merge_size": 2, "window_size": 112,
                           "fullatt_block_indexes": [1], "out_hidden_size": 256, "hidden_act": "silu", "in_channels": 3},
     },
+    "cornserve-b200/tiny-qwen2-vl": {"model_type": "qwen2_vl", "torch_dtype": "float32", "vision_config": {
+        "depth": 1, "embed_dim": 64, "num_heads": 2, "hidden_size": 96, "mlp_ratio": 2}},
+    "cornserve-b200/tiny-qwen3-vl": {"model_type": "qwen3_vl", "torch_dtype": "float32", "vision_config": {
+        "depth": 2, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "out_hidden_size": 96,
+        "num_position_embeddings": 16, "deepstack_visual_indexes": [0], "patch_size": 16}},
+    "cornserve-b200/tiny-qwen3-omni": {"model_type": "qwen3_omni_moe", "torch_dtype": "float32", "thinker_config": {
+        "vision_config": {"depth": 1, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "out_hidden_size": 96,
+                          "num_position_embeddings": 16, "deepstack_visual_indexes": [0], "patch_size": 16},
+        "audio_config": {"num_mel_bins": 128, "d_model": 64, "encoder_layers": 1, "encoder_attention_heads": 2,
+                         "encoder_ffn_dim": 64, "max_source_positions": 200, "n_window": 50, "output_dim": 96,
+                         "downsample_hidden_size": 8, "n_window_infer": 400}}},
+    "cornserve-b200/tiny-qwen2.5-omni": {"model_type": "qwen2_5_omni", "torch_dtype": "float32", "thinker_config": {
+        "vision_config": {"depth": 1, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "out_hidden_size": 96,
+                          "fullatt_block_indexes": [0]},
+        "audio_config": {"num_mel_bins": 128, "d_model": 64, "encoder_layers": 1, "encoder_attention_heads": 2,
+                         "encoder_ffn_dim": 64, "max_source_positions": 200, "n_window": 50, "output_dim": 96}}},
+    "cornserve-b200/tiny-gemma3": {"model_type": "gemma3", "torch_dtype": "float32", "mm_tokens_per_image": 4,
+                                   "text_config": {"hidden_size": 256},
+                                   "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 1,
+                                                     "num_attention_heads": 2, "image_size": 56, "patch_size": 14}},
+    "cornserve-b200/tiny-gemma3-large": {"model_type": "gemma3", "torch_dtype": "float32", "mm_tokens_per_image": 4,
+                                         "text_config": {"hidden_size": 512},
+                                         "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 1,
+                                                           "num_attention_heads": 2, "image_size": 56, "patch_size": 14}},
+    "cornserve-b200/tiny-llava-onevision": {"model_type": "llava_onevision", "torch_dtype": "float32",
+                                            "text_config": {"hidden_size": 96},
+                                            "image_grid_pinpoints": [[56, 56], [56, 112], [112, 56], [112, 112]],
+                                            "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+                                                              "num_attention_heads": 2, "image_size": 56, "patch_size": 14}},
+    "cornserve-b200/tiny-internvl": {"model_type": "internvl_chat", "torch_dtype": "float32", "llm_config": {"hidden_size": 96},
+                                     "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+                                                       "num_attention_heads": 2, "image_size": 56, "patch_size": 14}},
 }
 
 
@@ -118,7 +150,7 @@ def iter_safetensors(model_id: str, required_prefixes: list[str] | None = None, 
 
 
 def load_model_weights(model: torch.nn.Module, model_id: str, required_prefixes: list[str], strict: bool = True,
-                       ignored_prefixes: list[str] | None = None) -> bool:
+                       ignored_prefixes: list[str] | None = None, strip_prefixes: bool = True) -> bool:
     """Load checkpoint tensors through ``model.load_weights``.  Returns ``False`` (leaving the random
     initialisation in place) when the model has no weights on disk and random init is allowed."""
     if not has_weights(model_id):
@@ -126,7 +158,7 @@ def load_model_weights(model: torch.nn.Module, model_id: str, required_prefixes:
             raise FileNotFoundError(f"No safetensors found for {model_id}")
         logger.warning("No checkpoint for %s on this machine: keeping randomly initialised weights", model_id)
         return False
-    loaded = model.load_weights(iter_safetensors(model_id, required_prefixes, True, ignored_prefixes))
+    loaded = model.load_weights(iter_safetensors(model_id, required_prefixes, strip_prefixes, ignored_prefixes))
     expected = {n for n, _ in model.named_parameters()}
     logger.info("Loaded %d checkpoint tensors into %d parameters of %s", len(loaded), len(expected), model_id)
     if strict and not loaded:

@@ -131,13 +131,15 @@ __global__ void softmax_rows_kernel(const __nv_bfloat16* x, long long ldx, __nv_
 
 // ---------------------------------------------------------------------------------------
 // 3x3 tap gather for a channels-last image [B, H, W, C] -> rows [B*Ho*Wo, 9*C], tap-major (ky, kx, c), zero
-// padding 1.  up == 2 reads the source through a nearest-neighbour 2x upsampling (Ho = 2H, Wo = 2W).
+// padding 1.  up == 2 reads the source through a nearest-neighbour 2x upsampling (Ho = 2H, Wo = 2W); stride 2
+// halves the output extent (Ho = (H - 1) / 2 + 1).
 // silu != 0 applies SiLU to every gathered value (the activation that precedes the convolution).
 // ---------------------------------------------------------------------------------------
 __global__ void im2col3x3_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, int B, int H, int W, int C, int up,
-                                 int silu) {
+                                 int silu, int stride) {
   const int cv = C >> 3;
-  const int Ho = H * up, Wo = W * up;
+  const int Hu = H * up, Wu = W * up;                                   // (upsampled) input extent
+  const int Ho = (Hu - 1) / stride + 1, Wo = (Wu - 1) / stride + 1;     // output extent
   const long long total = static_cast<long long>(B) * Ho * Wo * 9 * cv;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -147,9 +149,9 @@ __global__ void im2col3x3_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, i
   const int xo = static_cast<int>(pix % Wo);
   const int yo = static_cast<int>((pix / Wo) % Ho);
   const int b = static_cast<int>(pix / (static_cast<long long>(Wo) * Ho));
-  const int ys = yo + tap / 3 - 1, xs = xo + tap % 3 - 1;
+  const int ys = yo * stride + tap / 3 - 1, xs = xo * stride + tap % 3 - 1;
   uint4 v = make_uint4(0, 0, 0, 0);
-  if (ys >= 0 && ys < Ho && xs >= 0 && xs < Wo) {
+  if (ys >= 0 && ys < Hu && xs >= 0 && xs < Wu) {
     const long long s = (static_cast<long long>(b) * H + ys / up) * W + xs / up;
     v = *reinterpret_cast<const uint4*>(src + s * C + c * 8);
     if (silu) {
@@ -165,13 +167,13 @@ __global__ void im2col3x3_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, i
 
 // ---------------------------------------------------------------------------------------
 // 1-D tap gather for channels-last sequences [B, T, C] -> rows [B*To, taps*C]:
-//   dst[b, t, j, :] = act(src[b, t + first + j * dilation, :])   (zero outside [0, T))
+//   dst[b, t, j, :] = act(src[b, t * stride + first + j * dilation, :])   (zero outside [0, T))
 // act == 1: SnakeBeta, x + sin^2(x * exp(alpha[c])) / (exp(beta[c]) + 1e-9).
 // A causal convolution with kernel k uses first = -(k - 1) * dilation; a stride-s transposed convolution
 // with kernel 2s uses taps = 2, first = -1 ... see the Python wrapper.
 // ---------------------------------------------------------------------------------------
 __global__ void im2col1d_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, int B, int T, int To, int C,
-                                int taps, int first, int dilation, int act, const float* alpha,
+                                int taps, int first, int dilation, int stride, int act, const float* alpha,
                                 const float* beta) {
   const int cv = C >> 3;
   const long long total = static_cast<long long>(B) * To * taps * cv;
@@ -182,7 +184,7 @@ __global__ void im2col1d_kernel(const __nv_bfloat16* src, __nv_bfloat16* dst, in
   const long long row = idx / (static_cast<long long>(taps) * cv);
   const int t = static_cast<int>(row % To);
   const int b = static_cast<int>(row / To);
-  const int ts = t + first + j * dilation;
+  const int ts = t * stride + first + j * dilation;
   uint4 v = make_uint4(0, 0, 0, 0);
   if (ts >= 0 && ts < T) {
     v = *reinterpret_cast<const uint4*>(src + (static_cast<long long>(b) * T + ts) * C + c * 8);
@@ -251,22 +253,24 @@ CS_API int cs_softmax_rows(const void* x, long long ldx, void* y, long long ldy,
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 
-CS_API int cs_im2col3x3(const void* src, void* dst, int B, int H, int W, int C, int up, int silu, void* stream) {
+CS_API int cs_im2col3x3(const void* src, void* dst, int B, int H, int W, int C, int up, int silu, int stride,
+                        void* stream) {
   if (B <= 0 || H <= 0 || W <= 0) return 0;
-  if ((C & 7) || (up != 1 && up != 2)) return -1;
-  const long long total = static_cast<long long>(B) * H * up * W * up * 9 * (C >> 3);
+  if ((C & 7) || (up != 1 && up != 2) || (stride != 1 && stride != 2)) return -1;
+  const long long Ho = (H * up - 1) / stride + 1, Wo = (W * up - 1) / stride + 1;
+  const long long total = static_cast<long long>(B) * Ho * Wo * 9 * (C >> 3);
   im2col3x3_kernel<<<blocks_for(total, 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, B, H, W, C, up, silu);
+      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, B, H, W, C, up, silu, stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 
 CS_API int cs_im2col1d(const void* src, void* dst, int B, int T, int To, int C, int taps, int first, int dilation,
-                       int act, const void* alpha, const void* beta, void* stream) {
+                       int stride, int act, const void* alpha, const void* beta, void* stream) {
   if (B <= 0 || To <= 0) return 0;
-  if ((C & 7) || taps <= 0 || (act == 1 && (alpha == nullptr || beta == nullptr))) return -1;
+  if ((C & 7) || taps <= 0 || stride <= 0 || (act == 1 && (alpha == nullptr || beta == nullptr))) return -1;
   const long long total = static_cast<long long>(B) * To * taps * (C >> 3);
   im2col1d_kernel<<<blocks_for(total, 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, B, T, To, C, taps, first, dilation, act, (const float*)alpha,
+      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, B, T, To, C, taps, first, dilation, stride, act, (const float*)alpha,
       (const float*)beta);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
@@ -285,5 +289,41 @@ CS_API int cs_to_rgb8(const void* x, long long ldx, void* y, long long pixels, v
   if (pixels <= 0) return 0;
   to_rgb8_kernel<<<blocks_for(pixels, 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx,
                                                                            (unsigned char*)y, pixels);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+// ---------------------------------------------------------------------------------------
+// Bilinear lookup in a learned 2-D position table, added in place:
+//   x[l, :] += sum_{i<4} wgt[i, l] * table[idx[i, l], :]
+// (the four neighbours and weights of every patch are computed on the host).  H is a multiple of 8.
+// ---------------------------------------------------------------------------------------
+namespace {
+__global__ void bilinear_embed_add_kernel(__nv_bfloat16* x, long long ldx, const __nv_bfloat16* table, long long ldt,
+                                          const int* idx, const float* wgt, long long L, int H) {
+  const int hv = H >> 3;
+  const long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (g >= L * hv) return;
+  const int c = static_cast<int>(g % hv);
+  const long long l = g / hv;
+  float acc[8];
+  unpack8g(*reinterpret_cast<const uint4*>(x + l * ldx + c * 8), acc);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float w = wgt[i * L + l];
+    float f[8];
+    unpack8g(*reinterpret_cast<const uint4*>(table + static_cast<long long>(idx[i * L + l]) * ldt + c * 8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += w * f[j];
+  }
+  *reinterpret_cast<uint4*>(x + l * ldx + c * 8) = pack8g(acc);
+}
+}  // namespace
+
+CS_API int cs_bilinear_embed_add(void* x, long long ldx, const void* table, long long ldt, const void* idx,
+                                 const void* wgt, long long L, int H, void* stream) {
+  if (L <= 0) return 0;
+  if ((H & 7) || (ldx & 7) || (ldt & 7)) return -1;
+  bilinear_embed_add_kernel<<<blocks_for(L * (H >> 3), 256), 256, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)table, ldt, (const int*)idx, (const float*)wgt, L, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
