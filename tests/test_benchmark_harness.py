@@ -1,0 +1,28 @@
+"""Load generator: arrival processes and latency metric definitions."""
+
+import numpy as np
+
+from benchmark.load_generator import RequestRecord, arrival_times, duty_cycle_times, percentiles, summarise
+
+
+def test_arrival_processes():
+    t = arrival_times(20000, rate=10.0, burstiness=1.0, seed=1)
+    gaps = np.diff(t)
+    assert t[0] == 0 and abs(gaps.mean() - 0.1) < 0.005 and abs(gaps.std() - 0.1) < 0.01   # exponential gaps
+    regular = np.diff(arrival_times(20000, 10.0, burstiness=8.0, seed=1))
+    assert abs(regular.mean() - 0.1) < 0.005 and regular.std() < 0.05                        # same rate, less variance
+    assert (arrival_times(5, float("inf")) == 0).all()
+    d = duty_cycle_times(2000, rate_on=50.0, on_s=1.0, off_s=3.0, seed=2)
+    assert ((d % 4.0) < 1.0 + 1e-9).all()                                                      # traffic only in the "on" second
+
+
+def test_latency_metrics():
+    r = RequestRecord(send_time=10.0, chunk_times=[10.5, 10.6, 10.8, 11.1], output_tokens=4, ok=True)
+    assert abs(r.ttft - 0.5) < 1e-9 and abs(r.e2el - 1.1) < 1e-9
+    assert np.allclose(r.itl, [0.1, 0.2, 0.3]) and abs(r.tpot - 0.2) < 1e-9
+    bad = RequestRecord(send_time=10.0, error="boom")
+    s = summarise([r, bad], duration_s=2.0)
+    assert s.completed == 1 and s.failed == 1 and s.request_throughput == 0.5 and s.output_token_throughput == 2.0
+    assert abs(s.ttft_ms["median"] - 500.0) < 1e-6 and abs(s.itl_ms["p99"] - 298.0) < 1.0
+    p = percentiles(list(range(1, 101)))
+    assert p["median"] == 50.5 and abs(p["p99"] - 99.01) < 1e-6
