@@ -1,0 +1,1 @@
+"""Monolithic ("no fission") baseline executor."""
