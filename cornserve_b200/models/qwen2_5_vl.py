@@ -200,28 +200,87 @@ class Qwen25VisionTransformer(nn.Module):
         unit = cfg.spatial_merge_size ** 2
         x = pixel_patches.to(device=dev, dtype=self.dtype, non_blocking=True)
         L = x.shape[0]
-        # host-side indices
+        widx_d, cs_d, cu_win_d, cu_full_d, max_win, max_full = self._index_tables(grid_thw, L)
+
+        x = self.patch_embed(x)
+        x = ops.gather_rows(x.view(L // unit, unit * cfg.hidden_size), widx_d).view(L, cfg.hidden_size)
+        att = [(cu_full_d, max_full) if i in cfg.fullatt_block_indexes else (cu_win_d, max_win) for i in range(len(self.blocks))]
+        tp = self._fused_tp(L)
+        if tp is not None:
+            y = self._blocks_fused(tp, x, cs_d, att)
+        else:
+            for blk, (cu, mx) in zip(self.blocks, att):
+                x = blk(x, cs_d, cu, mx)
+            y = self.merger(x)  # [L/unit, out] in window order
+        out = torch.empty_like(y)
+        ops.scatter_rows_(out, widx_d, y)  # undo the window permutation
+        return out
+
+    def _index_tables(self, grid_thw: np.ndarray, L: int):
+        """Window permutation, rotary table and attention boundaries of a batch, on the device.  Built on the host
+        with NumPy (no device synchronisation) and kept per grid signature: serving traffic repeats a few shapes."""
+        cfg, dev = self.cfg, self.device
+        key = (str(dev), grid_thw.astype(np.int64).tobytes())
+        cache = self.__dict__.setdefault("_tables", {})
+        hit = cache.get(key)
+        if hit is not None:
+            return hit
+        unit = cfg.spatial_merge_size ** 2
         widx, cu_win = window_index(grid_thw, cfg.window_size, cfg.spatial_merge_size, cfg.patch_size)
         cs = self.rotary_table(grid_thw).reshape(L // unit, unit, 2, -1)[widx].reshape(L, 2, -1)
         frames = np.repeat(grid_thw[:, 1] * grid_thw[:, 2], grid_thw[:, 0])
         cu_full = np.concatenate([[0], np.cumsum(frames)]).astype(np.int32)
-        max_full = int(frames.max())
-        max_win = int(np.diff(cu_win).max())
         to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True)  # noqa: E731
-        widx_d, cs_d = to_dev(widx.astype(np.int32)), to_dev(cs)
-        cu_win_d, cu_full_d = to_dev(cu_win), to_dev(cu_full)
-
-        x = self.patch_embed(x)
-        x = ops.gather_rows(x.view(L // unit, unit * cfg.hidden_size), widx_d).view(L, cfg.hidden_size)
-        for i, blk in enumerate(self.blocks):
-            if i in cfg.fullatt_block_indexes:
-                x = blk(x, cs_d, cu_full_d, max_full)
-            else:
-                x = blk(x, cs_d, cu_win_d, max_win)
-        y = self.merger(x)  # [L/unit, out] in window order
-        out = torch.empty_like(y)
-        ops.scatter_rows_(out, widx_d, y)  # undo the window permutation
+        out = (to_dev(widx.astype(np.int32)), to_dev(cs), to_dev(cu_win), to_dev(cu_full), int(np.diff(cu_win).max()),
+               int(frames.max()))
+        if len(cache) >= 64:
+            cache.pop(next(iter(cache)))
+        cache[key] = out
         return out
+
+    # -- tensor-parallel path without library collectives ------------------------------------------------
+    def _fused_tp(self, rows: int):
+        """The peer-memory context for ``rows`` patch tokens, or ``None`` when the plain path applies (one GPU, no
+        fabric, or too few rows to give every rank a 128-row block)."""
+        g = self.group
+        if g.size == 1 or g.fabric is None or self.device.type != "cuda" or rows < 128 * g.size or rows % 4:
+            return None
+        from ..parallel.fused import FusedEncoderTP
+
+        tp = getattr(self, "_tp_ctx", None)
+        if tp is None or tp.S_cap < rows:
+            # sized by the first batch that needs it (collective: all ranks run the same batches)
+            tp = self._tp_ctx = FusedEncoderTP(g, self.cfg.hidden_size, max(rows, 40960))
+        return tp
+
+    def _blocks_fused(self, tp, x: torch.Tensor, cs: torch.Tensor, att: list) -> torch.Tensor:
+        """All blocks and the merger with row-sharded activations between GEMMs.  ``x`` is the full (replicated)
+        patch-embedding output; every rank keeps only its rows of the residual stream from here on."""
+        cfg = self.cfg
+        T = x.shape[0]
+        tp.begin(T)
+        lo, hi = tp.row_range
+        xs = x[lo:hi].contiguous()
+        eps = cfg.rms_norm_eps
+        blocks = list(self.blocks)
+        tp.reduce_norm_push(bias=None, residual=xs, norm_w=blocks[0].norm1.weight, eps=eps, dst=0, reduce=False)
+        for i, (blk, (cu, mx)) in enumerate(zip(blocks, att)):
+            hl, d = blk.heads_local, cfg.head_dim
+            qkv = tp.gemm_gathered(0, blk.qkv.weight, blk.qkv.bias)
+            ops.rope_(qkv[:, : 2 * hl * d].view(T, 2 * hl, d), cs)
+            q, k, v = (qkv[:, j * hl * d:(j + 1) * hl * d].view(T, hl, d) for j in range(3))
+            a = ops.attention_varlen(q, k, v, cu, cu, mx)
+            tp.gemm_push(a.view(T, hl * d), blk.proj.weight)
+            xs = tp.reduce_norm_push(bias=blk.proj.bias, residual=xs, norm_w=blk.norm2.weight, eps=eps, dst=1)
+            h = tp.gemm_gathered(1, blk.gate_up.weight, blk.gate_up.bias, act=cfg.hidden_act, swiglu=True)
+            tp.gemm_push(h, blk.down.weight)
+            last = i + 1 == len(blocks)
+            nxt = self.merger.ln_q.weight if last else blocks[i + 1].norm1.weight
+            xs = tp.reduce_norm_push(bias=blk.down.bias, residual=xs, norm_w=nxt, eps=eps, dst=2 if last else 0,
+                                     gather_chunk=128 * self.merger.unit if last else 128)
+        m = self.merger
+        h = tp.gemm_gathered(2, m.fc1.weight, m.fc1.bias, act="gelu", a_rpr=m.unit)
+        return m.fc2(h)  # small: [T/4, out] partial sums reduced by the library collective
 
     # -- checkpoint loading (HF names, prefix "visual." already stripped) ---------------------------
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:

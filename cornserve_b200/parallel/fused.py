@@ -62,3 +62,138 @@ class FusedRowParallel:
             raise RuntimeError(f"cs_gemm_skinny_allreduce failed with code {rc}")
         _count()
         return h, normed
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Tensor-parallel encoder blocks: all-gather -> GEMM and GEMM -> reduce-scatter without library collectives
+# ------------------------------------------------------------------------------------------------------------
+from ctypes import c_uint  # noqa: E402
+
+import torch.distributed as dist  # noqa: E402
+
+_lib.register_signature("cs_gemm_bf16_tp",
+                        [P, L, P, L, P, L, P, I, I, I, I, I, I, P, I, c_uint, I, I, I, P, P, I, L, P], I)
+_lib.register_signature("cs_tp_reduce_norm_push",
+                        [I, I, I, I, I, P, L, P, c_uint, P, P, L, P, L, P, F, P, P, L, I, P], I)
+
+_ACTS = {"none": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "quick_gelu": 4, "relu": 5}
+
+
+class FusedEncoderTP:
+    """Peer-memory plumbing of a tensor-parallel encoder tower whose activations are sharded by rows between blocks.
+
+    Per half-block three kernels run on every rank and meet only through counters in peer memory:
+
+    * :meth:`gemm_push` - row-parallel GEMM whose epilogue stores bf16 partial tiles straight into the receive buffer
+      of the rank that owns the rows (the reduce-scatter is the GEMM's store);
+    * :meth:`reduce_norm_push` - per owned row: wait for all partials, add bias + residual, keep the new residual
+      shard, RMSNorm, write the normalised row into every rank's operand buffer (the all-gather is this store);
+    * :meth:`gemm_gathered` - column-parallel GEMM whose TMA producer waits per 128-row chunk of that operand.
+
+    ``begin(S)`` is called once per forward pass: it fixes the row ownership (``rows_per_rank`` a multiple of 128),
+    clears the counters and meets the peers once (the only library collective of the pass).
+    Operand buffers: 0 and 1 alternate between the attention and MLP halves; 2 is read four rows at a time by the
+    patch merger.
+    """
+
+    def __init__(self, group: ParallelGroup, hidden: int, max_rows: int):
+        if group.fabric is None:
+            raise RuntimeError("FusedEncoderTP needs the peer-memory fabric")
+        self.group, self.H = group, hidden
+        T = group.size
+        self.R_cap = -(-max_rows // (T * 128)) * 128
+        self.S_cap = self.R_cap * T
+        fab: Fabric = group.fabric
+        self.gather = [fab.alloc(self.S_cap * hidden, torch.bfloat16, zero=False) for _ in range(3)]
+        self.gflags = [fab.alloc(self.S_cap // 128 + 1, torch.int32) for _ in range(3)]
+        self.recv = fab.alloc(T * self.R_cap * hidden, torch.bfloat16, zero=False)
+        self.rflags = fab.alloc(self.R_cap // 128 + 1, torch.int32)
+        self._gptr = [b.ptr_array() for b in self.gather]
+        self._gfptr = [b.ptr_array() for b in self.gflags]
+        self._rptr = self.recv.ptr_array()
+        self._rfptr = self.rflags.ptr_array()
+        self._sync = torch.zeros(1, device=group.device, dtype=torch.float32)
+        self.S = self.R = self.rows_local = 0
+        self.g_epoch = [0, 0, 0]
+        self.r_epoch = 0
+        self._last_push_tiles_n = 0
+
+    def begin(self, S: int) -> None:
+        T, r = self.group.size, self.group.rank
+        R = -(-S // (T * 128)) * 128
+        if R > self.R_cap:
+            raise ValueError(f"{S} rows exceed the capacity of this fused context ({self.S_cap})")
+        self.S, self.R = S, R
+        self.rows_local = max(0, min(R, S - r * R))
+        for f in (*self.gflags, self.rflags):
+            f.local.zero_()
+        dist.all_reduce(self._sync, group=self.group.group)  # nobody pushes before everyone has cleared
+        self.g_epoch = [0, 0, 0]
+        self.r_epoch = 0
+
+    @property
+    def row_range(self) -> tuple[int, int]:
+        lo = self.group.rank * self.R
+        return lo, lo + self.rows_local
+
+    # -- kernels ---------------------------------------------------------------------------------------------
+    def reduce_norm_push(self, *, bias: torch.Tensor | None, residual: torch.Tensor, norm_w: torch.Tensor | None, eps: float,
+                         dst: int | None, reduce: bool = True, gather_chunk: int = 128) -> torch.Tensor:
+        """``x' = sum_ranks(partials) + bias + residual`` on this rank's rows (``reduce=False``: ``x' = residual``),
+        then ``RMSNorm(x')`` pushed into operand buffer ``dst`` of every rank.  Returns ``x'`` (the residual shard)."""
+        g = self.group
+        rows, H = self.rows_local, self.H
+        x_out = torch.empty((rows, H), device=g.device, dtype=torch.bfloat16) if reduce else residual
+        if dst is not None:
+            self.g_epoch[dst] += 1
+        lib = _lib.load()
+        rc = lib.cs_tp_reduce_norm_push(
+            rows, H, g.size, g.rank, self.R,
+            self.recv.local.data_ptr() if reduce else None, H, self.rflags.local.data_ptr(),
+            self.r_epoch * self._last_push_tiles_n * g.size,
+            _ptr(bias) if reduce else None, residual.data_ptr(), residual.stride(0),
+            x_out.data_ptr() if reduce else None, H, _ptr(norm_w), float(eps),
+            ctypes.cast(self._gptr[dst], c_void_p) if dst is not None else None,
+            ctypes.cast(self._gfptr[dst], c_void_p) if dst is not None else None, H, gather_chunk, _stream())
+        if rc != 0:
+            raise RuntimeError(f"cs_tp_reduce_norm_push failed with code {rc}")
+        _count()
+        return x_out
+
+    def gemm_gathered(self, src: int, w: torch.Tensor, bias: torch.Tensor | None, *, act: str | None = None,
+                      swiglu: bool = False, a_rpr: int = 1) -> torch.Tensor:
+        """``act(A w.T + bias)`` where ``A`` is operand buffer ``src`` (``[S / a_rpr, a_rpr * H]``), consumed chunk by
+        chunk as the peers' rows land."""
+        g = self.group
+        M, K = self.S // a_rpr, self.H * a_rpr
+        N = w.shape[0] // (2 if swiglu else 1)
+        out = torch.empty((M, N), device=g.device, dtype=torch.bfloat16)
+        m_rot = (g.rank * self.R // a_rpr) // 128
+        lib = _lib.load()
+        rc = lib.cs_gemm_bf16_tp(
+            self.gather[src].local.data_ptr(), K, w.data_ptr(), w.stride(0), out.data_ptr(), N, _ptr(bias), M, N, K,
+            _ACTS[act or "none"], 1 if swiglu else 0, 0, self.gflags[src].local.data_ptr(), a_rpr, self.g_epoch[src], m_rot,
+            0, 0, None, None, 128, 0, _stream())
+        if rc != 0:
+            raise RuntimeError(f"cs_gemm_bf16_tp (gathered) failed with code {rc}")
+        _count()
+        return out
+
+    def gemm_push(self, x: torch.Tensor, w: torch.Tensor) -> None:
+        """Row-parallel ``x w.T``: this rank's partial sums travel to the owners of the rows from the epilogue."""
+        g = self.group
+        M, K = x.shape
+        N = w.shape[0]
+        assert M == self.S and N == self.H and x.stride(1) == 1
+        tiles_m = -(-M // 128)
+        bn = 256 if tiles_m * -(-N // 256) >= 148 else 128
+        self._last_push_tiles_n = -(-N // bn)
+        self.r_epoch += 1
+        lib = _lib.load()
+        rc = lib.cs_gemm_bf16_tp(
+            x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), None, 0, None, M, N, K, 0, 0, bn, None, 1, 0,
+            (((g.rank + 1) % g.size) * self.R) // 128, g.size, g.rank, ctypes.cast(self._rptr, c_void_p), ctypes.cast(self._rfptr, c_void_p),
+            self.R, self.H, _stream())
+        if rc != 0:
+            raise RuntimeError(f"cs_gemm_bf16_tp (push) failed with code {rc}")
+        _count()

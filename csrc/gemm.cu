@@ -40,7 +40,22 @@ struct GemmParams {
   int up_row_offset;      // SwiGLU: row of W where the "up" half starts
   uint32_t idesc;
   int* err;
+  // ---- tensor-parallel coupling (COMM variant of the kernel only) ----
+  // A-side: A is a buffer that peers fill row by row (an all-gather in flight).  a_flags[c] counts the rows of
+  // chunk c that have landed (each "pushed row" is 1/a_rpr of a GEMM row); a tile waits for the chunks it reads.
+  const unsigned* a_flags;   // null = A is ready
+  int a_chunk;               // pushed rows per flag (128 * a_rpr)
+  int a_total;               // pushed rows in total (M * a_rpr)
+  unsigned a_epoch;          // flag value per pushed row of this call
+  int m_rot;                 // tile-row rotation so that every rank starts with the rows it owns
+  // C-side: partial sums go to the rank that owns the output rows (a reduce-scatter in flight) instead of C.
+  __nv_bfloat16* push_dst[8];  // per owner: [world][rows_per_rank][push_ld]
+  unsigned* push_flags[8];     // per owner: one arrival counter per 128-row block of its shard
+  int push_world, push_rank, rows_per_rank;
+  long long push_ld;
 };
+
+constexpr uint64_t kFlagSpinCheck = 0x3f;
 
 // f[j] += bias[j] for the first n (<= 32) columns; bias + 0 is 16-byte aligned when col0 is.
 __device__ __forceinline__ void add_bias32(float (&f)[32], const __nv_bfloat16* b, int n) {
@@ -103,7 +118,27 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gm;
 }
 
-template <int BN, bool SWIGLU>
+// Bounded wait until *flag >= target (flag written by other GPUs with release semantics).
+__device__ __forceinline__ bool wait_flag_ge(const unsigned* flag, unsigned target, volatile int* abort_flag, int* err) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= target) return true;
+    if ((spin & kFlagSpinCheck) == kFlagSpinCheck) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > CS_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        cs_set_error(err, CS_ERR_TIMEOUT_PEER);
+        return false;
+      }
+    }
+  }
+}
+
+template <int BN, bool SWIGLU, bool COMM = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
@@ -121,6 +156,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int push_cnt[4];  // COMM push: epilogue warps that have sent their rows of the current / next tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -132,6 +168,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    push_cnt[0] = push_cnt[1] = push_cnt[2] = push_cnt[3] = 0;
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -153,6 +190,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
+  // COMM push: each epilogue warp stages its 32 x BN_OUT bf16 sub-tile here so that rows leave as contiguous
+  // 16-byte-per-lane stores (scattered 16-byte stores are slow over NVLink).  Row pitch padded against conflicts.
+  constexpr int STG_PITCH = BN_OUT * 2 + 16;
+  uint8_t* stg_base = smem + stages * STAGE_BYTES + (BM * BK * 2 - A_BYTES);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -164,7 +205,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tiles_m, tiles_n, tm, tn);
+        if (COMM) tm = (tm + p.m_rot) % tiles_m;
         const int m0 = tm * BM, n0 = tn * BN_OUT;
+        if (COMM && p.a_flags != nullptr) {
+          // the rows of this tile are chunk tm of the gathered operand: wait until all of them have landed
+          const int rows = min(p.a_chunk, p.a_total - tm * p.a_chunk);
+          if (!wait_flag_ge(p.a_flags + tm, p.a_epoch * static_cast<unsigned>(rows), abortp, p.err)) { ok = false; break; }
+          // the rows were written by ordinary stores (of other GPUs); the TMA unit reads through the async proxy
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp, p.err, CS_ERR_TIMEOUT_SLOT)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
@@ -218,9 +267,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may touch
     int acc = 0;
     uint32_t acc_phase = 0;
+    int n_push = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int tm, tn;
       tile_coords(t, tiles_m, tiles_n, tm, tn);
+      if (COMM) tm = (tm + p.m_rot) % tiles_m;
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN_OUT;
       if (!mbar_wait(&acc_full[acc], acc_phase, abortp, p.err, CS_ERR_TIMEOUT_MMA)) break;
@@ -311,6 +362,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) out[j] = f[j];
             }
+          } else if (COMM && p.push_world > 0) {
+            // stage this lane's 32 columns; the warp sends whole rows once the tile is complete (below)
+            uint4* sp = reinterpret_cast<uint4*>(stg_base + (q * 32 + lane) * STG_PITCH + c * 64);
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              uint4 w;
+              w.x = pack_bf16x2(f[j4 * 8 + 0], f[j4 * 8 + 1]);
+              w.y = pack_bf16x2(f[j4 * 8 + 2], f[j4 * 8 + 3]);
+              w.z = pack_bf16x2(f[j4 * 8 + 4], f[j4 * 8 + 5]);
+              w.w = pack_bf16x2(f[j4 * 8 + 6], f[j4 * 8 + 7]);
+              sp[j4] = w;
+            }
           } else {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
             if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
@@ -336,6 +399,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_arrive(&acc_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+      if (COMM && p.push_world > 0) {
+        // partial sums of this rank go to slot [rank] of the receive buffer of the rank that owns the rows:
+        // lanes_per_row lanes cover one row with consecutive 16-byte pieces
+        __syncwarp();
+        constexpr int LPR = BN_OUT / 8;               // lanes per row (32 for 256 columns, 16 for 128)
+        constexpr int RPI = 32 / LPR;                 // rows per store instruction
+        const int owner = (tm * BM) / p.rows_per_rank;
+        const long long slot_row0 = static_cast<long long>(p.push_rank) * p.rows_per_rank + (tm * BM - owner * p.rows_per_rank);
+        const int cc = lane % LPR;
+        const bool col_ok = n0 + cc * 8 < p.N;
+#pragma unroll 4
+        for (int r0 = 0; r0 < 32; r0 += RPI) {
+          const int rr = q * 32 + r0 + lane / LPR;    // row within the tile
+          if (col_ok && tm * BM + rr < p.M) {
+            const uint4 w = *reinterpret_cast<const uint4*>(stg_base + rr * STG_PITCH + cc * 16);
+            *reinterpret_cast<uint4*>(p.push_dst[owner] + (slot_row0 + rr) * p.push_ld + n0 + cc * 8) = w;
+          }
+        }
+        // The last of the four epilogue warps to finish the tile tells the owner of the rows (one system-scope
+        // release per tile: such releases are expensive).  The warps meet through a shared-memory counter, not a
+        // barrier, so a warp that gave up on a wait cannot strand the others; the owner's wait is bounded too.
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          const int par = n_push & 3;  // a warp cannot get four tiles ahead of another (two accumulators)
+          const int prev = atomicAdd(&push_cnt[par], 1);
+          if (prev == 3) {
+            push_cnt[par] = 0;
+            __threadfence_block();
+            const int blk = (tm * BM - owner * p.rows_per_rank) / BM;
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push_flags[owner] + blk) : "memory");
+          }
+        }
+        ++n_push;
+      }
     }
   }
 
@@ -347,7 +445,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <int BN, bool SWIGLU>
+template <int BN, bool SWIGLU, bool COMM = false>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t stream) {
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
   const int stage_bytes = p.a_bytes + BN * BK * 2;
@@ -357,12 +455,13 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaSt
   // The MMA always reads 128 rows of A; when fewer rows are fetched the read runs past the A slot,
   // so keep a tail pad that makes the last stage's read stay inside the allocation.
   const int tail_pad = BM * BK * 2 - p.a_bytes;
-  while (stages > 2 && stages * stage_bytes + 1024 + tail_pad > max_smem) --stages;
+  const int staging = COMM ? BM * (BN_OUT * 2 + 16) : 0;  // epilogue staging of the push variant
+  while (stages > 2 && stages * stage_bytes + 1024 + tail_pad + staging > max_smem) --stages;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   p.stages = stages;
-  const int smem = stages * stage_bytes + 1024 + tail_pad;
+  const int smem = stages * stage_bytes + 1024 + tail_pad + staging;
   static bool attr_done[64] = {false};
-  auto kern = gemm_bf16_kernel<BN, SWIGLU>;
+  auto kern = gemm_bf16_kernel<BN, SWIGLU, COMM>;
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
@@ -438,6 +537,65 @@ CS_API int cs_gemm_bf16(const void* A, long long lda, const void* W, long long l
     case 128: return launch<128, false>(tmA, tmB, p, stream);
     case 64: return launch<64, false>(tmA, tmB, p, stream);
     case 32: return launch<32, false>(tmA, tmB, p, stream);
+    default: return -4;
+  }
+}
+
+// Tensor-parallel coupled GEMM (one kernel per rank, the ranks meet only through flags in peer memory):
+//   * `a_flags` != null: A is the local copy of an operand that peers are still pushing row by row (the
+//     all-gather half of a column-parallel layer).  Tile row i waits until a_flags[i] >= a_epoch * (pushed rows in
+//     chunk i); a pushed row is 1/a_rpr of a GEMM row (a_rpr = 4 when [S, H] rows are read as [S/4, 4H]).
+//   * `push_world` > 0: the result is a partial sum of a row-parallel layer.  Tile rows go, as bf16, into slot
+//     [push_rank] of the receive buffer of the rank that owns them (rank o owns rows [o*rows_per_rank, ...),
+//     rows_per_rank a multiple of 128) and that rank's arrival counter of the 128-row block is bumped once per tile;
+//     C is unused.
+// `m_rot` rotates the tile rows so that a rank starts with rows that are already local.  Epilogue options as in
+// cs_gemm_bf16 (bias and residual are normally left to the reduction kernel when pushing).
+CS_API int cs_gemm_bf16_tp(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                           const void* bias, int M, int N, int K, int act, int swiglu, int bn, const void* a_flags,
+                           int a_rpr, unsigned a_epoch, int m_rot, int push_world, int push_rank,
+                           const void* const* push_dst, const void* const* push_flags, int rows_per_rank,
+                           long long push_ld, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (lda & 7) || (ldw & 7) || push_world > 8 || M < BM) return -1;
+  if (push_world > 0 && (rows_per_rank % BM != 0 || swiglu || (push_ld & 7))) return -1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.gate_rpb = 1;
+  p.act = act;
+  p.up_row_offset = N;
+  p.err = cs_error_word();
+  p.a_rows = BM;
+  p.a_bytes = BM * BK * 2;
+  p.a_flags = reinterpret_cast<const unsigned*>(a_flags);
+  p.a_chunk = BM * (a_rpr > 0 ? a_rpr : 1);
+  p.a_total = M * (a_rpr > 0 ? a_rpr : 1);
+  p.a_epoch = a_epoch;
+  const int tiles_m = (M + BM - 1) / BM;
+  p.m_rot = ((m_rot % tiles_m) + tiles_m) % tiles_m;
+  p.push_world = push_world; p.push_rank = push_rank; p.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : BM;
+  p.push_ld = push_ld;
+  for (int i = 0; i < push_world; ++i) {
+    p.push_dst[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(push_dst[i]));
+    p.push_flags[i] = reinterpret_cast<unsigned*>(const_cast<void*>(push_flags[i]));
+  }
+  if (bn == 0) bn = swiglu ? 256 : ((tiles_m * ((N + 255) / 256) >= cs_num_sms()) ? 256 : 128);
+  CUtensorMap tmA, tmB;
+  if (cs_encode_tmap_2d(&tmA, A, K, M, lda * 2, BK, BM, 2, 1) != 0) return -2;
+  if (cs_encode_tmap_2d(&tmB, W, K, swiglu ? 2 * N : N, ldw * 2, BK, swiglu ? bn / 2 : bn, 2, 1) != 0) return -3;
+  if (swiglu) {
+    switch (bn) {
+      case 256: return launch<256, true, true>(tmA, tmB, p, stream);
+      case 128: return launch<128, true, true>(tmA, tmB, p, stream);
+      default: return -4;
+    }
+  }
+  switch (bn) {
+    case 256: return launch<256, false, true>(tmA, tmB, p, stream);
+    case 128: return launch<128, false, true>(tmA, tmB, p, stream);
     default: return -4;
   }
 }

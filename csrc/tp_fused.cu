@@ -1,0 +1,186 @@
+// Row kernels of the tensor-parallel encoder path.  Together with cs_gemm_bf16_tp they replace
+// "GEMM -> NCCL reduce-scatter / all-reduce -> add -> RMSNorm -> NCCL all-gather -> GEMM" by three kernels per
+// half-block that meet only through counters in peer memory:
+//
+//   GEMM (epilogue pushes bf16 partial tiles to the owner of the rows)
+//     -> tp_reduce_norm_push (this file; per owned row: wait for the partials of all ranks, sum them with bias and
+//        residual, store the new residual stream, RMSNorm, write the normalised row into EVERY rank's copy of
+//        the next GEMM's operand and bump that rank's chunk counter)
+//     -> GEMM (TMA producer waits per 128-row chunk of its operand)
+//
+// One warp per row (32 rows per CTA, one flag update per CTA and peer), 16-byte accesses, fp32 math.  Every wait is bounded and records CS_ERR_TIMEOUT_PEER.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TP_MAX_WORLD = 8;
+constexpr int TP_MAXV = 8;  // uint4 per lane: H <= 32 * 8 * 8 = 2048
+
+struct ReduceNormPushParams {
+  int rows;                    // rows owned by this rank in this call
+  int H;
+  int world, rank;
+  int rows_per_rank;           // ownership stride (multiple of 128)
+  // partial sums: recv[slot][row][ldp], slot = source rank; null = no reduction (the input is `residual` itself)
+  const __nv_bfloat16* recv; long long ldp;
+  const unsigned* recv_flags;  // one counter per 128-row block of this rank's shard
+  unsigned recv_target;        // value that means "every rank delivered every tile of the block"
+  const __nv_bfloat16* bias;   // [H] or null
+  const __nv_bfloat16* residual; long long ldr;  // [rows, ldr] local shard of the residual stream (or null)
+  __nv_bfloat16* x_out; long long ldx;            // new residual stream [rows, ldx] (may alias residual; may be null)
+  const __nv_bfloat16* norm_w; float eps;          // RMSNorm weight [H]; null = push the un-normalised sum
+  __nv_bfloat16* gather[TP_MAX_WORLD]; long long ldg;  // every rank's copy of the next operand [total rows, ldg]
+  unsigned* gather_flags[TP_MAX_WORLD];                // per rank: one counter per `gather_chunk` rows
+  int gather_chunk;
+  int* err;
+};
+
+__device__ __forceinline__ void unpack8t(const uint4& w, float (&f)[8]) {
+  f[0] = bf16lo(w.x); f[1] = bf16hi(w.x); f[2] = bf16lo(w.y); f[3] = bf16hi(w.y);
+  f[4] = bf16lo(w.z); f[5] = bf16hi(w.z); f[6] = bf16lo(w.w); f[7] = bf16hi(w.w);
+}
+__device__ __forceinline__ uint4 pack8t(const float (&f)[8]) {
+  uint4 w;
+  w.x = pack_bf16x2(f[0], f[1]); w.y = pack_bf16x2(f[2], f[3]);
+  w.z = pack_bf16x2(f[4], f[5]); w.w = pack_bf16x2(f[6], f[7]);
+  return w;
+}
+
+constexpr int TP_ROWS_PER_CTA = 32;  // 8 warps x 4 rows; divides every flag chunk (multiples of 128 rows)
+
+__global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNormPushParams p) {
+  __shared__ int wait_ok;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r_first = blockIdx.x * TP_ROWS_PER_CTA;
+  const int r_end = min(r_first + TP_ROWS_PER_CTA, p.rows);
+  const int nvec = p.H >> 3;
+  // ---- wait (once per CTA) until every rank has delivered this 128-row block ----
+  if (p.recv != nullptr) {
+    if (threadIdx.x == 0) {
+      const unsigned* flag = p.recv_flags + (r_first >> 7);
+      uint64_t t0 = 0;
+      wait_ok = 1;
+      for (uint32_t spin = 0;; ++spin) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= p.recv_target) break;
+        if ((spin & 0x3f) == 0x3f) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          // on a timeout the rows are still written (with whatever arrived) so that no later wait starves
+          if (now - t0 > CS_WAIT_LIMIT_NS) { cs_set_error(p.err, CS_ERR_TIMEOUT_PEER); wait_ok = 0; break; }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int r = r_first + warp; r < r_end; r += 8) {
+    // ---- sum partials + bias + residual ----
+    float acc[TP_MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < TP_MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        if (p.recv != nullptr) {
+          for (int s = 0; s < p.world; ++s) {
+            float f[8];
+            const __nv_bfloat16* src = p.recv + (static_cast<long long>(s) * p.rows_per_rank + r) * p.ldp + v * 8;
+            unpack8t(__ldcg(reinterpret_cast<const uint4*>(src)), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
+          }
+        }
+        if (p.bias != nullptr) {
+          float f[8];
+          unpack8t(__ldg(reinterpret_cast<const uint4*>(p.bias + v * 8)), f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
+        }
+        if (p.residual != nullptr) {
+          float f[8];
+          unpack8t(*reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(r) * p.ldr + v * 8), f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
+        }
+        // the residual stream is kept in bf16: normalise what is stored
+        const uint4 packed = pack8t(acc[i]);
+        if (p.x_out != nullptr) *reinterpret_cast<uint4*>(p.x_out + static_cast<long long>(r) * p.ldx + v * 8) = packed;
+        unpack8t(packed, acc[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += acc[i][j] * acc[i][j];
+      }
+    }
+    if (p.gather[0] == nullptr) continue;
+    float rstd = 1.f;
+    if (p.norm_w != nullptr) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      rstd = rsqrtf(ss / static_cast<float>(p.H) + p.eps);
+    }
+    // ---- normalise and write the row into every rank's operand buffer ----
+    const long long g = static_cast<long long>(p.rank) * p.rows_per_rank + r;  // row in the gathered operand
+#pragma unroll
+    for (int i = 0; i < TP_MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float y[8];
+        if (p.norm_w != nullptr) {
+          float w[8];
+          unpack8t(__ldg(reinterpret_cast<const uint4*>(p.norm_w + v * 8)), w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) y[j] = acc[i][j] * rstd * w[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) y[j] = acc[i][j];
+        }
+        const uint4 packed = pack8t(y);
+        for (int peer = 0; peer < p.world; ++peer)
+          *reinterpret_cast<uint4*>(p.gather[peer] + g * p.ldg + v * 8) = packed;
+      }
+    }
+  }
+  if (p.gather[0] == nullptr) return;
+  // ---- one release per CTA and peer: the CTA's rows all lie in one flag chunk ----
+  __syncthreads();
+  if (threadIdx.x < p.world && r_end > r_first) {
+    const long long g0 = static_cast<long long>(p.rank) * p.rows_per_rank + r_first;
+    unsigned* flag = p.gather_flags[threadIdx.x] + g0 / p.gather_chunk;
+    const unsigned n = static_cast<unsigned>(r_end - r_first);
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(n) : "memory");
+  }
+}
+
+}  // namespace
+
+// See the top of this file.  `rows` = rows this rank owns in this call (<= rows_per_rank); `recv` may be null (then
+// the kernel only normalises `residual` and pushes it: the entry of the chain).  `gather_ptrs` may be null (then the
+// kernel only reduces into `x_out`: the exit of the chain).
+CS_API int cs_tp_reduce_norm_push(int rows, int H, int world, int rank, int rows_per_rank, const void* recv, long long ldp,
+                                  const void* recv_flags, unsigned recv_target, const void* bias, const void* residual,
+                                  long long ldr, void* x_out, long long ldx, const void* norm_w, float eps,
+                                  const void* const* gather_ptrs, const void* const* gather_flag_ptrs, long long ldg,
+                                  int gather_chunk, void* stream) {
+  if (rows <= 0) return 0;
+  if ((H & 7) || H > 32 * 8 * TP_MAXV || world < 1 || world > TP_MAX_WORLD || (ldp & 7) || (ldr & 7) || (ldx & 7) || (ldg & 7))
+    return -1;
+  ReduceNormPushParams p{};
+  p.rows = rows; p.H = H; p.world = world; p.rank = rank; p.rows_per_rank = rows_per_rank;
+  p.recv = (const __nv_bfloat16*)recv; p.ldp = ldp;
+  p.recv_flags = (const unsigned*)recv_flags; p.recv_target = recv_target;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
+  p.x_out = (__nv_bfloat16*)x_out; p.ldx = ldx;
+  p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
+  p.ldg = ldg; p.gather_chunk = gather_chunk > 0 ? gather_chunk : 128;
+  for (int i = 0; i < world; ++i) {
+    p.gather[i] = gather_ptrs ? (__nv_bfloat16*)const_cast<void*>(gather_ptrs[i]) : nullptr;
+    p.gather_flags[i] = gather_flag_ptrs ? (unsigned*)const_cast<void*>(gather_flag_ptrs[i]) : nullptr;
+  }
+  p.err = cs_error_word();
+  if (p.gather_chunk % TP_ROWS_PER_CTA != 0 || rows_per_rank % TP_ROWS_PER_CTA != 0) return -1;
+  tp_reduce_norm_push_kernel<<<(rows + TP_ROWS_PER_CTA - 1) / TP_ROWS_PER_CTA, 256, 0, (cudaStream_t)stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
