@@ -41,7 +41,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--requests-per-gpu", type=int, default=48)
+    ap.add_argument("--requests-per-gpu", type=int, default=128)
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--prompt-tokens", type=int, default=128)
     ap.add_argument("--small", action="store_true", help="tiny model/config for smoke runs (not a valid number)")

@@ -353,6 +353,23 @@ def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: 
         out = torch.empty((Tq, Hq, d), device=q.device, dtype=torch.bfloat16)
     B = cu_q.numel() - 1
     lib = _lib.load()
+    if max_q_len == 1 and Tq == B and d == 128 and Hq // Hkv <= 16 and pack_gqa and causal:
+        # decode: the swapped-operand kernel (keys on the 128-row side of the tile, grouped query heads on the other)
+        if kv_splits == 0:
+            kv_splits = _decode_kv_splits(B * Hkv, lib.cs_sm_count(), block_table.shape[1])
+        ws_ptr, ws_bytes = None, 0
+        if kv_splits > 1:
+            ws, _ = _skinny_workspace(q.device)
+            if B * Hq * kv_splits * 130 * 4 > ws.numel():
+                kv_splits = 1
+            else:
+                ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+        rc = lib.cs_attention_decode(q.data_ptr(), q.stride(0), cache.data_ptr(), out.data_ptr(), out.stride(0),
+                                     kv_len.data_ptr(), block_table.data_ptr(), block_table.stride(0), pages, B, Hq, Hkv,
+                                     float(scale), kv_splits, ws_ptr, ws_bytes, _stream())
+        _chk(rc, "cs_attention_decode")
+        _count(2 if kv_splits > 1 else 1)
+        return out
     if kv_splits == 0:
         # decode (one query token per sequence): spread the keys of each sequence over idle SMs
         items = B * (Hkv if pack_gqa else Hq)

@@ -298,3 +298,36 @@ def test_attention_sliding_window(window):
     got = ops.attention_varlen(q, k, v, cu, cu, max(lens), causal=True, window=window)
     want = ref.attention_varlen(q, k, v, cu, cu, 1 / math.sqrt(d), True, window)
     _close(got, want, 2e-2, 2e-2, f"sliding window {window}")
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(28, 4), (16, 16), (32, 2), (8, 2)])
+@pytest.mark.parametrize("ctx,kv_splits", [([1, 127, 128, 129, 700], 0), ([3500, 40, 2049], 1), ([3500, 40, 2049], 3),
+                                           ([5, 9], 4)])
+def test_attention_decode_swapped_operands(Hq, Hkv, ctx, kv_splits):
+    """The decode kernel (keys on the 128-row side, grouped query heads on the other) against the fp32 restatement;
+    the stale rows beyond kv_len in the last page hold large values and must not leak in."""
+    torch.manual_seed(15)
+    d, page = 128, 128
+    B = len(ctx)
+    nblk = [(c + page - 1) // page for c in ctx]
+    pages = sum(nblk) + 3
+    cache = (torch.randn(pages, 2, Hkv, page, d, device=DEV) * 30).bfloat16()  # garbage everywhere, overwritten below
+    perm = torch.randperm(pages - 1)[: sum(nblk)] + 1
+    bt = torch.zeros(B, max(nblk) + 1, dtype=torch.int32)
+    p = 0
+    for s in range(B):
+        bt[s, : nblk[s]] = perm[p: p + nblk[s]].int()
+        p += nblk[s]
+    bt = bt.to(DEV)
+    for s in range(B):
+        kv = _rand(2, ctx[s], Hkv, d)
+        for j in range(nblk[s]):
+            m = min(page, ctx[s] - j * page)
+            cache[bt[s, j], :, :, :m] = kv[:, j * page: j * page + m].permute(0, 2, 1, 3)
+    qkv = _rand(B, (Hq + 2 * Hkv) * d)
+    q = qkv[:, : Hq * d].view(B, Hq, d)  # strided view, as the engine passes it
+    cu = torch.arange(B + 1, device=DEV, dtype=torch.int32)
+    kv_len = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    o = ops.attention_paged(q, cache, bt, kv_len, cu, 1, causal=True, pack_gqa=True, kv_splits=kv_splits)
+    want = ref.attention_paged(q.cpu().float(), cache.cpu().float(), bt.cpu(), kv_len.cpu(), cu.cpu(), 1 / math.sqrt(d), True)
+    _close(o, want.to(DEV), 2e-2, 2e-2, f"decode attn Hq={Hq} Hkv={Hkv}")
