@@ -68,7 +68,10 @@ class InternVLEncoder(nn.Module):
         self.group = group or single_group(device)
         H, p = cfg.hidden_size, cfg.patch_size
         self.side = cfg.image_size // p
-        self.patch_embed = Linear(3 * p * p, H, bias=True, device=device)
+        self.k_raw = 3 * p * p
+        self.k_pad = (-self.k_raw) % 8   # TMA rows must be multiples of 16 bytes: 588 -> 592 zero-padded columns
+        self.patch_embed = Linear(self.k_raw + self.k_pad, H, bias=True, device=device)
+        self.patch_embed.weight.data[:, self.k_raw:].zero_()
         self.class_embedding = _param(1, H, device=device, dtype=torch.bfloat16)
         self.position_embedding = _param(self.side ** 2 + 1, H, device=device, dtype=torch.bfloat16)
         heads = cfg.num_attention_heads
@@ -106,6 +109,8 @@ class InternVLEncoder(nn.Module):
         H = cfg.hidden_size
         x = pixel_values.to(self.device, self.dtype).view(B, C, g, p, g, p).permute(0, 2, 4, 1, 3, 5).reshape(B * N, C * p * p)
         pos = self.position_embedding[1:].unsqueeze(0).expand(B, N, H).reshape(B * N, H)
+        if self.k_pad:
+            x = torch.nn.functional.pad(x, (0, self.k_pad))
         patches = self.patch_embed(x.contiguous(), residual=pos.contiguous()).view(B, N, H)
         cls = (self.class_embedding + self.position_embedding[:1]).expand(B, 1, H)
         x = torch.cat([cls, patches], dim=1).reshape(B * (N + 1), H)
@@ -137,7 +142,10 @@ class InternVLEncoder(nn.Module):
                 elif p[2] == "position_embedding":
                     self.position_embedding.data.copy_(t.reshape(-1, t.shape[-1]))
                 elif p[2] == "patch_embedding":
-                    self.patch_embed.load(**{leaf: t.reshape(t.shape[0], -1) if leaf == "weight" else t})
+                    if leaf == "weight":
+                        self.patch_embed.weight.data[:, : self.k_raw].copy_(t.reshape(t.shape[0], -1))
+                    else:
+                        self.patch_embed.load(bias=t)
                 else:
                     continue
             elif name.startswith("vision_model.encoder.layers."):

@@ -87,7 +87,7 @@ class AudioEncoder(nn.Module):
                          act=HF_ACT[cfg.activation_function])
         self.layers = nn.ModuleList([EncoderBlock(spec, self.group, device) for _ in range(cfg.encoder_layers)])
         self.ln_post = LayerNorm(D, 1e-5, device=device)
-        self.register_buffer("positions", sinusoid_positions(cfg.max_source_positions, D), persistent=False)
+        self.register_buffer("positions", sinusoid_positions(cfg.max_source_positions, D).to(device), persistent=False)
 
     @property
     def dtype(self) -> torch.dtype:

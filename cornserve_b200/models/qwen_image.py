@@ -160,18 +160,21 @@ class DualStreamBlock(nn.Module):
         # ---- joint attention ------------------------------------------------------------------------
         xi = self.norm(img, scale=mod_i[:, D:2 * D], shift=mod_i[:, :D], rows_per_batch=lay.n_img)
         xt = self.norm(txt, scale=mod_t[:, D:2 * D], shift=mod_t[:, :D], rows_per_batch=lay.n_txt)
-        qkv = torch.empty((lay.rows, 3 * D), device=img.device, dtype=img.dtype)
-        for b in range(B):
-            ops.linear(xt[b * lay.n_txt:(b + 1) * lay.n_txt], self.txt.qkv.weight, self.txt.qkv.bias,
-                       out=qkv[lay.txt_rows(b)])
-            ops.linear(xi[b * lay.n_img:(b + 1) * lay.n_img], self.img.qkv.weight, self.img.qkv.bias,
-                       out=qkv[lay.img_rows(b)])
-        for part, (ni, nt) in enumerate(((self.img.norm_q, self.txt.norm_q), (self.img.norm_k, self.txt.norm_k))):
-            heads = qkv[:, part * D:(part + 1) * D].view(lay.rows, H, d)
+        if lay.fused is not None:
+            attn = self._fused_sp_attention(xi, xt, lay)
+        else:
+            qkv = torch.empty((lay.rows, 3 * D), device=img.device, dtype=img.dtype)
             for b in range(B):
-                ops.head_norm_rope_(heads[lay.txt_rows(b)], nt.weight, 1e-6, lay.cs_txt)
-                ops.head_norm_rope_(heads[lay.img_rows(b)], ni.weight, 1e-6, lay.cs_img)
-        attn = lay.attention(qkv, H, d, self.group)  # [rows, D]
+                ops.linear(xt[b * lay.n_txt:(b + 1) * lay.n_txt], self.txt.qkv.weight, self.txt.qkv.bias,
+                           out=qkv[lay.txt_rows(b)])
+                ops.linear(xi[b * lay.n_img:(b + 1) * lay.n_img], self.img.qkv.weight, self.img.qkv.bias,
+                           out=qkv[lay.img_rows(b)])
+            for part, (ni, nt) in enumerate(((self.img.norm_q, self.txt.norm_q), (self.img.norm_k, self.txt.norm_k))):
+                heads = qkv[:, part * D:(part + 1) * D].view(lay.rows, H, d)
+                for b in range(B):
+                    ops.head_norm_rope_(heads[lay.txt_rows(b)], nt.weight, 1e-6, lay.cs_txt)
+                    ops.head_norm_rope_(heads[lay.img_rows(b)], ni.weight, 1e-6, lay.cs_img)
+            attn = lay.attention(qkv, H, d, self.group)  # [rows, D]
         for b in range(B):
             g_i, g_t = mod_i[b:b + 1, 2 * D:3 * D], mod_t[b:b + 1, 2 * D:3 * D]
             si, st = slice(b * lay.n_img, (b + 1) * lay.n_img), slice(b * lay.n_txt, (b + 1) * lay.n_txt)
@@ -185,6 +188,29 @@ class DualStreamBlock(nn.Module):
             h = sp.fc1(h, act="gelu_tanh")
             ops.linear(h, sp.fc2.weight, sp.fc2.bias, gate=mod[:, 5 * D:6 * D], gate_rows_per_batch=n, residual=x, out=x)
         return img, txt
+
+    def _fused_sp_attention(self, xi: torch.Tensor, xt: torch.Tensor, lay: "JointLayout") -> torch.Tensor:
+        """Sequence-parallel joint attention whose exchanges ride in the kernels: the q|k|v projections store each
+        head tile into the owning rank's buffer, the per-head norm and rotation run there on every token of the
+        rank's heads, and the attention output returns to the token owners by one peer-store kernel."""
+        cfg, fu = self.cfg, lay.fused
+        d = cfg.attention_head_dim
+        P, per = lay.sp, lay.per_sample
+        Hl, own = fu.Hl, fu.own
+        fu.qkv_scatter(xt, self.txt.qkv.weight, self.txt.qkv.bias, 0, lay.n_txt, per, per)
+        fu.qkv_scatter(xi, self.img.qkv.weight, self.img.qkv.bias, lay.n_txt, lay.n_img, per, per)
+        R = P * lay.rows
+        full = fu.gathered_qkv(R)  # [R, 3 * own], rows = (sample, rank, that rank's [text; image] tokens)
+        for part, (ni, nt) in enumerate(((self.img.norm_q, self.txt.norm_q), (self.img.norm_k, self.txt.norm_k))):
+            ops.head_norm_rope_(full[:, part * own:(part + 1) * own].view(R, Hl, d), nt.weight, 1e-6, lay.cs_full,
+                                w2=ni.weight, seg=per, n_first=lay.n_txt)
+        packed = full if lay.gather_idx is None else ops.gather_rows(full, lay.gather_idx)
+        T = packed.shape[0]
+        q, k, v = (packed[:, i * own:(i + 1) * own].view(T, Hl, d) for i in range(3))
+        o = ops.attention_varlen(q, k, v, lay.cu, lay.cu, lay.max_len).view(T, own)
+        if lay.gather_idx is not None:
+            o = ops.scatter_rows_(lay.o_full, lay.gather_idx, o)
+        return fu.push_heads(o, per)
 
 
 @dataclass
@@ -205,6 +231,9 @@ class JointLayout:
     cu: torch.Tensor | None = None
     max_len: int = 0
     gather_idx: torch.Tensor | None = None
+    fused: object | None = None         # FusedUlysses context when the exchanges are done by the kernels
+    cs_full: torch.Tensor | None = None  # rotary table of every token of every rank, in gathered row order
+    o_full: torch.Tensor | None = None   # zeroed [sp * rows, own] scratch for the scattered attention output
 
     @property
     def per_sample(self) -> int:
@@ -248,12 +277,13 @@ def ulysses_attention(qkv: torch.Tensor, H: int, d: int, lay: JointLayout, group
     # sample-major full sequences: [B, P, per_sample, ...]; padded text rows sit at known places and are masked
     # out by gathering only valid rows
     full = recv.permute(1, 0, 2, 3).reshape(lay.batch * P * lay.per_sample, 3 * Hl * d)
-    packed = ops.gather_rows(full, lay.gather_idx)
+    packed = full if lay.gather_idx is None else ops.gather_rows(full, lay.gather_idx)
     T = packed.shape[0]
     q, k, v = (packed[:, i * Hl * d:(i + 1) * Hl * d].view(T, Hl, d) for i in range(3))
-    o = ops.attention_varlen(q, k, v, lay.cu, lay.cu, lay.max_len).view(T, Hl * d)
-    o_full = torch.zeros((lay.batch * P * lay.per_sample, Hl * d), device=qkv.device, dtype=qkv.dtype)
-    ops.scatter_rows_(o_full, lay.gather_idx, o)
+    o_full = ops.attention_varlen(q, k, v, lay.cu, lay.cu, lay.max_len).view(T, Hl * d)
+    if lay.gather_idx is not None:
+        o_full = ops.scatter_rows_(torch.zeros((lay.batch * P * lay.per_sample, Hl * d), device=qkv.device, dtype=qkv.dtype),
+                                   lay.gather_idx, o_full)
     back = o_full.view(lay.batch, P, lay.per_sample, Hl * d).permute(1, 0, 2, 3).contiguous()
     out = group.all_to_all(back.view(P * R, Hl * d)).view(P, R, Hl * d)
     return out.permute(1, 0, 2).reshape(R, H * d)
@@ -279,6 +309,8 @@ class QwenImageDiT(nn.Module):
         self.norm_out_mod = Linear(D, 2 * D, device=device)
         self.proj_out = Linear(D, cfg.patch_size * cfg.patch_size * cfg.out_channels, device=device)
         self.rope = RopeTable(cfg)
+        self.fused_exchange = True  # sequence parallel: let the kernels do the exchanges when peer memory is there
+        self._fused = None
 
     @property
     def device(self) -> torch.device:
@@ -290,7 +322,7 @@ class QwenImageDiT(nn.Module):
 
     def make_layout(self, batch: int, txt_len: list[int], n_txt_pad: int, grid_hw: tuple[int, int]) -> JointLayout:
         """Precompute rotary tables, attention boundaries and (sequence parallel) gather indices."""
-        dev = self.device
+        dev, cfg = self.device, self.cfg
         h, w = grid_hw
         P, r = self.group.size, self.group.rank
         n_img_full = h * w
@@ -302,9 +334,10 @@ class QwenImageDiT(nn.Module):
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
         lay = JointLayout(batch, n_txt, n_img, list(txt_len), t(cs_txt), t(cs_img), P, r)
         per = n_txt + n_img
-        if P == 1 and all(n == n_txt_pad for n in txt_len):
-            lay.cu = t(np.arange(batch + 1, dtype=np.int32) * per)
-            lay.max_len = per
+        if all(n == n_txt_pad for n in txt_len):
+            # no padding: a sample's rows are contiguous whatever the rank order inside (attention is not causal)
+            lay.cu = t(np.arange(batch + 1, dtype=np.int32) * per * P)
+            lay.max_len = per * P
         else:
             idx, cu = [], [0]
             for b in range(batch):
@@ -320,6 +353,19 @@ class QwenImageDiT(nn.Module):
             lay.gather_idx = t(np.asarray(idx, dtype=np.int32))
             lay.cu = t(np.asarray(cu, dtype=np.int32))
             lay.max_len = int(np.diff(cu).max())
+        own = (cfg.num_attention_heads // P) * cfg.attention_head_dim
+        if P > 1 and self.fused_exchange and self.group.fabric is not None and dev.type == "cuda" and own % 128 == 0:
+            from ..parallel.fused import FusedUlysses
+
+            if self._fused is None or self._fused.cap < lay.rows:
+                self._fused = FusedUlysses(self.group, cfg.inner_dim, cfg.num_attention_heads, cfg.attention_head_dim, lay.rows)
+            lay.fused = self._fused
+            full_txt, full_img = self.rope.text(n_txt_pad, h, w), self.rope.image(1, h, w)
+            seg = np.concatenate([np.concatenate([full_txt[p * n_txt:(p + 1) * n_txt], full_img[p * n_img:(p + 1) * n_img]])
+                                  for p in range(P)])
+            lay.cs_full = t(np.tile(seg, (batch, 1, 1)))
+            if lay.gather_idx is not None:
+                lay.o_full = torch.zeros((P * lay.rows, own), device=dev, dtype=self.dtype)
         return lay
 
     @torch.inference_mode()
@@ -333,6 +379,8 @@ class QwenImageDiT(nn.Module):
         temb_act = ops.act_mul(torch.cat([temb, torch.ones_like(temb)], dim=-1), "silu")  # silu(temb)
         img = self.img_in(latents)
         txt = self.txt_in(self.txt_norm(prompt))
+        if lay.fused is not None:
+            lay.fused.begin_pass()
         for blk in self.blocks:
             img, txt = blk(img, txt, temb_act, lay)
         mod = self.norm_out_mod(temb_act)  # [B, 2D] = scale | shift

@@ -53,7 +53,10 @@ class SiglipVisionTower(nn.Module):
         super().__init__()
         self.cfg = cfg
         H, p = cfg.hidden_size, cfg.patch_size
-        self.patch_embed = Linear(cfg.num_channels * p * p, H, bias=True, device=device)
+        self.k_raw = cfg.num_channels * p * p
+        self.k_pad = (-self.k_raw) % 8   # TMA rows must be multiples of 16 bytes: 3*14*14 = 588 -> 592 zero-padded columns
+        self.patch_embed = Linear(self.k_raw + self.k_pad, H, bias=True, device=device)
+        self.patch_embed.weight.data[:, self.k_raw:].zero_()
         self.pos_embed = _param(cfg.num_patches, H, device=device, dtype=torch.bfloat16)
         spec = BlockSpec(H, cfg.num_attention_heads, cfg.intermediate_size, norm="layer", eps=cfg.layer_norm_eps,
                          act=HF_ACT[cfg.hidden_act])
@@ -68,6 +71,8 @@ class SiglipVisionTower(nn.Module):
         N = g * g
         x = pixel_values.to(self.patch_embed.weight.dtype).view(B, C, g, p, g, p).permute(0, 2, 4, 1, 3, 5).reshape(B * N, C * p * p)
         pos = self.pos_embed.unsqueeze(0).expand(B, N, -1).reshape(B * N, -1)
+        if self.k_pad:
+            x = F.pad(x, (0, self.k_pad))
         x = self.patch_embed(x.contiguous(), residual=pos.contiguous())
         cu = torch.arange(B + 1, device=x.device, dtype=torch.int32) * N
         for layer in self.layers:
@@ -83,7 +88,10 @@ class SiglipVisionTower(nn.Module):
             p = name.split(".")
             leaf = p[-1]
             if name.startswith("embeddings.patch_embedding."):
-                self.patch_embed.load(**{leaf: t.reshape(t.shape[0], -1) if leaf == "weight" else t})
+                if leaf == "weight":
+                    self.patch_embed.weight.data[:, : self.k_raw].copy_(t.reshape(t.shape[0], -1))
+                else:
+                    self.patch_embed.load(bias=t)
             elif name == "embeddings.position_embedding.weight":
                 self.pos_embed.data.copy_(t)
             elif p[0] == "encoder" and p[1] == "layers":

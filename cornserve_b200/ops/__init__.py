@@ -528,18 +528,27 @@ def l2_flush(buf: torch.Tensor, value: int = 0) -> None:
 # --------------------------------------------------------------------------------------------
 # generator models: per-head norm + rotary, soft-max, convolutions as tap gather + tcgen05 GEMM
 # --------------------------------------------------------------------------------------------
-def head_norm_rope_(x: torch.Tensor, w: torch.Tensor | None, eps: float, cs: torch.Tensor | None) -> torch.Tensor:
+def head_norm_rope_(x: torch.Tensor, w: torch.Tensor | None, eps: float, cs: torch.Tensor | None, *,
+                    w2: torch.Tensor | None = None, seg: int = 0, n_first: int = 0) -> torch.Tensor:
     """In place on ``x`` = ``[T, heads, d]`` (token-strided view is fine): RMSNorm over ``d`` with weight
-    ``w`` (skipped when ``None``), then rotate-half RoPE with ``cs`` = ``[T, 2, d/2]`` (skipped when ``None``)."""
+    ``w`` (skipped when ``None``), then rotate-half RoPE with ``cs`` = ``[T, 2, d/2]`` (skipped when ``None``).
+    With ``w2``, rows whose index inside a segment of ``seg`` rows is ``>= n_first`` are normalised with ``w2``
+    (two token streams interleaved segment by segment)."""
     T, heads, d = x.shape
     if not x.is_cuda:
-        x.copy_(reference.head_norm_rope(x, w, eps, cs))
+        if w2 is None:
+            x.copy_(reference.head_norm_rope(x, w, eps, cs))
+        else:
+            first = (torch.arange(T, device=x.device) % seg) < n_first
+            a = reference.head_norm_rope(x, w, eps, cs)
+            b = reference.head_norm_rope(x, w2, eps, cs)
+            x.copy_(torch.where(first[:, None, None], a, b))
         return x
     assert x.stride(2) == 1 and x.stride(1) == d and x.dtype == torch.bfloat16
     assert cs is None or (cs.dtype == torch.float32 and cs.is_contiguous() and cs.shape[-1] * 2 == d)
     lib = _lib.load()
-    _chk(lib.cs_head_norm_rope(x.data_ptr(), x.stride(0), T, heads, d, _ptr(w), float(eps), _ptr(cs), _stream()),
-         "cs_head_norm_rope")
+    _chk(lib.cs_head_norm_rope(x.data_ptr(), x.stride(0), T, heads, d, _ptr(w), float(eps), _ptr(cs), _ptr(w2), seg, n_first,
+                               _stream()), "cs_head_norm_rope")
     _count()
     return x
 

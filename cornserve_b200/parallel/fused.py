@@ -197,3 +197,93 @@ class FusedEncoderTP:
         if rc != 0:
             raise RuntimeError(f"cs_gemm_bf16_tp (push) failed with code {rc}")
         _count()
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Ulysses sequence parallelism for the diffusion transformer without library all-to-all
+# ------------------------------------------------------------------------------------------------------------
+_lib.register_signature("cs_gemm_bf16_a2a", [P, L, P, L, P, I, I, I, I, I, P, P, L, I, I, I, I, I, I, P], I)
+_lib.register_signature("cs_a2a_push_heads", [P, L, I, I, I, I, I, P, L, P, P, P], I)
+_lib.register_signature("cs_wait_flag", [P, c_uint, P], I)
+
+
+class FusedUlysses:
+    """Token shards outside attention, head shards inside it, with the exchanges done by the kernels themselves:
+
+    * the q|k|v projection's epilogue stores every 128-column head tile straight into the buffer of the rank that
+      owns the head (:meth:`qkv_scatter`), so the "tokens -> heads" all-to-all is the GEMM's store;
+    * after attention one copy kernel returns every rank's head slice of every token to the token's owner
+      (:meth:`push_heads`), landing in the operand buffer of the output projection;
+    * consumers are ordered behind the peers' stores by one-thread wait kernels (bounded) on arrival counters.
+
+    ``begin_pass`` (once per denoiser forward) clears the counters and meets the peers once.
+    """
+
+    def __init__(self, group: ParallelGroup, hidden: int, heads: int, head_dim: int, max_local_rows: int):
+        if group.fabric is None:
+            raise RuntimeError("FusedUlysses needs the peer-memory fabric")
+        self.group, self.D, self.H, self.d = group, hidden, heads, head_dim
+        Pn = group.size
+        self.Hl = heads // Pn
+        self.own = self.Hl * head_dim
+        if self.own % 128 or hidden % 128:
+            raise ValueError("head slices must be multiples of 128 columns")
+        self.cap = max_local_rows
+        fab: Fabric = group.fabric
+        self.qkv = fab.alloc(Pn * max_local_rows * 3 * self.own, torch.bfloat16, zero=False)
+        self.qkv_flag = fab.alloc(4, torch.int32)
+        self.o = fab.alloc(max_local_rows * hidden, torch.bfloat16, zero=False)
+        self.o_flag = fab.alloc(4, torch.int32)
+        self._qkv_ptr, self._qkv_fptr = self.qkv.ptr_array(), self.qkv_flag.ptr_array()
+        self._o_ptr, self._o_fptr = self.o.ptr_array(), self.o_flag.ptr_array()
+        self.done = torch.zeros(1, device=group.device, dtype=torch.int32)
+        self._sync = torch.zeros(1, device=group.device, dtype=torch.float32)
+        self.qkv_expected = 0
+        self.o_expected = 0
+
+    def begin_pass(self) -> None:
+        self.qkv_flag.local.zero_()
+        self.o_flag.local.zero_()
+        dist.all_reduce(self._sync, group=self.group.group)
+        self.qkv_expected = 0
+        self.o_expected = 0
+
+    def qkv_scatter(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, row0: int, run: int, stride: int,
+                    seg: int) -> None:
+        """``x w.T + bias`` with ``w`` = ``[3D, D]``, scattered by head owner.  Row ``m`` of ``x`` is row
+        ``row0 + (m // run) * stride + m % run`` of this rank's token order (one stream of every sample in one call);
+        ``seg`` = this rank's rows per sample."""
+        g = self.group
+        M, K = x.shape
+        lib = _lib.load()
+        rc = lib.cs_gemm_bf16_a2a(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), M, 3 * self.D, K, g.size, g.rank,
+                                  ctypes.cast(self._qkv_ptr, c_void_p), ctypes.cast(self._qkv_fptr, c_void_p), 3 * self.own,
+                                  self.D, self.own, seg, row0, run, stride, _stream())
+        if rc != 0:
+            raise RuntimeError(f"cs_gemm_bf16_a2a failed with code {rc}")
+        _count()
+        # every rank makes the same calls: each delivers tiles_m x (3 * own / 128) tiles to every destination
+        self.qkv_expected += g.size * (-(-M // 128)) * (3 * self.own // 128)
+
+    def gathered_qkv(self, rows_total: int) -> torch.Tensor:
+        """Waits for all ranks' tiles, then returns ``[rows_total, 3 * own]`` (this rank's heads, every token)."""
+        lib = _lib.load()
+        lib.cs_wait_flag(self.qkv_flag.local.data_ptr(), self.qkv_expected, _stream())
+        _count()
+        return self.qkv.local[: rows_total * 3 * self.own].view(rows_total, 3 * self.own)
+
+    def push_heads(self, o_full: torch.Tensor, seg: int) -> torch.Tensor:
+        """``o_full`` = ``[world * rows_local, own]`` (every token, this rank's heads) -> ``[rows_local, D]`` with all heads."""
+        g = self.group
+        rows_total = o_full.shape[0]
+        lib = _lib.load()
+        rc = lib.cs_a2a_push_heads(o_full.data_ptr(), o_full.stride(0), rows_total, self.own, g.size, g.rank, seg,
+                                   ctypes.cast(self._o_ptr, c_void_p), self.D, ctypes.cast(self._o_fptr, c_void_p),
+                                   self.done.data_ptr(), _stream())
+        if rc != 0:
+            raise RuntimeError(f"cs_a2a_push_heads failed with code {rc}")
+        self.o_expected += g.size
+        lib.cs_wait_flag(self.o_flag.local.data_ptr(), self.o_expected, _stream())
+        _count(2)
+        rows_local = rows_total // g.size
+        return self.o.local[: rows_local * self.D].view(rows_local, self.D)

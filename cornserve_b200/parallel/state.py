@@ -44,8 +44,9 @@ class ParallelGroup:
         if self.size == 1:
             return x
         x = x.contiguous()
-        out = torch.empty((self.size, *x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x, group=self.group)
+        flat = torch.empty((self.size * x.shape[0], *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x, group=self.group)  # the concatenated form works on NCCL and gloo alike
+        out = flat.view(self.size, *x.shape)
         if dim < 0:
             dim += x.dim()
         out = out.movedim(0, dim)

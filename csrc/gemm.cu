@@ -53,6 +53,12 @@ struct GemmParams {
   unsigned* push_flags[8];     // per owner: one arrival counter per 128-row block of its shard
   int push_world, push_rank, rows_per_rank;
   long long push_ld;
+  // push_mode 2 (all-to-all of heads, Ulysses): a tile of output columns goes to the rank that owns those heads.
+  // Columns are [part][D] (q | k | v); within a part, rank o owns columns [o*own, (o+1)*own).  Rows are this rank's
+  // tokens: row r lands at ((r0+r)/seg)*seg*world + rank*seg + (r0+r)%seg of the owner's [world*rows, parts*own] buffer.
+  int push_mode;             // 1 = by row owner (reduce-scatter), 2 = by column owner
+  int a2a_part_cols, a2a_own_cols, a2a_seg, a2a_row0;
+  int a2a_run, a2a_stride;   // input row m sits at row a2a_row0 + (m / run) * stride + m % run of this rank's token order
 };
 
 constexpr uint64_t kFlagSpinCheck = 0x3f;
@@ -405,16 +411,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         constexpr int LPR = BN_OUT / 8;               // lanes per row (32 for 256 columns, 16 for 128)
         constexpr int RPI = 32 / LPR;                 // rows per store instruction
-        const int owner = (tm * BM) / p.rows_per_rank;
-        const long long slot_row0 = static_cast<long long>(p.push_rank) * p.rows_per_rank + (tm * BM - owner * p.rows_per_rank);
         const int cc = lane % LPR;
         const bool col_ok = n0 + cc * 8 < p.N;
+        int owner;
+        if (p.push_mode == 2) {
+          const int part = n0 / p.a2a_part_cols, within = n0 - part * p.a2a_part_cols;
+          owner = within / p.a2a_own_cols;
+          const int dcol = part * p.a2a_own_cols + (within - owner * p.a2a_own_cols) + cc * 8;
 #pragma unroll 4
-        for (int r0 = 0; r0 < 32; r0 += RPI) {
-          const int rr = q * 32 + r0 + lane / LPR;    // row within the tile
-          if (col_ok && tm * BM + rr < p.M) {
-            const uint4 w = *reinterpret_cast<const uint4*>(stg_base + rr * STG_PITCH + cc * 16);
-            *reinterpret_cast<uint4*>(p.push_dst[owner] + (slot_row0 + rr) * p.push_ld + n0 + cc * 8) = w;
+          for (int r0 = 0; r0 < 32; r0 += RPI) {
+            const int rr = q * 32 + r0 + lane / LPR;    // row within the tile
+            if (col_ok && tm * BM + rr < p.M) {
+              const int mrow = tm * BM + rr;             // row in this rank's token order: runs of a2a_run rows
+              const int lr = p.a2a_row0 + (mrow / p.a2a_run) * p.a2a_stride + mrow % p.a2a_run;
+              const long long drow = static_cast<long long>(lr / p.a2a_seg) * p.a2a_seg * p.push_world +
+                                     static_cast<long long>(p.push_rank) * p.a2a_seg + lr % p.a2a_seg;
+              const uint4 w = *reinterpret_cast<const uint4*>(stg_base + rr * STG_PITCH + cc * 16);
+              *reinterpret_cast<uint4*>(p.push_dst[owner] + drow * p.push_ld + dcol) = w;
+            }
+          }
+        } else {
+          owner = (tm * BM) / p.rows_per_rank;
+          const long long slot_row0 = static_cast<long long>(p.push_rank) * p.rows_per_rank + (tm * BM - owner * p.rows_per_rank);
+#pragma unroll 4
+          for (int r0 = 0; r0 < 32; r0 += RPI) {
+            const int rr = q * 32 + r0 + lane / LPR;    // row within the tile
+            if (col_ok && tm * BM + rr < p.M) {
+              const uint4 w = *reinterpret_cast<const uint4*>(stg_base + rr * STG_PITCH + cc * 16);
+              *reinterpret_cast<uint4*>(p.push_dst[owner] + (slot_row0 + rr) * p.push_ld + n0 + cc * 8) = w;
+            }
           }
         }
         // The last of the four epilogue warps to finish the tile tells the owner of the rows (one system-scope
@@ -428,7 +453,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (prev == 3) {
             push_cnt[par] = 0;
             __threadfence_block();
-            const int blk = (tm * BM - owner * p.rows_per_rank) / BM;
+            const int blk = p.push_mode == 2 ? 0 : (tm * BM - owner * p.rows_per_rank) / BM;
             asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push_flags[owner] + blk) : "memory");
           }
         }
@@ -578,6 +603,7 @@ CS_API int cs_gemm_bf16_tp(const void* A, long long lda, const void* W, long lon
   p.m_rot = ((m_rot % tiles_m) + tiles_m) % tiles_m;
   p.push_world = push_world; p.push_rank = push_rank; p.rows_per_rank = rows_per_rank > 0 ? rows_per_rank : BM;
   p.push_ld = push_ld;
+  p.push_mode = 1;
   for (int i = 0; i < push_world; ++i) {
     p.push_dst[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(push_dst[i]));
     p.push_flags[i] = reinterpret_cast<unsigned*>(const_cast<void*>(push_flags[i]));
@@ -598,4 +624,40 @@ CS_API int cs_gemm_bf16_tp(const void* A, long long lda, const void* W, long lon
     case 128: return launch<128, false, true>(tmA, tmB, p, stream);
     default: return -4;
   }
+}
+
+// Column-parallel projection whose output leaves as an all-to-all (Ulysses sequence parallelism): this rank holds
+// `M` token rows and all `parts * part_cols` output columns (q | k | v over all heads); the column tile of heads
+// [o*own_cols, (o+1)*own_cols) of every part goes, from the epilogue, to rank o's buffer [world * rows, parts*own_cols]
+// at row ((row0+r)/seg)*seg*world + rank*seg + (row0+r)%seg.  One arrival per tile on `flag_ptrs[o][0]`.
+// Tiles are 128 columns wide: own_cols and part_cols must be multiples of 128.  M >= 128.
+CS_API int cs_gemm_bf16_a2a(const void* A, long long lda, const void* W, long long ldw, const void* bias, int M, int N, int K,
+                            int world, int rank, const void* const* dst_ptrs, const void* const* flag_ptrs, long long dst_ld,
+                            int part_cols, int own_cols, int seg, int row0, int run, int run_stride, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (lda & 7) || (ldw & 7) || world < 1 || world > 8 || run <= 0 || (own_cols % 128) || (part_cols % 128) ||
+      (N % part_cols) || seg <= 0 || (dst_ld & 7))
+    return -1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.gate_rpb = 1;
+  p.up_row_offset = N;
+  p.err = cs_error_word();
+  p.a_rows = M >= BM ? BM : ((M + 7) & ~7);
+  p.a_bytes = p.a_rows * BK * 2;
+  p.a_chunk = BM; p.a_total = M;
+  p.push_world = world; p.push_rank = rank; p.rows_per_rank = BM; p.push_ld = dst_ld;
+  p.push_mode = 2;
+  p.a2a_part_cols = part_cols; p.a2a_own_cols = own_cols; p.a2a_seg = seg; p.a2a_row0 = row0;
+  p.a2a_run = run; p.a2a_stride = run_stride;
+  for (int i = 0; i < world; ++i) {
+    p.push_dst[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dst_ptrs[i]));
+    p.push_flags[i] = reinterpret_cast<unsigned*>(const_cast<void*>(flag_ptrs[i]));
+  }
+  CUtensorMap tmA, tmB;
+  if (cs_encode_tmap_2d(&tmA, A, K, M, lda * 2, BK, p.a_rows, 2, 1) != 0) return -2;
+  if (cs_encode_tmap_2d(&tmB, W, K, N, ldw * 2, BK, 128, 2, 1) != 0) return -3;
+  return launch<128, false, true>(tmA, tmB, p, stream);
 }

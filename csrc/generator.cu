@@ -33,15 +33,19 @@ inline unsigned blocks_for(long long n, int per) { return static_cast<unsigned>(
 
 // ---------------------------------------------------------------------------------------
 // Per-head RMSNorm followed by rotate-half RoPE, in place.  x: [T, heads, d] with token stride ldx;
-// w: [d] bf16 or null (no norm); cs: [T, 2, d/2] fp32 or null (no rotation).  One warp per (token, head);
+// w: [d] bf16 or null (no norm); cs: [T, 2, d/2] fp32 or null (no rotation); optional second weight w2 for rows
+// whose index within a segment of `seg` rows is >= n_first.  One warp per (token, head);
 // lane l owns the pairs (l + 32 j, l + 32 j + d/2).  d is a multiple of 64, d <= 256.
 // ---------------------------------------------------------------------------------------
 __global__ void head_norm_rope_kernel(__nv_bfloat16* x, long long ldx, long long T, int heads, int d,
-                                      const __nv_bfloat16* w, float eps, const float* cs) {
+                                      const __nv_bfloat16* w, float eps, const float* cs, const __nv_bfloat16* w2,
+                                      int seg, int n_first) {
   const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (item >= T * heads) return;
   const long long t = item / heads;
+  // rows come in segments of `seg`; the first `n_first` rows of a segment use w, the others w2 (two token streams)
+  if (w2 != nullptr && static_cast<int>(t % seg) >= n_first) w = w2;
   const int h = static_cast<int>(item % heads);
   const int half = d >> 1;
   const int per = half >> 5;  // pairs per lane (1..4)
@@ -235,12 +239,13 @@ __global__ void to_rgb8_kernel(const __nv_bfloat16* x, long long ldx, unsigned c
 }  // namespace
 
 CS_API int cs_head_norm_rope(void* x, long long ldx, long long T, int heads, int d, const void* w, float eps,
-                             const void* cs, void* stream) {
+                             const void* cs, const void* w2, int seg, int n_first, void* stream) {
   if (T <= 0 || heads <= 0) return 0;
-  if ((d & 63) || d > 256) return -1;
+  if ((d & 63) || d > 256 || (w2 != nullptr && (w == nullptr || seg <= 0))) return -1;
   const long long warps = T * heads;
   head_norm_rope_kernel<<<blocks_for(warps, 8), 256, 0, (cudaStream_t)stream>>>(
-      (__nv_bfloat16*)x, ldx, T, heads, d, (const __nv_bfloat16*)w, eps, (const float*)cs);
+      (__nv_bfloat16*)x, ldx, T, heads, d, (const __nv_bfloat16*)w, eps, (const float*)cs, (const __nv_bfloat16*)w2, seg,
+      n_first);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 

@@ -184,3 +184,89 @@ CS_API int cs_tp_reduce_norm_push(int rows, int H, int world, int rank, int rows
   tp_reduce_norm_push_kernel<<<(rows + TP_ROWS_PER_CTA - 1) / TP_ROWS_PER_CTA, 256, 0, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Ulysses, the way back: after attention every rank holds ALL tokens for ITS heads, `src` = [world * rows, cols]
+// in the order ((b, source rank, row in segment)); token rows return to the rank they came from, landing in
+// columns [rank*cols, (rank+1)*cols) of that rank's [rows, world*cols] operand of the output projection.
+// The CTA that finishes last publishes the whole transfer with one release per destination (`flags[o][0] += 1`).
+// `done` is a local counter that must be zero before the call (the kernel leaves it at zero).
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+struct A2APushParams {
+  const __nv_bfloat16* src; long long lds;
+  int rows_total, vec_per_row, world, rank, seg;
+  __nv_bfloat16* dst[TP_MAX_WORLD]; long long ldd;
+  unsigned* flags[TP_MAX_WORLD];
+  unsigned* done;
+};
+
+__global__ void __launch_bounds__(256) a2a_push_heads_kernel(const A2APushParams p) {
+  const long long total = static_cast<long long>(p.rows_total) * p.vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % p.vec_per_row);
+    const long long r = i / p.vec_per_row;
+    const int in_seg = static_cast<int>(r % p.seg);
+    const int owner = static_cast<int>((r / p.seg) % p.world);
+    const long long b = r / (static_cast<long long>(p.seg) * p.world);
+    const long long drow = b * p.seg + in_seg;
+    const uint4 w = *reinterpret_cast<const uint4*>(p.src + r * p.lds + v * 8);
+    *reinterpret_cast<uint4*>(p.dst[owner] + drow * p.ldd + static_cast<long long>(p.rank) * p.vec_per_row * 8 + v * 8) = w;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(p.done, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done = 0;
+      __threadfence();
+      for (int o = 0; o < p.world; ++o)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.flags[o]) : "memory");
+    }
+  }
+}
+
+// One thread waits (bounded) until *flag >= target: orders later kernels of the stream after the peers' pushes.
+__global__ void wait_flag_kernel(const unsigned* flag, unsigned target, int* err) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= target) return;
+    if ((spin & 0x3f) == 0x3f) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > CS_WAIT_LIMIT_NS) { cs_set_error(err, CS_ERR_TIMEOUT_PEER); return; }
+    }
+  }
+}
+}  // namespace
+
+CS_API int cs_a2a_push_heads(const void* src, long long lds, int rows_total, int cols, int world, int rank, int seg,
+                             const void* const* dst_ptrs, long long ldd, const void* const* flag_ptrs, void* done,
+                             void* stream) {
+  if (rows_total <= 0) return 0;
+  if ((cols & 7) || (lds & 7) || (ldd & 7) || world < 1 || world > TP_MAX_WORLD || seg <= 0 || rows_total % (seg * world)) return -1;
+  A2APushParams p{};
+  p.src = (const __nv_bfloat16*)src; p.lds = lds;
+  p.rows_total = rows_total; p.vec_per_row = cols >> 3; p.world = world; p.rank = rank; p.seg = seg;
+  p.ldd = ldd;
+  for (int i = 0; i < world; ++i) {
+    p.dst[i] = (__nv_bfloat16*)const_cast<void*>(dst_ptrs[i]);
+    p.flags[i] = (unsigned*)const_cast<void*>(flag_ptrs[i]);
+  }
+  p.done = (unsigned*)done;
+  const long long total = static_cast<long long>(rows_total) * p.vec_per_row;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  a2a_push_heads_kernel<<<static_cast<unsigned>(blocks), 256, 0, (cudaStream_t)stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+CS_API int cs_wait_flag(const void* flag, unsigned target, void* stream) {
+  wait_flag_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((const unsigned*)flag, target, cs_error_word());
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}

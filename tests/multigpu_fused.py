@@ -213,6 +213,92 @@ def tp_vision_tower(g):
         print(f"ViT depth {cfg.depth}, 4 images, TP={g.size}: fused {t_fused:.2f} ms   NCCL path {t_nccl:.2f} ms   one GPU {t_one:.2f} ms", flush=True)
 
 
+def sp_diffusion_transformer(g):
+    """Sequence-parallel MMDiT: the kernel-driven exchanges (q|k|v projection that stores head tiles at their owners,
+    peer-store return of the attention output) against one GPU and against the library all-to-all path; timed."""
+    from cornserve_b200.models.qwen_image import QwenImageDiT, QwenImageDiTConfig
+    from cornserve_b200.parallel.state import single_group
+
+    rank, P = g.rank, g.size
+    dev = g.device
+    cfg = QwenImageDiTConfig(in_channels=64, out_channels=16, num_layers=2, attention_head_dim=128, num_attention_heads=8,
+                             joint_attention_dim=256, axes_dims_rope=(16, 56, 56))
+    D, J = cfg.inner_dim, cfg.joint_attention_dim
+    gen = torch.Generator().manual_seed(7)
+    r = lambda *s, std=0.03: (torch.randn(*s, generator=gen) * std).bfloat16()  # noqa: E731
+    w = {"txt_norm.weight": 1 + r(J), "img_in.weight": r(D, cfg.in_channels, std=0.2), "img_in.bias": r(D),
+         "txt_in.weight": r(D, J, std=0.1), "txt_in.bias": r(D),
+         "time_text_embed.timestep_embedder.linear_1.weight": r(D, 256), "time_text_embed.timestep_embedder.linear_1.bias": r(D),
+         "time_text_embed.timestep_embedder.linear_2.weight": r(D, D), "time_text_embed.timestep_embedder.linear_2.bias": r(D),
+         "norm_out.linear.weight": r(2 * D, D), "norm_out.linear.bias": r(2 * D),
+         "proj_out.weight": r(cfg.patch_size ** 2 * cfg.out_channels, D), "proj_out.bias": r(cfg.patch_size ** 2 * cfg.out_channels)}
+    for i in range(cfg.num_layers):
+        p = f"transformer_blocks.{i}."
+        for s in ("img", "txt"):
+            w[p + f"{s}_mod.1.weight"], w[p + f"{s}_mod.1.bias"] = r(6 * D, D), r(6 * D, std=0.2)
+            w[p + f"{s}_mlp.net.0.proj.weight"], w[p + f"{s}_mlp.net.0.proj.bias"] = r(4 * D, D), r(4 * D)
+            w[p + f"{s}_mlp.net.2.weight"], w[p + f"{s}_mlp.net.2.bias"] = r(D, 4 * D), r(D)
+        for n in ("to_q", "to_k", "to_v", "add_q_proj", "add_k_proj", "add_v_proj", "to_out.0", "to_add_out"):
+            w[p + f"attn.{n}.weight"], w[p + f"attn.{n}.bias"] = r(D, D), r(D)
+        for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+            w[p + f"attn.{n}.weight"] = 1 + r(cfg.attention_head_dim, std=0.2)
+    sp = QwenImageDiT(cfg, group=g, device=dev)
+    sp.load_weights(w.items())
+    lib = QwenImageDiT(cfg, group=g, device=dev)
+    lib.load_weights(w.items())
+    lib.fused_exchange = False
+    one = QwenImageDiT(cfg, group=single_group(dev), device=dev)
+    one.load_weights(w.items())
+
+    def shard(x, B, n):  # [B*n, C] full -> this rank's [B*(n/P), C]
+        return x.view(B, P, n // P, -1)[:, rank].reshape(B * (n // P), -1).contiguous()
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    for B, (h, wd), n_txt, txt_len in ((2, (32, 32), 64, [64, 64]), (2, (64, 64), 128, [128, 77]), (1, (16, 24), 32, [19])):
+        n_img = h * wd
+        lat = torch.randn(B * n_img, cfg.in_channels, generator=gen).bfloat16().to(dev)
+        prompt = torch.randn(B * n_txt, J, generator=gen).bfloat16().to(dev)
+        t = torch.linspace(0.9, 0.3, B).to(dev)
+        lay1 = one.make_layout(B, txt_len, n_txt, (h, wd))
+        want = one(lat, prompt, t, lay1)
+        outs = {}
+        for name, model in (("fused", sp), ("library", lib)):
+            lay = model.make_layout(B, txt_len, n_txt, (h, wd))
+            assert (lay.fused is not None) == (name == "fused")
+            got = model(shard(lat, B, n_img), shard(prompt, B, n_txt), t, lay)
+            torch.cuda.synchronize()
+            ops.check_error(f"sequence-parallel DiT ({name})")
+            outs[name] = got
+            cos = torch.nn.functional.cosine_similarity(got.float().flatten(), shard(want, B, n_img).float().flatten(), dim=0).item()
+            assert cos > 0.995, f"{name} sequence-parallel DiT differs from one GPU (cos {cos:.4f}, grid {h}x{wd})"
+        check(f"fused vs library exchange {h}x{wd}", outs["fused"], outs["library"])
+    # timing at a 1024x1024 image (4096 image tokens), 512 prompt tokens, batch 2 (condition + guidance)
+    B, h, wd, n_txt = 2, 64, 64, 512
+    lat = torch.randn(B * h * wd // P, cfg.in_channels, device=dev).bfloat16()
+    prompt = torch.randn(B * n_txt // P, J, device=dev).bfloat16()
+    t = torch.full((B,), 0.5, device=dev)
+    times = {}
+    for name, model in (("fused", sp), ("library", lib)):
+        lay = model.make_layout(B, [n_txt] * B, n_txt, (h, wd))
+        times[name] = timed(lambda: model(lat, prompt, t, lay))
+    ops.check_error("sequence-parallel DiT timing")
+    if rank == 0:
+        print(f"DiT {cfg.num_layers} blocks D={D}, 2x(4096+512) tokens, SP={P}: fused exchange {times['fused']:.3f} ms   "
+              f"NCCL all-to-all {times['library']:.3f} ms", flush=True)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     g = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
@@ -289,6 +375,7 @@ def main():
             print(f"fused GEMM+AR+res+norm M={M} K={K} world={world}: {t_f:.1f} us   cuBLAS+NCCL+eager: {t_b:.1f} us", flush=True)
     tp_llm_matches_single_gpu(g)
     tp_vision_tower(g)
+    sp_diffusion_transformer(g)
     if rank == 0:
         print("MULTIGPU_FUSED_OK", flush=True)
     dist.barrier()

@@ -331,3 +331,55 @@ def test_attention_decode_swapped_operands(Hq, Hkv, ctx, kv_splits):
     o = ops.attention_paged(q, cache, bt, kv_len, cu, 1, causal=True, pack_gqa=True, kv_splits=kv_splits)
     want = ref.attention_paged(q.cpu().float(), cache.cpu().float(), bt.cpu(), kv_len.cpu(), cu.cpu(), 1 / math.sqrt(d), True)
     _close(o, want.to(DEV), 2e-2, 2e-2, f"decode attn Hq={Hq} Hkv={Hkv}")
+
+
+def test_strided_tap_gathers_and_bilinear_embed():
+    torch.manual_seed(16)
+    B, H, W, C = 2, 9, 12, 16
+    x = _rand(B * H * W, C)
+    got, want = ops.im2col3x3(x, B, H, W, stride=2), ref.im2col3x3(x, B, H, W, stride=2)
+    assert got.shape == want.shape == (B * 5 * 6, 9 * C) and torch.equal(got, want)
+    T = 41
+    s = _rand(B * T, C)
+    To = (T - 1) // 2 + 1
+    assert torch.equal(ops.im2col1d(s, B, T, To, 3, -1, stride=2), ref.im2col1d(s, B, T, To, 3, -1, 1, stride=2))
+    table = _rand(36, 64)
+    L = 77
+    idx = torch.randint(0, 36, (4, L), device=DEV, dtype=torch.int32)
+    wgt = torch.rand(4, L, device=DEV)
+    xe = _rand(L, 64)
+    want = (xe.float() + (table.float()[idx.long()] * wgt[:, :, None]).sum(0))
+    ops.bilinear_embed_add_(xe, table, idx, wgt)
+    _close(xe, want, 2e-2, 2e-2, "bilinear embed")
+
+
+@pytest.mark.parametrize("model_id,modality", [("cornserve-b200/tiny-qwen3-vl", "image"), ("cornserve-b200/tiny-qwen3-omni", "audio"),
+                                               ("cornserve-b200/tiny-internvl", "image"), ("cornserve-b200/tiny-llava-onevision", "image")])
+def test_encoder_families_cuda_vs_cpu(model_id, modality, monkeypatch):
+    """The same random weights on the CUDA kernels and on the fp32 reference path give the same embeddings."""
+    import numpy as np
+
+    from cornserve_b200.executors.eric.config import EricConfig, ModelConfig
+    from cornserve_b200.executors.eric.schema import Batch, Modality
+    from cornserve_b200.executors.eric.worker import Worker
+
+    rng = np.random.default_rng(0)
+    if modality == "audio":
+        data = {"raw_audio": [torch.from_numpy(rng.standard_normal(16000 * 2).astype(np.float32) * 0.1)]}
+    else:
+        data = {"raw_images": [torch.from_numpy(rng.integers(0, 256, (70, 120, 3), dtype=np.uint8))]}
+    outs = {}
+    for dev in ("cpu", "cuda"):
+        monkeypatch.setenv("CORNSERVE_DEVICE", dev)
+        monkeypatch.setenv("CORNSERVE_SEED", "0")
+        w = Worker(EricConfig(model=ModelConfig(id=model_id, modality=Modality(modality))))
+        if dev == "cuda":
+            w.model.load_state_dict(outs["state"])
+            w.model.bfloat16()
+        else:
+            outs["state"] = {k: v.clone() for k, v in w.model.state_dict().items()}
+        with torch.inference_mode():
+            y = w.model(modality, model_id, w.prepare(Batch(Modality(modality), model_id, ["r"], ["d"], [None], dict(data))))
+        outs[dev] = torch.cat(y).float().cpu()
+    cos = torch.nn.functional.cosine_similarity(outs["cpu"].flatten(), outs["cuda"].flatten(), dim=0).item()
+    assert outs["cpu"].shape == outs["cuda"].shape and cos > 0.98, cos
