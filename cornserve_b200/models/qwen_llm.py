@@ -171,6 +171,12 @@ class SparseMoE(nn.Module):
         from ..parallel import moe
 
         logits = self.router(x, out_dtype=torch.float32)
+        if x.is_cuda and (self.group.size == 1 or self.group.fabric is not None):
+            cfg = self.cfg
+            fm = moe.fused_layer(self.group, cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, cfg.moe_intermediate_size,
+                                 -(-x.shape[0] // self.group.size), cfg.norm_topk_prob)
+            # tensor-parallel ranks hold the same tokens: each routes a slice, the combine kernel fills every rank's output
+            return fm.forward(x, logits, self.w_gate_up, self.w_down, replicated=self.group.size > 1)
         return moe.moe_forward(x, logits, self.w_gate_up, self.w_down, self.cfg.num_experts_per_tok,
                                self.cfg.norm_topk_prob, self.group)
 

@@ -7,6 +7,7 @@
   python -m cornserve_b200.ops.microbench attn-full 16 80 4784 0   # heads, head_dim, length, causal
   python -m cornserve_b200.ops.microbench attn-decode 48 3500      # sequences, context
   python -m cornserve_b200.ops.microbench norm 19136 1280
+  python -m cornserve_b200.ops.microbench moe 128 128 8 2048 768   # tokens, experts, top-k, hidden, expert FFN width
 
 Each line printed gives the time per launch, the achieved rate and the fraction of the measured peak
 (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).  The same
@@ -130,6 +131,18 @@ def main() -> None:
         x, r, w = rnd(rows, H), rnd(rows, H), rnd(H)
         secs = t(lambda: ops.rms_norm(x, w, 1e-6, residual=r))
         report(f"rms_norm+residual {rows}x{H}", secs, 0.0, 2.0 * 4 * rows * H)
+    elif k == "moe":
+        from cornserve_b200.parallel.moe import FusedMoE
+        from cornserve_b200.parallel.state import single_group
+
+        T, E, kk, H, I = (a.args + [128, 128, 8, 2048, 768][len(a.args):])[:5]
+        layer = FusedMoE(single_group(dev), E, kk, H, I, max(T, 1024))
+        x, logits = rnd(T, H), torch.randn(T, E, device=dev, generator=g)
+        wgu, wd = rnd(E, 2 * I, H, std=H ** -0.5), rnd(E, H, I, std=I ** -0.5)
+        secs = t(lambda: layer.forward(x, logits, wgu, wd))
+        touched = min(E, T * kk)  # experts whose weights must be read (upper bound when tokens collide)
+        report(f"moe layer T={T} E={E} top{kk} H={H} I={I} (row tile {layer.tile_rows_for(T)})", secs, 6.0 * T * kk * H * I,
+               2.0 * (touched * 3 * H * I + 2 * T * kk * (H + I) + 2 * T * H))
     else:
         raise SystemExit(f"unknown kernel {k}")
 

@@ -56,9 +56,21 @@ struct GemmParams {
   // push_mode 2 (all-to-all of heads, Ulysses): a tile of output columns goes to the rank that owns those heads.
   // Columns are [part][D] (q | k | v); within a part, rank o owns columns [o*own, (o+1)*own).  Rows are this rank's
   // tokens: row r lands at ((r0+r)/seg)*seg*world + rank*seg + (r0+r)%seg of the owner's [world*rows, parts*own] buffer.
-  int push_mode;             // 1 = by row owner (reduce-scatter), 2 = by column owner
+  int push_mode;             // 1 = by row owner (reduce-scatter), 2 = by column owner, 3 = by per-row table
   int a2a_part_cols, a2a_own_cols, a2a_seg, a2a_row0;
   int a2a_run, a2a_stride;   // input row m sits at row a2a_row0 + (m / run) * stride + m % run of this rank's token order
+  // ---- grouped GEMM (mixture of experts; COMM variant only) ----
+  // A holds the rows of every local expert, each expert's segment padded to a multiple of grp_tile_rows.  Row tile t
+  // covers rows [t * grp_tile_rows, ...) and multiplies with rows [e * grp_w_rows, ...) of W, e = grp_tile_expert[t].
+  // The tables are written on the device by the layout kernel of the same stream (no host round trip).
+  const int* grp_tile_expert;  // null = not grouped
+  const int* grp_tile_valid;   // rows of tile t that hold tokens (the rest is padding)
+  const int* grp_num_tiles;    // device word: row tiles in use
+  int grp_tile_rows, grp_w_rows;
+  // push_mode 3 (expert outputs return to the token owners): A row r goes to row grp_row_meta[r].y of rank
+  // grp_row_meta[r].x; the last CTA to finish bumps every rank's arrival counter once (grp_done counts CTAs).
+  const int2* grp_row_meta;
+  unsigned* grp_done;
 };
 
 constexpr uint64_t kFlagSpinCheck = 0x3f;
@@ -167,7 +179,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int stages = p.stages;
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const bool grouped = COMM && p.grp_tile_expert != nullptr;
+  const int tile_rows = grouped ? p.grp_tile_rows : BM;
+  const int tiles_m = grouped ? *p.grp_num_tiles : (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN_OUT - 1) / BN_OUT;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -212,7 +226,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int tm, tn;
         tile_coords(t, tiles_m, tiles_n, tm, tn);
         if (COMM) tm = (tm + p.m_rot) % tiles_m;
-        const int m0 = tm * BM, n0 = tn * BN_OUT;
+        const int m0 = tm * tile_rows;
+        const int n0 = tn * BN_OUT + (grouped ? p.grp_tile_expert[tm] * p.grp_w_rows : 0);  // row of W
         if (COMM && p.a_flags != nullptr) {
           // the rows of this tile are chunk tm of the gathered operand: wait until all of them have landed
           const int rows = min(p.a_chunk, p.a_total - tm * p.a_chunk);
@@ -278,12 +293,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int tm, tn;
       tile_coords(t, tiles_m, tiles_n, tm, tn);
       if (COMM) tm = (tm + p.m_rot) % tiles_m;
-      const int row = tm * BM + q * 32 + lane;
+      const int row = tm * tile_rows + q * 32 + lane;
       const int n0 = tn * BN_OUT;
+      const int tile_valid = grouped ? p.grp_tile_valid[tm] : BM;
       if (!mbar_wait(&acc_full[acc], acc_phase, abortp, p.err, CS_ERR_TIMEOUT_MMA)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      const bool row_ok = row < p.M;
+      const bool row_ok = grouped ? (q * 32 + lane < tile_valid) : (row < p.M);
       const __nv_bfloat16* gate_row =
           (p.gate != nullptr && row_ok) ? p.gate + static_cast<long long>(row / p.gate_rpb) * p.ldg : nullptr;
 #pragma unroll 1
@@ -413,8 +429,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         constexpr int RPI = 32 / LPR;                 // rows per store instruction
         const int cc = lane % LPR;
         const bool col_ok = n0 + cc * 8 < p.N;
-        int owner;
-        if (p.push_mode == 2) {
+        int owner = 0;
+        if (p.push_mode == 3) {
+#pragma unroll 4
+          for (int r0 = 0; r0 < 32; r0 += RPI) {
+            const int rr = q * 32 + r0 + lane / LPR;    // row within the tile
+            if (col_ok && rr < tile_valid) {
+              const int2 meta = __ldcg(&p.grp_row_meta[tm * tile_rows + rr]);  // written by peers: not through L1
+              const uint4 w = *reinterpret_cast<const uint4*>(stg_base + rr * STG_PITCH + cc * 16);
+              *reinterpret_cast<uint4*>(p.push_dst[meta.x] + static_cast<long long>(meta.y) * p.push_ld + n0 + cc * 8) = w;
+            }
+          }
+        } else if (p.push_mode == 2) {
           const int part = n0 / p.a2a_part_cols, within = n0 - part * p.a2a_part_cols;
           owner = within / p.a2a_own_cols;
           const int dcol = part * p.a2a_own_cols + (within - owner * p.a2a_own_cols) + cc * 8;
@@ -446,7 +472,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // release per tile: such releases are expensive).  The warps meet through a shared-memory counter, not a
         // barrier, so a warp that gave up on a wait cannot strand the others; the owner's wait is bounded too.
         __syncwarp();
-        if (lane == 0) {
+        if (lane == 0 && p.push_mode != 3) {
           __threadfence_block();
           const int par = n_push & 3;  // a warp cannot get four tiles ahead of another (two accumulators)
           const int prev = atomicAdd(&push_cnt[par], 1);
@@ -462,11 +488,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
 
+  if (COMM && p.push_mode == 3) __threadfence();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (COMM && p.push_mode == 3 && threadIdx.x == 0) {
+    // every row of this CTA has left; the last CTA of the grid tells all ranks that this rank's experts are done
+    __threadfence();
+    const unsigned prev = atomicAdd(p.grp_done, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.grp_done = 0;
+      __threadfence();
+      for (int o = 0; o < p.push_world; ++o)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.push_flags[o]) : "memory");
+    }
   }
 }
 
@@ -494,7 +532,8 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaSt
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     attr_done[dev] = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN_OUT - 1) / BN_OUT);
+  const int rows_per_tile = (COMM && p.grp_tile_expert != nullptr) ? p.grp_tile_rows : BM;
+  const int tiles = ((p.M + rows_per_tile - 1) / rows_per_tile) * ((p.N + BN_OUT - 1) / BN_OUT);
   int grid = tiles < cs_num_sms() ? tiles : cs_num_sms();
   if (grid < 1) return 0;
   p.idesc = umma_idesc_bf16(128, BN, 0, 0);
@@ -659,5 +698,50 @@ CS_API int cs_gemm_bf16_a2a(const void* A, long long lda, const void* W, long lo
   CUtensorMap tmA, tmB;
   if (cs_encode_tmap_2d(&tmA, A, K, M, lda * 2, BK, p.a_rows, 2, 1) != 0) return -2;
   if (cs_encode_tmap_2d(&tmB, W, K, N, ldw * 2, BK, 128, 2, 1) != 0) return -3;
+  return launch<128, false, true>(tmA, tmB, p, stream);
+}
+
+// Grouped GEMM over the rows of this rank's experts (see GemmParams::grp_*): C = A W_e^T per row tile, with the SwiGLU
+// epilogue (W_e = [gate; up], 2N rows) or, with push_world > 0, with every valid output row stored at
+// (rank, row) = row_meta[A row] of dst_ptrs and one arrival on every rank's flag when the whole launch is done.
+// M_cap bounds the rows of A (the grid is sized from it; the tiles actually in use are read on the device).
+CS_API int cs_gemm_bf16_grouped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int M_cap,
+                                int N, int K, int swiglu, int experts, int tile_rows, const void* tile_expert,
+                                const void* tile_valid, const void* num_tiles, int push_world, const void* const* dst_ptrs,
+                                const void* const* flag_ptrs, long long push_ld, const void* row_meta, void* done,
+                                void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M_cap <= 0 || N <= 0 || experts <= 0) return 0;
+  if (K <= 0 || (lda & 7) || (ldw & 7) || push_world < 0 || push_world > 8 || tile_rows < 8 || tile_rows > BM || (tile_rows & 7) ||
+      tile_expert == nullptr || tile_valid == nullptr || num_tiles == nullptr || (push_world > 0 && (swiglu || (push_ld & 7))))
+    return -1;
+  GemmParams p{};
+  p.M = M_cap; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.gate_rpb = 1;
+  p.act = swiglu ? ACT_SILU : ACT_NONE;
+  p.up_row_offset = N;
+  p.err = cs_error_word();
+  p.a_rows = tile_rows;
+  p.a_bytes = tile_rows * BK * 2;
+  p.a_chunk = BM; p.a_total = M_cap;
+  p.grp_tile_expert = reinterpret_cast<const int*>(tile_expert);
+  p.grp_tile_valid = reinterpret_cast<const int*>(tile_valid);
+  p.grp_num_tiles = reinterpret_cast<const int*>(num_tiles);
+  p.grp_tile_rows = tile_rows;
+  p.grp_w_rows = swiglu ? 2 * N : N;
+  if (push_world > 0) {
+    p.push_world = push_world; p.push_mode = 3; p.push_ld = push_ld; p.rows_per_rank = BM;
+    p.grp_row_meta = reinterpret_cast<const int2*>(row_meta);
+    p.grp_done = reinterpret_cast<unsigned*>(done);
+    for (int i = 0; i < push_world; ++i) {
+      p.push_dst[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(dst_ptrs[i]));
+      p.push_flags[i] = reinterpret_cast<unsigned*>(const_cast<void*>(flag_ptrs[i]));
+    }
+  }
+  CUtensorMap tmA, tmB;
+  if (cs_encode_tmap_2d(&tmA, A, K, M_cap, lda * 2, BK, tile_rows, 2, 1) != 0) return -2;
+  if (cs_encode_tmap_2d(&tmB, W, K, static_cast<long long>(experts) * p.grp_w_rows, ldw * 2, BK, 128, 2, 1) != 0) return -3;
+  if (swiglu) return launch<256, true, true>(tmA, tmB, p, stream);
   return launch<128, false, true>(tmA, tmB, p, stream);
 }
