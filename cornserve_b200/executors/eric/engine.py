@@ -10,6 +10,7 @@ import queue
 import threading
 import traceback
 
+from ... import ops
 from ...logging import get_logger
 from ...parallel.state import ParallelGroup
 from .config import EricConfig
@@ -55,6 +56,7 @@ class Engine:
         getattr(self.worker, method)(*args)
 
     def _run(self) -> None:
+        ops.bind_thread(self.worker.device)  # a new thread starts on CUDA device 0
         try:
             while True:
                 if not self.scheduler.has_waiting_requests():

@@ -55,7 +55,7 @@ class Worker:
             raise ValueError(f"{model_type} does not encode {config.model.modality}")
         model_cls, cfg_cls = self.entry.load_classes()
         self.model_cfg = cfg_cls.from_hf(hf_cfg)
-        dtype = torch.float32 if (self.device.type == "cpu" or hf_cfg.get("torch_dtype") == "float32") else torch.bfloat16
+        dtype = torch.float32 if self.device.type == "cpu" else torch.bfloat16  # the CUDA kernels are bf16
         torch.manual_seed(int(os.environ.get("CORNSERVE_SEED", "0")))  # reproducible random-weight runs
         kw = {"model_id": config.model.id} if self.entry.adapter_attr else {}
         self.model = model_cls(self.model_cfg, group=self.group, device=self.device, **kw)

@@ -86,6 +86,7 @@ class Engine:
 
     # -- engine thread -----------------------------------------------------------------------------------
     def _run(self) -> None:
+        ops.bind_thread(self.device)  # a new thread starts on CUDA device 0
         try:
             while True:
                 if not self.scheduler.has_waiting_requests():

@@ -15,6 +15,7 @@ from ...services.process import free_port
 from ...sidecar.api import Sidecar
 from ...sidecar.schema import SidecarConfig
 from ...tracing import configure_otel
+from ... import ops
 from ..eric.worker import pick_device
 from .config import GeriConfig
 from .engine import Engine
@@ -31,6 +32,7 @@ def main(argv: list[str] | None = None) -> None:
     group = None
     children: list[subprocess.Popen] = []
     device = pick_device(0)
+    ops.bind_thread(device)  # also for the sidecar client: forwarded tensors are mapped onto the current GPU
     if sp > 1:
         port = free_port()
         for r in range(1, sp):

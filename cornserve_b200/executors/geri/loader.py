@@ -94,7 +94,7 @@ def build_qwen_image(model_id: str, desc: dict, device: torch.device, group: Par
         logger.warning("No checkpoint for %s on this machine: keeping randomly initialised weights", model_id)
     else:
         raise FileNotFoundError(f"No safetensors found for {model_id}")
-    if desc.get("torch_dtype") == "float32" or device.type == "cpu":
+    if device.type == "cpu":  # the CUDA kernels are bf16
         model.dit.float()
         model.vae.float()
     return model

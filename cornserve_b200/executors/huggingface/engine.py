@@ -10,6 +10,7 @@ from collections.abc import AsyncIterator
 
 import torch
 
+from ... import ops
 from ...logging import get_logger
 from .api import HuggingFaceRequest, HuggingFaceResponse, ModelType, Status
 from .config import HuggingFaceConfig
@@ -20,7 +21,7 @@ logger = get_logger(__name__)
 
 class Engine:
     def __init__(self, config: HuggingFaceConfig, device: torch.device):
-        self.config = config
+        self.config, self.device = config, device
         if config.model.model_type == ModelType.QWEN_IMAGE:
             self.model = QwenImageMonolith(config.model.id, device, config.model.text_encoder_id)
         else:
@@ -31,7 +32,11 @@ class Engine:
     async def generate(self, req: HuggingFaceRequest) -> HuggingFaceResponse:
         async with self.lock:
             try:
-                img = await asyncio.to_thread(self.model.generate, req.prompt, req.height, req.width, req.num_inference_steps)
+                def image():
+                    ops.bind_thread(self.device)  # pool threads start on CUDA device 0
+                    return self.model.generate(req.prompt, req.height, req.width, req.num_inference_steps)
+
+                img = await asyncio.to_thread(image)
                 return HuggingFaceResponse(status=Status.SUCCESS, image=img)
             except Exception as e:  # noqa: BLE001
                 logger.exception("image generation failed")
@@ -43,6 +48,7 @@ class Engine:
 
         def work():
             try:
+                ops.bind_thread(self.device)
                 for chunk in self.model.generate(req.messages or [], req.max_completion_tokens or 256, req.ignore_eos,
                                                  bool(req.return_audio)):
                     loop.call_soon_threadsafe(q.put_nowait, HuggingFaceResponse(status=Status.SUCCESS, text_chunk=chunk))

@@ -29,7 +29,7 @@ def _build_llm(model_id: str, device: torch.device, pages: int = 256) -> tuple[L
     hf_cfg = load_config(model_id)
     cfg = LLMConfig.from_hf(hf_cfg)
     llm = QwenLLM(cfg, device=device)
-    if device.type == "cpu" or hf_cfg.get("torch_dtype") == "float32":
+    if device.type == "cpu":  # the CUDA kernels are bf16
         llm = llm.float()
     load_model_weights(llm, model_id, ["model.language_model.", "language_model.", "thinker.model.", "model.", "lm_head.", ""],
                        strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower.", "audio_tower."])

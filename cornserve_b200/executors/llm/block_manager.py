@@ -46,6 +46,14 @@ class BlockManager:
         for p in self._owned.pop(seq_id, []):
             self._free.append(p)
 
+    def detach(self, seq_id: str) -> list[int]:
+        """Give up the bookkeeping of ``seq_id`` without freeing its pages (they are held for a remote reader)."""
+        return self._owned.pop(seq_id, [])
+
+    def release(self, pages: list[int]) -> None:
+        """Return detached pages to the pool."""
+        self._free.extend(pages)
+
     def adopt(self, seq_id: str, pages: list[int]) -> None:
         """Take ownership of pages filled by someone else (prefill/decode disaggregation)."""
         for p in pages:

@@ -3,6 +3,11 @@
 This is the in-process core of the LLM executor (the reference uses an external vLLM fork for this
 role; its contract is in tasklib/cornserve_tasklib/task_executors/descriptor/llm.py:68-210).
 
+Prefill/decode disaggregation: a sequence with ``hold_kv`` keeps its pages after it finished (the prefill executor's
+one-token requests); ``kv_transfer_params`` describes them, ``release_held`` frees them.  A sequence that arrives
+with ``prefilled`` set skips the prompt computation: its pages are pulled from the producer's cache by one copy
+kernel (``ops.kv_copy_pages``: over NVLink / CUDA IPC) or filled from bytes fetched over the network.
+
 Scheduling: first-come-first-served.  A step is either a *prefill* step (waiting prompts, possibly
 chunked, packed up to ``max_batched_tokens`` tokens) or a *decode burst* (``decode_burst`` tokens for
 every running sequence).  During a burst the sampled token, the positions, the key counts and the
@@ -44,6 +49,28 @@ class MMItem:
     grid_thw: tuple[int, int, int] | None = None
 
 
+@dataclass
+class PrefilledKV:
+    """Where the KV pages of an already-prefilled prompt are: ``src_cache`` is the producer's cache
+    ``[layers, pages, 2, heads, 128, d]`` (mapped into this process) with the page numbers ``src_pages``; or ``raw``
+    holds the pages themselves ``[layers, len(src_pages), 2, heads, 128, d]``."""
+
+    first_token: int
+    next_pos: int
+    src_pages: list[int]
+    src_cache: torch.Tensor | None = None
+    raw: torch.Tensor | None = None
+
+
+@dataclass
+class HeldKV:
+    pages: list[int]
+    num_tokens: int
+    next_pos: int
+    first_token: int
+    held_at: float = field(default_factory=time.monotonic)
+
+
 class SeqStatus(enum.Enum):
     WAITING = 0
     RUNNING = 1
@@ -57,6 +84,9 @@ class Sequence:
     params: SamplingParams = field(default_factory=SamplingParams)
     mm_items: list[MMItem] = field(default_factory=list)
     return_hidden: bool = False
+    hold_kv: bool = False                   # keep the pages after finishing (prefill half of a disaggregated pair)
+    prefilled: PrefilledKV | None = None    # the prompt's KV comes from another executor (decode half)
+    kv_source: str | None = None            # "mapped" (peer copy kernel) or "network" once prefilled was consumed
     positions: np.ndarray | None = None     # [3, T]
     next_pos: int = 0
     status: SeqStatus = SeqStatus.WAITING
@@ -127,17 +157,27 @@ class LLMEngine:
         self.on_gpu = self.device.type == "cuda"
         self.blocks = BlockManager(self.cfg.num_pages)
         self.kv_caches = model.alloc_kv_cache(self.cfg.num_pages)
+        self.kv_backing: torch.Tensor = model.kv_backing  # [layers, pages, 2, heads, 128, d]; kv_caches are its views
         self.max_blocks = -(-self.cfg.max_model_len // PAGE_SIZE)
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self._decode_states: dict[int, _DecodeState] = {}
         self._copy_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
-        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0}
+        self.held: dict[str, HeldKV] = {}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "kv_pages_pulled": 0}
 
     # ---------------------------------------------------------------------------------------------
     # requests
     # ---------------------------------------------------------------------------------------------
     def add_request(self, seq: Sequence) -> None:
+        if seq.prefilled is not None:
+            if seq.prompt_len + seq.params.max_tokens > self.cfg.max_model_len:
+                raise ValueError("request exceeds max_model_len")
+            if len(seq.prefilled.src_pages) < -(-seq.prompt_len // PAGE_SIZE):
+                raise ValueError("the transferred pages do not cover the prompt")
+            seq.next_pos = seq.prefilled.next_pos
+            self.waiting.append(seq)
+            return
         if seq.positions is None:
             grids = [it.grid_thw for it in seq.mm_items if it.grid_thw is not None]
             if grids:
@@ -167,12 +207,78 @@ class LLMEngine:
     # ---------------------------------------------------------------------------------------------
     def step(self) -> list[StepOutput]:
         self.stats["steps"] += 1
+        outs = self._admit_prefilled()
+        if outs:
+            return outs
         batch = self._schedule_prefill()
         if batch:
             return self._run_prefill(batch)
         if self.running:
             return self._run_decode_burst()
         return []
+
+    def _admit_prefilled(self) -> list[StepOutput]:
+        """Sequences whose prompt was computed elsewhere: allocate pages, pull the prompt's KV, start decoding."""
+        outs: list[StepOutput] = []
+        while self.waiting and self.waiting[0].prefilled is not None and len(self.running) < self.cfg.max_num_seqs:
+            s = self.waiting[0]
+            total = s.prompt_len + s.params.max_tokens + 1
+            if not self.blocks.can_allocate(total, s.seq_id):
+                break
+            self.waiting.popleft()
+            pf = s.prefilled
+            s.kv_source = "network" if pf.raw is not None else "mapped"
+            n = -(-s.prompt_len // PAGE_SIZE)
+            pages = self.blocks.ensure(s.seq_id, total)[:n]
+            dst = self.kv_backing
+            if pf.raw is not None:
+                dst[:, torch.as_tensor(pages, device=self.device)] = pf.raw[:, :n].to(self.device, dst.dtype)
+            else:
+                i32 = lambda a: self._to_dev(np.asarray(a, dtype=np.int32))  # noqa: E731
+                ops.kv_copy_pages(dst, pf.src_cache, i32(pf.src_pages[:n]), i32(pages))
+            self.stats["kv_pages_pulled"] += n
+            s.prefilled = None  # drops the reference to the producer's mapping / the fetched bytes
+            s.num_computed = s.prompt_len
+            s.status = SeqStatus.RUNNING
+            s.first_token_time = time.monotonic()
+            s.output_ids.append(int(pf.first_token))
+            self.running.append(s)
+            outs.append(self._emit(s, [int(pf.first_token)]))
+        if outs:
+            if self.on_gpu:
+                torch.cuda.current_stream(self.device).synchronize()  # the producer may free its pages after this
+            self._reap()
+        return outs
+
+    # -- producer side of a transfer ---------------------------------------------------------------------------
+    def kv_transfer_params(self, seq_id: str) -> dict:
+        h = self.held[seq_id]
+        return {"request_id": seq_id, "num_tokens": h.num_tokens, "pages": h.pages[: -(-h.num_tokens // PAGE_SIZE)],
+                "next_pos": h.next_pos, "first_token": h.first_token}
+
+    def release_held(self, seq_id: str) -> bool:
+        h = self.held.pop(seq_id, None)
+        if h is None:
+            return False
+        self.blocks.release(h.pages)
+        return True
+
+    def expire_held(self, max_age_s: float) -> list[str]:
+        """Free the pages of transfers nobody fetched (a decode executor that died, a cancelled request)."""
+        now = time.monotonic()
+        old = [sid for sid, h in self.held.items() if now - h.held_at > max_age_s]
+        for sid in old:
+            self.release_held(sid)
+        return old
+
+    def read_pages(self, pages: list[int]) -> torch.Tensor:
+        """The pages themselves, on the host: ``[layers, len(pages), 2, heads, 128, d]`` (network fallback)."""
+        idx = torch.as_tensor(pages, device=self.device, dtype=torch.long)
+        return self.kv_backing[:, idx].cpu()
+
+    def kv_geometry(self) -> dict:
+        kv = self.kv_backing
+        return {"shape": list(kv.shape), "dtype": str(kv.dtype).replace("torch.", "")}
 
     def _schedule_prefill(self) -> list[tuple[Sequence, int]]:
         """Pick prompt chunks for one prefill step: unfinished chunked prefills first, then new arrivals
@@ -187,6 +293,8 @@ class LLMEngine:
                 budget -= n
         while self.waiting and budget > 0 and len(self.running) + len(batch) < self.cfg.max_num_seqs:
             s = self.waiting[0]
+            if s.prefilled is not None:
+                break  # first come, first served: it is admitted by _admit_prefilled once pages are free
             total = s.prompt_len + s.params.max_tokens + 1
             if not self.blocks.can_allocate(total, s.seq_id):
                 break
@@ -363,7 +471,10 @@ class LLMEngine:
     def _reap(self) -> None:
         for s in [s for s in self.running if s.status is SeqStatus.FINISHED]:
             self.running.remove(s)
-            self.blocks.free(s.seq_id)
+            if s.hold_kv and s.output_ids and (s.finish_reason or "").startswith(("length", "stop")):
+                self.held[s.seq_id] = HeldKV(self.blocks.detach(s.seq_id), s.prompt_len, s.next_pos, s.output_ids[0])
+            else:
+                self.blocks.free(s.seq_id)
 
     # ---------------------------------------------------------------------------------------------
     # batch helper

@@ -10,6 +10,13 @@ tasklib/cornserve_tasklib/task_executors/descriptor/llm.py:68-563 and docker/vll
   (the monolithic, no-fission deployment).
 * ``vllm_xargs`` carries forwarding instructions: ``cornserve_hidden_states_forward_id/_ranks`` sends the
   prompt's final hidden states to another executor instead of generating text.
+* Prefill/decode disaggregation (``--kv-transfer-config {"kv_role": "kv_producer" | "kv_consumer"}``; the reference
+  delegates this to vLLM's NIXL connector, descriptor/llm.py:213-563).  A producer answers a request after one token,
+  keeps the prompt's KV pages and forwards ``kv_transfer_params`` (page numbers, first token, how to reach the cache)
+  under ``cornserve_kv_transfer_params_forward_id``.  A consumer that gets ``cornserve_kv_transfer_params_recv_id``
+  maps the producer's cache (CUDA IPC, once per producer), pulls the pages with one copy kernel over NVLink and
+  decodes; when the producer's GPU is not reachable it fetches the pages over HTTP instead.  Either way it then tells
+  the producer to free the pages (``POST /kv/release``).
 
 The command line accepts the flags the descriptors pass (vLLM-style names); flags that only make sense for
 vLLM are accepted and ignored.
@@ -20,10 +27,14 @@ from __future__ import annotations
 import argparse
 import ast
 import asyncio
+import base64
+import concurrent.futures
 import io
 import json
 import os
+import pickle
 import re
+import socket
 import threading
 import time
 import uuid
@@ -36,6 +47,7 @@ import uvicorn
 from fastapi import FastAPI, Request, Response
 from fastapi.responses import JSONResponse, StreamingResponse
 
+from ... import ops
 from ...logging import get_logger
 from ...models.qwen_llm import LLMConfig, QwenLLM
 from ...parallel.state import ParallelGroup
@@ -43,7 +55,7 @@ from ...tracing import configure_otel
 from ...utils.hub import load_config, load_model_weights
 from ..eric.preprocess import smart_resize
 from ..eric.processor import fetch_bytes
-from .engine import EngineConfig, LLMEngine, MMItem, SamplingParams, Sequence, StepOutput
+from .engine import EngineConfig, LLMEngine, MMItem, PrefilledKV, SamplingParams, Sequence, StepOutput
 from .tokenizer import load_tokenizer
 
 logger = get_logger(__name__)
@@ -94,6 +106,7 @@ class AsyncLLM:
         self.engine = engine
         self.pending: dict[str, _Pending] = {}
         self.inbox: list[Sequence] = []
+        self.calls: list[tuple[Any, concurrent.futures.Future]] = []
         self.cv = threading.Condition()
         self.alive = True
         self.thread = threading.Thread(target=self._run, name="llm-engine", daemon=True)
@@ -107,6 +120,14 @@ class AsyncLLM:
             self.cv.notify()
         return q
 
+    def call(self, fn) -> concurrent.futures.Future:
+        """Run ``fn()`` on the engine thread (the engine's state is not shared between threads)."""
+        fut: concurrent.futures.Future = concurrent.futures.Future()
+        with self.cv:
+            self.calls.append((fn, fut))
+            self.cv.notify()
+        return fut
+
     def _deliver(self, out: StepOutput) -> None:
         p = self.pending.get(out.seq_id)
         if p is None:
@@ -116,12 +137,24 @@ class AsyncLLM:
         p.loop.call_soon_threadsafe(p.queue.put_nowait, out)
 
     def _run(self) -> None:
+        ops.bind_thread(self.engine.device)  # a new thread starts on CUDA device 0
         try:
             while self.alive:
                 with self.cv:
-                    while self.alive and not self.inbox and not self.engine.has_work():
+                    while self.alive and not self.inbox and not self.calls and not self.engine.has_work():
                         self.cv.wait(timeout=0.5)
+                        if self.engine.held:
+                            break
                     new, self.inbox = self.inbox, []
+                    calls, self.calls = self.calls, []
+                for fn, fut in calls:
+                    try:
+                        fut.set_result(fn())
+                    except Exception as e:
+                        fut.set_exception(e)
+                if self.engine.held:
+                    for sid in self.engine.expire_held(float(os.environ.get("CORNSERVE_KV_HOLD_SECONDS", "600"))):
+                        logger.warning("Freed the KV pages of %s: nobody fetched them", sid)
                 for s in new:
                     try:
                         self.engine.add_request(s)
@@ -151,8 +184,8 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
         torch.cuda.set_device(device)
     torch.manual_seed(int(os.environ.get("CORNSERVE_SEED", "0")))  # reproducible random-weight runs
     model = QwenLLM(cfg, group=group, device=device)
-    if device.type == "cpu" or hf_cfg.get("torch_dtype") == "float32":
-        model = model.float()
+    if device.type == "cpu":
+        model = model.float()  # the CUDA kernels are bf16; fp32 is the CPU restatement's precision
     load_model_weights(model, args.model, ["model.language_model.", "language_model.", "model.", "lm_head.", ""],
                        strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower."])
     model.eval()
@@ -189,6 +222,11 @@ class LLMServer:
                                                  send_tensor_dtype=dtype, send_tensor_shape=(-1, self.cfg.hidden_size),
                                                  recv_tensor_dtype=dtype, recv_tensor_shape=(-1, self.cfg.hidden_size)))
         self.vision = None  # built lazily for requests that carry raw URLs
+        kv_cfg = json.loads(args.kv_transfer_config) if args.kv_transfer_config else {}
+        self.kv_role = kv_cfg.get("kv_role")
+        self.engine_id = uuid.uuid4().hex
+        self._kv_export: dict[str, Any] | None = None
+        self._kv_maps: dict[str, torch.Tensor] = {}   # producer engine id -> its cache mapped into this process
 
     # -- multimodal inputs ----------------------------------------------------------------------------------
     def _grid_of(self, modality: str, url: str, n_rows: int) -> tuple[int, int, int] | None:
@@ -290,14 +328,137 @@ class LLMServer:
             except Exception:
                 logger.exception("mark_done failed for %s", rid)
 
+    # -- prefill/decode disaggregation ---------------------------------------------------------------------
+    def kv_export(self) -> dict[str, Any]:
+        """How another executor reaches this engine's KV cache (a CUDA-IPC handle of the one cache allocation when the
+        cache is on a GPU, and the URL that serves pages to executors that cannot map it)."""
+        if self._kv_export is None:
+            eng = self.engine
+            info: dict[str, Any] = {"engine_id": self.engine_id, "base_url": f"http://{self.args.host}:{self.args.port}",
+                                    "hostname": socket.gethostname(), **eng.kv_geometry()}
+            if eng.on_gpu:
+                from torch.multiprocessing.reductions import reduce_tensor
+
+                _, ipc_args = reduce_tensor(eng.kv_backing)
+                info["ipc"] = base64.b64encode(pickle.dumps(ipc_args)).decode()
+                info["gpu_uuid"] = str(torch.cuda.get_device_properties(eng.device).uuid)
+            self._kv_export = info
+        return self._kv_export
+
+    def _map_producer_cache(self, params: dict[str, Any]) -> torch.Tensor | None:
+        """The producer's cache as a tensor of this process, or ``None`` when it cannot be mapped (other host, GPU not
+        visible here, CPU engines).  Mapped once per producer."""
+        eid = params.get("engine_id")
+        if eid == self.engine_id:
+            return self.engine.kv_backing
+        if not self.engine.on_gpu or "ipc" not in params or params.get("hostname") != socket.gethostname():
+            return None
+        if eid in self._kv_maps:
+            return self._kv_maps[eid]
+        mine = self.engine.device.index
+        theirs = next((i for i in range(torch.cuda.device_count())
+                       if str(torch.cuda.get_device_properties(i).uuid) == params.get("gpu_uuid")), None)
+        if theirs is None or (theirs != mine and not torch.cuda.can_device_access_peer(mine, theirs)):
+            return None
+        import inspect
+
+        from torch.multiprocessing.reductions import rebuild_cuda_tensor
+
+        try:
+            # The handle is opened with THIS executor's GPU current (the open then enables peer access between the two
+            # GPUs as needed), so the mapping is addressable by kernels of this GPU; the tensor is labelled accordingly.
+            args = list(pickle.loads(base64.b64decode(params["ipc"])))  # from an executor of the same deployment
+            args[list(inspect.signature(rebuild_cuda_tensor).parameters).index("storage_device")] = mine
+            mapped = rebuild_cuda_tensor(*args)
+            # reach it once through the driver's copy path (which reports an error instead of faulting) before any
+            # kernel reads it
+            probe = torch.empty(8, dtype=mapped.dtype, device=self.engine.device)
+            probe.copy_(mapped.reshape(-1)[:8])
+            torch.cuda.synchronize(self.engine.device)
+        except Exception:
+            logger.exception("Could not map the KV cache of engine %s; falling back to the network path", eid)
+            return None
+        self._kv_maps[eid] = mapped
+        return mapped
+
+    async def _fetch_pages(self, params: dict[str, Any]) -> torch.Tensor:
+        import aiohttp
+
+        async with aiohttp.ClientSession() as sess:
+            async with sess.post(f"{params['base_url']}/kv/pages", json={"request_id": params["request_id"]}) as r:
+                r.raise_for_status()
+                data = await r.read()
+        shape = list(params["shape"])
+        shape[1] = len(params["pages"])
+        return torch.frombuffer(bytearray(data), dtype=getattr(torch, params["dtype"])).view(shape)
+
+    async def _release_at_producer(self, params: dict[str, Any]) -> None:
+        if params.get("engine_id") == self.engine_id:
+            await asyncio.wrap_future(self.llm.call(lambda: self.engine.release_held(params["request_id"])))
+            return
+        import aiohttp
+
+        try:
+            async with aiohttp.ClientSession() as sess:
+                async with sess.post(f"{params['base_url']}/kv/release", json={"request_id": params["request_id"]}) as r:
+                    await r.read()
+        except Exception:
+            logger.exception("Could not tell %s to free the pages of %s", params.get("base_url"), params.get("request_id"))
+
+    async def _sidecar_parts(self, body: dict[str, Any]) -> list[str]:
+        """Forwarded embeddings named by a request that does not need them (its prompt is already prefilled): receive
+        them so that they can be marked done."""
+        recv_ids: list[str] = []
+        for m in body["messages"]:
+            if isinstance(m["content"], str):
+                continue
+            for p in m["content"]:
+                if p.get("type", "text") == "text":
+                    continue
+                hit = _SIDECAR_URI.match(p[p["type"]]["url"])
+                if hit is None or self.sidecar is None:
+                    continue
+                k = 0
+                while await self.sidecar.recv(hit["id"], k) is not None:
+                    k += 1
+                recv_ids.extend(f"{hit['id']}:{i}" for i in range(k))
+        return recv_ids
+
+    async def build_prefilled_sequence(self, body: dict[str, Any], params: dict[str, Any]) -> tuple[Sequence, list[str]]:
+        src = self._map_producer_cache(params)
+        raw = None if src is not None else await self._fetch_pages(params)
+        pf = PrefilledKV(int(params["first_token"]), int(params["next_pos"]), [int(p) for p in params["pages"]], src_cache=src, raw=raw)
+        sp = SamplingParams(max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
+                            ignore_eos=bool(body.get("ignore_eos", False)))
+        seq = Sequence(body.get("request_id") or uuid.uuid4().hex, np.zeros(int(params["num_tokens"]), dtype=np.int32), sp,
+                       prefilled=pf)
+        return seq, await self._sidecar_parts(body)
+
     # -- request handling ---------------------------------------------------------------------------------------
     async def chat(self, body: dict[str, Any]):
+        xargs = body.get("vllm_xargs") or {}
+        kv_in: dict[str, Any] | None = None
         try:
-            seq, recv_ids = await self.build_sequence(body)
+            recv_kv = xargs.get("cornserve_kv_transfer_params_recv_id")
+            if recv_kv is not None:
+                if self.sidecar is None:
+                    raise ValueError("request refers to forwarded KV parameters but this executor has no sidecar")
+                kv_in = await self.sidecar.recv(recv_kv)
+                await self.sidecar.mark_done(recv_kv)
+            elif isinstance(body.get("kv_transfer_params"), dict) and "pages" in body["kv_transfer_params"]:
+                kv_in = body["kv_transfer_params"]
+            if kv_in is not None:
+                seq, recv_ids = await self.build_prefilled_sequence(body, kv_in)
+            else:
+                seq, recv_ids = await self.build_sequence(body)
         except Exception as e:
             logger.exception("Bad request")
             return JSONResponse({"error": {"message": str(e), "type": "invalid_request_error"}}, status_code=400)
-        xargs = body.get("vllm_xargs") or {}
+        producer = kv_in is None and "cornserve_hidden_states_forward_id" not in xargs and (
+            self.kv_role == "kv_producer" or bool((body.get("kv_transfer_params") or {}).get("do_remote_decode")))
+        if producer:
+            seq.hold_kv = True
+            seq.params.max_tokens = 1
         created, rid, model = int(time.time()), f"chatcmpl-{seq.seq_id}", body.get("model", self.args.model)
         queue = self.llm.submit(seq)
         include_usage = bool((body.get("stream_options") or {}).get("include_usage", False))
@@ -316,9 +477,12 @@ class LLMServer:
             first = True
             while True:
                 out: StepOutput = await queue.get()
-                if first and recv_ids:
+                if first:
                     first = False
-                    await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
+                    if recv_ids:
+                        await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
+                    if kv_in is not None:
+                        await self._release_at_producer(kv_in)  # the pages were pulled before the first output
                 all_ids.extend(out.new_token_ids)
                 text = self.tokenizer.decode(all_ids)
                 if text.endswith("�") and not out.finished:
@@ -341,6 +505,27 @@ class LLMServer:
                     await asyncio.to_thread(self.sidecar.flush)
             return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
                                  "choices": [], "cornserve": {"hidden_states_rows": 0 if hidden is None else hidden.shape[0]}})
+
+        if producer:
+            text, last = "", None
+            async for delta, last, _ in consume():
+                text += delta
+            if last is None or (last.finish_reason or "").startswith("error"):
+                return JSONResponse({"error": {"message": getattr(last, "finish_reason", "no output")}}, status_code=500)
+            held = await asyncio.wrap_future(self.llm.call(lambda: self.engine.kv_transfer_params(seq.seq_id)))
+            params = {**self.kv_export(), **held}
+            fid = xargs.get("cornserve_kv_transfer_params_forward_id")
+            if fid and self.sidecar is not None:
+                ranks = ast.literal_eval(xargs.get("cornserve_kv_transfer_params_forward_ranks", "[]")) or []
+                if ranks:
+                    self.sidecar.send(params, id=fid, dst_sidecar_ranks=ranks)
+                    await asyncio.to_thread(self.sidecar.flush)
+            return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
+                                 "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
+                                              "finish_reason": "length"}],
+                                 "usage": {"prompt_tokens": seq.prompt_len, "completion_tokens": 1,
+                                           "total_tokens": seq.prompt_len + 1},
+                                 "kv_transfer_params": params})
 
         if body.get("stream"):
             async def sse():
@@ -369,7 +554,8 @@ class LLMServer:
                              "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
                                           "finish_reason": reason}],
                              "usage": {"prompt_tokens": seq.prompt_len, "completion_tokens": n,
-                                       "total_tokens": seq.prompt_len + n}})
+                                       "total_tokens": seq.prompt_len + n},
+                             **({"cornserve": {"kv_source": seq.kv_source}} if kv_in is not None else {})})
 
     def create_app(self) -> FastAPI:
         app = FastAPI(title="cornserve-b200 LLM executor")
@@ -385,6 +571,27 @@ class LLMServer:
         @app.post("/v1/chat/completions")
         async def chat(raw: Request):
             return await self.chat(await raw.json())
+
+        @app.post("/kv/release")
+        async def kv_release(raw: Request):
+            rid = (await raw.json())["request_id"]
+            ok = await asyncio.wrap_future(self.llm.call(lambda: self.engine.release_held(rid)))
+            return {"released": bool(ok)}
+
+        @app.post("/kv/pages")
+        async def kv_pages(raw: Request):
+            rid = (await raw.json())["request_id"]
+
+            def read() -> bytes | None:
+                if rid not in self.engine.held:
+                    return None
+                pages = self.engine.kv_transfer_params(rid)["pages"]
+                return self.engine.read_pages(pages).contiguous().view(torch.uint8).numpy().tobytes()
+
+            data = await asyncio.wrap_future(self.llm.call(read))
+            if data is None:
+                return JSONResponse({"error": {"message": f"no held pages for {rid}"}}, status_code=404)
+            return Response(content=data, media_type="application/octet-stream")
 
         return app
 

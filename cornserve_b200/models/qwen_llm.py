@@ -245,10 +245,12 @@ class QwenLLM(nn.Module):
         return self.layers[0].self_attn.hkv
 
     def alloc_kv_cache(self, num_pages: int) -> list[torch.Tensor]:
-        """One zero-initialised cache ``[pages, 2, Hkv_local, 128, d]`` per layer."""
-        shape = (num_pages, 2, self.kv_heads_local, PAGE_SIZE, self.cfg.head_dim)
-        return [torch.zeros(shape, device=self.device, dtype=self.embed_tokens.weight.dtype)
-                for _ in range(self.cfg.num_hidden_layers)]
+        """One zero-initialised cache ``[pages, 2, Hkv_local, 128, d]`` per layer, all views of one allocation
+        ``[layers, pages, 2, Hkv_local, 128, d]`` (kept as ``self.kv_backing``) so that another executor can map the
+        whole cache with one handle and copy pages of every layer in one launch."""
+        shape = (self.cfg.num_hidden_layers, num_pages, 2, self.kv_heads_local, PAGE_SIZE, self.cfg.head_dim)
+        self.kv_backing = torch.zeros(shape, device=self.device, dtype=self.embed_tokens.weight.dtype)
+        return list(self.kv_backing.unbind(0))
 
     def kv_bytes_per_page(self) -> int:
         return 2 * self.kv_heads_local * PAGE_SIZE * self.cfg.head_dim * 2 * self.cfg.num_hidden_layers

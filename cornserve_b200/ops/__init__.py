@@ -41,6 +41,21 @@ def _count(n: int = 1) -> None:
     _launches += n
 
 
+def bind_thread(device: torch.device | str) -> None:
+    """Make ``device`` the CUDA device of the calling thread.  The current device is a per-thread setting and new
+    threads start on device 0, while the kernels of this library launch on the current device: every thread that
+    runs them for a model on another GPU calls this first."""
+    device = torch.device(device)
+    if device.type == "cuda":
+        torch.cuda.set_device(device)
+
+
+def _on_current_device(t: torch.Tensor) -> None:
+    if t.device.index is not None and t.device.index != torch.cuda.current_device():
+        raise RuntimeError(f"tensor on {t.device} but the thread's CUDA device is {torch.cuda.current_device()}: "
+                           "call ops.bind_thread(device) at the start of the thread")
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -148,6 +163,7 @@ def linear(
             return out
         return y.view(*shape[:-1], w.shape[0])
     assert x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "CUDA GEMM is bf16"
+    _on_current_device(x2)
     M, K = x2.shape
     N = w.shape[0]
     assert w.shape[1] == K and w.stride(1) == 1
@@ -673,3 +689,28 @@ def bilinear_embed_add_(x: torch.Tensor, table: torch.Tensor, idx: torch.Tensor,
                                    wgt.contiguous().data_ptr(), L, H, _stream()), "cs_bilinear_embed_add")
     _count()
     return x
+
+
+def kv_copy_pages(dst: torch.Tensor, src: torch.Tensor, src_pages: torch.Tensor, dst_pages: torch.Tensor) -> None:
+    """``dst[:, dst_pages[i]] = src[:, src_pages[i]]`` for KV caches ``[layers, pages, ...]`` (page-contiguous).
+
+    ``src`` may live on another GPU of the node or belong to another process (a CUDA-IPC mapping): the kernel runs on
+    ``dst``'s device and reads the pages over NVLink.  Page lists are int32 tensors on ``dst``'s device."""
+    assert dst.shape[0] == src.shape[0] and dst.shape[2:] == src.shape[2:] and dst.dtype == src.dtype
+    if not dst.is_cuda:
+        dst[:, dst_pages.long()] = src[:, src_pages.long()]
+        return
+    assert src.is_cuda and dst[0, 0].is_contiguous() and src[0, 0].is_contiguous()
+    lib = _lib.load()
+    if src.device != dst.device:
+        with torch.cuda.device(dst.device):
+            rc = lib.cs_enable_peer_access(src.device.index)
+        if rc != 0:
+            raise RuntimeError(f"{dst.device} cannot read the memory of {src.device} (code {rc})")
+    page_bytes = dst[0, 0].numel() * dst.element_size()
+    with torch.cuda.device(dst.device):
+        _chk(lib.cs_kv_copy_pages(dst.data_ptr(), src.data_ptr(), dst.stride(0) * dst.element_size(),
+                                  src.stride(0) * src.element_size(), page_bytes, dst.shape[0], int(src_pages.numel()),
+                                  dst.shape[1], src.shape[1], src_pages.data_ptr(), dst_pages.data_ptr(), _stream()),
+             "cs_kv_copy_pages")
+    _count()

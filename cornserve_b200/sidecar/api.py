@@ -104,9 +104,15 @@ class Sidecar:
                 return cached
             info = pickle.loads(Path(slab_handle_path(rank)).read_bytes())
             if info["kind"] == "cuda_ipc":
+                import inspect
+
                 from torch.multiprocessing.reductions import rebuild_cuda_tensor
 
-                slab = rebuild_cuda_tensor(*info["args"])
+                # Open the handle with THIS process's GPU current (the open enables peer access to the slab's GPU as
+                # needed): kernels of this GPU can then read the slab in place, over NVLink when it lives elsewhere.
+                args = list(info["args"])
+                args[list(inspect.signature(rebuild_cuda_tensor).parameters).index("storage_device")] = torch.cuda.current_device()
+                slab = rebuild_cuda_tensor(*args)
             else:
                 slab = torch.from_file(info["path"], shared=True, size=info["numel"], dtype=serde.dtype_from_name(info["dtype"]))
             self._slabs[rank] = slab

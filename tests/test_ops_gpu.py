@@ -453,3 +453,24 @@ def test_fused_moe_layer_replays_from_a_cuda_graph():
     want, _ = _moe_reference(x, logits, wgu, wd, k, True)
     assert (out.float().cpu() - want).abs().max().item() < 0.03 * want.abs().max().item() + 0.02
     assert eager.shape == out.shape
+
+
+def test_kv_page_copy_is_byte_exact():
+    L, pages, hkv, d = 3, 40, 2, 64
+    src = torch.randn(L, pages, 2, hkv, 128, d, device="cuda").bfloat16()
+    dst = torch.zeros(L, 24, 2, hkv, 128, d, device="cuda", dtype=torch.bfloat16)
+    sp = torch.tensor([7, 39, 1, 18, 2], device="cuda", dtype=torch.int32)
+    dp = torch.tensor([23, 0, 5, 6, 11], device="cuda", dtype=torch.int32)
+    ops.kv_copy_pages(dst, src, sp, dp)
+    torch.cuda.synchronize()
+    ops.check_error("kv copy")
+    want = torch.zeros_like(dst)
+    want[:, dp.long()] = src[:, sp.long()]
+    assert torch.equal(dst.view(torch.int16), want.view(torch.int16))
+    # a page number outside the cache is refused by the kernel (error status), nothing is written
+    before = dst.clone()
+    ops.kv_copy_pages(dst, src, torch.tensor([40], device="cuda", dtype=torch.int32), torch.tensor([1], device="cuda", dtype=torch.int32))
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError):
+        ops.check_error("kv copy with a bad page")
+    assert torch.equal(dst.view(torch.int16), before.view(torch.int16))
