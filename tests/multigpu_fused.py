@@ -1,5 +1,7 @@
 """Multi-GPU checks of the fused compute+collective kernels.  Launched by ``test_multigpu.py`` as
-``torchrun --nproc-per-node N tests/multigpu_fused.py`` (one rank per GPU); exits non-zero on a mismatch."""
+``torchrun --nproc-per-node N tests/multigpu_fused.py [section ...]`` (one rank per GPU); exits non-zero on a mismatch.
+Sections: ``allreduce`` (decode GEMM + all-reduce tail), ``llm`` (tensor-parallel decoder), ``vit`` (encoder chain),
+``dit`` (sequence-parallel diffusion transformer), ``moe`` (expert parallelism); all of them when none is named."""
 
 import os
 import sys
@@ -354,12 +356,9 @@ def ep_mixture_of_experts(g):
                   f"library all-to-all + per-expert GEMMs {t_l:.0f} us", flush=True)
 
 
-def main():
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    g = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
-                         master_port=int(os.environ["MASTER_PORT"]), local_device=int(os.environ.get("LOCAL_RANK", rank)))
-    assert g.fabric is not None, "fabric missing"
-    dev = g.device
+def decode_allreduce_tail(g):
+    """Decode-time row-parallel projection: GEMM + all-reduce + residual + RMSNorm in one kernel per rank."""
+    rank, world, dev = g.rank, g.size, g.device
     torch.manual_seed(1234)  # same full problem on every rank, then sharded
     N = 3584
     fused = FusedRowParallel(g, N, m_cap=128)
@@ -428,10 +427,20 @@ def main():
         t_b = timeit(baseline)
         if rank == 0:
             print(f"fused GEMM+AR+res+norm M={M} K={K} world={world}: {t_f:.1f} us   cuBLAS+NCCL+eager: {t_b:.1f} us", flush=True)
-    tp_llm_matches_single_gpu(g)
-    tp_vision_tower(g)
-    sp_diffusion_transformer(g)
-    ep_mixture_of_experts(g)
+
+
+SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower,
+            "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts}
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    g = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
+                         master_port=int(os.environ["MASTER_PORT"]), local_device=int(os.environ.get("LOCAL_RANK", rank)))
+    assert g.fabric is not None, "fabric missing"
+    for name in (sys.argv[1:] or list(SECTIONS)):
+        SECTIONS[name](g)
+        dist.barrier()
     if rank == 0:
         print("MULTIGPU_FUSED_OK", flush=True)
     dist.barrier()
