@@ -62,6 +62,7 @@ __device__ __forceinline__ void act16(float (&f)[16], int act) {
 // halves by call parity (a rank can never run two calls ahead of a peer), counters only ever grow, and the
 // call number lives in device memory so that a CUDA graph can replay the kernel.
 constexpr int AR_MAX_WORLD = 8;
+constexpr int AR_STG_PITCH = 128 + 8;  // bf16 elements per staged row (16 bytes of padding against bank conflicts)
 struct AllReduceParams {
   int world, rank;
   __nv_bfloat16* recv[AR_MAX_WORLD];  // per peer: [2][world][m_cap][n_cap]
@@ -269,17 +270,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         const bool writer = row_valid && (!p.swiglu || r < 64);
         if (p.ar.world > 1) {
-          // push this rank's partial (bias already applied on rank 0 only by the caller) to every peer
+          // stage this rank's partial (bias already applied on rank 0 only by the caller) row-major in shared memory
+          // (the operand ring is free: every MMA of this CTA has completed); it leaves as 16-byte row pieces below
           if (writer) {
-            const int n = n0 + r;
             const int mmax = min(16, p.M - c * 16);
-            const long long slot = (static_cast<long long>(ar_parity) * p.ar.world + p.ar.rank) * p.ar.m_cap;
-            for (int peer = 0; peer < p.ar.world; ++peer) {
-              __nv_bfloat16* dst = p.ar.recv[peer] + (slot + c * 16) * p.ar.n_cap + n;
+            __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(smem) + static_cast<long long>(c * 16) * AR_STG_PITCH + r;
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (i < mmax) dst[static_cast<long long>(i) * p.ar.n_cap] = __float2bfloat16(f[i]);
-            }
+            for (int i = 0; i < 16; ++i)
+              if (i < mmax) st[i * AR_STG_PITCH] = __float2bfloat16(f[i]);
           }
           continue;
         }
@@ -306,6 +304,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       }
       if (p.ar.world > 1) {
+        // Work item u = (row, 8-column group) of the M x 128 tile: 16 consecutive lanes cover one row, so every
+        // global access below is a 16-byte piece of a 256-byte row segment.
+        const int units = p.M * 16;
+        const unsigned slot_base = ar_parity * static_cast<unsigned>(p.ar.world);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // ---- push this rank's partial tile into slot [rank] of every peer ----
+        for (int base = 0; base < units; base += 128) {
+          const int u = base + r, row = u >> 4, col = n0 + (u & 15) * 8;
+          if (u < units && col < p.N) {
+            const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(smem) +
+                                                            static_cast<long long>(row) * AR_STG_PITCH + (u & 15) * 8);
+            const long long off = (static_cast<long long>(slot_base + p.ar.rank) * p.ar.m_cap + row) * p.ar.n_cap + col;
+            for (int peer = 0; peer < p.ar.world; ++peer) *reinterpret_cast<uint4*>(p.ar.recv[peer] + off) = v;
+          }
+        }
         // ---- signal: all stores of this CTA are visible system-wide before the counters move ----
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -331,44 +344,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         // ---- reduce: sum the world partials (+ residual), keep the new residual, gather row norms ----
-        const int n = n0 + r;
-        for (int c = 0; c < chunks; ++c) {
-          const int mmax = min(16, p.M - c * 16);
-          float h[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) h[i] = 0.f;
-          if (row_valid) {
+        for (int base = 0; base < units; base += 128) {
+          const int u = base + r, row = u >> 4, col = n0 + (u & 15) * 8;
+          const bool live = u < units && col < p.N;
+          float sq = 0.f;
+          if (live) {
+            float h[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int src = 0; src < p.ar.world; ++src) {
-              const __nv_bfloat16* part = p.ar.recv[p.ar.rank] +
-                  ((static_cast<long long>(ar_parity) * p.ar.world + src) * p.ar.m_cap + c * 16) * p.ar.n_cap + n;
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (i < mmax) h[i] += __bfloat162float(__ldcg(part + static_cast<long long>(i) * p.ar.n_cap));
+              const uint4 q4 = __ldcg(reinterpret_cast<const uint4*>(
+                  p.ar.recv[p.ar.rank] + (static_cast<long long>(slot_base + src) * p.ar.m_cap + row) * p.ar.n_cap + col));
+              h[0] += bf16lo(q4.x); h[1] += bf16hi(q4.x); h[2] += bf16lo(q4.y); h[3] += bf16hi(q4.y);
+              h[4] += bf16lo(q4.z); h[5] += bf16hi(q4.z); h[6] += bf16lo(q4.w); h[7] += bf16hi(q4.w);
             }
             if (p.residual != nullptr) {
-              const __nv_bfloat16* rp = p.residual + static_cast<long long>(c * 16) * p.ldr + n;
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (i < mmax) h[i] += __bfloat162float(rp[static_cast<long long>(i) * p.ldr]);
+              const uint4 q4 = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(row) * p.ldr + col);
+              h[0] += bf16lo(q4.x); h[1] += bf16hi(q4.x); h[2] += bf16lo(q4.y); h[3] += bf16hi(q4.y);
+              h[4] += bf16lo(q4.z); h[5] += bf16hi(q4.z); h[6] += bf16lo(q4.w); h[7] += bf16hi(q4.w);
             }
-            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(c * 16) * p.ldc + n;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              if (i < mmax) {
-                const __nv_bfloat16 hb = __float2bfloat16(h[i]);
-                op[static_cast<long long>(i) * p.ldc] = hb;
-                h[i] = __bfloat162float(hb);  // the norm sees the stored (rounded) value
-              }
-            }
+            uint4 o;
+            o.x = pack_bf16x2(h[0], h[1]); o.y = pack_bf16x2(h[2], h[3]); o.z = pack_bf16x2(h[4], h[5]); o.w = pack_bf16x2(h[6], h[7]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col) = o;
+            // the norm sees the stored (rounded) values
+            const float g0 = bf16lo(o.x), g1 = bf16hi(o.x), g2 = bf16lo(o.y), g3 = bf16hi(o.y);
+            const float g4 = bf16lo(o.z), g5 = bf16hi(o.z), g6 = bf16lo(o.w), g7 = bf16hi(o.w);
+            sq = g0 * g0 + g1 * g1 + g2 * g2 + g3 * g3 + g4 * g4 + g5 * g5 + g6 * g6 + g7 * g7;
           }
           if (p.ar.norm_w != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float sq = (row_valid && i < mmax) ? h[i] * h[i] : 0.f;
-#pragma unroll
-              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-              if (lane == 0 && i < mmax) atomicAdd(&p.ar.ssq[c * 16 + i], sq);
-            }
+            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // the 16 lanes of a row
+            if ((lane & 15) == 0 && u < units) atomicAdd(&p.ar.ssq[row], sq);
           }
         }
         // ---- once every tile of this rank is reduced, each tile CTA normalises its own 128 columns ----
@@ -391,22 +395,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (p.ar.norm_w != nullptr && row_valid) {
-          const float wn = __bfloat162float(p.ar.norm_w[n]);
+        if (p.ar.norm_w != nullptr) {
           const float inv_n = 1.0f / static_cast<float>(p.N);
-          for (int c = 0; c < chunks; ++c) {
-            const int mmax = min(16, p.M - c * 16);
-            const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(p.C) + static_cast<long long>(c * 16) * p.ldc + n;
-            __nv_bfloat16* op = p.ar.normed + static_cast<long long>(c * 16) * p.ar.ldn + n;
-            float hv[16], sv[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              hv[i] = i < mmax ? __bfloat162float(hp[static_cast<long long>(i) * p.ldc]) : 0.f;
-              sv[i] = i < mmax ? __ldcg(&p.ar.ssq[c * 16 + i]) : 1.f;
+          for (int base = 0; base < units; base += 128) {
+            const int u = base + r, row = u >> 4, col = n0 + (u & 15) * 8;
+            if (u < units && col < p.N) {
+              const uint4 hq = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.C) +
+                                                               static_cast<long long>(row) * p.ldc + col);
+              const uint4 wq = *reinterpret_cast<const uint4*>(p.ar.norm_w + col);
+              const float s = rsqrtf(__ldcg(&p.ar.ssq[row]) * inv_n + p.ar.eps);
+              uint4 o;
+              o.x = pack_bf16x2(bf16lo(hq.x) * s * bf16lo(wq.x), bf16hi(hq.x) * s * bf16hi(wq.x));
+              o.y = pack_bf16x2(bf16lo(hq.y) * s * bf16lo(wq.y), bf16hi(hq.y) * s * bf16hi(wq.y));
+              o.z = pack_bf16x2(bf16lo(hq.z) * s * bf16lo(wq.z), bf16hi(hq.z) * s * bf16hi(wq.z));
+              o.w = pack_bf16x2(bf16lo(hq.w) * s * bf16lo(wq.w), bf16hi(hq.w) * s * bf16hi(wq.w));
+              *reinterpret_cast<uint4*>(p.ar.normed + static_cast<long long>(row) * p.ar.ldn + col) = o;
             }
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (i < mmax) op[static_cast<long long>(i) * p.ar.ldn] = __float2bfloat16(hv[i] * rsqrtf(sv[i] * inv_n + p.ar.eps) * wn);
           }
         }
         // ---- the CTA that leaves last re-arms the scratch for the next call ----
@@ -530,6 +534,11 @@ CS_API int cs_gemm_skinny_allreduce(const void* X, long long ldx, const void* W,
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
   if (M > 256 || K <= 0 || (ldx & 7) || (ldw & 7) || (N & 7) || world < 1 || world > AR_MAX_WORLD) return -1;
+  // the reduction works on 16-byte row pieces of H, the residual, the norm weight and the normalised output
+  if ((ldh & 7) || (residual != nullptr && (ldr & 7)) || (normed != nullptr && (ldn & 7)) || (n_cap & 7) ||
+      ((reinterpret_cast<uintptr_t>(H) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(normed) |
+        reinterpret_cast<uintptr_t>(norm_w)) & 15))
+    return -1;
   SkinnyParams p{};
   p.M = M; p.N = N; p.K = K;
   p.m_pad = (M + 15) & ~15;

@@ -316,7 +316,7 @@ def ep_mixture_of_experts(g):
     El = E // W
     wgu_l, wd_l = wgu[rank * El:(rank + 1) * El].contiguous(), wd[rank * El:(rank + 1) * El].contiguous()
     ep = moe.FusedMoE(g, E, k, H, I, max_tokens=4096)
-    one = moe.FusedMoE(single_group(dev), E, k, H, I, max_tokens=8192)
+    one = moe.FusedMoE(single_group(dev), E, k, H, I, max_tokens=max(8192, 1500 * W))
     for T in (1, 33, 1500):
         x_all = torch.randn(W * T, H, device=dev, generator=gen).bfloat16()       # same on every rank (same seed)
         lg_all = torch.randn(W * T, E, device=dev, generator=gen) * 2
