@@ -714,3 +714,70 @@ def kv_copy_pages(dst: torch.Tensor, src: torch.Tensor, src_pages: torch.Tensor,
                                   dst.shape[1], src.shape[1], src_pages.data_ptr(), dst_pages.data_ptr(), _stream()),
              "cs_kv_copy_pages")
     _count()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# fp8 (e4m3) linear layers with block scales: 1 x 128 blocks of the activations, 128 x 128 blocks of the weight
+# ---------------------------------------------------------------------------------------------------------
+FP8_MAX = 448.0
+
+
+def quantize_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``w`` ``[N, K]`` (``K % 128 == 0``) -> ``(wq [N, K] float8_e4m3fn, scales [ceil(N/128), K/128] fp32)``; done once
+    per checkpoint, so plain tensor ops."""
+    N, K = w.shape
+    assert K % 128 == 0
+    nb = -(-N // 128)
+    wp = torch.zeros((nb * 128, K), device=w.device, dtype=torch.float32)
+    wp[:N] = w.float()
+    blocks = wp.view(nb, 128, K // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3))
+    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).view(nb * 128, K)[:N]
+    return q.to(torch.float8_e4m3fn).contiguous(), scale.contiguous()
+
+
+def quantize_fp8_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``x`` ``[M, K]`` bf16 -> ``(xq [M, K] float8_e4m3fn, scales [K/128, M] fp32)``: one scale per row and 128 columns."""
+    M, K = x.shape
+    assert K % 128 == 0
+    if not x.is_cuda:
+        b = x.float().view(M, K // 128, 128)
+        amax = b.abs().amax(dim=2)
+        scale = torch.where(amax > 0, amax * (1.0 / FP8_MAX), torch.ones_like(amax))  # same arithmetic as the kernel
+        q = (b * (1.0 / scale)[:, :, None]).clamp(-FP8_MAX, FP8_MAX).view(M, K).to(torch.float8_e4m3fn)
+        return q, scale.t().contiguous()
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    q = torch.empty((M, K), device=x.device, dtype=torch.float8_e4m3fn)
+    scales = torch.empty((K // 128, M), device=x.device, dtype=torch.float32)
+    lib = _lib.load()
+    _chk(lib.cs_quant_fp8_rows(x.data_ptr(), x.stride(0), M, K, q.data_ptr(), q.stride(0), scales.data_ptr(), scales.stride(0),
+                               _stream()), "cs_quant_fp8_rows")
+    _count()
+    return q, scales
+
+
+def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, bias: torch.Tensor | None = None,
+               xq: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+    """``x @ dequant(wq).T + bias`` with the activations quantised on the fly (or given as ``xq``): the product of every
+    128-wide K block is scaled and summed in fp32 by the GEMM kernel itself.  Returns bf16 (fp32 on the CPU)."""
+    M, K = x.shape
+    N = wq.shape[0]
+    q, sa = xq if xq is not None else quantize_fp8_rows(x)
+    if not x.is_cuda:
+        a = (q.float().view(M, K // 128, 128) * sa.t()[:, :, None]).view(M, K)
+        nb = w_scale.shape[0]
+        wp = torch.zeros((nb * 128, K), dtype=torch.float32)
+        wp[:N] = wq.float()
+        w = (wp.view(nb, 128, K // 128, 128) * w_scale[:, None, :, None]).view(nb * 128, K)[:N]
+        y = a @ w.t()
+        return y if bias is None else y + bias.float()
+    _on_current_device(x)
+    assert wq.dtype == torch.float8_e4m3fn and wq.is_contiguous() and w_scale.is_contiguous() and w_scale.dtype == torch.float32
+    out = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+    lib = _lib.load()
+    _chk(lib.cs_gemm_fp8_blockscaled(q.data_ptr(), q.stride(0), wq.data_ptr(), wq.stride(0), sa.data_ptr(), sa.stride(0),
+                                     w_scale.data_ptr(), out.data_ptr(), out.stride(0), _ptr(bias), M, N, K, _stream()),
+         "cs_gemm_fp8_blockscaled")
+    _count()
+    return out

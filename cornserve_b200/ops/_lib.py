@@ -54,6 +54,8 @@ _SIGNATURES = {
     "cs_im2col1d": ([P, P, I, I, I, I, I, I, I, I, I, P, P, P], I),
     "cs_dwconv1d": ([P, P, P, P, I, I, I, I, P], I),
     "cs_bilinear_embed_add": ([P, L, P, L, P, P, L, I, P], I),
+    "cs_gemm_fp8_blockscaled": ([P, L, P, L, P, L, P, P, L, P, I, I, I, P], I),
+    "cs_quant_fp8_rows": ([P, L, I, I, P, L, P, L, P], I),
     "cs_kv_copy_pages": ([P, P, L, L, L, I, I, I, I, P, P, P], I),
     "cs_enable_peer_access": ([I], I),
     "cs_to_rgb8": ([P, L, P, L, P], I),

@@ -7,6 +7,7 @@
   python -m cornserve_b200.ops.microbench attn-full 16 80 4784 0   # heads, head_dim, length, causal
   python -m cornserve_b200.ops.microbench attn-decode 48 3500      # sequences, context
   python -m cornserve_b200.ops.microbench norm 19136 1280
+  python -m cornserve_b200.ops.microbench gemm-fp8 16384 3584 3584 # e4m3 with 1x128 / 128x128 block scales
   python -m cornserve_b200.ops.microbench moe 128 128 8 2048 768   # tokens, experts, top-k, hidden, expert FFN width
 
 Each line printed gives the time per launch, the achieved rate and the fraction of the measured peak
@@ -131,6 +132,15 @@ def main() -> None:
         x, r, w = rnd(rows, H), rnd(rows, H), rnd(H)
         secs = t(lambda: ops.rms_norm(x, w, 1e-6, residual=r))
         report(f"rms_norm+residual {rows}x{H}", secs, 0.0, 2.0 * 4 * rows * H)
+    elif k == "gemm-fp8":
+        M, N, K = a.args[:3]
+        x = rnd(M, K)
+        wq, ws = ops.quantize_fp8_weight(rnd(N, K, std=K ** -0.5))
+        xq = ops.quantize_fp8_rows(x)
+        secs = t(lambda: ops.linear_fp8(x, wq, ws, xq=xq))
+        report(f"gemm-fp8 {M}x{N}x{K} (operands already quantised)", secs, 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N)
+        secs = t(lambda: ops.quantize_fp8_rows(x))
+        report(f"quantise rows {M}x{K}", secs, 0.0, 3.0 * M * K)
     elif k == "moe":
         from cornserve_b200.parallel.moe import FusedMoE
         from cornserve_b200.parallel.state import single_group

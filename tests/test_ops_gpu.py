@@ -474,3 +474,32 @@ def test_kv_page_copy_is_byte_exact():
     with pytest.raises(RuntimeError):
         ops.check_error("kv copy with a bad page")
     assert torch.equal(dst.view(torch.int16), before.view(torch.int16))
+
+
+# ------------------------------------------------------------------------------------------------
+# fp8 block-scaled GEMM
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(5, 256, 512), (128, 384, 1024), (300, 200, 256), (1000, 3584, 3584)])
+def test_fp8_blockscaled_linear(M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = (torch.randn(M, K, device="cuda", generator=g) * (1 + 3 * torch.rand(M, 1, device="cuda", generator=g))).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g).bfloat16()
+    wq, ws = ops.quantize_fp8_weight(w)
+    xq, xs = ops.quantize_fp8_rows(x)
+    # the quantiser against its restatement on the CPU
+    xq_c, xs_c = ops.quantize_fp8_rows(x.cpu())
+    assert torch.allclose(xs.cpu(), xs_c, rtol=1e-6, atol=0)
+    assert (xq.float().cpu() - xq_c.float()).abs().max().item() <= 32.0  # at most one e4m3 step at the top of the range
+    assert (xq.float().cpu() != xq_c.float()).float().mean().item() < 1e-3
+    got = ops.linear_fp8(x, wq, ws, bias, xq=(xq, xs)).float().cpu()
+    torch.cuda.synchronize()
+    ops.check_error("fp8 gemm")
+    # exact oracle: the same quantised operands, dequantised and multiplied in fp32 on the CPU
+    want = ops.linear_fp8(x.cpu(), wq.cpu(), ws.cpu(), bias.cpu(), xq=(xq.cpu(), xs.cpu()))
+    err = (got - want).abs().max().item()
+    assert err < 0.01 * want.abs().max().item() + 0.02, err
+    # and it is a faithful 8-bit approximation of the bf16 layer
+    ref = x.float().cpu() @ w.float().cpu().t() + bias.float().cpu()
+    rel = (got - ref).norm().item() / ref.norm().item()
+    assert rel < 0.06, rel
