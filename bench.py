@@ -214,9 +214,11 @@ def main() -> None:
             },
             "clocks": clocks,
             "e2e": {"value": total_req / (e2e_ms / 1e3), "unit": "req/s", "ms_per_step": e2e_ms / args.steps,
-                    "h2d_bytes_per_step": pipe.h2d_bytes // args.steps, "d2h_bytes_per_step": pipe.d2h_bytes // args.steps,
+                    # whole job, like `value`: every rank copies its own batch (the ranks' batches have the same shape)
+                    "h2d_bytes_per_step": world * pipe.h2d_bytes // args.steps,
+                    "d2h_bytes_per_step": world * pipe.d2h_bytes // args.steps,
                     "api": "cornserve_b200.pipelines.MLLMPipeline.generate"},
-            "gpu_launches": launches,
+            "gpu_launches": launches * world,
             "output_tokens_per_second": total_req * out_tok / (dev_ms / 1e3),
         }
         print(json.dumps(line))
