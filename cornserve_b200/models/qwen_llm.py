@@ -49,6 +49,7 @@ class LLMConfig:
     num_experts_per_tok: int = 8
     moe_intermediate_size: int = 768
     norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0   # > 0: a dense expert with a sigmoid gate runs beside the routed ones
     # multimodal placeholder token ids (used by the executor to place encoder embeddings)
     image_token_id: int = 151655
     video_token_id: int = 151656
@@ -166,8 +167,19 @@ class SparseMoE(nn.Module):
                                       .normal_(0, 0.02), requires_grad=False)
         self.w_down = nn.Parameter(torch.empty(self.e_local, H, inter, device=device, dtype=torch.bfloat16)
                                    .normal_(0, 0.02), requires_grad=False)
+        self.shared = None
+        if cfg.shared_expert_intermediate_size > 0:
+            self.shared = MLP(cfg, group, device, intermediate=cfg.shared_expert_intermediate_size)
+            self.shared_gate = Linear(H, 1, bias=False, device=device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self._routed(x)
+        if self.shared is None:
+            return y
+        g = torch.sigmoid(torch.nn.functional.linear(x.float(), self.shared_gate.weight.float()))  # [T, 1]: too narrow for a tile
+        return torch.addcmul(y.float(), g, self.shared(x).float()).to(x.dtype)
+
+    def _routed(self, x: torch.Tensor) -> torch.Tensor:
         from ..parallel import moe
 
         logits = self.router(x, out_dtype=torch.float32)
@@ -269,10 +281,14 @@ class QwenLLM(nn.Module):
             ops.scatter_rows_(x, idx, rows)
         return x
 
-    def forward_hidden(self, m: BatchMeta, kv_caches: list[torch.Tensor]) -> torch.Tensor:
-        """Final-norm hidden states of every token ``[T, H]``."""
+    def forward_hidden(self, m: BatchMeta, kv_caches: list[torch.Tensor], capture: dict[int, torch.Tensor] | None = None) -> torch.Tensor:
+        """Final-norm hidden states of every token ``[T, H]``.  ``capture``: keys are indices into the sequence
+        "embeddings, output of layer 0, output of layer 1, ..." (un-normalised residual stream); the tensors are
+        filled in."""
         cfg = self.cfg
         x = self.embed(m)
+        if capture is not None and 0 in capture:
+            capture[0] = x.clone()
         half = cfg.head_dim // 2
         sections = cfg.mrope_section or [half, 0, 0]
         cs = ops.mrope_table(m.positions, half, cfg.rope_theta, sections)
@@ -283,6 +299,8 @@ class QwenLLM(nn.Module):
         for i, (layer, cache) in enumerate(zip(self.layers, kv_caches)):
             next_norm = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
             h, residual = layer(h, residual, cs, cache, m, next_norm, fused)
+            if capture is not None and i + 1 in capture:
+                capture[i + 1] = residual.clone()
         return h
 
     def _fused_tail(self):
@@ -351,6 +369,18 @@ class QwenLLM(nn.Module):
                     layer.mlp.down.load(**kw)
                 elif sub == "mlp.gate":
                     layer.mlp.router.load(weight=t)
+                elif sub == "mlp.shared_expert_gate":
+                    layer.mlp.shared_gate.weight.data.copy_(t)
+                elif sub in ("mlp.shared_expert.gate_proj", "mlp.shared_expert.up_proj"):
+                    layer.mlp.shared.gate_up.load("gate" if "gate_proj" in sub else "up", **kw)
+                elif sub == "mlp.shared_expert.down_proj":
+                    layer.mlp.shared.down.load(**kw)
+                elif n.endswith("mlp.experts.gate_up_proj") or n.endswith("mlp.experts.down_proj"):
+                    # stacked form: [E, 2I, H] (gate rows then up rows) and [E, H, I]
+                    moe_l: SparseMoE = layer.mlp
+                    lo = moe_l.group.rank * moe_l.e_local
+                    dst = moe_l.w_gate_up if leaf == "gate_up_proj" else moe_l.w_down
+                    dst.data.copy_(t[lo: lo + moe_l.e_local])
                 elif sub.startswith("mlp.experts."):
                     e = int(p[4])
                     moe: SparseMoE = layer.mlp
