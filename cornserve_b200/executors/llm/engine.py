@@ -84,6 +84,7 @@ class Sequence:
     params: SamplingParams = field(default_factory=SamplingParams)
     mm_items: list[MMItem] = field(default_factory=list)
     return_hidden: bool = False
+    capture_layers: tuple[int, ...] = ()    # return these points of the residual stream instead (0 = embeddings, i = after layer i-1)
     hold_kv: bool = False                   # keep the pages after finishing (prefill half of a disaggregated pair)
     prefilled: PrefilledKV | None = None    # the prompt's KV comes from another executor (decode half)
     kv_source: str | None = None            # "mapped" (peer copy kernel) or "network" once prefilled was consumed
@@ -339,8 +340,10 @@ class LLMEngine:
             m.mm_embeds = mm_rows  # placed row by row by the scatter kernel, from wherever they live
             m.mm_index = [f(i) for i in mm_idx]
         want_hidden = any(s.return_hidden for s, _ in batch)
+        cap_layers = sorted({layer for s, _ in batch for layer in s.capture_layers})
+        capture = dict.fromkeys(cap_layers) if cap_layers else None
         with torch.inference_mode():
-            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden)
+            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden, capture=capture)
         toks = next_tok.tolist()
         self.stats["prefill_tokens"] += tok
         outs: list[StepOutput] = []
@@ -349,7 +352,9 @@ class LLMEngine:
             s.num_computed += n
             if s not in self.running:
                 self.running.append(s)
-            if s.return_hidden and hidden is not None:
+            if s.capture_layers:
+                s.hidden_chunks.append(torch.cat([capture[layer][cu[b]: cu[b + 1]] for layer in s.capture_layers], dim=1))
+            elif s.return_hidden and hidden is not None:
                 s.hidden_chunks.append(hidden[cu[b]: cu[b + 1]])
             if s.num_computed < s.prompt_len:
                 continue
@@ -464,7 +469,7 @@ class LLMEngine:
         hidden = None
         if done:
             s.status = SeqStatus.FINISHED
-            if s.return_hidden and s.hidden_chunks:
+            if (s.return_hidden or s.capture_layers) and s.hidden_chunks:
                 hidden = torch.cat(s.hidden_chunks, dim=0)
         return StepOutput(s.seq_id, new, done, s.finish_reason, hidden)
 

@@ -178,7 +178,8 @@ class AsyncLLM:
 
 def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -> tuple[LLMEngine, dict[str, Any]]:
     hf_cfg = load_config(args.model)
-    cfg = LLMConfig.from_hf(hf_cfg)
+    # any-to-any checkpoints keep their language model under "thinker"
+    cfg = LLMConfig.from_hf(hf_cfg.get("thinker_config") or hf_cfg)
     device = group.device if group is not None else pick_device()
     if device.type == "cuda":
         torch.cuda.set_device(device)
@@ -186,8 +187,9 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
     model = QwenLLM(cfg, group=group, device=device)
     if device.type == "cpu":
         model = model.float()  # the CUDA kernels are bf16; fp32 is the CPU restatement's precision
-    load_model_weights(model, args.model, ["model.language_model.", "language_model.", "model.", "lm_head.", ""],
-                       strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower."])
+    load_model_weights(model, args.model, ["thinker.model.", "thinker.", "model.language_model.", "language_model.", "model.", "lm_head.", ""],
+                       strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower.", "thinker.visual.", "thinker.audio_tower.",
+                                                       "talker.", "code2wav."])
     model.eval()
     pages = args.num_kv_pages
     if pages <= 0:
@@ -209,7 +211,8 @@ class LLMServer:
         self.engine, self.hf_cfg = build_engine(args)
         self.llm = AsyncLLM(self.engine)
         self.cfg = self.engine.mcfg
-        self.tokenizer = load_tokenizer(args.model, self.hf_cfg, self.cfg.vocab_size)
+        self.tokenizer = load_tokenizer(args.model, {**(self.hf_cfg.get("thinker_config") or {}), **self.hf_cfg}, self.cfg.vocab_size)
+        self.omni_cfg = self.hf_cfg if "talker_config" in self.hf_cfg else None
         self.receive_embeddings = os.environ.get("CORNSERVE_VLLM_DISABLE_MULTIMODAL") == "1"
         self.sidecar = None
         if args.cornserve_sidecar_ranks:
@@ -434,6 +437,47 @@ class LLMServer:
                        prefilled=pf)
         return seq, await self._sidecar_parts(body)
 
+    async def _omni_thinker_forward(self, seq: Sequence, queue: asyncio.Queue, xargs: dict[str, Any], rid: str, created: int, model: str):
+        """Thinker half of a spoken answer: generate the text, then run the whole conversation (prompt + answer) once more
+        to capture what the talker conditions on (token embeddings and the hidden states of the accepted layer), and forward
+        that view together with the embeddings of the TTS control tokens (:func:`models.omni_talker.pack_thinker_view`)."""
+        from ...models.omni_talker import pack_thinker_view
+
+        tokens: list[int] = []
+        while True:
+            out: StepOutput = await queue.get()
+            tokens.extend(out.new_token_ids)
+            if out.finished:
+                break
+        if (out.finish_reason or "").startswith("error"):
+            return JSONResponse({"error": {"message": out.finish_reason}}, status_code=500)
+        tc = self.omni_cfg["talker_config"]
+        full = np.concatenate([seq.prompt_ids, np.asarray(tokens, dtype=np.int32)])
+        view_seq = Sequence(seq.seq_id + "-view", full, SamplingParams(max_tokens=1, ignore_eos=True), mm_items=seq.mm_items,
+                            capture_layers=(0, int(tc.get("accept_hidden_layer", 18))))
+        q2 = self.llm.submit(view_seq)
+        while True:
+            out2: StepOutput = await q2.get()
+            if out2.finished:
+                break
+        if out2.hidden is None:
+            return JSONResponse({"error": {"message": out2.finish_reason or "no hidden states"}}, status_code=500)
+        H = self.cfg.hidden_size
+        tts_ids = [int(self.omni_cfg.get(k, d)) for k, d in (("tts_bos_token_id", 151672), ("tts_eos_token_id", 151673),
+                                                            ("tts_pad_token_id", 151671))]
+        dev = self.engine.device
+        tts = await asyncio.wrap_future(self.llm.call(
+            lambda: self.engine.model.embed_tokens(torch.tensor(tts_ids, dtype=torch.int32, device=dev))))
+        rows = pack_thinker_view(full, out2.hidden[:, :H], out2.hidden[:, H:], tts)
+        ranks = ast.literal_eval(xargs.get("cornserve_hidden_states_forward_ranks", "[]")) or []
+        if ranks and self.sidecar is not None:
+            self.sidecar.send(rows.contiguous(), id=xargs["cornserve_hidden_states_forward_id"], dst_sidecar_ranks=ranks)
+            await asyncio.to_thread(self.sidecar.flush)
+        return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
+                             "choices": [{"index": 0, "message": {"role": "assistant", "content": self.tokenizer.decode(tokens)},
+                                          "finish_reason": out.finish_reason}],
+                             "cornserve": {"hidden_states_rows": int(rows.shape[0])}})
+
     # -- request handling ---------------------------------------------------------------------------------------
     async def chat(self, body: dict[str, Any]):
         xargs = body.get("vllm_xargs") or {}
@@ -460,7 +504,16 @@ class LLMServer:
             seq.hold_kv = True
             seq.params.max_tokens = 1
         created, rid, model = int(time.time()), f"chatcmpl-{seq.seq_id}", body.get("model", self.args.model)
+        omni_view = "cornserve_hidden_states_forward_id" in xargs and self.omni_cfg is not None and kv_in is None
+        if omni_view:
+            seq.return_hidden = False   # the answer is generated first; the talker's view is captured in a second pass
+            held_ids, recv_ids = recv_ids, []   # the encoder rows are needed again by that pass: release them afterwards
         queue = self.llm.submit(seq)
+        if omni_view:
+            try:
+                return await self._omni_thinker_forward(seq, queue, xargs, rid, created, model)
+            finally:
+                await self._release(held_ids)
         include_usage = bool((body.get("stream_options") or {}).get("include_usage", False))
 
         def chunk(delta: dict[str, Any], finish: str | None = None, usage: dict | None = None) -> str:
@@ -604,7 +657,12 @@ class LLMServer:
 def main(argv: list[str] | None = None) -> None:
     args = parse_args(argv)
     configure_otel("llm")
-    server = LLMServer(args)
+    if args.run_talker:
+        from .talker_server import TalkerServer
+
+        server = TalkerServer(args)
+    else:
+        server = LLMServer(args)
     try:
         uvicorn.run(server.create_app(), host=args.host, port=args.port, log_level="warning")
     finally:

@@ -65,6 +65,31 @@ class TalkerConfig:
                    speaker_id=dict(cfg.get("speaker_id") or {}), **kw)
 
 
+def pack_thinker_view(token_ids: np.ndarray, embeds: torch.Tensor, hidden: torch.Tensor, tts_embeds: torch.Tensor) -> torch.Tensor:
+    """What the thinker executor forwards to the talker executor, as one tensor (the forwarding path carries tensors of
+    one dtype, in slots of the thinker's hidden width ``H``): per token ``[embedding | hidden state of the accepted layer |
+    token id digits, zero padded to H]``, followed by three rows whose embedding part holds the thinker's embeddings of
+    the TTS bos / eos / pad tokens.  Ids travel as base-256 digits, which are exact in bf16."""
+    T, H = embeds.shape
+    rows = torch.zeros((T + 3, 3 * H), device=embeds.device, dtype=embeds.dtype)
+    rows[:T, :H] = embeds
+    rows[:T, H: 2 * H] = hidden
+    ids = torch.from_numpy(np.asarray(token_ids, dtype=np.int64)).to(embeds.device)
+    for d in range(3):
+        rows[:T, 2 * H + d] = ((ids >> (8 * d)) & 255).to(embeds.dtype)
+    rows[T:, :H] = tts_embeds
+    return rows
+
+
+def unpack_thinker_view(rows: torch.Tensor) -> tuple[np.ndarray, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Inverse of :func:`pack_thinker_view`: ``(token_ids, embeds, hidden, tts_embeds)``."""
+    H = rows.shape[1] // 3
+    T = rows.shape[0] - 3
+    digits = rows[:T, 2 * H: 2 * H + 3].float().round().long().cpu()
+    ids = (digits[:, 0] + (digits[:, 1] << 8) + (digits[:, 2] << 16)).numpy()
+    return ids, rows[:T, :H], rows[:T, H: 2 * H], rows[T:, :H]
+
+
 class ResizeMLP(nn.Module):
     def __init__(self, d_in: int, d_mid: int, d_out: int, device):
         super().__init__()
@@ -121,14 +146,17 @@ class Talker(nn.Module):
                      speaker: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """From the thinker's view of the whole conversation (prompt + answer): ``token_ids`` ``[T]``, token embeddings and
         hidden states of the accepted layer ``[T, thinker_hidden]``, the embeddings of the TTS bos / eos / pad tokens
-        ``[3, thinker_hidden]``.  ``special`` holds the ids of ``im_start``, ``system``, ``user``, ``assistant`` and the
-        multimodal placeholder tokens.  Returns ``(prefill [P, D], trailing_text [n, D], tts_pad [D])``."""
+        ``[3, thinker_hidden]``.  ``special`` holds the ids of ``im_start``, ``system``, ``user``, ``assistant`` (the token
+        that follows ``im_start``), the multimodal placeholder tokens and optionally ``assistant_header`` (tokens of
+        ``<|im_start|>assistant\n``: 3 with the checkpoint's tokenizer).  Returns ``(prefill [P, D], trailing_text
+        [n, D], tts_pad [D])``."""
         cfg = self.cfg
         ids = np.asarray(token_ids)
         T = ids.shape[0]
         starts = [int(i) for i in np.nonzero(ids == special["im_start"])[0]] + [T]
         mm = np.isin(ids, list(special["multimodal"]))
         tts_bos, tts_eos, tts_pad = self.text_projection(tts.to(self.dtype)).unbind(0)
+        hd = int(special.get("assistant_header", 3))
         parts: list[torch.Tensor] = []
         trailing = tts_eos[None]
         for i in range(len(starts) - 1):
@@ -146,15 +174,15 @@ class Talker(nn.Module):
                 parts.append(part)
             elif role == special["assistant"] and i == len(starts) - 2:
                 a = self.text_projection(embeds[lo:hi].to(self.dtype))
-                if a.shape[0] < 4:
+                if a.shape[0] < hd + 1:
                     raise ValueError("the assistant turn must hold its header and at least one answer token")
-                text = torch.cat([a[:3], tts_pad[None].expand(4, -1), tts_bos[None], a[3:4]])
+                text = torch.cat([a[:hd], tts_pad[None].expand(4, -1), tts_bos[None], a[hd: hd + 1]])
                 codec_ids = torch.tensor([cfg.codec_nothink_id, cfg.codec_think_bos_id, cfg.codec_think_eos_id, speaker,
                                           cfg.codec_pad_id, cfg.codec_bos_id], device=self.device)
-                codec = torch.cat([torch.zeros((3, a.shape[1]), device=self.device, dtype=self.dtype),
+                codec = torch.cat([torch.zeros((hd, a.shape[1]), device=self.device, dtype=self.dtype),
                                    self.decoder.embed_tokens(codec_ids.to(torch.int32))])
                 parts.append(text + codec)
-                trailing = torch.cat([a[4:], tts_eos[None]])
+                trailing = torch.cat([a[hd + 1:], tts_eos[None]])
         if not parts:
             raise ValueError("no user or assistant turn found in the thinker's tokens")
         return torch.cat(parts), trailing, tts_pad
@@ -163,8 +191,9 @@ class Talker(nn.Module):
     @torch.inference_mode()
     def generate(self, prefill: torch.Tensor, trailing: torch.Tensor, tts_pad: torch.Tensor, max_frames: int = 2048,
                  sample: bool = True, temperature: float = 0.9, top_k: int = 50, top_p: float = 1.0,
-                 generator: torch.Generator | None = None) -> Iterator[torch.Tensor]:
-        """Yields one frame of codes ``[num_code_groups]`` (int64) per step until the codec end token."""
+                 generator: torch.Generator | None = None, min_frames: int = 0) -> Iterator[torch.Tensor]:
+        """Yields one frame of codes ``[num_code_groups]`` (int64) per step until the codec end token (which cannot be
+        drawn during the first ``min_frames`` frames)."""
         cfg, dev = self.cfg, self.device
         G = cfg.num_code_groups
         total = prefill.shape[0] + max_frames + 1
@@ -178,6 +207,9 @@ class Talker(nn.Module):
         allowed[: min(cfg.predictor.vocab_size, cfg.text.vocab_size)] = True
         if cfg.codec_eos_token_id < cfg.text.vocab_size:
             allowed[cfg.codec_eos_token_id] = True
+        no_eos = allowed.clone()
+        if cfg.codec_eos_token_id < cfg.text.vocab_size:
+            no_eos[cfg.codec_eos_token_id] = False
 
         def pick(logits: torch.Tensor, mask: torch.Tensor | None, k: int, p: float) -> int:
             logits = logits.float().flatten()
@@ -206,7 +238,7 @@ class Talker(nn.Module):
         h = step(self.decoder, kv, prefill, 0, pages)[-1:]
         pos = prefill.shape[0]
         for frame in range(max_frames):
-            code0 = pick(self.decoder.compute_logits(h), allowed, top_k, top_p)
+            code0 = pick(self.decoder.compute_logits(h), allowed if frame >= min_frames else no_eos, top_k, top_p)
             if code0 == cfg.codec_eos_token_id:
                 return
             e0 = self.decoder.embed_tokens(torch.tensor([code0], dtype=torch.int32, device=dev))

@@ -319,9 +319,10 @@ class QwenLLM(nn.Module):
             logits = self.group.all_gather(logits, dim=-1)
         return logits[:, : self.cfg.vocab_size]
 
-    def forward(self, m: BatchMeta, kv_caches: list[torch.Tensor], return_hidden: bool = False):
+    def forward(self, m: BatchMeta, kv_caches: list[torch.Tensor], return_hidden: bool = False,
+                capture: dict[int, torch.Tensor] | None = None):
         """Returns ``(next_token_ids [B] int32, hidden [T, H] or None)`` (greedy)."""
-        h = self.forward_hidden(m, kv_caches)
+        h = self.forward_hidden(m, kv_caches, capture)
         h_last = ops.gather_rows(h, m.logits_idx)
         logits = self.compute_logits(h_last)
         return ops.argmax(logits), (h if return_hidden else None)

@@ -64,6 +64,32 @@ BUILTIN_CONFIGS: dict[str, dict[str, Any]] = {
         "audio_config": {"num_mel_bins": 128, "d_model": 64, "encoder_layers": 1, "encoder_attention_heads": 2,
                          "encoder_ffn_dim": 64, "max_source_positions": 200, "n_window": 50, "output_dim": 96,
                          "downsample_hidden_size": 8, "n_window_infer": 400}}},
+    # thinker (MoE decoder + encoders) + talker + vocoder of a Qwen3-Omni-shaped model, small enough for CPU tests
+    "cornserve-b200/tiny-omni": {
+        "model_type": "qwen3_omni_moe", "torch_dtype": "float32", "tts_bos_token_id": 500, "tts_eos_token_id": 501,
+        "tts_pad_token_id": 502,
+        "thinker_config": {
+            "text_config": {"model_type": "qwen3_omni_moe_text", "hidden_size": 128, "num_hidden_layers": 2, "num_attention_heads": 2,
+                            "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 128, "vocab_size": 512, "num_experts": 4,
+                            "num_experts_per_tok": 2, "moe_intermediate_size": 64, "rope_theta": 10000.0},
+            "vision_config": {"depth": 1, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "out_hidden_size": 128,
+                              "num_position_embeddings": 16, "deepstack_visual_indexes": [0], "patch_size": 16},
+            "audio_config": {"num_mel_bins": 128, "d_model": 64, "encoder_layers": 1, "encoder_attention_heads": 2,
+                             "encoder_ffn_dim": 64, "max_source_positions": 200, "n_window": 50, "output_dim": 128,
+                             "downsample_hidden_size": 8, "n_window_infer": 400}},
+        "talker_config": {
+            "thinker_hidden_size": 128, "accept_hidden_layer": 1, "num_code_groups": 4, "codec_eos_token_id": 70,
+            "codec_nothink_id": 71, "codec_think_bos_id": 72, "codec_think_eos_id": 73, "codec_pad_id": 74, "codec_bos_id": 75,
+            "speaker_id": {"ethan": 80},
+            "text_config": {"vocab_size": 96, "hidden_size": 128, "intermediate_size": 64, "num_hidden_layers": 2,
+                            "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 64, "moe_intermediate_size": 64,
+                            "num_experts_per_tok": 2, "num_experts": 4, "shared_expert_intermediate_size": 64, "rope_theta": 10000.0},
+            "code_predictor_config": {"vocab_size": 32, "hidden_size": 128, "intermediate_size": 128, "num_hidden_layers": 2,
+                                      "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 64, "num_code_groups": 4,
+                                      "rope_theta": 10000.0}},
+        "code2wav_config": {"codebook_size": 32, "hidden_size": 64, "num_attention_heads": 2, "num_key_value_heads": 2,
+                            "sliding_window": 6, "intermediate_size": 128, "num_hidden_layers": 2, "num_quantizers": 4,
+                            "upsample_rates": [3, 2, 2, 2], "upsampling_ratios": [2, 2], "decoder_dim": 128}},
     "cornserve-b200/tiny-qwen2.5-omni": {"model_type": "qwen2_5_omni", "torch_dtype": "float32", "thinker_config": {
         "vision_config": {"depth": 1, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "out_hidden_size": 96,
                           "fullatt_block_indexes": [0]},

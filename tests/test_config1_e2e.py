@@ -113,7 +113,11 @@ def test_gpu_plumbing_across_gpus(tmp_path, monkeypatch, app):
     assert texts[4] == _expected_text("describe picture 1", "synthetic:224x224:1", 16, device="cuda")
 
 
-def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu"):
+def _text_of(chunks):
+    return "".join((ch["choices"][0]["delta"].get("content") or "") for ch in chunks if ch.get("choices"))
+
+
+def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu", collect=_text_of):
     base = _port_block(16)
     ns = uuid.uuid4().hex[:8]
     monkeypatch.delenv("CORNSERVE_DEVICE", raising=False)
@@ -181,7 +185,7 @@ def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu"):
                         assert resp.status == 200, await resp.text()
                         chunks = [json.loads(l) async for l in resp.content if l.strip()]
                     assert all("error" not in ch for ch in chunks), chunks
-                    return "".join((ch["choices"][0]["delta"].get("content") or "") for ch in chunks if ch.get("choices"))
+                    return collect(chunks)
 
                 texts = await asyncio.gather(*(ask(i) for i in range(4)))
                 if device == "cpu":
