@@ -27,7 +27,7 @@ IMAGE_PROMPT_SKIP_TOKENS = 34
 
 def _build_llm(model_id: str, device: torch.device, pages: int = 256) -> tuple[LLMEngine, Any, dict]:
     hf_cfg = load_config(model_id)
-    cfg = LLMConfig.from_hf(hf_cfg)
+    cfg = LLMConfig.from_hf(hf_cfg.get("thinker_config") or hf_cfg)
     llm = QwenLLM(cfg, device=device)
     if device.type == "cpu":  # the CUDA kernels are bf16
         llm = llm.float()
@@ -35,7 +35,7 @@ def _build_llm(model_id: str, device: torch.device, pages: int = 256) -> tuple[L
                        strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower.", "audio_tower."])
     llm.eval()
     engine = LLMEngine(llm, EngineConfig(num_pages=pages, decode_burst=4, max_model_len=8192, use_cuda_graph=device.type == "cuda"))
-    return engine, load_tokenizer(model_id, hf_cfg, cfg.vocab_size), hf_cfg
+    return engine, load_tokenizer(model_id, {**(hf_cfg.get("thinker_config") or {}), **hf_cfg}, cfg.vocab_size), hf_cfg
 
 
 class QwenImageMonolith:
@@ -64,22 +64,72 @@ class QwenImageMonolith:
 
 
 class QwenOmniMonolith:
-    """Thinker served in-process; yields OpenAI-style text chunks.  Spoken answers need the talker, which this
-    baseline does not include."""
+    """Thinker, talker and vocoder in one process; yields OpenAI-style chunks: the text first, then (when asked) the
+    spoken answer as base64 PCM16 in ``delta.audio.data``."""
 
     def __init__(self, model_id: str, device: torch.device):
-        self.model_id = model_id
-        self.engine, self.tok, _ = _build_llm(model_id, device)
+        self.model_id, self.device = model_id, device
+        self.engine, self.tok, self.hf_cfg = _build_llm(model_id, device)
+        self.talker = self.vocoder = None
+        if "talker_config" in self.hf_cfg:
+            from ...models.code2wav import Code2Wav, Code2WavConfig
+            from ...models.omni_talker import Talker, TalkerConfig
+            from ..llm.talker_server import special_tokens
 
-    def generate(self, messages: list[dict], max_tokens: int, ignore_eos: bool, return_audio: bool) -> Iterator[dict]:
-        if return_audio:
-            raise NotImplementedError("the monolithic omni baseline produces text only (return_audio must be false)")
-        ids, _ = self.tok.render_chat(messages)
-        rid = uuid.uuid4().hex
-        self.engine.add_request(Sequence(rid, np.asarray(ids, dtype=np.int32), SamplingParams(max_tokens, ignore_eos)))
-        created = int(time.time())
+            torch.manual_seed(1)
+            self.talker = Talker(TalkerConfig.from_hf(self.hf_cfg["talker_config"]), device=device)
+            self.vocoder = Code2Wav(Code2WavConfig.from_hf(self.hf_cfg.get("code2wav_config") or {}), device=device)
+            if device.type == "cpu":
+                self.talker.float()
+                self.vocoder.float()
+            load_model_weights(self.talker, model_id, ["talker."], strict=False)
+            load_model_weights(self.vocoder, model_id, ["code2wav."], strict=False)
+            self.special = special_tokens(self.hf_cfg, self.tok)
+
+    def _run(self, seq: Sequence):
+        self.engine.add_request(seq)
         while self.engine.has_work():
-            for out in self.engine.step():
-                text = self.tok.decode(out.new_token_ids)
-                yield {"id": rid, "object": "chat.completion.chunk", "created": created, "model": self.model_id,
-                       "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": out.finish_reason if out.finished else None}]}
+            yield from self.engine.step()
+
+    def generate(self, messages: list[dict], max_tokens: int, ignore_eos: bool, return_audio: bool, greedy_audio: bool = False,
+                 min_audio_frames: int = 0) -> Iterator[dict]:
+        if return_audio and self.talker is None:
+            raise NotImplementedError(f"{self.model_id} has no talker: it produces text only (return_audio must be false)")
+        ids, _ = self.tok.render_chat(messages)
+        rid, created = uuid.uuid4().hex, int(time.time())
+        prompt = np.asarray(ids, dtype=np.int32)
+
+        def chunk(delta: dict, finish=None) -> dict:
+            return {"id": rid, "object": "chat.completion.chunk", "created": created, "model": self.model_id,
+                    "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+
+        tokens: list[int] = []
+        for out in self._run(Sequence(rid, prompt, SamplingParams(max_tokens, ignore_eos))):
+            tokens.extend(out.new_token_ids)
+            yield chunk({"content": self.tok.decode(out.new_token_ids)}, out.finish_reason if out.finished and not return_audio else None)
+        if not return_audio:
+            return
+        import base64
+
+        from ... import ops
+        from ...models.omni_talker import pack_thinker_view, unpack_thinker_view
+
+        tc = self.hf_cfg["talker_config"]
+        full = np.concatenate([prompt, np.asarray(tokens, dtype=np.int32)])
+        view = None
+        for out in self._run(Sequence(rid + "-view", full, SamplingParams(1, True), capture_layers=(0, int(tc.get("accept_hidden_layer", 18))))):
+            view = out.hidden if out.hidden is not None else view
+        H = self.engine.mcfg.hidden_size
+        tts_ids = [int(self.hf_cfg.get(k, d)) for k, d in (("tts_bos_token_id", 151672), ("tts_eos_token_id", 151673), ("tts_pad_token_id", 151671))]
+        with torch.inference_mode():
+            tts = self.engine.model.embed_tokens(torch.tensor(tts_ids, dtype=torch.int32, device=self.device))
+            ids2, emb, hid, tts = unpack_thinker_view(pack_thinker_view(full, view[:, :H], view[:, H:], tts))
+            speaker = next(iter(self.talker.cfg.speaker_id.values()), self.talker.cfg.codec_pad_id)
+            prefill, trailing, pad = self.talker.build_inputs(ids2, emb, hid, tts, self.special, speaker)
+            frames = list(self.talker.generate(prefill, trailing, pad, max_frames=4 * int(trailing.shape[0]) + 64, sample=not greedy_audio,
+                                               min_frames=min_audio_frames))
+            if frames:
+                wav = self.vocoder(torch.stack(frames).t()[None].contiguous())
+                pcm = ops.pcm16(wav[0, : self.vocoder.output_length(len(frames))].contiguous()).cpu().numpy().tobytes()
+                yield chunk({"audio": {"data": base64.b64encode(pcm).decode()}})
+        yield chunk({}, "stop")

@@ -48,3 +48,25 @@ def test_omni_monolith_streams_text(cpu):
     with client.stream("POST", "/generate", json={**body, "return_audio": True}) as r:
         items = [json.loads(line) for line in r.iter_lines() if line]
     assert items[-1]["status"] == 1 and "text only" in items[-1]["error_message"]
+
+
+def test_omni_monolith_speaks(cpu):
+    """Thinker, talker and vocoder in one process: text chunks first, then the spoken answer as PCM16."""
+    from fastapi.testclient import TestClient
+
+    from cornserve_b200.executors.huggingface.config import HuggingFaceConfig, ModelConfig
+    from cornserve_b200.executors.huggingface.engine import Engine
+    from cornserve_b200.executors.huggingface.router import create_app
+
+    cfg = HuggingFaceConfig(model=ModelConfig(id="cornserve-b200/tiny-omni", model_type="QWEN_OMNI"))
+    client = TestClient(create_app(cfg, Engine(cfg, torch.device("cpu"))))
+    body = {"messages": [{"role": "user", "content": "hello there"}], "max_completion_tokens": 5, "ignore_eos": True, "return_audio": True}
+    with client.stream("POST", "/generate", json=body) as r:
+        items = [json.loads(line) for line in r.iter_lines() if line]
+    assert items and all(i["status"] == 0 for i in items), items[-1]
+    deltas = [i["text_chunk"]["choices"][0]["delta"] for i in items]
+    assert any(d.get("content") for d in deltas)
+    audio = b"".join(base64.b64decode(d["audio"]["data"]) for d in deltas if d.get("audio"))
+    # sampled speech: its length is open, but the talker cannot stop before a frame and every frame is 48 samples here
+    assert len(audio) % 2 == 0
+    assert items[-1]["text_chunk"]["choices"][0]["finish_reason"] == "stop"
