@@ -130,10 +130,13 @@ async def one_request(http: aiohttp.ClientSession, url: str, payload: dict, rec:
                     rec.error = str(chunk["error"])
                     return
                 choices = chunk.get("choices") if isinstance(chunk, dict) else None
-                if choices and (choices[0].get("delta") or {}).get("content"):
+                if choices:
+                    # every streamed chunk is an arrival; it counts as a token when it carries text or audio (a
+                    # chunk may be empty, e.g. while the bytes of a multi-byte character are still incomplete)
+                    delta = choices[0].get("delta") or {}
                     rec.chunk_times.append(now)
-                    rec.output_tokens += 1
-                elif not choices and not (isinstance(chunk, dict) and chunk.get("usage")):
+                    rec.output_tokens += 1 if (delta.get("content") or delta.get("audio")) else 0
+                elif not (isinstance(chunk, dict) and chunk.get("usage")):
                     rec.chunk_times.append(now)  # apps with their own chunk type: every line counts as one token
                     rec.output_tokens += 1
             rec.ok = bool(rec.chunk_times)

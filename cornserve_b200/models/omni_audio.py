@@ -19,7 +19,7 @@ from torch import nn
 from .. import ops
 from ..parallel.state import ParallelGroup, single_group
 from .layers import LayerNorm, Linear, _param
-from .vit import HF_ACT, BlockSpec, EncoderBlock, sinusoid_positions
+from .vit import HF_ACT, BlockSpec, EncoderBlock, fused_tp_blocks, fused_tp_context, sinusoid_positions
 
 
 @dataclass
@@ -171,8 +171,12 @@ class AudioEncoder(nn.Module):
             seg = [int(a) for a in after]
         cu = torch.from_numpy(np.concatenate([[0], np.cumsum(seg)]).astype(np.int32)).to(dev)
         max_len = max(seg)
-        for layer in self.layers:
-            x = layer(x, None, cu, max_len)
+        tp = fused_tp_context(self, self.group, cfg.d_model, x.shape[0], self.layers[0].spec)
+        if tp is not None:
+            x = fused_tp_blocks(tp, list(self.layers), x, None, [(cu, max_len)] * len(self.layers))
+        else:
+            for layer in self.layers:
+                x = layer(x, None, cu, max_len)
         outs = []
         for h in x.split(audio_after, dim=0):
             if cfg.conv2d_stem:

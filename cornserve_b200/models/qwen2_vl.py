@@ -13,7 +13,7 @@ from torch import nn
 
 from ..parallel.state import ParallelGroup, single_group
 from .layers import ColumnParallelLinear, LayerNorm, Linear, RowParallelLinear
-from .vit import HF_ACT, BlockSpec, EncoderBlock, frame_cu_seqlens, rotary_table_2d
+from .vit import HF_ACT, BlockSpec, EncoderBlock, frame_cu_seqlens, fused_tp_blocks, fused_tp_context, rotary_table_2d
 
 
 @dataclass
@@ -112,8 +112,12 @@ class Qwen2VisionTransformer(nn.Module):
         cu, max_len = frame_cu_seqlens(grid_thw)
         cu = torch.from_numpy(cu).to(dev)
         x = self.patch_embed(x)
-        for blk in self.blocks:
-            x = blk(x, cs, cu, max_len)
+        tp = fused_tp_context(self, self.group, cfg.embed_dim, x.shape[0], self.blocks[0].spec)
+        if tp is not None:
+            x = fused_tp_blocks(tp, list(self.blocks), x, cs, [(cu, max_len)] * len(self.blocks))
+        else:
+            for blk in self.blocks:
+                x = blk(x, cs, cu, max_len)
         return self.merger(x)
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:

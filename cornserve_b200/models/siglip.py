@@ -21,7 +21,7 @@ from torch import nn
 from .. import ops
 from ..parallel.state import ParallelGroup, single_group
 from .layers import LayerNorm, Linear, RMSNorm, _param
-from .vit import HF_ACT, BlockSpec, EncoderBlock
+from .vit import HF_ACT, BlockSpec, EncoderBlock, fused_tp_blocks, fused_tp_context
 
 
 @dataclass
@@ -75,8 +75,12 @@ class SiglipVisionTower(nn.Module):
             x = F.pad(x, (0, self.k_pad))
         x = self.patch_embed(x.contiguous(), residual=pos.contiguous())
         cu = torch.arange(B + 1, device=x.device, dtype=torch.int32) * N
-        for layer in self.layers:
-            x = layer(x, None, cu, N)
+        tp = fused_tp_context(self, self.layers[0].group, cfg.hidden_size, x.shape[0], self.layers[0].spec) if len(self.layers) else None
+        if tp is not None:
+            x = fused_tp_blocks(tp, list(self.layers), x, None, [(cu, N)] * len(self.layers))
+        else:
+            for layer in self.layers:
+                x = layer(x, None, cu, N)
         if self.post_layernorm is not None:
             x = self.post_layernorm(x)
         return x.view(B, N, -1)

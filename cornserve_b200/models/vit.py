@@ -133,6 +133,61 @@ class EncoderBlock(nn.Module):
             self.fc1.load(name, **kw)
 
 
+def fused_tp_context(owner: nn.Module, group: ParallelGroup, hidden: int, rows: int, spec: BlockSpec):
+    """The peer-memory context that runs a tower's blocks without library collectives, or ``None`` when the plain path
+    applies: one GPU, no fabric, too few rows to give every rank a 128-row block, or a block variant that the
+    reduction kernel does not cover (learned layer scale, q/k norm over all heads)."""
+    if (not getattr(owner, "fused_tp", True) or group.size == 1 or group.fabric is None or rows < 128 * group.size or hidden > 2048 or spec.layer_scale or spec.qk_norm
+            or next(owner.parameters()).device.type != "cuda"):
+        return None
+    from ..parallel.fused import FusedEncoderTP
+
+    tp = getattr(owner, "_tp_ctx", None)
+    if tp is None or tp.S_cap < rows:
+        tp = owner._tp_ctx = FusedEncoderTP(group, hidden, max(rows, 16384))   # collective: all ranks see the same batches
+    return tp
+
+
+def fused_tp_blocks(tp, blocks: list["EncoderBlock"], x: torch.Tensor, cs: torch.Tensor | None, att: list[tuple[torch.Tensor, int]]) -> torch.Tensor:
+    """Runs ``blocks`` on the full (replicated) rows ``x`` with row-sharded activations between the GEMMs: every
+    row-parallel GEMM pushes its partial tiles to the owner of the rows, a reduce + residual + norm kernel pushes the
+    normalised rows into every rank's next operand, and the following GEMM consumes them chunk by chunk.  Returns the
+    full rows again (one library all-gather at the end of the tower)."""
+    T = x.shape[0]
+    tp.begin(T)
+    lo, hi = tp.row_range
+    xs = x[lo:hi].contiguous()
+
+    def norm_args(n):
+        ln = isinstance(n, LayerNorm)
+        return dict(norm_w=n.weight, eps=n.eps, norm_b=getattr(n, "bias", None) if ln else None, layer_norm=ln)
+
+    tp.reduce_norm_push(bias=None, residual=xs, dst=0, reduce=False, **norm_args(blocks[0].norm1))
+    for i, (blk, (cu, mx)) in enumerate(zip(blocks, att)):
+        spec, hl, d = blk.spec, blk.heads_local, blk.spec.head_dim
+        qkv = tp.gemm_gathered(0, blk.qkv.weight, blk.qkv.bias)
+        if cs is not None:
+            ops.rope_(qkv[:, : 2 * hl * d].view(T, 2 * hl, d), cs)
+        q, k, v = (qkv[:, j * hl * d:(j + 1) * hl * d].view(T, hl, d) for j in range(3))
+        a = ops.attention_varlen(q, k, v, cu, cu, mx)
+        tp.gemm_push(a.view(T, hl * d), blk.proj.weight)
+        xs = tp.reduce_norm_push(bias=blk.proj.bias, residual=xs, dst=1, **norm_args(blk.norm2))
+        h = tp.gemm_gathered(1, blk.fc1.weight, blk.fc1.bias, act=spec.act, swiglu=spec.gated)
+        tp.gemm_push(h, blk.fc2.weight)
+        if i + 1 < len(blocks):
+            xs = tp.reduce_norm_push(bias=blk.fc2.bias, residual=xs, dst=0, **norm_args(blocks[i + 1].norm1))
+        else:
+            xs = tp.reduce_norm_push(bias=blk.fc2.bias, residual=xs, norm_w=None, eps=0.0, dst=None)
+    # rows of the residual stream back on every rank: owners hold R rows each (the last one fewer)
+    full = torch.zeros((tp.group.size * tp.R, x.shape[1]), device=x.device, dtype=x.dtype)
+    mine = full[lo: lo + tp.R]
+    mine[: xs.shape[0]] = xs
+    import torch.distributed as dist
+
+    dist.all_gather_into_tensor(full, mine.clone(), group=tp.group.group)
+    return full[:T]
+
+
 def rot_pos_ids(grid_thw: np.ndarray, merge: int) -> np.ndarray:
     """(row, column) of every patch in merge-block order: ``[L, 2]``."""
     out = []

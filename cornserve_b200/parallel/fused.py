@@ -74,7 +74,7 @@ import torch.distributed as dist  # noqa: E402
 _lib.register_signature("cs_gemm_bf16_tp",
                         [P, L, P, L, P, L, P, I, I, I, I, I, I, P, I, c_uint, I, I, I, P, P, I, L, P], I)
 _lib.register_signature("cs_tp_reduce_norm_push",
-                        [I, I, I, I, I, P, L, P, c_uint, P, P, L, P, L, P, F, P, P, L, I, P], I)
+                        [I, I, I, I, I, P, L, P, c_uint, P, P, L, P, L, P, F, P, I, P, P, L, I, P], I)
 
 _ACTS = {"none": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "quick_gelu": 4, "relu": 5}
 
@@ -138,9 +138,11 @@ class FusedEncoderTP:
 
     # -- kernels ---------------------------------------------------------------------------------------------
     def reduce_norm_push(self, *, bias: torch.Tensor | None, residual: torch.Tensor, norm_w: torch.Tensor | None, eps: float,
-                         dst: int | None, reduce: bool = True, gather_chunk: int = 128) -> torch.Tensor:
+                         dst: int | None, reduce: bool = True, gather_chunk: int = 128, norm_b: torch.Tensor | None = None,
+                         layer_norm: bool = False) -> torch.Tensor:
         """``x' = sum_ranks(partials) + bias + residual`` on this rank's rows (``reduce=False``: ``x' = residual``),
-        then ``RMSNorm(x')`` pushed into operand buffer ``dst`` of every rank.  Returns ``x'`` (the residual shard)."""
+        then ``RMSNorm(x')`` (or ``LayerNorm`` with ``norm_b``) pushed into operand buffer ``dst`` of every rank.
+        Returns ``x'`` (the residual shard)."""
         g = self.group
         rows, H = self.rows_local, self.H
         x_out = torch.empty((rows, H), device=g.device, dtype=torch.bfloat16) if reduce else residual
@@ -152,7 +154,7 @@ class FusedEncoderTP:
             self.recv.local.data_ptr() if reduce else None, H, self.rflags.local.data_ptr(),
             self.r_epoch * self._last_push_tiles_n * g.size,
             _ptr(bias) if reduce else None, residual.data_ptr(), residual.stride(0),
-            x_out.data_ptr() if reduce else None, H, _ptr(norm_w), float(eps),
+            x_out.data_ptr() if reduce else None, H, _ptr(norm_w), float(eps), _ptr(norm_b), 1 if layer_norm else 0,
             ctypes.cast(self._gptr[dst], c_void_p) if dst is not None else None,
             ctypes.cast(self._gfptr[dst], c_void_p) if dst is not None else None, H, gather_chunk, _stream())
         if rc != 0:

@@ -4,7 +4,7 @@
 //
 //   GEMM (epilogue pushes bf16 partial tiles to the owner of the rows)
 //     -> tp_reduce_norm_push (this file; per owned row: wait for the partials of all ranks, sum them with bias and
-//        residual, store the new residual stream, RMSNorm, write the normalised row into EVERY rank's copy of
+//        residual, store the new residual stream, RMSNorm or LayerNorm, write the normalised row into EVERY rank's copy of
 //        the next GEMM's operand and bump that rank's chunk counter)
 //     -> GEMM (TMA producer waits per 128-row chunk of its operand)
 //
@@ -28,7 +28,8 @@ struct ReduceNormPushParams {
   const __nv_bfloat16* bias;   // [H] or null
   const __nv_bfloat16* residual; long long ldr;  // [rows, ldr] local shard of the residual stream (or null)
   __nv_bfloat16* x_out; long long ldx;            // new residual stream [rows, ldx] (may alias residual; may be null)
-  const __nv_bfloat16* norm_w; float eps;          // RMSNorm weight [H]; null = push the un-normalised sum
+  const __nv_bfloat16* norm_w; float eps;          // norm weight [H]; null = push the un-normalised sum
+  const __nv_bfloat16* norm_b; int layer_norm;     // LayerNorm (mean removed, optional bias [H]) instead of RMSNorm
   __nv_bfloat16* gather[TP_MAX_WORLD]; long long ldg;  // every rank's copy of the next operand [total rows, ldg]
   unsigned* gather_flags[TP_MAX_WORLD];                // per rank: one counter per `gather_chunk` rows
   int gather_chunk;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNo
   for (int r = r_first + warp; r < r_end; r += 8) {
     // ---- sum partials + bias + residual ----
     float acc[TP_MAXV][8];
-    float ss = 0.f;
+    float ss = 0.f, sm = 0.f;
 #pragma unroll
     for (int i = 0; i < TP_MAXV; ++i) {
       const int v = lane + 32 * i;
@@ -110,15 +111,24 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNo
         if (p.x_out != nullptr) *reinterpret_cast<uint4*>(p.x_out + static_cast<long long>(r) * p.ldx + v * 8) = packed;
         unpack8t(packed, acc[i]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += acc[i][j] * acc[i][j];
+        for (int j = 0; j < 8; ++j) { ss += acc[i][j] * acc[i][j]; sm += acc[i][j]; }
       }
     }
     if (p.gather[0] == nullptr) continue;
-    float rstd = 1.f;
+    float rstd = 1.f, mean = 0.f;
     if (p.norm_w != nullptr) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      rstd = rsqrtf(ss / static_cast<float>(p.H) + p.eps);
+      for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        sm += __shfl_xor_sync(0xffffffffu, sm, o);
+      }
+      const float inv_h = 1.f / static_cast<float>(p.H);
+      if (p.layer_norm) {
+        mean = sm * inv_h;
+        rstd = rsqrtf(fmaxf(ss * inv_h - mean * mean, 0.f) + p.eps);
+      } else {
+        rstd = rsqrtf(ss * inv_h + p.eps);
+      }
     }
     // ---- normalise and write the row into every rank's operand buffer ----
     const long long g = static_cast<long long>(p.rank) * p.rows_per_rank + r;  // row in the gathered operand
@@ -131,7 +141,13 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNo
           float w[8];
           unpack8t(__ldg(reinterpret_cast<const uint4*>(p.norm_w + v * 8)), w);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) y[j] = acc[i][j] * rstd * w[j];
+          for (int j = 0; j < 8; ++j) y[j] = (acc[i][j] - mean) * rstd * w[j];
+          if (p.norm_b != nullptr) {
+            float b[8];
+            unpack8t(__ldg(reinterpret_cast<const uint4*>(p.norm_b + v * 8)), b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] += b[j];
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) y[j] = acc[i][j];
@@ -161,7 +177,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNo
 CS_API int cs_tp_reduce_norm_push(int rows, int H, int world, int rank, int rows_per_rank, const void* recv, long long ldp,
                                   const void* recv_flags, unsigned recv_target, const void* bias, const void* residual,
                                   long long ldr, void* x_out, long long ldx, const void* norm_w, float eps,
-                                  const void* const* gather_ptrs, const void* const* gather_flag_ptrs, long long ldg,
+                                  const void* norm_b, int layer_norm, const void* const* gather_ptrs, const void* const* gather_flag_ptrs, long long ldg,
                                   int gather_chunk, void* stream) {
   if (rows <= 0) return 0;
   if ((H & 7) || H > 32 * 8 * TP_MAXV || world < 1 || world > TP_MAX_WORLD || (ldp & 7) || (ldr & 7) || (ldx & 7) || (ldg & 7))
@@ -174,6 +190,7 @@ CS_API int cs_tp_reduce_norm_push(int rows, int H, int world, int rank, int rows
   p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
   p.x_out = (__nv_bfloat16*)x_out; p.ldx = ldx;
   p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
+  p.norm_b = (const __nv_bfloat16*)norm_b; p.layer_norm = layer_norm;
   p.ldg = ldg; p.gather_chunk = gather_chunk > 0 ? gather_chunk : 128;
   for (int i = 0; i < world; ++i) {
     p.gather[i] = gather_ptrs ? (__nv_bfloat16*)const_cast<void*>(gather_ptrs[i]) : nullptr;

@@ -429,8 +429,67 @@ def decode_allreduce_tail(g):
             print(f"fused GEMM+AR+res+norm M={M} K={K} world={world}: {t_f:.1f} us   cuBLAS+NCCL+eager: {t_b:.1f} us", flush=True)
 
 
-SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower,
+SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower, "towers": tp_layernorm_towers,
             "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts}
+
+
+def tp_layernorm_towers(g):
+    """Towers built from the shared encoder block (LayerNorm, plain or gated MLP): the peer-memory chain with the
+    LayerNorm variant of the reduce kernel against one GPU, and timed against the library-collective path."""
+    import numpy as np
+
+    from cornserve_b200.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
+    from cornserve_b200.parallel.state import single_group
+
+    dev, rank = g.device, g.rank
+
+    def timed(fn, n=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # Qwen2-VL tower: 2 blocks, 1280 wide, 16 heads, MLP 5120, 2 images of 1288x728
+    cfg = Qwen2VisionConfig(depth=2, embed_dim=1280, num_heads=16, hidden_size=3584, mlp_ratio=4)
+    E, I, O = cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio), cfg.hidden_size
+    gen = torch.Generator().manual_seed(5)
+    r = lambda *s, std=0.03: (torch.randn(*s, generator=gen) * std).bfloat16()  # noqa: E731
+    sd = {"patch_embed.proj.weight": r(E, cfg.patch_dim), "merger.ln_q.weight": 1 + r(E), "merger.ln_q.bias": r(E),
+          "merger.mlp.0.weight": r(4 * E, 4 * E, std=0.01), "merger.mlp.0.bias": r(4 * E), "merger.mlp.2.weight": r(O, 4 * E, std=0.01),
+          "merger.mlp.2.bias": r(O)}
+    for i in range(cfg.depth):
+        p = f"blocks.{i}."
+        sd.update({p + "norm1.weight": 1 + r(E), p + "norm1.bias": r(E), p + "norm2.weight": 1 + r(E), p + "norm2.bias": r(E),
+                   p + "attn.qkv.weight": r(3 * E, E), p + "attn.qkv.bias": r(3 * E), p + "attn.proj.weight": r(E, E),
+                   p + "attn.proj.bias": r(E), p + "mlp.fc1.weight": r(I, E), p + "mlp.fc1.bias": r(I), p + "mlp.fc2.weight": r(E, I),
+                   p + "mlp.fc2.bias": r(E)})
+    one = Qwen2VisionTransformer(cfg, group=single_group(dev), device=dev)
+    tp = Qwen2VisionTransformer(cfg, group=g, device=dev)
+    lib = Qwen2VisionTransformer(cfg, group=g, device=dev)
+    lib.fused_tp = False
+    for m in (one, tp, lib):
+        loaded = m.load_weights(sd.items())
+        assert loaded == set(sd), sorted(set(sd) - loaded)[:5]
+    grid = np.asarray([[1, 52, 92], [1, 52, 92]])
+    L = int(grid.prod(axis=1).sum())
+    pix = (torch.randn(L, cfg.patch_dim, generator=torch.Generator().manual_seed(3)) * 0.5).bfloat16().to(dev)
+    want, got, got_lib = one.encode(pix, grid), tp.encode(pix, grid), lib.encode(pix, grid)
+    torch.cuda.synchronize()
+    ops.check_error("LayerNorm tower")
+    assert getattr(tp, "_tp_ctx", None) is not None and getattr(lib, "_tp_ctx", None) is None
+    for name, out in (("peer-memory", got), ("library", got_lib)):
+        c = torch.nn.functional.cosine_similarity(out.float().flatten(), want.float().flatten(), dim=0).item()
+        assert c > 0.995, f"Qwen2-VL tower ({name}) differs from one GPU (cos {c:.4f})"
+    t_f, t_l = timed(lambda: tp.encode(pix, grid)), timed(lambda: lib.encode(pix, grid))
+    if rank == 0:
+        print(f"Qwen2-VL tower (LayerNorm, GELU MLP) depth 2, {L} rows, TP={g.size}: peer-memory chain {t_f:.2f} ms   NCCL path {t_l:.2f} ms", flush=True)
 
 
 def main():

@@ -26,3 +26,31 @@ def test_latency_metrics():
     assert abs(s.ttft_ms["median"] - 500.0) < 1e-6 and abs(s.itl_ms["p99"] - 298.0) < 1.0
     p = percentiles(list(range(1, 101)))
     assert p["median"] == 50.5 and abs(p["p99"] - 99.01) < 1e-6
+
+
+def test_experiment_configurations_and_app_sources():
+    """Backend shapes of the comparison harness: validation, result naming, and that every generated app is a valid
+    app whose unit tasks are the parts the configuration names."""
+    import json
+
+    import pytest
+
+    from benchmark.experiment import BACKENDS, PARTS, ExperimentConfig, Workload, app_source, part_of
+    from cornserve_b200.services.gateway.app_manager import load_module_from_source, validate_app_module
+
+    with pytest.raises(ValueError):
+        ExperimentConfig("EV", gpus={"llm": 2})
+    with pytest.raises(ValueError):
+        ExperimentConfig("XX")
+    a = ExperimentConfig("EPD", gpus={"encoder": 2, "prefill": 2, "decode": 4}, workload=Workload(request_rate=5))
+    b = ExperimentConfig("EPD", gpus={"encoder": 2, "prefill": 2, "decode": 4}, workload=Workload(request_rate=6))
+    assert a.total_gpus == 8 and a.key() != b.key() and a.key() == ExperimentConfig(**{**a.__dict__}).key()
+    assert a.result_path("x").name.endswith(".json") and "EPD" in a.key() and "d4-e2-p2" in a.key()
+    for backend in BACKENDS:
+        cfg = ExperimentConfig(backend, "cornserve-b200/tiny-vlm", {p: 1 for p in PARTS[backend]})
+        module = load_module_from_source(app_source(cfg), f"bench_app_{backend}")
+        classes = validate_app_module(module)
+        from cornserve_b200.task.base import discover_unit_tasks
+
+        parts = {part_of(json.dumps({"class_name": type(t).__name__})) for t in discover_unit_tasks(classes.config_cls.tasks.values())}
+        assert parts == set(PARTS[backend]), (backend, parts)

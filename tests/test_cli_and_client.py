@@ -182,6 +182,16 @@ def test_cli_and_notebook_client_against_local_cluster(tmp_path, monkeypatch, ca
         assert args.fn(args) == 0
         args = cli.build_parser().parse_args(["deploy_profiles", os.path.join(os.path.dirname(__file__), "..", "deploy_profiles"), "--dry-run"])
         assert args.fn(args) == 0
+        # the comparison harness on the same cluster: deploy a backend shape, drive open-loop load, keep the result by config
+        from benchmark.experiment import ExperimentConfig, Workload, run_experiment
+
+        exp = ExperimentConfig("EV", "cornserve-b200/tiny-vlm", {"encoder": 1, "llm": 1},
+                               Workload(input_len=8, output_len=4, num_prompts=4, num_warmups=1, request_rate=50.0,
+                                        image_width=224, image_height=224))
+        res = asyncio.run(run_experiment(exp, cluster.url, str(tmp_path / "bench")))
+        assert res["result"]["completed"] == 4 and res["result"]["failed"] == 0, res["result"]
+        assert res["result"]["ttft_ms"]["median"] > 0 and exp.result_path(tmp_path / "bench").is_file()
+        assert asyncio.run(run_experiment(exp, cluster.url, str(tmp_path / "bench")))["key"] == res["key"]   # served from the file
     finally:
         asyncio.run_coroutine_threadsafe(cluster.stop(), loop).result(timeout=120)
         loop.call_soon_threadsafe(loop.stop)
