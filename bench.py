@@ -8,7 +8,7 @@ One *step* serves a fixed batch of synthetic requests to completion on every GPU
 real architecture, synthetic data).
 
   python bench.py --gpus N --steps K --warmup W          # N > 1: launched with torch.distributed.run
-  python bench.py --impl reference ...                   # reference arm
+  python bench.py --impl reference ...                   # reference arm: prints why it cannot run here
 
 Rank 0 prints one JSON line.  ``value`` is timed on the device (CUDA events, max over ranks) with the
 inputs already resident; ``e2e.value`` is the same work through ``MLLMPipeline.generate`` with the
