@@ -46,6 +46,13 @@ struct Item {
   bool valid;
 };
 
+// 2^x on the special-function unit (ex2.approx: 2 ulp, flushes denormals; -inf -> 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ Item decode_item(const AttnParams& p, int w) {
   Item it;
   it.split = w % p.kv_splits;
@@ -251,25 +258,31 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const int kbase = (it.j0 + j) * KV_TILE + hf * 64;
         // 32-key chunks of this half that hold any visible key of the tile (uniform over the CTA)
         const int n_ch = max(0, min(2, (it.k_end - kbase + 31) / 32));
+        // the scores of this half are read from TMEM once and stay in registers for both passes
+        uint32_t sv[2][32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          if (c < n_ch) tmem_ld32(tS + c * 32, sv[c]);
+        if (n_ch > 0) tmem_wait_ld();
         // pass 1: row max over this half
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-        for (int c = 0; c < n_ch; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tS + c * 32, v);
-          tmem_wait_ld();
-          const int nvalid = lim - (kbase + c * 32);
-          const int nlow = lo - (kbase + c * 32);
-          if (kWindow && nlow > 0) {  // sliding window: keys below the window count as -inf
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < nlow) v[i] = 0xff800000u;
-          }
+        for (int c = 0; c < 2; ++c) {
+          if (c < n_ch) {
+            const int nvalid = lim - (kbase + c * 32);
+            const int nlow = lo - (kbase + c * 32);
+            if (kWindow && nlow > 0) {  // sliding window: keys below the window count as -inf
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            if (i < nvalid) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
-            if (i + 1 < nvalid) mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
-            if (i + 2 < nvalid) mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
-            if (i + 3 < nvalid) mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+              for (int i = 0; i < 32; ++i)
+                if (i < nlow) sv[c][i] = 0xff800000u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (i < nvalid) mx0 = fmaxf(mx0, __uint_as_float(sv[c][i]));
+              if (i + 1 < nvalid) mx1 = fmaxf(mx1, __uint_as_float(sv[c][i + 1]));
+              if (i + 2 < nvalid) mx2 = fmaxf(mx2, __uint_as_float(sv[c][i + 2]));
+              if (i + 3 < nvalid) mx3 = fmaxf(mx3, __uint_as_float(sv[c][i + 3]));
+            }
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
@@ -278,27 +291,18 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const float mx_row = fmaxf(mx, xmax[j & 1][hf ^ 1][r]);
         const float m_new = fmaxf(m, mx_row * p.scale_log2);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m - m_use);  // m = -inf -> 0
+        const float alpha = fast_exp2(m - m_use);  // m = -inf -> 0
         // pass 2: probabilities of this half, packed to bf16
         uint32_t pk[32];
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           if (c < n_ch) {
-            uint32_t v[32];
-            tmem_ld32(tS + c * 32, v);
-            tmem_wait_ld();
             const int nvalid = lim - (kbase + c * 32);
-            const int nlow = lo - (kbase + c * 32);
-            if (kWindow && nlow > 0) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < nlow) v[i] = 0xff800000u;
-            }
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float e0 = (i < nvalid) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
-              const float e1 = (i + 1 < nvalid) ? exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
+              const float e0 = (i < nvalid) ? fast_exp2(__uint_as_float(sv[c][i]) * p.scale_log2 - m_use) : 0.f;
+              const float e1 = (i + 1 < nvalid) ? fast_exp2(__uint_as_float(sv[c][i + 1]) * p.scale_log2 - m_use) : 0.f;
               const uint32_t wv = pack_bf16x2(e0, e1);
               // accumulate the rounded values so that the normaliser matches what the MMA sums
               sum0 += bf16lo(wv);
