@@ -503,3 +503,42 @@ def test_fp8_blockscaled_linear(M, N, K):
     ref = x.float().cpu() @ w.float().cpu().t() + bias.float().cpu()
     rel = (got - ref).norm().item() / ref.norm().item()
     assert rel < 0.06, rel
+
+
+@pytest.mark.parametrize("layer_norm", [False, True])
+def test_reduce_norm_push_kernel_single_rank(layer_norm):
+    """The reduce + bias + residual + norm kernel of the tensor-parallel encoder chain with one rank playing the whole
+    group: two partial-sum slots are summed, the new residual is stored, and the normalised rows (RMSNorm or LayerNorm)
+    land in the operand buffer with their arrival counters."""
+    import ctypes
+
+    from cornserve_b200.ops import _lib
+    from cornserve_b200.parallel import fused  # noqa: F401  (declares the entry point's signature)
+
+    rows, H = 256, 1280
+    g = torch.Generator(device="cuda").manual_seed(7)
+    part = torch.randn(1, rows, H, device="cuda", generator=g).bfloat16()
+    bias, res = torch.randn(H, device="cuda", generator=g).bfloat16(), torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+    w, b = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16(), torch.randn(H, device="cuda", generator=g).bfloat16()
+    flags = torch.full((rows // 128,), 5, device="cuda", dtype=torch.int32)       # "all tiles have arrived"
+    x_out = torch.empty(rows, H, device="cuda", dtype=torch.bfloat16)
+    gathered = torch.zeros(rows, H, device="cuda", dtype=torch.bfloat16)
+    gflags = torch.zeros(rows // 128, device="cuda", dtype=torch.int32)
+    gp, fp = (ctypes.c_void_p * 1)(gathered.data_ptr()), (ctypes.c_void_p * 1)(gflags.data_ptr())
+    lib = _lib.load()
+    rc = lib.cs_tp_reduce_norm_push(rows, H, 1, 0, rows, part.data_ptr(), H, flags.data_ptr(), 5, bias.data_ptr(), res.data_ptr(), H,
+                                    x_out.data_ptr(), H, w.data_ptr(), 1e-6, b.data_ptr() if layer_norm else None, int(layer_norm),
+                                    ctypes.cast(gp, ctypes.c_void_p), ctypes.cast(fp, ctypes.c_void_p), H, 128,
+                                    torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    ops.check_error("reduce norm push")
+    want_x = (part[0].float() + bias.float() + res.float()).bfloat16()
+    assert torch.equal(x_out, want_x)
+    xf = want_x.float()
+    if layer_norm:
+        want = torch.nn.functional.layer_norm(xf, (H,), w.float(), b.float(), 1e-6)
+    else:
+        want = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert torch.allclose(gathered.float(), want, atol=3e-2, rtol=3e-2)
+    assert gflags.tolist() == [128, 128]
