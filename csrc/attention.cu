@@ -289,7 +289,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         xmax[j & 1][hf][r] = mx;  // double-buffered by tile parity: the next write to this slot is two barriers away
         asm volatile("bar.sync 2, 256;" ::: "memory");
         const float mx_row = fmaxf(mx, xmax[j & 1][hf ^ 1][r]);
-        const float m_new = fmaxf(m, mx_row * p.scale_log2);
+        // The reference point of the exponents only moves when the row maximum has grown by more than 2^8 since it was
+        // set: probabilities then stay below 256 (exact enough in bf16, harmless in the fp32 normaliser), and most key
+        // tiles need no rescaling of O at all.  Both threads of a row see the same maxima, so they decide alike.
+        const float m_cand = fmaxf(m, mx_row * p.scale_log2);
+        const float m_new = (m_cand - m > 8.f) ? m_cand : m;   // m = -inf: the difference is +inf (or NaN when both are)
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = fast_exp2(m - m_use);  // m = -inf -> 0
         // pass 2: probabilities of this half, packed to bf16
