@@ -276,12 +276,22 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
               for (int i = 0; i < 32; ++i)
                 if (i < nlow) sv[c][i] = 0xff800000u;
             }
+            if (nvalid >= 32) {  // every key of the chunk is visible to this row: no per-element tests
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              if (i < nvalid) mx0 = fmaxf(mx0, __uint_as_float(sv[c][i]));
-              if (i + 1 < nvalid) mx1 = fmaxf(mx1, __uint_as_float(sv[c][i + 1]));
-              if (i + 2 < nvalid) mx2 = fmaxf(mx2, __uint_as_float(sv[c][i + 2]));
-              if (i + 3 < nvalid) mx3 = fmaxf(mx3, __uint_as_float(sv[c][i + 3]));
+              for (int i = 0; i < 32; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sv[c][i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv[c][i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sv[c][i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sv[c][i + 3]));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                if (i < nvalid) mx0 = fmaxf(mx0, __uint_as_float(sv[c][i]));
+                if (i + 1 < nvalid) mx1 = fmaxf(mx1, __uint_as_float(sv[c][i + 1]));
+                if (i + 2 < nvalid) mx2 = fmaxf(mx2, __uint_as_float(sv[c][i + 2]));
+                if (i + 3 < nvalid) mx3 = fmaxf(mx3, __uint_as_float(sv[c][i + 3]));
+              }
             }
           }
         }
@@ -303,15 +313,25 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         for (int c = 0; c < 2; ++c) {
           if (c < n_ch) {
             const int nvalid = lim - (kbase + c * 32);
+            // (keys masked by the window hold -inf and come out as 0; the normaliser sums the unrounded values)
+            if (nvalid >= 32) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float e0 = (i < nvalid) ? fast_exp2(__uint_as_float(sv[c][i]) * p.scale_log2 - m_use) : 0.f;
-              const float e1 = (i + 1 < nvalid) ? fast_exp2(__uint_as_float(sv[c][i + 1]) * p.scale_log2 - m_use) : 0.f;
-              const uint32_t wv = pack_bf16x2(e0, e1);
-              // accumulate the rounded values so that the normaliser matches what the MMA sums
-              sum0 += bf16lo(wv);
-              sum1 += bf16hi(wv);
-              pk[c * 16 + (i >> 1)] = wv;
+              for (int i = 0; i < 32; i += 2) {
+                const float e0 = fast_exp2(__uint_as_float(sv[c][i]) * p.scale_log2 - m_use);
+                const float e1 = fast_exp2(__uint_as_float(sv[c][i + 1]) * p.scale_log2 - m_use);
+                sum0 += e0;
+                sum1 += e1;
+                pk[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float e0 = (i < nvalid) ? fast_exp2(__uint_as_float(sv[c][i]) * p.scale_log2 - m_use) : 0.f;
+                const float e1 = (i + 1 < nvalid) ? fast_exp2(__uint_as_float(sv[c][i + 1]) * p.scale_log2 - m_use) : 0.f;
+                sum0 += e0;
+                sum1 += e1;
+                pk[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+              }
             }
           } else {
 #pragma unroll
