@@ -37,13 +37,28 @@ def hf_style_weights(cfg, seed=0):
                   p + "self_attn.q_proj.weight": r(hq * d, H), p + "self_attn.q_proj.bias": r(hq * d),
                   p + "self_attn.k_proj.weight": r(hkv * d, H), p + "self_attn.k_proj.bias": r(hkv * d),
                   p + "self_attn.v_proj.weight": r(hkv * d, H), p + "self_attn.v_proj.bias": r(hkv * d),
-                  p + "self_attn.o_proj.weight": r(H, hq * d), p + "mlp.gate_proj.weight": r(inter, H),
-                  p + "mlp.up_proj.weight": r(inter, H), p + "mlp.down_proj.weight": r(H, inter)})
+                  p + "self_attn.o_proj.weight": r(H, hq * d)})
+        if cfg.num_experts > 0:
+            mi = cfg.moe_intermediate_size
+            w[p + "mlp.gate.weight"] = r(cfg.num_experts, H, std=0.5)
+            for e in range(cfg.num_experts):
+                w.update({p + f"mlp.experts.{e}.gate_proj.weight": r(mi, H), p + f"mlp.experts.{e}.up_proj.weight": r(mi, H),
+                          p + f"mlp.experts.{e}.down_proj.weight": r(H, mi)})
+        else:
+            w.update({p + "mlp.gate_proj.weight": r(inter, H), p + "mlp.up_proj.weight": r(inter, H),
+                      p + "mlp.down_proj.weight": r(H, inter)})
     return w
 
 
 def tp_llm_matches_single_gpu(g):
-    """The tensor-parallel decoder (fused all-reduce tails, CUDA-graph decode) against the same weights on one GPU."""
+    """The tensor-parallel decoder (fused all-reduce tails, CUDA-graph decode) against the same weights on one GPU:
+    a dense model, and a mixture-of-experts model whose experts are spread over the ranks (tokens are replicated, every
+    rank routes a slice, the combine kernel fills all ranks' outputs; the whole layer sits inside the decode graph)."""
+    _tp_llm(g, {})
+    _tp_llm(g, dict(num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256))
+
+
+def _tp_llm(g, extra):
     import numpy as np
 
     from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
@@ -51,7 +66,7 @@ def tp_llm_matches_single_gpu(g):
     from cornserve_b200.parallel.state import single_group
 
     cfg = LLMConfig(hidden_size=512, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
-                    intermediate_size=1024, vocab_size=2048, eos_token_id=2047)
+                    intermediate_size=1024, vocab_size=2048, eos_token_id=2047, **extra)
     weights = hf_style_weights(cfg)
     outs = {}
     for name, group in (("tp", g), ("single", single_group(g.device))):
@@ -429,10 +444,6 @@ def decode_allreduce_tail(g):
             print(f"fused GEMM+AR+res+norm M={M} K={K} world={world}: {t_f:.1f} us   cuBLAS+NCCL+eager: {t_b:.1f} us", flush=True)
 
 
-SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower, "towers": tp_layernorm_towers,
-            "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts}
-
-
 def tp_layernorm_towers(g):
     """Towers built from the shared encoder block (LayerNorm, plain or gated MLP): the peer-memory chain with the
     LayerNorm variant of the reduce kernel against one GPU, and timed against the library-collective path."""
@@ -490,6 +501,10 @@ def tp_layernorm_towers(g):
     t_f, t_l = timed(lambda: tp.encode(pix, grid)), timed(lambda: lib.encode(pix, grid))
     if rank == 0:
         print(f"Qwen2-VL tower (LayerNorm, GELU MLP) depth 2, {L} rows, TP={g.size}: peer-memory chain {t_f:.2f} ms   NCCL path {t_l:.2f} ms", flush=True)
+
+
+SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower, "towers": tp_layernorm_towers,
+            "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts}
 
 
 def main():
