@@ -503,8 +503,47 @@ def tp_layernorm_towers(g):
         print(f"Qwen2-VL tower (LayerNorm, GELU MLP) depth 2, {L} rows, TP={g.size}: peer-memory chain {t_f:.2f} ms   NCCL path {t_l:.2f} ms", flush=True)
 
 
+def flag_protocol_stress(g):
+    """Shakes the orderings of the peer-memory protocols: every iteration each rank stalls its stream for a random time
+    before its kernels (so the ranks arrive at the flags in a different order every time, sometimes a whole call
+    apart) and the results must stay bit-identical to the first iteration's on every rank."""
+    import random
+
+    from cornserve_b200.parallel import moe
+
+    rank, W, dev = g.rank, g.size, g.device
+    rng = random.Random(1000 + rank)
+    torch.manual_seed(99)
+    N, M, K = 3584, 48, 3584
+    fused = FusedRowParallel(g, N, m_cap=128)
+    x = (torch.randn(M, K // W, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K // W, device=dev) * K ** -0.5).bfloat16()
+    res, nw = torch.randn(M, N, device=dev).bfloat16(), torch.ones(N, device=dev).bfloat16()
+    E, k, H, I, T = 32, 4, 1024, 256, 200
+    gen = torch.Generator(device=dev).manual_seed(5)
+    wgu = (torch.randn(E // W, 2 * I, H, device=dev, generator=gen) * H ** -0.5).bfloat16()
+    wd = (torch.randn(E // W, H, I, device=dev, generator=gen) * I ** -0.5).bfloat16()
+    xm, lg = torch.randn(T, H, device=dev, generator=gen).bfloat16(), torch.randn(T, E, device=dev, generator=gen)
+    ep = moe.FusedMoE(g, E, k, H, I, max_tokens=1024)
+    first = None
+    for it in range(40):
+        torch.cuda._sleep(rng.randrange(0, 3_000_000))          # up to ~1.5 ms of stall on this rank's stream
+        h, normed = fused(x, w, None, res, nw, 1e-6)
+        torch.cuda._sleep(rng.randrange(0, 3_000_000))
+        y = ep.forward(xm, lg, wgu, wd).clone()
+        torch.cuda.synchronize()
+        ops.check_error(f"stress iteration {it}")
+        cur = (h.clone(), normed.clone(), y)
+        if first is None:
+            first = cur
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(cur, first)), f"results changed in iteration {it}"
+    if rank == 0:
+        print("flag protocols: 40 iterations with random per-rank stalls, results bit-identical", flush=True)
+
+
 SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower, "towers": tp_layernorm_towers,
-            "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts}
+            "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts, "stress": flag_protocol_stress}
 
 
 def main():
