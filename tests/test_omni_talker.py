@@ -114,3 +114,46 @@ def test_greedy_generation_matches_a_loop_over_the_hf_modules():
             nxt = total + (trailing[f] if f < trailing.shape[0] else tts_pad)
             seq = torch.cat([seq, nxt], dim=1)
     assert got.tolist() == want
+
+
+def test_thinker_view_round_trip_in_bf16():
+    from cornserve_b200.models.omni_talker import pack_thinker_view, unpack_thinker_view
+
+    ids = np.asarray([0, 255, 256, 65535, 65536, 151671, 151936 - 1], dtype=np.int64)
+    emb = torch.randn(len(ids), 64).bfloat16()
+    hid = torch.randn(len(ids), 64).bfloat16()
+    tts = torch.randn(3, 64).bfloat16()
+    rows = pack_thinker_view(ids, emb, hid, tts)
+    assert rows.shape == (len(ids) + 3, 3 * 64) and rows.dtype == torch.bfloat16
+    ids2, emb2, hid2, tts2 = unpack_thinker_view(rows)
+    assert ids2.tolist() == ids.tolist() and torch.equal(emb2, emb) and torch.equal(hid2, hid) and torch.equal(tts2, tts)
+
+
+@pytest.mark.gpu
+def test_talker_on_gpu_matches_cpu():
+    """The same talker (bf16 on the GPU through the paged-KV kernels and the fused expert path, fp32 on the CPU): the
+    decoder's hidden states of a prefill agree, and generation yields frames of valid codes."""
+    from cornserve_b200.models.omni_talker import _embeds_meta
+    from cornserve_b200.utils.hub import load_config
+
+    cfg = TalkerConfig.from_hf(load_config("cornserve-b200/tiny-omni")["talker_config"])
+    torch.manual_seed(3)
+    cpu = Talker(cfg, device="cpu").float()
+    gpu = Talker(cfg, device="cuda")
+    gpu.load_state_dict({k: v.to(torch.bfloat16) for k, v in cpu.state_dict().items()})
+    x = torch.randn(40, cfg.text.hidden_size) * 0.5
+    with torch.inference_mode():
+        outs = []
+        for m, dev in ((cpu, "cpu"), (gpu, "cuda")):
+            meta = _embeds_meta(40, 0, [1], torch.device(dev), decode=False)
+            meta.mm_embeds, meta.mm_index = x.to(dev, m.dtype), torch.arange(40, dtype=torch.int32, device=dev)
+            outs.append(m.decoder.forward_hidden(meta, m.decoder.alloc_kv_cache(2)).float().cpu())
+        cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0).item()
+        assert cos > 0.99, cos
+        pre = (torch.randn(20, cfg.text.hidden_size) * 0.5).to("cuda", torch.bfloat16)
+        trail = (torch.randn(5, cfg.text.hidden_size) * 0.5).to("cuda", torch.bfloat16)
+        frames = list(gpu.generate(pre, trail, trail[0], max_frames=6, sample=False, min_frames=6))
+    from cornserve_b200 import ops
+
+    ops.check_error("talker on the GPU")
+    assert len(frames) == 6 and all(f.shape == (cfg.num_code_groups,) and int(f.max()) < cfg.predictor.vocab_size for f in frames)
