@@ -101,6 +101,24 @@ def window_index(grid_thw: np.ndarray, window: int, merge: int, patch: int) -> t
     return np.concatenate(index), np.asarray(cu, dtype=np.int32)
 
 
+def pack_windows(cu_win: np.ndarray, limit: int = 128) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Groups consecutive attention windows (tokens are already in window order) into runs of at most ``limit`` tokens,
+    so that short windows share one 128-row attention tile.  Returns ``(cu_groups, lo [L], hi [L])``: the group
+    boundaries and, for every token, the key range of its own window."""
+    sizes = np.diff(cu_win)
+    cu = [0]
+    run = 0
+    for n in sizes.tolist():
+        if run and run + n > limit:
+            cu.append(cu[-1] + run)
+            run = 0
+        run += n
+    cu.append(cu[-1] + run)
+    lo = np.repeat(cu_win[:-1], sizes).astype(np.int32)
+    hi = np.repeat(cu_win[1:], sizes).astype(np.int32)
+    return np.asarray(cu, dtype=np.int32), lo, hi
+
+
 class VisionBlock(nn.Module):
     def __init__(self, cfg: Qwen25VisionConfig, group: ParallelGroup, device):
         super().__init__()
@@ -115,7 +133,7 @@ class VisionBlock(nn.Module):
                                       in_padded=self.gate_up.inter_padded, device=device)
         self.heads_local = self.qkv.heads_local
 
-    def forward(self, x: torch.Tensor, cs: torch.Tensor, cu: torch.Tensor, max_len: int) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cs: torch.Tensor, cu: torch.Tensor, max_len: int, bounds=None) -> torch.Tensor:
         T = x.shape[0]
         hl, d = self.heads_local, self.cfg.head_dim
         qkv = self.qkv(self.norm1(x))  # [T, 3 * hl * d] = q heads | k heads | v heads
@@ -124,7 +142,7 @@ class VisionBlock(nn.Module):
         q = qkv[:, : hl * d].view(T, hl, d)
         k = qkv[:, hl * d: 2 * hl * d].view(T, hl, d)
         v = qkv[:, 2 * hl * d:].view(T, hl, d)
-        a = ops.attention_varlen(q, k, v, cu, cu, max_len)
+        a = ops.attention_varlen(q, k, v, cu, cu, max_len, row_bounds=bounds)
         x = self.proj(a.view(T, hl * d), residual=x)
         h = self.gate_up(self.norm2(x), act=self.cfg.hidden_act)
         return self.down(h, residual=x)
@@ -200,17 +218,18 @@ class Qwen25VisionTransformer(nn.Module):
         unit = cfg.spatial_merge_size ** 2
         x = pixel_patches.to(device=dev, dtype=self.dtype, non_blocking=True)
         L = x.shape[0]
-        widx_d, cs_d, cu_win_d, cu_full_d, max_win, max_full = self._index_tables(grid_thw, L)
+        widx_d, cs_d, cu_win_d, cu_full_d, max_win, max_full, win_bounds = self._index_tables(grid_thw, L)
 
         x = self.patch_embed(x)
         x = ops.gather_rows(x.view(L // unit, unit * cfg.hidden_size), widx_d).view(L, cfg.hidden_size)
-        att = [(cu_full_d, max_full) if i in cfg.fullatt_block_indexes else (cu_win_d, max_win) for i in range(len(self.blocks))]
+        att = [(cu_full_d, max_full, None) if i in cfg.fullatt_block_indexes else (cu_win_d, max_win, win_bounds)
+               for i in range(len(self.blocks))]
         tp = self._fused_tp(L)
         if tp is not None:
             y = self._blocks_fused(tp, x, cs_d, att)
         else:
-            for blk, (cu, mx) in zip(self.blocks, att):
-                x = blk(x, cs_d, cu, mx)
+            for blk, (cu, mx, bounds) in zip(self.blocks, att):
+                x = blk(x, cs_d, cu, mx, bounds)
             y = self.merger(x)  # [L/unit, out] in window order
         out = torch.empty_like(y)
         ops.scatter_rows_(out, widx_d, y)  # undo the window permutation
@@ -231,8 +250,13 @@ class Qwen25VisionTransformer(nn.Module):
         frames = np.repeat(grid_thw[:, 1] * grid_thw[:, 2], grid_thw[:, 0])
         cu_full = np.concatenate([[0], np.cumsum(frames)]).astype(np.int32)
         to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True)  # noqa: E731
+        bounds = None
+        if dev.type == "cuda" and int(np.diff(cu_win).max()) <= 64:
+            # windows of at most 64 tokens: two or more fit into one 128-row attention tile
+            cu_pack, lo, hi = pack_windows(cu_win)
+            cu_win, bounds = cu_pack, (to_dev(lo), to_dev(hi))
         out = (to_dev(widx.astype(np.int32)), to_dev(cs), to_dev(cu_win), to_dev(cu_full), int(np.diff(cu_win).max()),
-               int(frames.max()))
+               int(frames.max()), bounds)
         if len(cache) >= 64:
             cache.pop(next(iter(cache)))
         cache[key] = out
@@ -264,12 +288,12 @@ class Qwen25VisionTransformer(nn.Module):
         eps = cfg.rms_norm_eps
         blocks = list(self.blocks)
         tp.reduce_norm_push(bias=None, residual=xs, norm_w=blocks[0].norm1.weight, eps=eps, dst=0, reduce=False)
-        for i, (blk, (cu, mx)) in enumerate(zip(blocks, att)):
+        for i, (blk, (cu, mx, bounds)) in enumerate(zip(blocks, att)):
             hl, d = blk.heads_local, cfg.head_dim
             qkv = tp.gemm_gathered(0, blk.qkv.weight, blk.qkv.bias)
             ops.rope_(qkv[:, : 2 * hl * d].view(T, 2 * hl, d), cs)
             q, k, v = (qkv[:, j * hl * d:(j + 1) * hl * d].view(T, hl, d) for j in range(3))
-            a = ops.attention_varlen(q, k, v, cu, cu, mx)
+            a = ops.attention_varlen(q, k, v, cu, cu, mx, row_bounds=bounds)
             tp.gemm_push(a.view(T, hl * d), blk.proj.weight)
             xs = tp.reduce_norm_push(bias=blk.proj.bias, residual=xs, norm_w=blk.norm2.weight, eps=eps, dst=1)
             h = tp.gemm_gathered(1, blk.gate_up.weight, blk.gate_up.bias, act=cfg.hidden_act, swiglu=True)

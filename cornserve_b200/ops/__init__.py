@@ -304,14 +304,28 @@ def rope_kv_write_(qkv: torch.Tensor, Hq: int, Hkv: int, d: int, cs: torch.Tenso
 # attention
 # --------------------------------------------------------------------------------------------
 def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = None, causal: bool = False,
-                     out: torch.Tensor | None = None, window: int = 0) -> torch.Tensor:
+                     out: torch.Tensor | None = None, window: int = 0,
+                     row_bounds: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
     """Packed variable-length attention.  q ``[Tq, Hq, d]``, k/v ``[Tk, Hkv, d]`` (strided views are
     fine as long as heads are ``d`` apart); ``cu_*`` are int32 prefix sums.  Returns ``[Tq, Hq, d]``.
-    ``window > 0`` (causal only): each query sees the last ``window`` keys up to its own position."""
+    ``window > 0`` (causal only): each query sees the last ``window`` keys up to its own position.
+    ``row_bounds`` = ``(lo [Tq], hi [Tq])`` int32 (self attention only): token ``t`` sees keys ``[lo[t], hi[t])`` of the
+    packed numbering; with it ``cu_*`` may group several short sequences (attention windows) into one, so that they
+    share a 128-row tile instead of occupying one each."""
     Tq, Hq, d = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     if not q.is_cuda:
-        o = reference.attention_varlen(q, k, v, cu_q, cu_k, scale, causal, window)
+        if row_bounds is not None:
+            lo, hi = (t.long() for t in row_bounds)
+            pos = torch.arange(k.shape[0])
+            mask = (pos[None, :] >= lo[:, None]) & (pos[None, :] < hi[:, None])          # [Tq, Tk]
+            g = Hq // k.shape[1]
+            kk, vv = k.float().repeat_interleave(g, dim=1), v.float().repeat_interleave(g, dim=1)
+            sc = torch.einsum("qhd,khd->hqk", q.float(), kk) * scale
+            sc = sc.masked_fill(~mask[None], float("-inf"))
+            o = torch.einsum("hqk,khd->qhd", torch.softmax(sc, dim=-1), vv).to(q.dtype)
+        else:
+            o = reference.attention_varlen(q, k, v, cu_q, cu_k, scale, causal, window)
         if out is not None:
             out.copy_(o)
             return out
@@ -326,7 +340,8 @@ def attention_varlen(q, k, v, cu_q, cu_k, max_q_len: int, scale: float | None = 
     rc = lib.cs_attention(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
         out.data_ptr(), out.stride(0), cu_q.data_ptr(), cu_k.data_ptr(), None, None, 0, 0,
-        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, 1, None, 0, int(window), _stream(),
+        B, Tq, Tk, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 0, 1, None, 0, int(window),
+        None if row_bounds is None else row_bounds[0].data_ptr(), None if row_bounds is None else row_bounds[1].data_ptr(), _stream(),
     )
     _chk(rc, "cs_attention")
     _count()
@@ -402,7 +417,7 @@ def attention_paged(q, cache, block_table, kv_len, cu_q, max_q_len: int, scale: 
         q.data_ptr(), q.stride(0), cache.data_ptr(), 0, None, 0, out.data_ptr(), out.stride(0),
         cu_q.data_ptr(), None, kv_len.data_ptr(), block_table.data_ptr(), block_table.stride(0), pages,
         B, Tq, 0, max_q_len, Hq, Hkv, d, float(scale), 1 if causal else 0, 1 if pack_gqa else 0,
-        kv_splits, ws_ptr, ws_bytes, 0, _stream(),
+        kv_splits, ws_ptr, ws_bytes, 0, None, None, _stream(),
     )
     _chk(rc, "cs_attention(paged)")
     _count(2 if kv_splits > 1 else 1)

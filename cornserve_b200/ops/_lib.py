@@ -59,7 +59,7 @@ _SIGNATURES = {
     "cs_kv_copy_pages": ([P, P, L, L, L, I, I, I, I, P, P, P], I),
     "cs_enable_peer_access": ([I], I),
     "cs_to_rgb8": ([P, L, P, L, P], I),
-    "cs_attention": ([P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, L, I, P], I),
+    "cs_attention": ([P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, L, I, P, P, P], I),
 }
 
 

@@ -3,7 +3,7 @@
   python -m cornserve_b200.ops.microbench gemm 16384 3584 3584
   python -m cornserve_b200.ops.microbench swiglu 19136 3424 1280
   python -m cornserve_b200.ops.microbench skinny 64 3584 18944
-  python -m cornserve_b200.ops.microbench attn-window 4            # Qwen2.5-VL windows of 4 1280x720 images
+  python -m cornserve_b200.ops.microbench attn-window 4 [1]        # Qwen2.5-VL windows of 4 1280x720 images (1: packed tiles)
   python -m cornserve_b200.ops.microbench attn-full 16 80 4784 0   # heads, head_dim, length, causal
   python -m cornserve_b200.ops.microbench attn-decode 48 3500      # sequences, context
   python -m cornserve_b200.ops.microbench norm 19136 1280
@@ -96,19 +96,24 @@ def main() -> None:
             secs = t(lambda: ops.linear(x, w, out=out, bn=a.bn, skinny=(k == "skinny")))
             report(f"{k} {M}x{N}x{K}", secs, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N))
     elif k == "attn-window":
-        from cornserve_b200.models.qwen2_5_vl import window_index
+        from cornserve_b200.models.qwen2_5_vl import pack_windows, window_index
 
         n = a.args[0] if a.args else 4
+        packed = len(a.args) > 1 and a.args[1] == 1   # second argument 1: windows packed into shared 128-row tiles
         grid = np.array([[1, 52, 92]] * n)
         _, cu = window_index(grid, 112, 2, 14)
+        bounds = None
+        lens = np.diff(cu).astype(np.float64)
+        if packed:
+            cu, lo, hi = pack_windows(cu)
+            bounds = (torch.from_numpy(lo).cuda(), torch.from_numpy(hi).cuda())
         T, H, d = 4784 * n, 16, 80
         qkv = rnd(T, 3 * H * d)
         q, kk, v = (qkv[:, i * H * d:(i + 1) * H * d].view(T, H, d) for i in range(3))
         cu_d = torch.from_numpy(cu).cuda()
         mx = int(np.diff(cu).max())
-        secs = t(lambda: ops.attention_varlen(q, kk, v, cu_d, cu_d, mx))
-        lens = np.diff(cu).astype(np.float64)
-        report(f"attn-window {n} images ({len(lens)} windows)", secs, 4.0 * H * d * float((lens ** 2).sum()),
+        secs = t(lambda: ops.attention_varlen(q, kk, v, cu_d, cu_d, mx, row_bounds=bounds))
+        report(f"attn-window {n} images ({len(lens)} windows{', packed' if packed else ''})", secs, 4.0 * H * d * float((lens ** 2).sum()),
                2.0 * 4 * T * H * d)
     elif k == "attn-full":
         H, d, L, causal = (a.args + [16, 80, 4784, 0][len(a.args):])[:4]

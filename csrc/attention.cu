@@ -31,6 +31,9 @@ struct AttnParams {
   int Hq, Hkv, d, G;      // G = query heads packed per tile (1, or Hq/Hkv)
   int causal, paged;
   int window;             // > 0 (with causal): query i only sees the last `window` keys up to its own position
+  // packed segments (several short sequences, e.g. attention windows, share one 128-row tile): query token t only
+  // sees keys [seg_lo[t], seg_hi[t]) (indices in the packed token numbering); null = not used
+  const int* seg_lo; const int* seg_hi;
   int max_q_tiles, head_blks, total_items;
   int kv_splits;          // > 1: every item covers 1/kv_splits of the key tiles and writes fp32 partials
   float* ws_o;            // [Tq*Hq, kv_splits, d] unnormalised partial outputs
@@ -236,8 +239,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       if (!it.valid) continue;
       const bool row_ok = tl < it.n_tok;
       const int qi = it.t0 + tl;
-      const int lim = p.causal ? min(it.k_len, qi + it.shift + 1) : it.k_len;  // keys [lo, lim) are visible
-      const int lo = kWindow ? max(0, qi + it.shift + 1 - p.window) : 0;
+      int lim = p.causal ? min(it.k_len, qi + it.shift + 1) : it.k_len;  // keys [lo, lim) are visible
+      int lo = (kWindow && p.window > 0) ? max(0, qi + it.shift + 1 - p.window) : 0;
+      if (kWindow && p.seg_lo != nullptr && row_ok) {
+        lo = p.seg_lo[it.q_beg + qi] - it.k_beg;
+        lim = min(lim, p.seg_hi[it.q_beg + qi] - it.k_beg);
+      }
       float m = -INFINITY, l = 0.f;
       // A warp whose 32 tile rows all lie beyond the item's tokens (decode: 7 of 128 rows are real) only keeps
       // the barriers company: it neither reads S nor writes P (rows of the MMA are independent, and the rows
@@ -500,7 +507,8 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
                         void* o, long long ldo, const void* cu_q, const void* cu_k, const void* kv_len,
                         const void* block_table, int bt_stride, int num_pages, int B, int Tq, int Tk,
                         int max_q_len, int Hq, int Hkv, int d, float scale, int causal, int pack_gqa,
-                        int kv_splits, void* ws, long long ws_bytes, int window, void* stream_) {
+                        int kv_splits, void* ws, long long ws_bytes, int window, const void* seg_lo, const void* seg_hi,
+                        void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (B <= 0 || Tq <= 0) return 0;
   if (d > 128 || (d & 7) || Hkv <= 0 || Hq % Hkv != 0) return -1;
@@ -514,6 +522,9 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
   p.block_table = (const int*)block_table; p.bt_stride = bt_stride;
   p.Hq = Hq; p.Hkv = Hkv; p.d = d; p.G = G; p.causal = causal; p.paged = paged;
   p.window = (window > 0 && causal) ? window : 0;
+  p.seg_lo = reinterpret_cast<const int*>(seg_lo);
+  p.seg_hi = reinterpret_cast<const int*>(seg_hi);
+  if ((p.seg_lo == nullptr) != (p.seg_hi == nullptr) || (p.seg_lo != nullptr && (paged || pack_gqa))) return -1;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int dpad = (d + 15) & ~15;
   p.idesc_s = umma_idesc_bf16(128, 128, 0, 0);
@@ -556,7 +567,7 @@ CS_API int cs_attention(const void* q, long long ldq, const void* k, long long l
   if (total <= 0 || total > 0x7fffffffLL) return -1;
   p.total_items = static_cast<int>(total);
   const int grid = p.total_items < cs_num_sms() ? p.total_items : cs_num_sms();
-  if (p.window > 0) attn_kernel<true><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p);
+  if (p.window > 0 || p.seg_lo != nullptr) attn_kernel<true><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p);
   else attn_kernel<false><<<grid, 320, smem, stream>>>(tmQ, tmK, tmV, p);
   if (kv_splits > 1) {
     const int rows = Tq * Hq;

@@ -542,3 +542,33 @@ def test_reduce_norm_push_kernel_single_rank(layer_norm):
         want = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
     assert torch.allclose(gathered.float(), want, atol=3e-2, rtol=3e-2)
     assert gflags.tolist() == [128, 128]
+
+
+def test_packed_attention_windows_match_unpacked():
+    """Several short windows sharing one 128-row tile (per-token key bounds) against one window per tile."""
+    from cornserve_b200.models.qwen2_5_vl import pack_windows, window_index
+
+    grid = np.array([[1, 52, 92], [1, 16, 24], [2, 20, 28]])
+    _, cu = window_index(grid, 112, 2, 14)
+    T, H, d = int(cu[-1]), 4, 80
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v = (torch.randn(T, H, d, device="cuda", generator=g).bfloat16() for _ in range(3))
+    cu_d = torch.from_numpy(cu).cuda()
+    want = ops.attention_varlen(q, k, v, cu_d, cu_d, int(np.diff(cu).max()))
+    cu_p, lo, hi = pack_windows(cu)
+    assert len(cu_p) < len(cu) and int(np.diff(cu_p).max()) <= 128 and cu_p[-1] == cu[-1]
+    cu_pd = torch.from_numpy(cu_p).cuda()
+    got = ops.attention_varlen(q, k, v, cu_pd, cu_pd, int(np.diff(cu_p).max()),
+                               row_bounds=(torch.from_numpy(lo).cuda(), torch.from_numpy(hi).cuda()))
+    torch.cuda.synchronize()
+    ops.check_error("packed windows")
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    # and the CPU restatement of the bounded form agrees with the plain CPU path
+    qc, kc, vc = q[:400].float().cpu(), k[:400].float().cpu(), v[:400].float().cpu()
+    n = int(np.searchsorted(cu, 400, side="right")) - 1
+    cu_c = torch.from_numpy(cu[: n + 1])
+    Tn = int(cu[n])
+    plain = ops.attention_varlen(qc[:Tn], kc[:Tn], vc[:Tn], cu_c, cu_c, 64)
+    one = torch.tensor([0, Tn], dtype=torch.int32)
+    bounded = ops.attention_varlen(qc[:Tn], kc[:Tn], vc[:Tn], one, one, Tn, row_bounds=(torch.from_numpy(lo[:Tn]), torch.from_numpy(hi[:Tn])))
+    assert torch.allclose(plain, bounded, atol=1e-4)
