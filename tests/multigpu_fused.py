@@ -72,7 +72,10 @@ def _tp_llm(g, extra):
     for name, group in (("tp", g), ("single", single_group(g.device))):
         model = QwenLLM(cfg, group=group, device=g.device)
         loaded = model.load_weights(weights.items())
-        assert len(loaded) == len(weights), (len(loaded), len(weights))
+        foreign = 0   # expert tensors that belong to other ranks are skipped by the loader
+        if cfg.num_experts > 0 and group.size > 1:
+            foreign = cfg.num_hidden_layers * 3 * (cfg.num_experts - cfg.num_experts // group.size)
+        assert len(loaded) == len(weights) - foreign, (len(loaded), len(weights), foreign)
         eng = LLMEngine(model, EngineConfig(num_pages=32, max_batched_tokens=512, decode_burst=4, max_model_len=1024))
         seqs = [Sequence(f"s{i}", np.arange(5 + i, 200 + 40 * i, dtype=np.int32), SamplingParams(12, True), return_hidden=True)
                 for i in range(3)]
