@@ -1,7 +1,9 @@
 """Multi-GPU checks of the fused compute+collective kernels.  Launched by ``test_multigpu.py`` as
 ``torchrun --nproc-per-node N tests/multigpu_fused.py [section ...]`` (one rank per GPU); exits non-zero on a mismatch.
 Sections: ``allreduce`` (decode GEMM + all-reduce tail), ``llm`` (tensor-parallel decoder), ``vit`` (encoder chain),
-``dit`` (sequence-parallel diffusion transformer), ``moe`` (expert parallelism); all of them when none is named."""
+``towers`` (LayerNorm towers), ``dit`` (sequence-parallel diffusion transformer), ``moe`` (expert parallelism); those when
+none is named.  ``llm_moe`` (tensor-parallel mixture-of-experts decoder) and ``stress`` (random per-rank stalls) run on
+request."""
 
 import os
 import sys
@@ -55,6 +57,10 @@ def tp_llm_matches_single_gpu(g):
     a dense model, and a mixture-of-experts model whose experts are spread over the ranks (tokens are replicated, every
     rank routes a slice, the combine kernel fills all ranks' outputs; the whole layer sits inside the decode graph)."""
     _tp_llm(g, {})
+
+
+def tp_moe_llm_matches_single_gpu(g):
+    """Same check with a mixture-of-experts decoder (see :func:`tp_llm_matches_single_gpu`)."""
     _tp_llm(g, dict(num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256))
 
 
@@ -545,8 +551,12 @@ def flag_protocol_stress(g):
         print("flag protocols: 40 iterations with random per-rank stalls, results bit-identical", flush=True)
 
 
-SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "vit": tp_vision_tower, "towers": tp_layernorm_towers,
+SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu, "llm_moe": tp_moe_llm_matches_single_gpu,
+            "vit": tp_vision_tower, "towers": tp_layernorm_towers,
             "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts, "stress": flag_protocol_stress}
+
+
+DEFAULT_SECTIONS = ["allreduce", "llm", "vit", "towers", "dit", "moe"]
 
 
 def main():
@@ -554,7 +564,7 @@ def main():
     g = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
                          master_port=int(os.environ["MASTER_PORT"]), local_device=int(os.environ.get("LOCAL_RANK", rank)))
     assert g.fabric is not None, "fabric missing"
-    for name in (sys.argv[1:] or list(SECTIONS)):
+    for name in (sys.argv[1:] or DEFAULT_SECTIONS):
         SECTIONS[name](g)
         dist.barrier()
     if rank == 0:
