@@ -546,6 +546,8 @@ def test_reduce_norm_push_kernel_single_rank(layer_norm):
 
 def test_packed_attention_windows_match_unpacked():
     """Several short windows sharing one 128-row tile (per-token key bounds) against one window per tile."""
+    import numpy as np
+
     from cornserve_b200.models.qwen2_5_vl import pack_windows, window_index
 
     grid = np.array([[1, 52, 92], [1, 16, 24], [2, 20, 28]])
