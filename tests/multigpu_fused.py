@@ -2,8 +2,8 @@
 ``torchrun --nproc-per-node N tests/multigpu_fused.py [section ...]`` (one rank per GPU); exits non-zero on a mismatch.
 Sections: ``allreduce`` (decode GEMM + all-reduce tail), ``llm`` (tensor-parallel decoder), ``vit`` (encoder chain),
 ``towers`` (LayerNorm towers), ``dit`` (sequence-parallel diffusion transformer), ``moe`` (expert parallelism); those when
-none is named.  ``llm_moe`` (tensor-parallel mixture-of-experts decoder) and ``stress`` (random per-rank stalls) run on
-request."""
+``stress`` (random per-rank stalls before the fused kernels); those when none is named.  ``llm_moe`` (tensor-parallel
+mixture-of-experts decoder) runs on request."""
 
 import os
 import sys
@@ -102,7 +102,8 @@ def _tp_llm(g, extra):
         assert cos > 0.99, f"{sid}: prefill hidden states differ (cos {cos:.4f})"
         ta, tb = outs["tp"][0][sid], outs["single"][0][sid]
         agree = sum(x == y for x, y in zip(ta, tb)) / len(tb)
-        assert ta[0] == tb[0] and agree >= 0.5, f"{sid}: tokens {ta} vs {tb}"
+        # with experts a near-tie in the router sends a token elsewhere and the greedy continuations part ways sooner
+        assert ta[0] == tb[0] and agree >= (0.25 if extra else 0.5), f"{sid}: tokens {ta} vs {tb}"
     # every rank must have produced the same tokens (the engines run in lock-step)
     mine = torch.tensor([t for sid in sorted(outs["tp"][0]) for t in outs["tp"][0][sid]], device=g.device)
     ref_t = mine.clone()
@@ -556,7 +557,7 @@ SECTIONS = {"allreduce": decode_allreduce_tail, "llm": tp_llm_matches_single_gpu
             "dit": sp_diffusion_transformer, "moe": ep_mixture_of_experts, "stress": flag_protocol_stress}
 
 
-DEFAULT_SECTIONS = ["allreduce", "llm", "vit", "towers", "dit", "moe"]
+DEFAULT_SECTIONS = ["allreduce", "llm", "vit", "towers", "dit", "moe", "stress"]
 
 
 def main():
