@@ -169,11 +169,8 @@ class DualStreamBlock(nn.Module):
                            out=qkv[lay.txt_rows(b)])
                 ops.linear(xi[b * lay.n_img:(b + 1) * lay.n_img], self.img.qkv.weight, self.img.qkv.bias,
                            out=qkv[lay.img_rows(b)])
-            for part, (ni, nt) in enumerate(((self.img.norm_q, self.txt.norm_q), (self.img.norm_k, self.txt.norm_k))):
-                heads = qkv[:, part * D:(part + 1) * D].view(lay.rows, H, d)
-                for b in range(B):
-                    ops.head_norm_rope_(heads[lay.txt_rows(b)], nt.weight, 1e-6, lay.cs_txt)
-                    ops.head_norm_rope_(heads[lay.img_rows(b)], ni.weight, 1e-6, lay.cs_img)
+            ops.qk_norm_rope_(qkv, H, d, D, self.txt.norm_q.weight, self.txt.norm_k.weight, 1e-6, lay.cs_rows,
+                              wq2=self.img.norm_q.weight, wk2=self.img.norm_k.weight, seg=lay.per_sample, n_first=lay.n_txt)
             attn = lay.attention(qkv, H, d, self.group)  # [rows, D]
         for b in range(B):
             g_i, g_t = mod_i[b:b + 1, 2 * D:3 * D], mod_t[b:b + 1, 2 * D:3 * D]
@@ -201,9 +198,8 @@ class DualStreamBlock(nn.Module):
         fu.qkv_scatter(xi, self.img.qkv.weight, self.img.qkv.bias, lay.n_txt, lay.n_img, per, per)
         R = P * lay.rows
         full = fu.gathered_qkv(R)  # [R, 3 * own], rows = (sample, rank, that rank's [text; image] tokens)
-        for part, (ni, nt) in enumerate(((self.img.norm_q, self.txt.norm_q), (self.img.norm_k, self.txt.norm_k))):
-            ops.head_norm_rope_(full[:, part * own:(part + 1) * own].view(R, Hl, d), nt.weight, 1e-6, lay.cs_full,
-                                w2=ni.weight, seg=per, n_first=lay.n_txt)
+        ops.qk_norm_rope_(full, Hl, d, own, self.txt.norm_q.weight, self.txt.norm_k.weight, 1e-6, lay.cs_full,
+                          wq2=self.img.norm_q.weight, wk2=self.img.norm_k.weight, seg=per, n_first=lay.n_txt)
         packed = full if lay.gather_idx is None else ops.gather_rows(full, lay.gather_idx)
         T = packed.shape[0]
         q, k, v = (packed[:, i * own:(i + 1) * own].view(T, Hl, d) for i in range(3))
@@ -233,6 +229,7 @@ class JointLayout:
     gather_idx: torch.Tensor | None = None
     fused: object | None = None         # FusedUlysses context when the exchanges are done by the kernels
     cs_full: torch.Tensor | None = None  # rotary table of every token of every rank, in gathered row order
+    cs_rows: torch.Tensor | None = None  # rotary table of this rank's rows ([text; image] per sample)
     o_full: torch.Tensor | None = None   # zeroed [sp * rows, own] scratch for the scattered attention output
 
     @property
@@ -333,6 +330,7 @@ class QwenImageDiT(nn.Module):
         cs_txt = self.rope.text(n_txt_pad, h, w)[r * n_txt:(r + 1) * n_txt]
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
         lay = JointLayout(batch, n_txt, n_img, list(txt_len), t(cs_txt), t(cs_img), P, r)
+        lay.cs_rows = t(np.tile(np.concatenate([cs_txt, cs_img]), (batch, 1, 1)))
         per = n_txt + n_img
         if all(n == n_txt_pad for n in txt_len):
             # no padding: a sample's rows are contiguous whatever the rank order inside (attention is not causal)
@@ -522,8 +520,12 @@ class QwenImageModel:
     @torch.inference_mode()
     def denoise(self, prompt_embeds: list[torch.Tensor], height: int, width: int, num_inference_steps: int,
                 negative_embeds: list[torch.Tensor] | None = None, true_cfg_scale: float = 4.0,
-                latents: torch.Tensor | None = None) -> torch.Tensor:
-        """Run the sampler; returns clean latents ``[B, 16, height/8, width/8]`` (fp32)."""
+                latents: torch.Tensor | None = None, batch_cfg: bool = True) -> torch.Tensor:
+        """Run the sampler; returns clean latents ``[B, 16, height/8, width/8]`` (fp32).
+
+        With a negative prompt, ``batch_cfg`` runs the conditional and the unconditional samples as one batch of
+        ``2B`` per step (the reference pipeline calls the denoiser twice): the text-stream GEMMs and the modulation
+        projections read their weights once instead of twice, and every launch carries twice the rows."""
         cfg, dev, P = self.cfg, self.device, self.group.size
         B = len(prompt_embeds)
         vs, patch = cfg.vae_scale_factor, cfg.dit.patch_size
@@ -540,20 +542,30 @@ class QwenImageModel:
         def prep(embeds: list[torch.Tensor]):
             lens = [int(e.shape[0]) for e in embeds]
             n_pad = -(-max(lens) // P) * P
-            buf = torch.zeros((B, n_pad, self.embedding_dim), device=dev, dtype=self.dtype)
+            buf = torch.zeros((len(embeds), n_pad, self.embedding_dim), device=dev, dtype=self.dtype)
             for b, e in enumerate(embeds):
                 buf[b, : lens[b]] = e.to(dev, self.dtype)
-            lay = self.dit.make_layout(B, lens, n_pad, (gh, gw))
+            lay = self.dit.make_layout(len(embeds), lens, n_pad, (gh, gw))
             return self._shard(buf, n_pad // P), lay
 
-        cond, lay_c = prep(prompt_embeds)
-        unc = prep(negative_embeds) if negative_embeds is not None else None
+        both = unc = None
+        if negative_embeds is not None and batch_cfg:
+            both = prep(list(prompt_embeds) + list(negative_embeds))
+        else:
+            cond, lay_c = prep(prompt_embeds)
+            unc = prep(negative_embeds) if negative_embeds is not None else None
         sig = flow_match_sigmas(num_inference_steps, gh * gw, cfg.sched)
+        rows = B * n_img
         for i in range(num_inference_steps):
-            t = torch.full((B,), float(sig[i]), device=dev, dtype=torch.float32)
             xin = x.to(self.dtype)
-            v_c = self.dit(xin, cond, t, lay_c)
-            v_u = self.dit(xin, unc[0], t, unc[1]) if unc is not None else None
+            if both is not None:
+                t = torch.full((2 * B,), float(sig[i]), device=dev, dtype=torch.float32)
+                v = self.dit(torch.cat([xin, xin]), both[0], t, both[1])
+                v_c, v_u = v[:rows], v[rows:]
+            else:
+                t = torch.full((B,), float(sig[i]), device=dev, dtype=torch.float32)
+                v_c = self.dit(xin, cond, t, lay_c)
+                v_u = self.dit(xin, unc[0], t, unc[1]) if unc is not None else None
             ops.flow_step_(x, v_c.contiguous(), None if v_u is None else v_u.contiguous(), true_cfg_scale,
                            float(sig[i + 1] - sig[i]), norm_rescale=True)
         x = x.view(B, n_img, -1)

@@ -584,6 +584,26 @@ def head_norm_rope_(x: torch.Tensor, w: torch.Tensor | None, eps: float, cs: tor
     return x
 
 
+def qk_norm_rope_(x: torch.Tensor, heads: int, d: int, part_stride: int, wq: torch.Tensor, wk: torch.Tensor, eps: float,
+                  cs: torch.Tensor, *, wq2: torch.Tensor | None = None, wk2: torch.Tensor | None = None, seg: int = 0,
+                  n_first: int = 0) -> torch.Tensor:
+    """In place on the q and k parts of a fused projection ``x`` = ``[T, >= part_stride + heads*d]``: q heads start at
+    column 0, k heads at column ``part_stride``.  Each head row gets :func:`head_norm_rope_` with ``wq`` / ``wk``
+    (``wq2`` / ``wk2`` for rows past ``n_first`` inside a segment of ``seg`` rows).  One launch for ``d == 128``."""
+    T = x.shape[0]
+    if not (x.is_cuda and d == 128):
+        for off, w, w2 in ((0, wq, wq2), (part_stride, wk, wk2)):
+            head_norm_rope_(x[:, off:off + heads * d].view(T, heads, d), w, eps, cs, w2=w2, seg=seg, n_first=n_first)
+        return x
+    assert x.stride(1) == 1 and x.dtype == torch.bfloat16 and x.shape[1] >= part_stride + heads * d
+    assert cs.dtype == torch.float32 and cs.is_contiguous() and cs.shape[-1] * 2 == d and cs.shape[0] >= T
+    lib = _lib.load()
+    _chk(lib.cs_qk_norm_rope128(x.data_ptr(), x.stride(0), T, heads, part_stride, _ptr(wq), _ptr(wk), _ptr(wq2), _ptr(wk2),
+                                float(eps), _ptr(cs), seg, n_first, _stream()), "cs_qk_norm_rope128")
+    _count()
+    return x
+
+
 def softmax_rows(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     """Row soft-max of ``scale * x`` for a 2-D bf16 matrix (columns a multiple of 8)."""
     if not x.is_cuda:

@@ -87,6 +87,67 @@ __global__ void head_norm_rope_kernel(__nv_bfloat16* x, long long ldx, long long
 }
 
 // ---------------------------------------------------------------------------------------
+// The same operation for d = 128 on the q and the k part of a fused [T, q | k | v] projection in one launch.
+// One warp per (token, group of HG heads): the token's rotary row and the four norm weights are loaded once, all
+// 2 * HG head rows are fetched before the first is reduced.  Lane l owns the adjacent pair (2l, 2l+1) of the first
+// half and its partners (2l+64, 2l+65), so every access is one 4-byte word per lane (128 contiguous bytes per warp).
+// ---------------------------------------------------------------------------------------
+template <int HG>
+__global__ void qk_norm_rope128_kernel(__nv_bfloat16* x, long long ldx, long long T, int heads, long long part_stride,
+                                       const __nv_bfloat16* wq, const __nv_bfloat16* wk, const __nv_bfloat16* wq2,
+                                       const __nv_bfloat16* wk2, float eps, const float* cs, int seg, int n_first) {
+  const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int groups = heads / HG;
+  if (item >= T * groups) return;
+  const long long t = item / groups;
+  const int g = static_cast<int>(item - t * groups);
+  if (wq2 != nullptr && static_cast<int>(t % seg) >= n_first) { wq = wq2; wk = wk2; }
+  const float2 c = *reinterpret_cast<const float2*>(cs + t * 128 + 2 * lane);
+  const float2 sn = *reinterpret_cast<const float2*>(cs + t * 128 + 64 + 2 * lane);
+  __nv_bfloat16* row = x + t * ldx + static_cast<long long>(g) * HG * 128 + 2 * lane;
+  __nv_bfloat162 lo[2][HG], hi[2][HG];
+#pragma unroll
+  for (int p = 0; p < 2; ++p)
+#pragma unroll
+    for (int h = 0; h < HG; ++h) {
+      const __nv_bfloat16* b = row + p * part_stride + h * 128;
+      lo[p][h] = *reinterpret_cast<const __nv_bfloat162*>(b);
+      hi[p][h] = *reinterpret_cast<const __nv_bfloat162*>(b + 64);
+    }
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const __nv_bfloat16* w = p == 0 ? wq : wk;
+    const float2 wl = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + 2 * lane));
+    const float2 wh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + 64 + 2 * lane));
+    float ss[HG];
+    float2 a[HG], b[HG];
+#pragma unroll
+    for (int h = 0; h < HG; ++h) {
+      a[h] = __bfloat1622float2(lo[p][h]);
+      b[h] = __bfloat1622float2(hi[p][h]);
+      ss[h] = a[h].x * a[h].x + a[h].y * a[h].y + b[h].x * b[h].x + b[h].y * b[h].y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int h = 0; h < HG; ++h) ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], o);
+#pragma unroll
+    for (int h = 0; h < HG; ++h) {
+      const float rstd = rsqrtf(ss[h] * (1.f / 128.f) + eps);
+      // round to bf16 after the norm, as a separate norm kernel would
+      const float ax = __bfloat162float(__float2bfloat16(a[h].x * rstd * wl.x));
+      const float ay = __bfloat162float(__float2bfloat16(a[h].y * rstd * wl.y));
+      const float bx = __bfloat162float(__float2bfloat16(b[h].x * rstd * wh.x));
+      const float by = __bfloat162float(__float2bfloat16(b[h].y * rstd * wh.y));
+      __nv_bfloat16* d = row + p * part_stride + h * 128;
+      *reinterpret_cast<__nv_bfloat162*>(d) = __floats2bfloat162_rn(ax * c.x - bx * sn.x, ay * c.y - by * sn.y);
+      *reinterpret_cast<__nv_bfloat162*>(d + 64) = __floats2bfloat162_rn(bx * c.x + ax * sn.x, by * c.y + ay * sn.y);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // y[r, :] = softmax(scale * x[r, :]) over `cols` columns, bf16 in / out, one CTA of 256 threads per row.
 // ---------------------------------------------------------------------------------------
 __global__ void softmax_rows_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* y, long long ldy,
@@ -246,6 +307,27 @@ CS_API int cs_head_norm_rope(void* x, long long ldx, long long T, int heads, int
   head_norm_rope_kernel<<<blocks_for(warps, 8), 256, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)x, ldx, T, heads, d, (const __nv_bfloat16*)w, eps, (const float*)cs, (const __nv_bfloat16*)w2, seg,
       n_first);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+// q and k parts of x = [T, ...] (q heads at column 0, k heads at column part_stride), d = 128, in one launch.
+CS_API int cs_qk_norm_rope128(void* x, long long ldx, long long T, int heads, long long part_stride, const void* wq,
+                              const void* wk, const void* wq2, const void* wk2, float eps, const void* cs, int seg,
+                              int n_first, void* stream) {
+  if (T <= 0 || heads <= 0) return 0;
+  if (wq == nullptr || wk == nullptr || cs == nullptr || (ldx & 1) || (part_stride & 1) ||
+      ((wq2 == nullptr) != (wk2 == nullptr)) || (wq2 != nullptr && seg <= 0) || (reinterpret_cast<uintptr_t>(x) & 3) ||
+      (reinterpret_cast<uintptr_t>(cs) & 7))
+    return -1;
+  auto s = (cudaStream_t)stream;
+#define CS_QK_LAUNCH(HG)                                                                                          \
+  qk_norm_rope128_kernel<HG><<<blocks_for(T * (heads / HG), 8), 256, 0, s>>>(                                     \
+      (__nv_bfloat16*)x, ldx, T, heads, part_stride, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wk,         \
+      (const __nv_bfloat16*)wq2, (const __nv_bfloat16*)wk2, eps, (const float*)cs, seg, n_first)
+  if (heads % 4 == 0) CS_QK_LAUNCH(4);
+  else if (heads % 2 == 0) CS_QK_LAUNCH(2);
+  else CS_QK_LAUNCH(1);
+#undef CS_QK_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 

@@ -347,3 +347,20 @@ def test_code2wav_matches_hf(device):
     assert full.shape[0] == want_chunks.shape[1]
     assert F.cosine_similarity(full, want_chunks[0], dim=0).item() > 0.98
     assert len(pieces[1]) == 2  # the shorter request ends early
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_batched_cfg_matches_two_passes(device):
+    """Conditional and unconditional samples in one batch of 2B give the latents of two separate denoiser calls,
+    also when the negative prompt is shorter (padded text rows are masked out of the joint attention)."""
+    dit = QwenImageDiTConfig(in_channels=64, out_channels=16, num_layers=2, attention_head_dim=64, num_attention_heads=2,
+                             joint_attention_dim=64, axes_dims_rope=(8, 28, 28))
+    cfg = QwenImagePipelineConfig(dit=dit, vae=TINY_VAE)
+    model = QwenImageModel(cfg, device=device, seed=3)
+    g = torch.Generator().manual_seed(5)
+    emb = [torch.randn(6, 64, generator=g).bfloat16(), torch.randn(4, 64, generator=g).bfloat16()]
+    neg = [torch.randn(2, 64, generator=g).bfloat16(), torch.randn(6, 64, generator=g).bfloat16()]
+    one = model.denoise(emb, 64, 32, 3, negative_embeds=neg, true_cfg_scale=3.0, batch_cfg=True).float().cpu()
+    two = model.denoise(emb, 64, 32, 3, negative_embeds=neg, true_cfg_scale=3.0, batch_cfg=False).float().cpu()
+    tol = 1e-4 if device == "cpu" else 0.06
+    assert (one - two).abs().max().item() <= tol * max(1.0, two.abs().max().item())

@@ -229,6 +229,29 @@ def test_head_norm_rope(d, heads, with_norm, with_rope):
     assert torch.equal(buf[:, : heads * d], before[:, : heads * d]) and torch.equal(buf[:, 2 * heads * d:], before[:, 2 * heads * d:])
 
 
+@pytest.mark.parametrize("heads,two_streams", [(24, True), (6, False), (3, True), (2, True)])
+def test_qk_norm_rope_one_launch(heads, two_streams):
+    """q and k parts of a fused projection in one launch (d = 128) against the per-part fp32 restatement."""
+    torch.manual_seed(14)
+    T, d, seg, n_first = 93, 128, 31, 7
+    D = heads * d
+    buf = _rand(T, 3 * D + 8)[:, :3 * D]     # row stride wider than the columns
+    ws = [(1 + 0.2 * torch.randn(d, device=DEV)).bfloat16() for _ in range(4)]
+    ang = torch.rand(T, d // 2, device=DEV) * 6.28
+    cs = torch.stack([ang.cos(), ang.sin()], dim=1).contiguous()
+    first = (torch.arange(T, device=DEV) % seg) < n_first
+    want = buf.clone()
+    for part, (w, w2) in enumerate(((ws[0], ws[2]), (ws[1], ws[3]))):
+        x = buf[:, part * D:(part + 1) * D].reshape(T, heads, d)
+        a = ref.head_norm_rope(x.clone(), w, 1e-6, cs)
+        b = ref.head_norm_rope(x.clone(), w2, 1e-6, cs) if two_streams else a
+        want[:, part * D:(part + 1) * D] = torch.where(first[:, None, None], a, b).reshape(T, D).to(want.dtype)
+    kw = dict(wq2=ws[2], wk2=ws[3], seg=seg, n_first=n_first) if two_streams else {}
+    ops.qk_norm_rope_(buf, heads, d, D, ws[0], ws[1], 1e-6, cs, **kw)
+    _close(buf[:, :2 * D], want[:, :2 * D], 2e-2, 2e-2, "qk_norm_rope")
+    assert torch.equal(buf[:, 2 * D:], want[:, 2 * D:])
+
+
 def test_softmax_rows():
     torch.manual_seed(11)
     x = _rand(300, 1032, scale=4.0)
