@@ -7,6 +7,8 @@
   python -m cornserve_b200.ops.microbench attn-full 16 80 4784 0   # heads, head_dim, length, causal
   python -m cornserve_b200.ops.microbench attn-decode 48 3500      # sequences, context
   python -m cornserve_b200.ops.microbench norm 19136 1280
+  python -m cornserve_b200.ops.microbench adaln 8192 3072          # LayerNorm + AdaLN modulation (two samples)
+  python -m cornserve_b200.ops.microbench qk-norm-rope 8704 24     # per-head RMSNorm + rotation of q and k, d = 128
   python -m cornserve_b200.ops.microbench gemm-fp8 16384 3584 3584 # e4m3 with 1x128 / 128x128 block scales
   python -m cornserve_b200.ops.microbench moe 128 128 8 2048 768   # tokens, experts, top-k, hidden, expert FFN width
 
@@ -137,6 +139,19 @@ def main() -> None:
         x, r, w = rnd(rows, H), rnd(rows, H), rnd(H)
         secs = t(lambda: ops.rms_norm(x, w, 1e-6, residual=r))
         report(f"rms_norm+residual {rows}x{H}", secs, 0.0, 2.0 * 4 * rows * H)
+    elif k == "adaln":
+        rows, H = a.args[:2]
+        x, mod = rnd(rows, H), rnd(2, 2 * H, std=0.1)
+        secs = t(lambda: ops.layer_norm(x, None, None, 1e-6, scale=mod[:, :H], shift=mod[:, H:], rows_per_batch=rows // 2))
+        report(f"modulated layer_norm {rows}x{H}", secs, 0.0, 2.0 * 2 * rows * H)
+    elif k == "qk-norm-rope":
+        T, heads = a.args[:2]
+        d = 128
+        qkv, ws = rnd(T, 3 * heads * d), [rnd(d) for _ in range(4)]
+        cs = torch.randn(T, 2, d // 2, device=dev, generator=g)
+        secs = t(lambda: ops.qk_norm_rope_(qkv, heads, d, heads * d, ws[0], ws[1], 1e-6, cs, wq2=ws[2], wk2=ws[3],
+                                           seg=T // 2, n_first=T // 34))
+        report(f"q/k head norm + rotation {T} tokens x {heads} heads", secs, 0.0, 2.0 * 2 * 2 * T * heads * d + 4.0 * T * d)
     elif k == "gemm-fp8":
         M, N, K = a.args[:3]
         x = rnd(M, K)

@@ -140,36 +140,41 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_kernel(const NormParams p) 
   }
 }
 
-// Same math with one warp per row (no block-wide synchronisation); used when H <= 2048.
-constexpr int WNORM_MAXV = 8;
+// Same math with one warp per row (no block-wide synchronisation).  The row stays in registers as the packed bf16
+// words that were loaded (or stored to `res_out`), so MAXV = 16 (4096 columns) costs 64 registers.
+template <int MAXV>
 __global__ void __launch_bounds__(256) norm_warp_kernel(const NormParams p) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
   const int nvec = p.H >> 3;
-  float v[WNORM_MAXV][8];
+  uint4 raw[MAXV];
   const uint4* xr = reinterpret_cast<const uint4*>(p.x + (long long)row * p.ldx);
   const uint4* rr = p.residual ? reinterpret_cast<const uint4*>(p.residual + (long long)row * p.ldres) : nullptr;
   uint4* ro = p.res_out ? reinterpret_cast<uint4*>(p.res_out + (long long)row * p.ldro) : nullptr;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) raw[i] = xr[c];
+  }
   float s = 0.f, ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < WNORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int c = lane + i * 32;
     if (c < nvec) {
-      unpack8(xr[c], v[i]);
+      float v[8];
+      unpack8(raw[i], v);
       if (rr) {
         float r[8];
         unpack8(rr[c], r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+        for (int j = 0; j < 8; ++j) v[j] += r[j];
+        raw[i] = pack8(v);   // normalise the value that is stored (bf16-rounded), like the unfused sequence
+        unpack8(raw[i], v);
       }
-      if (ro) {
-        uint4 w = pack8(v[i]);
-        ro[c] = w;
-        unpack8(w, v[i]);
-      }
+      if (ro) ro[c] = raw[i];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
+      for (int j = 0; j < 8; ++j) { s += v[j]; ss += v[j] * v[j]; }
     }
   }
   float mean = 0.f, rstd;
@@ -177,11 +182,13 @@ __global__ void __launch_bounds__(256) norm_warp_kernel(const NormParams p) {
     mean = warp_sum(s) / p.H;
     float var = 0.f;
 #pragma unroll
-    for (int i = 0; i < WNORM_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       const int c = lane + i * 32;
       if (c < nvec) {
+        float v[8];
+        unpack8(raw[i], v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; var += d * d; }
+        for (int j = 0; j < 8; ++j) { float d = v[j] - mean; var += d * d; }
       }
     }
     rstd = rsqrtf(warp_sum(var) / p.H + p.eps);
@@ -195,15 +202,16 @@ __global__ void __launch_bounds__(256) norm_warp_kernel(const NormParams p) {
   const uint4* sh4 = p.shift ? reinterpret_cast<const uint4*>(p.shift + mrow) : nullptr;
   uint4* yr = reinterpret_cast<uint4*>(p.y + (long long)row * p.ldy);
 #pragma unroll
-  for (int i = 0; i < WNORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int c = lane + i * 32;
     if (c < nvec) {
-      float o[8], w[8], b[8];
+      float v[8], o[8], w[8], b[8];
+      unpack8(raw[i], v);
       if (w4) unpack8(__ldg(w4 + c), w);
       if (b4) unpack8(__ldg(b4 + c), b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float t = (v[i][j] - mean) * rstd;
+        float t = (v[j] - mean) * rstd;
         if (w4) t *= (p.mode == 1 ? 1.0f + w[j] : w[j]);
         if (b4) t += b[j];
         o[j] = t;
@@ -510,8 +518,10 @@ CS_API int cs_norm(const void* x, long long ldx, const void* residual, long long
   p.ldmod = ldmod; p.rpb = rpb > 0 ? rpb : 1;
   p.y = (__nv_bfloat16*)y; p.ldy = ldy;
   p.rows = rows; p.H = H; p.eps = eps; p.mode = mode;
-  if (H <= 32 * 8 * WNORM_MAXV && rows >= 64)
-    norm_warp_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(p);
+  if (H <= 2048 && rows >= 64)
+    norm_warp_kernel<8><<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(p);
+  else if (H <= 4096 && rows >= 2048 && mode == 2)  // two reductions per row: a warp needs no block-wide barrier for them
+    norm_warp_kernel<16><<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(p);
   else
     norm_kernel<<<rows, NORM_THREADS, 0, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
