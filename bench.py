@@ -44,6 +44,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--requests-per-gpu", type=int, default=128)
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--prompt-tokens", type=int, default=128)
+    ap.add_argument("--prefill-tokens", type=int, default=18944, help="token budget of one prefill step (148 SMs x 128 rows)")
+    ap.add_argument("--vit-patches", type=int, default=34000, help="patch budget of one vision-tower call (7 images of 1280x720)")
     ap.add_argument("--small", action="store_true", help="tiny model/config for smoke runs (not a valid number)")
     return ap.parse_args()
 
@@ -140,8 +142,12 @@ def main() -> None:
     llm = QwenLLM(lcfg, device=dev)
     tokens_per_img = 1196 if not args.small else 64
     pages = R * (-(-(4 * (tokens_per_img + 2) + prompt_tok + out_tok + 2) // 128) + 1) + 8
-    pipe = MLLMPipeline(vision, llm, EngineConfig(num_pages=pages, max_batched_tokens=16384, max_num_seqs=max(R, 1),
-                                                  decode_burst=16, max_model_len=8192))
+    # 148 SMs x 128-row tiles: with 18944 tokens per prefill step every GEMM of the decoder has a whole number of tile
+    # waves (14, 18 and 74 column tiles per row tile); 7 images of 4784 patches do the same for the vision tower
+    # (262 row tiles x 5 / 14 / 15 column tiles = 8.85 / 24.8 / 26.6 waves, against 10.1 / 28.3 / 30.3 for 8 images)
+    pipe = MLLMPipeline(vision, llm, EngineConfig(num_pages=pages, max_batched_tokens=args.prefill_tokens,
+                                                  max_num_seqs=max(R, 1), decode_burst=16, max_model_len=8192),
+                        max_patches_per_encode=args.vit_patches)
 
     rng = np.random.default_rng(rank)
     n_imgs = [1 + (i % 4) for i in range(R)]
