@@ -79,6 +79,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--splits", type=int, default=0, help="K splits of the weight-streaming kernel (0 = its own choice)")
     a = ap.parse_args()
     t = Timer(a.iters, a.warmup, not a.no_flush)
     dev = "cuda"
@@ -90,12 +91,12 @@ def main() -> None:
         x = rnd(M, K)
         if k == "swiglu":
             w = rnd(2 * N, K, std=K ** -0.5)
-            secs = t(lambda: ops.swiglu_linear(x, w, bn=a.bn))
+            secs = t(lambda: ops.swiglu_linear(x, w, bn=a.bn, skinny=True if a.splits else None, splits=a.splits))
             report(f"swiglu {M}x{N}x{K}", secs, 4.0 * M * N * K, 2.0 * (M * K + 2 * N * K + M * N))
         else:
             w = rnd(N, K, std=K ** -0.5)
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            secs = t(lambda: ops.linear(x, w, out=out, bn=a.bn, skinny=(k == "skinny")))
+            secs = t(lambda: ops.linear(x, w, out=out, bn=a.bn, skinny=(k == "skinny"), splits=a.splits))
             report(f"{k} {M}x{N}x{K}", secs, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N))
     elif k == "attn-window":
         from cornserve_b200.models.qwen2_5_vl import pack_windows, window_index
