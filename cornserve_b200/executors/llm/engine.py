@@ -106,7 +106,7 @@ class Sequence:
 @dataclass
 class EngineConfig:
     num_pages: int = 2048
-    max_batched_tokens: int = 16384
+    max_batched_tokens: int = 18944   # 148 SMs x 128-row tiles: every prefill GEMM gets whole tile waves
     max_num_seqs: int = 256
     decode_burst: int = 8
     use_cuda_graph: bool = True

@@ -72,7 +72,7 @@ def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
     ap.add_argument("--cornserve-sidecar-ranks", type=int, nargs="*", default=[])
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--max-model-len", type=int, default=32768)
-    ap.add_argument("--max-num-batched-tokens", type=int, default=16384)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=18944)
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--num-kv-pages", type=int, default=0, help="0 = size the cache from free memory")
     ap.add_argument("--decode-burst", type=int, default=4)
