@@ -18,6 +18,7 @@ reads the produced tokens once per burst.
 from __future__ import annotations
 
 import enum
+import random
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -37,6 +38,25 @@ class SamplingParams:
     max_tokens: int = 256
     ignore_eos: bool = False
     stop_token_ids: tuple[int, ...] = ()
+    temperature: float = 0.0      # 0 = greedy (arg-max); > 0 samples from softmax(logits / temperature)
+    top_p: float = 1.0            # nucleus: smallest set of most likely tokens whose mass reaches top_p
+    top_k: int = 0                # <= 0: off
+    seed: int | None = None       # names the request's random stream; None = drawn once when the request is added
+
+    @classmethod
+    def from_request(cls, body: dict, **kw) -> "SamplingParams":
+        """OpenAI-style request fields.  Without ``temperature`` the request decodes greedily."""
+        t = body.get("temperature")
+        k = body.get("top_k")
+        seed = body.get("seed")
+        return cls(temperature=float(t) if t is not None else 0.0,
+                   top_p=float(body["top_p"]) if body.get("top_p") is not None else 1.0,
+                   top_k=int(k) if k is not None and int(k) > 0 else 0,
+                   seed=int(seed) if seed is not None else None, **kw)
+
+    @property
+    def samples(self) -> bool:
+        return self.temperature > 0.0
 
 
 @dataclass
@@ -139,8 +159,18 @@ class _DecodeState:
         self.logits_idx = torch.arange(B, **i32)
         self.out_log = torch.zeros(max(burst, 1), B, **i32)
         self.step_counter = torch.zeros(1, **i32)
+        # sampling parameters of every row (used by the buckets whose graph ends in the sampling kernel)
+        self.temperature = torch.zeros(B, dtype=torch.float32, device=device)
+        self.top_p = torch.ones(B, dtype=torch.float32, device=device)
+        self.top_k = torch.zeros(B, **i32)
+        self.seed = torch.zeros(B, dtype=torch.int64, device=device)
+        self.draws = torch.zeros(B, **i32)
+        self.sampling = False
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_replay = 0
+
+    def sampler(self):
+        return (self.temperature, self.top_p, self.top_k, self.seed, self.draws) if self.sampling else None
 
     def meta(self) -> BatchMeta:
         return BatchMeta(self.input_ids, self.positions, self.slot, self.cu_q, self.kv_len, self.block_table,
@@ -171,6 +201,8 @@ class LLMEngine:
     # requests
     # ---------------------------------------------------------------------------------------------
     def add_request(self, seq: Sequence) -> None:
+        if seq.params.samples and seq.params.seed is None:
+            seq.params.seed = random.getrandbits(62)
         if seq.prefilled is not None:
             if seq.prompt_len + seq.params.max_tokens > self.cfg.max_model_len:
                 raise ValueError("request exceeds max_model_len")
@@ -342,8 +374,14 @@ class LLMEngine:
         want_hidden = any(s.return_hidden for s, _ in batch)
         cap_layers = sorted({layer for s, _ in batch for layer in s.capture_layers})
         capture = dict.fromkeys(cap_layers) if cap_layers else None
+        sampler = None
+        if any(s.params.samples for s, _ in batch):
+            # the first token of a sampled request is draw 0 of its stream (rows of greedy requests keep temperature 0)
+            sampler = (f([s.params.temperature for s, _ in batch], np.float32), f([s.params.top_p for s, _ in batch], np.float32),
+                       f([s.params.top_k for s, _ in batch]), f([s.params.seed or 0 for s, _ in batch], np.int64),
+                       f([len(s.output_ids) for s, _ in batch]))
         with torch.inference_mode():
-            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden, capture=capture)
+            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden, capture=capture, sampler=sampler)
         toks = next_tok.tolist()
         self.stats["prefill_tokens"] += tok
         outs: list[StepOutput] = []
@@ -381,9 +419,12 @@ class LLMEngine:
         burst = max(1, min(self.cfg.decode_burst, min(s.params.max_tokens - len(s.output_ids) for s in seqs)))
         n = len(seqs)
         B = self._bucket(n) if (self.on_gpu and self.cfg.use_cuda_graph) else n
-        st = self._decode_states.get(B)
+        sampling = any(s.params.samples for s in seqs)
+        key = (B, "sample") if sampling else B   # a bucket's graph ends either in the arg-max or in the sampling kernel
+        st = self._decode_states.get(key)
         if st is None:
-            st = self._decode_states[B] = _DecodeState(B, self.max_blocks, self.cfg.decode_burst, self.device)
+            st = self._decode_states[key] = _DecodeState(B, self.max_blocks, self.cfg.decode_burst, self.device)
+            st.sampling = sampling
         # host-side batch state
         ids = np.zeros(B, np.int32); pos = np.zeros((3, B), np.int32); slot = np.zeros(B, np.int32)
         kvl = np.ones(B, np.int32); act = np.zeros(B, np.int32)
@@ -400,6 +441,14 @@ class LLMEngine:
         for t, a in ((st.input_ids, ids), (st.positions, pos), (st.slot, slot), (st.kv_len, kvl), (st.active, act),
                      (st.block_table, bt)):
             t.copy_(self._pin(a), non_blocking=True)
+        if sampling:
+            temp = np.zeros(B, np.float32); tp = np.ones(B, np.float32); tk = np.zeros(B, np.int32)
+            sd = np.zeros(B, np.int64); dr = np.zeros(B, np.int32)
+            for b, s in enumerate(seqs):
+                temp[b], tp[b], tk[b] = s.params.temperature, s.params.top_p, s.params.top_k
+                sd[b], dr[b] = s.params.seed or 0, len(s.output_ids)
+            for t, a in ((st.temperature, temp), (st.top_p, tp), (st.top_k, tk), (st.seed, sd), (st.draws, dr)):
+                t.copy_(self._pin(a), non_blocking=True)
         st.step_counter.zero_()
         with torch.inference_mode():
             for _ in range(burst):
@@ -420,7 +469,7 @@ class LLMEngine:
 
     def _decode_once(self, st: _DecodeState) -> None:
         def body():
-            tok, _ = self.model(st.meta(), self.kv_caches)
+            tok, _ = self.model(st.meta(), self.kv_caches, sampler=st.sampler())
             ops.decode_advance_(tok, st.input_ids, st.positions, st.kv_len, st.slot, st.block_table, st.active,
                                 st.out_log, st.step_counter)
 
@@ -430,7 +479,7 @@ class LLMEngine:
         if st.graph is None:
             # warm-up run outside the graph (sets kernel attributes, fills allocator pools), then capture;
             # the state is restored afterwards so the warm-up leaves no trace
-            snap = [t.clone() for t in (st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter)]
+            snap = [t.clone() for t in (st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter, st.draws)]
             body()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -439,7 +488,7 @@ class LLMEngine:
                 body()
             st.launches_per_replay = ops.kernel_launches() - before
             st.graph = g
-            for t, v in zip((st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter), snap):
+            for t, v in zip((st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter, st.draws), snap):
                 t.copy_(v)
         st.graph.replay()
         ops._count(st.launches_per_replay)

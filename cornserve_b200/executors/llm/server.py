@@ -312,8 +312,8 @@ class LLMServer:
             out += [ids[pos]] * rows.shape[0]
             prev = pos + 1
         out += ids[prev:]
-        params = SamplingParams(max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
-                                ignore_eos=bool(body.get("ignore_eos", False)))
+        params = SamplingParams.from_request(body, max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
+                                             ignore_eos=bool(body.get("ignore_eos", False)))
         # without grids M-RoPE degrades to sequential positions (text-only layout)
         if any(it.grid_thw is None for it in items):
             for it in items:
@@ -431,8 +431,8 @@ class LLMServer:
         src = self._map_producer_cache(params)
         raw = None if src is not None else await self._fetch_pages(params)
         pf = PrefilledKV(int(params["first_token"]), int(params["next_pos"]), [int(p) for p in params["pages"]], src_cache=src, raw=raw)
-        sp = SamplingParams(max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
-                            ignore_eos=bool(body.get("ignore_eos", False)))
+        sp = SamplingParams.from_request(body, max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
+                                         ignore_eos=bool(body.get("ignore_eos", False)))
         seq = Sequence(body.get("request_id") or uuid.uuid4().hex, np.zeros(int(params["num_tokens"]), dtype=np.int32), sp,
                        prefilled=pf)
         return seq, await self._sidecar_parts(body)

@@ -320,12 +320,15 @@ class QwenLLM(nn.Module):
         return logits[:, : self.cfg.vocab_size]
 
     def forward(self, m: BatchMeta, kv_caches: list[torch.Tensor], return_hidden: bool = False,
-                capture: dict[int, torch.Tensor] | None = None):
-        """Returns ``(next_token_ids [B] int32, hidden [T, H] or None)`` (greedy)."""
+                capture: dict[int, torch.Tensor] | None = None, sampler: tuple | None = None):
+        """Returns ``(next_token_ids [B] int32, hidden [T, H] or None)``.  Greedy unless ``sampler`` gives the per-row
+        ``(temperature, top_p, top_k, seed, draws)`` tensors of :func:`ops.sample_rows` (every tensor-parallel rank
+        holds the same gathered logits and the same streams, so all ranks draw the same token)."""
         h = self.forward_hidden(m, kv_caches, capture)
         h_last = ops.gather_rows(h, m.logits_idx)
         logits = self.compute_logits(h_last)
-        return ops.argmax(logits), (h if return_hidden else None)
+        tok = ops.argmax(logits) if sampler is None else ops.sample_rows(logits, *sampler)
+        return tok, (h if return_hidden else None)
 
     # -- checkpoint loading -------------------------------------------------------------------------
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:

@@ -494,6 +494,29 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     return out
 
 
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, top_k: torch.Tensor,
+                seed: torch.Tensor, draws: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of fp32 ``logits`` by temperature / top-k / top-p sampling (int32).
+
+    Per row: ``temperature`` (<= 0: arg-max), ``top_p`` in (0, 1] and ``top_k`` (<= 0: off) restrict the candidates
+    (top-k first, top-p over what is left; ties at a cut-off stay in), ``seed`` (int64) names the row's random stream
+    and ``draws`` (int32, advanced in place) the position in it, so a (seed, draw) pair always gives the same token."""
+    if not logits.is_cuda:
+        return reference.sample_rows(logits, temperature, top_p, top_k, seed, draws)
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and top_k.dtype == torch.int32
+    assert seed.dtype == torch.int64 and draws.dtype == torch.int32
+    assert all(t.is_contiguous() and t.numel() >= rows for t in (temperature, top_p, top_k, seed, draws))
+    if out is None:
+        out = torch.empty((rows,), device=logits.device, dtype=torch.int32)
+    lib = _lib.load()
+    _chk(lib.cs_sample_rows(logits.data_ptr(), logits.stride(0), rows, V, temperature.data_ptr(), top_p.data_ptr(),
+                            top_k.data_ptr(), seed.data_ptr(), draws.data_ptr(), out.data_ptr(), _stream()), "cs_sample_rows")
+    _count()
+    return out
+
+
 def flow_step_(x: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor | None, cfg: float, dt: float,
                norm_rescale: bool = False) -> torch.Tensor:
     """In-place flow-matching Euler step with classifier-free guidance on fp32 latents ``[rows, C]``."""

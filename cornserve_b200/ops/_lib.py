@@ -50,6 +50,7 @@ _SIGNATURES = {
     "cs_attention_decode": ([P, L, P, P, L, P, P, I, I, I, I, I, F, I, P, L, P], I),
     "cs_head_norm_rope": ([P, L, L, I, I, P, F, P, P, I, I, P], I),
     "cs_qk_norm_rope128": ([P, L, L, I, L, P, P, P, P, F, P, I, I, P], I),
+    "cs_sample_rows": ([P, L, I, I, P, P, P, P, P, P, P], I),
     "cs_softmax_rows": ([P, L, P, L, I, I, F, P], I),
     "cs_im2col3x3": ([P, P, I, I, I, I, I, I, I, P], I),
     "cs_im2col1d": ([P, P, I, I, I, I, I, I, I, I, I, P, P, P], I),

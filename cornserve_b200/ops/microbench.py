@@ -9,6 +9,7 @@
   python -m cornserve_b200.ops.microbench norm 19136 1280
   python -m cornserve_b200.ops.microbench adaln 8192 3072          # LayerNorm + AdaLN modulation (two samples)
   python -m cornserve_b200.ops.microbench qk-norm-rope 8704 24     # per-head RMSNorm + rotation of q and k, d = 128
+  python -m cornserve_b200.ops.microbench sample 128 152064 50     # rows, vocabulary, top-k (temperature 1, top-p 0.9)
   python -m cornserve_b200.ops.microbench gemm-fp8 16384 3584 3584 # e4m3 with 1x128 / 128x128 block scales
   python -m cornserve_b200.ops.microbench moe 128 128 8 2048 768   # tokens, experts, top-k, hidden, expert FFN width
 
@@ -153,6 +154,17 @@ def main() -> None:
         secs = t(lambda: ops.qk_norm_rope_(qkv, heads, d, heads * d, ws[0], ws[1], 1e-6, cs, wq2=ws[2], wk2=ws[3],
                                            seg=T // 2, n_first=T // 34))
         report(f"q/k head norm + rotation {T} tokens x {heads} heads", secs, 0.0, 2.0 * 2 * 2 * T * heads * d + 4.0 * T * d)
+    elif k == "sample":
+        rows, V = (a.args + [128, 152064][len(a.args):])[:2]
+        top_k = a.args[2] if len(a.args) > 2 else 0
+        logits = torch.randn(rows, V, device=dev, generator=g) * 3
+        f = lambda v, dt: torch.full((rows,), v, device=dev, dtype=dt)  # noqa: E731
+        args = (f(1.0, torch.float32), f(0.9, torch.float32), f(top_k, torch.int32),
+                torch.arange(rows, device=dev, dtype=torch.int64), torch.zeros(rows, device=dev, dtype=torch.int32))
+        secs = t(lambda: ops.sample_rows(logits, *args))
+        report(f"sample (temperature 1, top_p 0.9, top_k {top_k}) {rows}x{V}", secs, 0.0, 4.0 * rows * V)
+        secs = t(lambda: ops.argmax(logits))
+        report(f"argmax {rows}x{V}", secs, 0.0, 4.0 * rows * V)
     elif k == "gemm-fp8":
         M, N, K = a.args[:3]
         x = rnd(M, K)

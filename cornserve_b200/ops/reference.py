@@ -190,6 +190,61 @@ def argmax(logits):
     return logits.float().argmax(dim=-1).to(torch.int32)
 
 
+_M64 = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def sample_kept_mask(logits_row, temperature: float, top_p: float, top_k: int):
+    """Which tokens of one row survive top-k then top-p (ties at a cut-off are kept), and their weights
+    (probabilities relative to the maximum, in 2^-40 fixed point, as the CUDA kernel counts them)."""
+    import numpy as np
+
+    x = logits_row.detach().float().cpu().numpy()
+    V = x.shape[0]
+    mx = np.float32(x.max())
+    inv = np.float32(1.4426950408889634) / np.float32(temperature)
+    w = np.floor(np.exp2((x - mx) * inv, dtype=np.float32).astype(np.float64) * float(1 << 40)).astype(np.uint64)
+    keep = np.ones(V, dtype=bool)
+    if 0 < top_k < V:
+        keep &= x >= np.sort(x)[V - top_k]
+    if 0.0 < top_p < 1.0:
+        idx = np.nonzero(keep)[0]
+        order = idx[np.argsort(-x[idx], kind="stable")]
+        cum = np.cumsum(w[order], dtype=np.uint64)
+        target = max(1, int(float(int(cum[-1])) * float(np.float32(top_p))))
+        pos = int(np.searchsorted(cum, np.uint64(target), side="left"))   # first prefix whose weight reaches the target
+        keep &= x >= x[order[min(pos, len(order) - 1)]]
+    return keep, w
+
+
+def sample_rows(logits, temperature, top_p, top_k, seed, draws):
+    """Temperature / top-k / top-p sampling of one token per row; ``draws`` (int32, the index of this draw in every
+    row's random stream) is advanced in place.  Rows with ``temperature <= 0`` take the arg-max."""
+    import numpy as np
+
+    rows = logits.shape[0]
+    out = torch.empty(rows, dtype=torch.int32)
+    for r in range(rows):
+        t = float(temperature[r])
+        d = int(draws[r])
+        draws[r] = d + 1
+        if not t > 0.0:
+            out[r] = int(logits[r].float().argmax())
+            continue
+        keep, w = sample_kept_mask(logits[r], t, float(top_p[r]), int(top_k[r]))
+        cum = np.cumsum(np.where(keep, w, np.uint64(0)), dtype=np.uint64)
+        total = int(cum[-1])
+        rnd = _mix64(_mix64(int(seed[r]) & _M64) ^ ((0x9E3779B97F4A7C15 * (d + 1)) & _M64))
+        target = (rnd * total) >> 64
+        out[r] = min(int(np.searchsorted(cum, np.uint64(target), side="right")), logits.shape[1] - 1)
+    return out.to(logits.device)
+
+
 def flow_step(x, cond, uncond, cfg, dt, norm_rescale=False):
     c = cond.float()
     v = c

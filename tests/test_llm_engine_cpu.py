@@ -83,6 +83,65 @@ def test_eos_stops_generation():
     assert out == free_run[: first + 1]
 
 
+def test_sampling_streams_are_reproducible_and_leave_greedy_requests_alone():
+    """temperature / top-k / top-p with a seed: the same request gives the same tokens whatever shares its batch, a
+    different seed gives other tokens, top_k = 1 equals greedy, and sampled tokens stay inside the allowed set."""
+    model = _model()
+    prompts = [np.arange(3, 40, dtype=np.int32), np.arange(50, 57, dtype=np.int32), np.arange(100, 130, dtype=np.int32)]
+
+    def run(params, chosen=(0, 1, 2)):
+        eng = LLMEngine(model, EngineConfig(num_pages=32, max_batched_tokens=64, decode_burst=3, max_model_len=512))
+        return eng.generate([Sequence(f"s{i}", prompts[i], params[i]) for i in chosen])
+
+    greedy = run([SamplingParams(9, True)] * 3)
+    sp = [SamplingParams(9, True), SamplingParams(9, True, temperature=1.3, top_p=0.9, seed=11),
+          SamplingParams(9, True, temperature=0.8, top_k=1, seed=5)]
+    a = run(sp)
+    assert a["s0"] == greedy["s0"]                       # a greedy request in a sampling batch
+    assert a["s2"] == greedy["s2"]                       # top_k = 1 leaves only the arg-max
+    assert a["s1"] != greedy["s1"]
+    assert run(sp, chosen=(1,))["s1"] == a["s1"]         # alone or in company: same stream
+    other = [sp[0], SamplingParams(9, True, temperature=1.3, top_p=0.9, seed=12), sp[2]]
+    assert run(other)["s1"] != a["s1"]
+    # without a seed the engine draws one per request
+    free = SamplingParams(9, True, temperature=1.3)
+    eng = LLMEngine(model, EngineConfig(num_pages=32, max_batched_tokens=64, decode_burst=3, max_model_len=512))
+    eng.generate([Sequence("x", prompts[1], free)])
+    assert free.seed is not None
+
+
+def test_sampling_params_from_request_fields():
+    p = SamplingParams.from_request({"temperature": 0.7, "top_p": 0.8, "top_k": 40, "seed": 3}, max_tokens=5)
+    assert (p.temperature, p.top_p, p.top_k, p.seed, p.max_tokens, p.samples) == (0.7, 0.8, 40, 3, 5, True)
+    q = SamplingParams.from_request({"top_k": -1}, max_tokens=2)
+    assert (q.temperature, q.top_p, q.top_k, q.seed, q.samples) == (0.0, 1.0, 0, None, False)
+
+
+def test_sampler_restatement_respects_cutoffs():
+    from cornserve_b200.ops import reference as ref
+
+    torch.manual_seed(3)
+    V, rows = 400, 600
+    base = torch.randn(V) * 2.5
+    logits = base[None].repeat(rows, 1)
+    temp, top_p, top_k = 0.9, 0.8, 25
+    keep, w = ref.sample_kept_mask(base, temp, top_p, top_k)
+    assert 1 <= keep.sum() <= top_k
+    probs = torch.softmax(base / temp, -1)
+    order = probs.argsort(descending=True)
+    topk_mass = probs[order[:top_k]].sum()
+    n_keep = int(keep.sum())
+    assert probs[order[:n_keep]].sum() >= top_p * topk_mass - 1e-4            # the kept prefix reaches the nucleus mass
+    assert n_keep == 1 or probs[order[:n_keep - 1]].sum() < top_p * topk_mass + 1e-4   # and is the smallest that does
+    draws = torch.zeros(rows, dtype=torch.int32)
+    toks = ref.sample_rows(logits, torch.full((rows,), temp), torch.full((rows,), top_p),
+                           torch.full((rows,), top_k, dtype=torch.int32), torch.arange(rows), draws)
+    assert bool(torch.from_numpy(keep)[toks.long()].all()) and int(draws.min()) == 1
+    want = (probs * torch.from_numpy(keep)) / (probs * torch.from_numpy(keep)).sum()
+    freq = torch.bincount(toks.long(), minlength=V).float() / rows
+    assert (freq - want).abs().max() < 0.06
+
+
 def test_block_manager():
     bm = BlockManager(5)
     assert bm.ensure("a", 129) == [1, 2] and bm.num_free == 2

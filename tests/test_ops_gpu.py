@@ -252,6 +252,64 @@ def test_qk_norm_rope_one_launch(heads, two_streams):
     assert torch.equal(buf[:, 2 * D:], want[:, 2 * D:])
 
 
+def _sample_args(rows, temp, top_p, top_k, seed0=0):
+    f = lambda v, dt: torch.full((rows,), v, device=DEV, dtype=dt)  # noqa: E731
+    return (f(temp, torch.float32), f(top_p, torch.float32), f(top_k, torch.int32),
+            torch.arange(seed0, seed0 + rows, device=DEV, dtype=torch.int64), torch.zeros(rows, device=DEV, dtype=torch.int32))
+
+
+def test_sample_rows_degenerate_cases_are_the_argmax():
+    torch.manual_seed(20)
+    logits = torch.randn(37, 152064, device=DEV) * 3
+    want = logits.argmax(-1).int()
+    for temp, top_p, top_k in ((0.0, 1.0, 0), (0.7, 1.0, 1), (1.0, 1e-6, 0)):
+        args = _sample_args(37, temp, top_p, top_k)
+        assert torch.equal(ops.sample_rows(logits, *args), want), (temp, top_p, top_k)
+        assert int(args[4].min()) == 1 and int(args[4].max()) == 1     # the draw index advanced once
+
+
+@pytest.mark.parametrize("V,temp,top_p,top_k", [(1000, 0.9, 0.8, 25), (152064, 1.0, 0.9, 0), (152064, 1.3, 1.0, 50),
+                                                (5000, 0.6, 0.95, 200), (777, 1.0, 1.0, 0)])
+def test_sample_rows_cutoffs_distribution_and_streams(V, temp, top_p, top_k):
+    """Every draw lies inside the set that the fp32 restatement keeps, follows the renormalised probabilities, and is a
+    function of (seed, draw index) alone."""
+    torch.manual_seed(21)
+    rows = 4096
+    base = torch.randn(V, device=DEV) * 2.5
+    logits = base[None].repeat(rows, 1).contiguous()
+    keep, _ = ref.sample_kept_mask(base, temp, top_p, top_k)
+    keep = torch.from_numpy(keep).to(DEV)
+    args = _sample_args(rows, temp, top_p, top_k)
+    toks = ops.sample_rows(logits, *args)
+    assert int(toks.min()) >= 0 and int(toks.max()) < V
+    inside = keep[toks.long()].float().mean().item()
+    assert inside >= 0.999, inside          # a logit that ties the cut-off to the last bit may fall either way
+    probs = torch.softmax(base.double() / temp, -1) * keep
+    probs = probs / probs.sum()
+    freq = torch.bincount(toks.long(), minlength=V).double() / rows
+    assert (freq - probs).abs().max().item() < 0.03
+    again = _sample_args(rows, temp, top_p, top_k)
+    assert torch.equal(ops.sample_rows(logits, *again), toks)                    # same seeds, same draw index
+    nxt = ops.sample_rows(logits, *args)                                         # draw index 1 of the same streams
+    assert (nxt != toks).float().mean().item() > 0.2 or int(keep.sum()) < 3
+    # the restatement on the CPU (same hash, same fixed-point weights) picks the same token almost everywhere
+    n = 64
+    cpu = ref.sample_rows(logits[:n].cpu(), *[a[:n].cpu() for a in _sample_args(rows, temp, top_p, top_k)])
+    assert (cpu.to(DEV) == toks[:n]).float().mean().item() >= 0.9
+
+
+def test_sample_rows_mixed_rows():
+    torch.manual_seed(22)
+    V, rows = 4096, 64
+    logits = torch.randn(rows, V, device=DEV) * 2
+    temp = torch.where(torch.arange(rows, device=DEV) % 2 == 0, 0.0, 1.0).float()
+    args = (temp, torch.ones(rows, device=DEV), torch.zeros(rows, device=DEV, dtype=torch.int32),
+            torch.arange(rows, device=DEV, dtype=torch.int64), torch.zeros(rows, device=DEV, dtype=torch.int32))
+    toks = ops.sample_rows(logits, *args)
+    assert torch.equal(toks[0::2], logits[0::2].argmax(-1).int())
+    assert (toks[1::2] != logits[1::2].argmax(-1).int()).float().mean().item() > 0.5
+
+
 def test_softmax_rows():
     torch.manual_seed(11)
     x = _rand(300, 1032, scale=4.0)

@@ -83,6 +83,32 @@ def test_llm_engine_gpu_graph_matches_eager_and_cpu_hidden():
         assert _cos(hid["g"][k], hid["c"][k]) > 0.99
 
 
+def test_llm_engine_gpu_sampling_in_graph_matches_eager():
+    """Sampled requests: the CUDA-graph bursts (the draw index advances on the device) give the tokens of eager
+    launches, a greedy request in the same batch keeps its tokens, and another seed changes the sampled ones."""
+    torch.manual_seed(2)
+    cfg = _llm_cfg()
+    g = QwenLLM(cfg, device="cuda")
+    for p in g.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.05)
+    prompts = [np.arange(5, 300, dtype=np.int32), np.arange(900, 917, dtype=np.int32), np.arange(30, 160, dtype=np.int32)]
+
+    def run(graph, seed, sample=True):
+        ps = [SamplingParams(20, True), SamplingParams(20, True, temperature=1.2 if sample else 0.0, top_p=0.9, seed=seed),
+              SamplingParams(20, True, temperature=0.8 if sample else 0.0, top_k=30, seed=seed + 1)]
+        eng = LLMEngine(g, EngineConfig(num_pages=32, max_batched_tokens=256, decode_burst=5, use_cuda_graph=graph,
+                                        max_model_len=1024))
+        return eng.generate([Sequence(f"s{i}", p, ps[i]) for i, p in enumerate(prompts)])
+
+    eager, graph, other, greedy = run(False, 3), run(True, 3), run(True, 4), run(True, 3, sample=False)
+    torch.cuda.synchronize()
+    ops.check_error("llm engine sampling")
+    assert graph == eager
+    assert graph["s0"] == greedy["s0"] and graph["s1"] != greedy["s1"] and graph["s2"] != greedy["s2"]
+    assert other["s1"] != graph["s1"] and other["s0"] == graph["s0"]
+
+
 def test_mllm_pipeline_end_to_end():
     torch.manual_seed(2)
     vcfg = Qwen25VisionConfig(depth=2, hidden_size=256, num_heads=4, intermediate_size=512, out_hidden_size=512,
