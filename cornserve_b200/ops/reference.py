@@ -201,14 +201,14 @@ def _mix64(z: int) -> int:
 
 def sample_kept_mask(logits_row, temperature: float, top_p: float, top_k: int):
     """Which tokens of one row survive top-k then top-p (ties at a cut-off are kept), and their weights
-    (probabilities relative to the maximum, in 2^-40 fixed point, as the CUDA kernel counts them)."""
+    (probabilities relative to the maximum, in 2^-36 fixed point, as the CUDA kernel counts them)."""
     import numpy as np
 
     x = logits_row.detach().float().cpu().numpy()
     V = x.shape[0]
     mx = np.float32(x.max())
     inv = np.float32(1.4426950408889634) / np.float32(temperature)
-    w = np.floor(np.exp2((x - mx) * inv, dtype=np.float32).astype(np.float64) * float(1 << 40)).astype(np.uint64)
+    w = np.floor(np.exp2((x - mx) * inv, dtype=np.float32).astype(np.float64) * float(1 << 36)).astype(np.uint64)
     keep = np.ones(V, dtype=bool)
     if 0 < top_k < V:
         keep &= x >= np.sort(x)[V - top_k]

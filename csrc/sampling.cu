@@ -2,7 +2,7 @@
 //
 // No sort: the cut-off is found by a radix select over the order-preserving 32-bit key of each logit, eight bits per
 // pass.  One routine serves both limits: every element carries an integer weight (1 for top-k, its probability in
-// 2^-40 fixed point for top-p) and the select returns the largest key T whose upper set {key >= T} weighs at least
+// 2^-36 fixed point for top-p) and the select returns the largest key T whose upper set {key >= T} weighs at least
 // the target.  Ties at T are kept.  With both limits, top-p applies to the distribution renormalised over the top-k
 // set.  The token is then drawn by inverting the cumulative weight of the kept set in index order.  All sums are
 // integers, so a row's result depends only on (logits, parameters, seed, draw index), never on the order in which
@@ -12,7 +12,8 @@
 namespace {
 
 constexpr int SAMPLE_THREADS = 1024;
-constexpr float kFixedOne = 1099511627776.0f;  // 2^40
+constexpr float kFixedOne = 68719476736.0f;  // 2^36
+constexpr int kSplitBits = 18;              // a weight enters the histograms as two 18-bit halves (32-bit counters)
 
 __device__ __forceinline__ unsigned order_key(float x) {
   const unsigned u = __float_as_uint(x);
@@ -25,7 +26,7 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
   return z ^ (z >> 31);
 }
 
-// probability of a logit in 2^-40 fixed point, relative to the row maximum (which maps to 2^40)
+// probability of a logit in 2^-36 fixed point, relative to the row maximum (which maps to 2^36)
 __device__ __forceinline__ unsigned long long fixed_prob(float logit, float mx, float inv_t_log2) {
   return static_cast<unsigned long long>(exp2f((logit - mx) * inv_t_log2) * kFixedOne);
 }
@@ -56,22 +57,49 @@ __device__ unsigned long long block_sum_u64(unsigned long long v, SelectScratch&
 // Largest key T such that the weight of {i : key_i >= T, key_i >= floor_key} is >= target (target >= 1; if the whole
 // set weighs less, the smallest key of the set is returned through the same walk).  kByMass: weight = fixed_prob,
 // else weight = 1.
+// The 256-bucket histogram of a pass is kept once per lane (`lanes_lo/hi[bucket * 32 + lane]`, 32-bit counters): the
+// lanes of a warp never meet on an address or a bank however skewed the digits are, and a column receives at most
+// V / 32 < 2^13 additions of an 18-bit half, which fits.
 template <bool kByMass>
 __device__ unsigned radix_select(const float* row, int V, float mx, float inv_t_log2, unsigned floor_key,
-                                 unsigned long long target, SelectScratch& sc) {
+                                 unsigned long long target, SelectScratch& sc, unsigned* lanes_lo, unsigned* lanes_hi) {
   unsigned prefix = 0;
   unsigned long long remaining = target;
+  const int lane = threadIdx.x & 31;
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int b = threadIdx.x; b < 256; b += SAMPLE_THREADS) sc.hist[b] = 0;
+    for (int b = threadIdx.x; b < 256 * 32; b += SAMPLE_THREADS) {
+      lanes_lo[b] = 0;
+      if (kByMass) lanes_hi[b] = 0;
+    }
     __syncthreads();
     const unsigned hi_mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
     for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
       const float x = row[i];
       const unsigned k = order_key(x);
       if (k >= floor_key && (k & hi_mask) == prefix) {
-        const unsigned long long w = kByMass ? fixed_prob(x, mx, inv_t_log2) : 1ull;
-        if (w) atomicAdd(&sc.hist[(k >> shift) & 255u], w);
+        const int slot = static_cast<int>((k >> shift) & 255u) * 32 + lane;
+        if (kByMass) {
+          const unsigned long long w = fixed_prob(x, mx, inv_t_log2);
+          if (w) {
+            atomicAdd(&lanes_lo[slot], static_cast<unsigned>(w & ((1u << kSplitBits) - 1u)));
+            atomicAdd(&lanes_hi[slot], static_cast<unsigned>(w >> kSplitBits));
+          }
+        } else {
+          atomicAdd(&lanes_lo[slot], 1u);
+        }
       }
+    }
+    __syncthreads();
+    if (threadIdx.x < 256) {
+      const int b = threadIdx.x;
+      unsigned long long lo = 0, hi = 0;
+#pragma unroll 8
+      for (int j = 0; j < 32; ++j) {
+        const int l = (j + b) & 31;  // skewed: the threads of a warp read 32 different banks
+        lo += lanes_lo[b * 32 + l];
+        if (kByMass) hi += lanes_hi[b * 32 + l];
+      }
+      sc.hist[b] = (hi << kSplitBits) + lo;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -95,6 +123,9 @@ __device__ unsigned radix_select(const float* row, int V, float mx, float inv_t_
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* logits, long long ld, int V, const float* temperature, const float* top_p,
                    const int* top_k, const long long* seed, int* draws, int* out) {
+  extern __shared__ unsigned lane_hist[];  // [2][256 * 32]
+  unsigned* lanes_lo = lane_hist;
+  unsigned* lanes_hi = lane_hist + 256 * 32;
   __shared__ SelectScratch sc;
   __shared__ float red_v[SAMPLE_THREADS / 32];
   __shared__ int red_i[SAMPLE_THREADS / 32];
@@ -146,7 +177,7 @@ sample_rows_kernel(const float* logits, long long ld, int V, const float* temper
   // ---- cut-off key -------------------------------------------------------------------------------------
   unsigned thr = 0;
   const int k = top_k[r];
-  if (k > 0 && k < V) thr = radix_select<false>(row, V, mx, inv_t_log2, 0u, static_cast<unsigned long long>(k), sc);
+  if (k > 0 && k < V) thr = radix_select<false>(row, V, mx, inv_t_log2, 0u, static_cast<unsigned long long>(k), sc, lanes_lo, lanes_hi);
   const float pp = top_p[r];
   if (pp > 0.f && pp < 1.f) {
     unsigned long long mass = 0;
@@ -157,7 +188,7 @@ sample_rows_kernel(const float* logits, long long ld, int V, const float* temper
     mass = block_sum_u64(mass, sc);
     unsigned long long target = static_cast<unsigned long long>(static_cast<double>(mass) * static_cast<double>(pp));
     if (target < 1) target = 1;
-    const unsigned tp = radix_select<true>(row, V, mx, inv_t_log2, thr, target, sc);
+    const unsigned tp = radix_select<true>(row, V, mx, inv_t_log2, thr, target, sc, lanes_lo, lanes_hi);
     thr = max(thr, tp);
   }
 
@@ -221,7 +252,16 @@ CS_API int cs_sample_rows(const void* logits, long long ld, int rows, int V, con
   if (V <= 0 || logits == nullptr || temperature == nullptr || top_p == nullptr || top_k == nullptr || seed == nullptr ||
       draws == nullptr || out == nullptr)
     return -1;
-  sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+  constexpr int kSmem = 2 * 256 * 32 * static_cast<int>(sizeof(unsigned));
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 16 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -10;
+    attr_set[dev] = true;
+  }
+  if (static_cast<long long>(V) >= (1ll << 18)) return -1;  // a lane's column would no longer fit 32 bits
+  sample_rows_kernel<<<rows, SAMPLE_THREADS, kSmem, (cudaStream_t)stream>>>(
       (const float*)logits, ld, V, (const float*)temperature, (const float*)top_p, (const int*)top_k,
       (const long long*)seed, (int*)draws, (int*)out);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
