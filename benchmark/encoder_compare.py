@@ -1,0 +1,100 @@
+"""Encoder forward pass: this package's Qwen2.5-VL vision tower against the reference's own module on one GPU.
+
+    python -m benchmark.encoder_compare --images 7 --iters 5
+
+The reference's LLM executor and control plane cannot run offline, but its encoder executor's model code can: when the
+reference package is installed under ``baseline/_ref`` its ``Qwen2_5_VisionTransformer`` (reference:
+python/cornserve/task_executors/eric/models/qwen2_5_vl.py:262-486; torch ``Linear`` on cuBLAS, flash-attn var-len
+attention, eager norms and rotary) is built unmodified with random bf16 weights of the 7B tower (32 layers, hidden 1280,
+16 heads, window attention with full attention at layers 7 / 15 / 23 / 31, 2x2 merger to 3584) and run through its own
+``forward`` on the same synthetic batch of 1280x720 images as this package's tower.  Both are timed with CUDA events
+after warm-up; one JSON line reports images per second of each and the ratio.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+VISION_7B = dict(depth=32, hidden_size=1280, num_heads=16, intermediate_size=3420, out_hidden_size=3584,
+                 fullatt_block_indexes=[7, 15, 23, 31], window_size=112, patch_size=14, spatial_merge_size=2,
+                 temporal_patch_size=2, hidden_act="silu", in_channels=3)
+
+
+def _time(fn, iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters / 1e3
+
+
+def time_ours(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int) -> float:
+    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+
+    torch.manual_seed(0)
+    tower = Qwen25VisionTransformer(Qwen25VisionConfig(), device="cuda")
+    pv, grid = torch.cat(pixels), np.asarray(grids)
+    with torch.inference_mode():
+        return _time(lambda: tower.encode(pv, grid), iters, warmup)
+
+
+def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int) -> float | str:
+    root = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+    if not (root / "cornserve").is_dir():
+        return "the reference package is not installed under baseline/_ref"
+    sys.path.insert(0, str(root))
+    try:
+        from cornserve.task_executors.eric.api import Modality
+        from cornserve.task_executors.eric.distributed import parallel
+        from cornserve.task_executors.eric.models.qwen2_5_vl import Qwen2_5_VisionTransformer
+        from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLConfig
+    except Exception as e:  # noqa: BLE001
+        return f"the reference encoder does not import here: {type(e).__name__}: {e}"
+    finally:
+        sys.path.remove(str(root))
+    parallel.init_distributed(world_size=1, rank=0)
+    torch.manual_seed(0)
+    tower = Qwen2_5_VisionTransformer(Qwen2_5_VLConfig(vision_config=VISION_7B)).to(device="cuda", dtype=torch.bfloat16).eval()
+    batch = {"pixel_values": pixels, "image_grid_thw": [torch.tensor([g]) for g in grids]}
+    with torch.inference_mode():
+        return _time(lambda: tower(Modality.IMAGE, "", batch), iters, warmup)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--images", type=int, default=7, help="1280x720 images per forward pass")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("encoder_compare needs a CUDA device")
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    grid = [1, 52, 92]   # 1280x720 -> 728 x 1288 after rounding to 28-pixel cells: 52 x 92 patches
+    pixels = [torch.randn(grid[1] * grid[2], 3 * 2 * 14 * 14, device="cuda", generator=gen).bfloat16() for _ in range(a.images)]
+    grids = [grid] * a.images
+    ours = time_ours(pixels, grids, a.iters, a.warmup)
+    ref = time_reference(pixels, grids, a.iters, a.warmup)
+    out = {"metric": "encoder_images_per_second", "n_gpus": 1, "dtype": "bf16", "images_per_pass": a.images,
+           "data": "synthetic (random patches, random-init weights)", "ours": {"seconds_per_pass": ours, "images_per_second": a.images / ours}}
+    if isinstance(ref, str):
+        out["reference"] = {"unavailable": ref}
+    else:
+        out["reference"] = {"seconds_per_pass": ref, "images_per_second": a.images / ref}
+        out["ours_over_reference"] = ref / ours
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
