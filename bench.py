@@ -31,7 +31,7 @@ MODEL = "Qwen2.5-VL-7B"
 REF_UNAVAILABLE = (
     "the reference's LLM executor is an empty git submodule (third_party/vllm) and its request path needs "
     "Kubernetes pods; only its Eric encoder modules import offline, so the MLLM request metric cannot be "
-    "produced by unmodified reference code"
+    "produced by unmodified reference code (the encoder module alone is timed by python -m benchmark.encoder_compare)"
 )
 
 
