@@ -1,6 +1,7 @@
 """Encoder forward pass: this package's Qwen2.5-VL vision tower against the reference's own module on one GPU.
 
     python -m benchmark.encoder_compare --images 7 --iters 5
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m benchmark.encoder_compare   # both at TP=2
 
 The reference's LLM executor and control plane cannot run offline, but its encoder executor's model code can: when the
 reference package is installed under ``baseline/_ref`` its ``Qwen2_5_VisionTransformer`` (reference:
@@ -8,13 +9,16 @@ python/cornserve/task_executors/eric/models/qwen2_5_vl.py:262-486; torch ``Linea
 attention, eager norms and rotary) is built unmodified with random bf16 weights of the 7B tower (32 layers, hidden 1280,
 16 heads, window attention with full attention at layers 7 / 15 / 23 / 31, 2x2 merger to 3584) and run through its own
 ``forward`` on the same synthetic batch of 1280x720 images as this package's tower.  Both are timed with CUDA events
-after warm-up; one JSON line reports images per second of each and the ratio.
+after warm-up; one JSON line reports images per second of each and the ratio.  Under ``torchrun`` both towers are
+tensor parallel over all ranks: the reference with its own column / row parallel layers over NCCL, this package with the
+exchanges inside its GEMM and norm kernels over peer memory; times are the maximum over ranks.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -39,17 +43,33 @@ def _time(fn, iters: int, warmup: int) -> float:
     return e0.elapsed_time(e1) / iters / 1e3
 
 
-def time_ours(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int) -> float:
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+def _max_over_ranks(seconds: float, world: int) -> float:
+    if world == 1:
+        return seconds
+    import torch.distributed as dist
 
+    t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_ours(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float:
+    from cornserve_b200 import ops
+    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve_b200.parallel.state import init_distributed
+
+    group = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
+                             master_port=int(os.environ.get("MASTER_PORT", "29511")), local_device=int(os.environ.get("LOCAL_RANK", rank)))
     torch.manual_seed(0)
-    tower = Qwen25VisionTransformer(Qwen25VisionConfig(), device="cuda")
+    tower = Qwen25VisionTransformer(Qwen25VisionConfig(), group=group, device=group.device)
     pv, grid = torch.cat(pixels), np.asarray(grids)
     with torch.inference_mode():
-        return _time(lambda: tower.encode(pv, grid), iters, warmup)
+        secs = _time(lambda: tower.encode(pv, grid), iters, warmup)
+    ops.check_error("encoder_compare")
+    return _max_over_ranks(secs, world)
 
 
-def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int) -> float | str:
+def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float | str:
     root = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
     if not (root / "cornserve").is_dir():
         return "the reference package is not installed under baseline/_ref"
@@ -63,12 +83,14 @@ def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: in
         return f"the reference encoder does not import here: {type(e).__name__}: {e}"
     finally:
         sys.path.remove(str(root))
-    parallel.init_distributed(world_size=1, rank=0)
+    parallel.init_distributed(world_size=world, rank=rank, init_method=f"tcp://{os.environ.get('MASTER_ADDR', '127.0.0.1')}:"
+                                                                       f"{os.environ.get('MASTER_PORT', '29511')}")
     torch.manual_seed(0)
     tower = Qwen2_5_VisionTransformer(Qwen2_5_VLConfig(vision_config=VISION_7B)).to(device="cuda", dtype=torch.bfloat16).eval()
     batch = {"pixel_values": pixels, "image_grid_thw": [torch.tensor([g]) for g in grids]}
     with torch.inference_mode():
-        return _time(lambda: tower(Modality.IMAGE, "", batch), iters, warmup)
+        secs = _time(lambda: tower(Modality.IMAGE, "", batch), iters, warmup)
+    return _max_over_ranks(secs, world)
 
 
 def main() -> None:
@@ -79,21 +101,30 @@ def main() -> None:
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("encoder_compare needs a CUDA device")
-    torch.cuda.set_device(0)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     gen = torch.Generator(device="cuda").manual_seed(1)
     grid = [1, 52, 92]   # 1280x720 -> 728 x 1288 after rounding to 28-pixel cells: 52 x 92 patches
     pixels = [torch.randn(grid[1] * grid[2], 3 * 2 * 14 * 14, device="cuda", generator=gen).bfloat16() for _ in range(a.images)]
     grids = [grid] * a.images
-    ours = time_ours(pixels, grids, a.iters, a.warmup)
-    ref = time_reference(pixels, grids, a.iters, a.warmup)
-    out = {"metric": "encoder_images_per_second", "n_gpus": 1, "dtype": "bf16", "images_per_pass": a.images,
-           "data": "synthetic (random patches, random-init weights)", "ours": {"seconds_per_pass": ours, "images_per_second": a.images / ours}}
+    # the reference first: it creates the process group (this package joins an existing one, the reference does not)
+    ref = time_reference(pixels, grids, a.iters, a.warmup, rank, world)
+    ours = time_ours(pixels, grids, a.iters, a.warmup, rank, world)
+    out = {"metric": "encoder_images_per_second", "n_gpus": world, "parallelism": f"tp{world}", "dtype": "bf16",
+           "images_per_pass": a.images, "data": "synthetic (random patches, random-init weights)",
+           "ours": {"seconds_per_pass": ours, "images_per_second": a.images / ours}}
     if isinstance(ref, str):
         out["reference"] = {"unavailable": ref}
     else:
         out["reference"] = {"seconds_per_pass": ref, "images_per_second": a.images / ref}
         out["ours_over_reference"] = ref / ours
-    print(json.dumps(out))
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
