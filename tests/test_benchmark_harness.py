@@ -1,6 +1,7 @@
 """Load generator: arrival processes and latency metric definitions."""
 
 import numpy as np
+import pytest
 
 from benchmark.load_generator import RequestRecord, arrival_times, duty_cycle_times, percentiles, summarise
 
@@ -54,3 +55,22 @@ def test_experiment_configurations_and_app_sources():
 
         parts = {part_of(json.dumps({"class_name": type(t).__name__})) for t in discover_unit_tasks(classes.config_cls.tasks.values())}
         assert parts == set(PARTS[backend]), (backend, parts)
+
+
+@pytest.mark.gpu
+def test_encoder_compare_reports_both_arms():
+    """The comparison tool runs this package's tower and, when the reference package is installed beside the repository,
+    the reference's own encoder module, and prints one JSON line with both rates."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, "-m", "benchmark.encoder_compare", "--images", "1", "--iters", "1", "--warmup", "1"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["metric"] == "encoder_images_per_second" and out["ours"]["images_per_second"] > 0
+    ref = out["reference"]
+    assert ("unavailable" in ref) or (ref["images_per_second"] > 0 and out["ours_over_reference"] > 0)
