@@ -28,6 +28,9 @@ import torch
 VISION_7B = dict(depth=32, hidden_size=1280, num_heads=16, intermediate_size=3420, out_hidden_size=3584,
                  fullatt_block_indexes=[7, 15, 23, 31], window_size=112, patch_size=14, spatial_merge_size=2,
                  temporal_patch_size=2, hidden_act="silu", in_channels=3)
+# Qwen2-VL-7B tower: LayerNorm, quick-GELU MLP of ratio 4, full attention in every layer
+VISION_QWEN2 = dict(depth=32, embed_dim=1280, hidden_size=3584, num_heads=16, mlp_ratio=4, in_channels=3, in_chans=3,
+                    patch_size=14, spatial_merge_size=2, temporal_patch_size=2, hidden_act="quick_gelu")
 
 
 def _time(fn, iters: int, warmup: int) -> float:
@@ -53,7 +56,7 @@ def _max_over_ranks(seconds: float, world: int) -> float:
     return float(t.item())
 
 
-def time_ours(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float:
+def time_ours(model: str, pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float:
     from cornserve_b200 import ops
     from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
     from cornserve_b200.parallel.state import init_distributed
@@ -61,7 +64,12 @@ def time_ours(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, wa
     group = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
                              master_port=int(os.environ.get("MASTER_PORT", "29511")), local_device=int(os.environ.get("LOCAL_RANK", rank)))
     torch.manual_seed(0)
-    tower = Qwen25VisionTransformer(Qwen25VisionConfig(), group=group, device=group.device)
+    if model == "qwen2_vl":
+        from cornserve_b200.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
+
+        tower = Qwen2VisionTransformer(Qwen2VisionConfig(), group=group, device=group.device)
+    else:
+        tower = Qwen25VisionTransformer(Qwen25VisionConfig(), group=group, device=group.device)
     pv, grid = torch.cat(pixels), np.asarray(grids)
     with torch.inference_mode():
         secs = _time(lambda: tower.encode(pv, grid), iters, warmup)
@@ -69,16 +77,25 @@ def time_ours(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, wa
     return _max_over_ranks(secs, world)
 
 
-def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float | str:
+def time_reference(model: str, pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float | str:
     root = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
     if not (root / "cornserve").is_dir():
         return "the reference package is not installed under baseline/_ref"
     sys.path.insert(0, str(root))
     try:
-        from cornserve.task_executors.eric.api import Modality
         from cornserve.task_executors.eric.distributed import parallel
-        from cornserve.task_executors.eric.models.qwen2_5_vl import Qwen2_5_VisionTransformer
-        from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLConfig
+
+        if model == "qwen2_vl":
+            from cornserve.task_executors.eric.models import qwen2_vl as ref_mod
+            from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLConfig
+
+            build = lambda: ref_mod.Qwen2VisionTransformer(Qwen2VLConfig(vision_config=VISION_QWEN2))  # noqa: E731
+        else:
+            from cornserve.task_executors.eric.models import qwen2_5_vl as ref_mod
+            from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLConfig
+
+            build = lambda: ref_mod.Qwen2_5_VisionTransformer(Qwen2_5_VLConfig(vision_config=VISION_7B))  # noqa: E731
+        Modality = ref_mod.Modality
     except Exception as e:  # noqa: BLE001
         return f"the reference encoder does not import here: {type(e).__name__}: {e}"
     finally:
@@ -86,7 +103,7 @@ def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: in
     parallel.init_distributed(world_size=world, rank=rank, init_method=f"tcp://{os.environ.get('MASTER_ADDR', '127.0.0.1')}:"
                                                                        f"{os.environ.get('MASTER_PORT', '29511')}")
     torch.manual_seed(0)
-    tower = Qwen2_5_VisionTransformer(Qwen2_5_VLConfig(vision_config=VISION_7B)).to(device="cuda", dtype=torch.bfloat16).eval()
+    tower = build().to(device="cuda", dtype=torch.bfloat16).eval()
     batch = {"pixel_values": pixels, "image_grid_thw": [torch.tensor([g]) for g in grids]}
     with torch.inference_mode():
         secs = _time(lambda: tower(Modality.IMAGE, "", batch), iters, warmup)
@@ -95,6 +112,7 @@ def time_reference(pixels: list[torch.Tensor], grids: list[list[int]], iters: in
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--model", default="qwen2_5_vl", choices=["qwen2_5_vl", "qwen2_vl"], help="which 7B vision tower")
     ap.add_argument("--images", type=int, default=7, help="1280x720 images per forward pass")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -108,9 +126,9 @@ def main() -> None:
     pixels = [torch.randn(grid[1] * grid[2], 3 * 2 * 14 * 14, device="cuda", generator=gen).bfloat16() for _ in range(a.images)]
     grids = [grid] * a.images
     # the reference first: it creates the process group (this package joins an existing one, the reference does not)
-    ref = time_reference(pixels, grids, a.iters, a.warmup, rank, world)
-    ours = time_ours(pixels, grids, a.iters, a.warmup, rank, world)
-    out = {"metric": "encoder_images_per_second", "n_gpus": world, "parallelism": f"tp{world}", "dtype": "bf16",
+    ref = time_reference(a.model, pixels, grids, a.iters, a.warmup, rank, world)
+    ours = time_ours(a.model, pixels, grids, a.iters, a.warmup, rank, world)
+    out = {"metric": "encoder_images_per_second", "model": a.model, "n_gpus": world, "parallelism": f"tp{world}", "dtype": "bf16",
            "images_per_pass": a.images, "data": "synthetic (random patches, random-init weights)",
            "ours": {"seconds_per_pass": ours, "images_per_second": a.images / ours}}
     if isinstance(ref, str):
