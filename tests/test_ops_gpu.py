@@ -81,6 +81,27 @@ def test_norms(H):
            3e-2, 1e-2, "adaln")
 
 
+@pytest.mark.parametrize("H,rows", [(3072, 2304), (4096, 2050), (2560, 4100), (1280, 3000)])
+def test_norms_many_rows_take_the_warp_per_row_kernels(H, rows):
+    """With thousands of rows the norms run one warp per row (up to 2048 columns for every mode, up to 4096 for
+    LayerNorm); same restatement as the block-per-row kernel."""
+    torch.manual_seed(33)
+    x, r, w, b = _rand(rows, H), _rand(rows, H), _rand(H), _rand(H)
+    sc, sh = _rand(2, H, scale=0.2), _rand(2, H, scale=0.2)
+    rpb = (rows + 1) // 2
+    _close(ops.layer_norm(x, None, None, 1e-6, sc, sh, rpb), ref.layer_norm(x.float(), None, None, 1e-6, sc, sh, rpb),
+           3e-2, 1e-2, "adaln")
+    _close(ops.layer_norm(x, w, b, 1e-5), ref.layer_norm(x.float(), w, b, 1e-5), 3e-2, 1e-2, "ln")
+    y, nr = ops.layer_norm(x, w, b, 1e-5, residual=r)
+    y0, nr0 = ref.layer_norm(x, w, b, 1e-5, residual=r)
+    _close(y, y0, 3e-2, 2e-2, "ln+res")
+    _close(nr, nr0, 1e-2, 1e-2, "res out")
+    y, nr = ops.rms_norm(x, w, 1e-6, residual=r)
+    y0, nr0 = ref.rms_norm(x, w, 1e-6, residual=r)
+    _close(y, y0, 3e-2, 2e-2, "rms+res")
+    _close(nr, nr0, 1e-2, 1e-2, "rms res out")
+
+
 def test_rope_and_tables():
     torch.manual_seed(4)
     T, H, d = 333, 16, 80
