@@ -73,6 +73,9 @@ def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--max-model-len", type=int, default=32768)
     ap.add_argument("--max-num-batched-tokens", type=int, default=18944)
+    ap.add_argument("--quantization", default=None, choices=[None, "fp8"],
+                    help="fp8: attention and MLP projections as e4m3 with 128x128 block scales (also chosen when the "
+                         "checkpoint's quantization_config says fp8)")
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--num-kv-pages", type=int, default=0, help="0 = size the cache from free memory")
     ap.add_argument("--decode-burst", type=int, default=4)
@@ -191,6 +194,10 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
                        strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower.", "thinker.visual.", "thinker.audio_tower.",
                                                        "talker.", "code2wav."])
     model.eval()
+    qcfg = hf_cfg.get("quantization_config") or (hf_cfg.get("thinker_config") or {}).get("quantization_config") or {}
+    if getattr(args, "quantization", None) == "fp8" or qcfg.get("quant_method") == "fp8":
+        model.quantize_fp8_()
+        logger.info("serving the attention and MLP projections in block-scaled fp8")
     pages = args.num_kv_pages
     if pages <= 0:
         if device.type == "cuda":

@@ -35,6 +35,20 @@ def round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+def quantize_fp8_(layer: nn.Module) -> None:
+    """Replace a layer's bf16 weight ``[N, K]`` (``K % 128 == 0``) by e4m3 values with one fp32 scale per 128 x 128 block
+    (``layer.fp8 = (wq, scales)``); the layer's ``forward`` then runs the block-scaled GEMM."""
+    w = layer.weight.data
+    if w.shape[1] % 128:
+        raise ValueError(f"fp8 block scaling needs an input width that is a multiple of 128, got {w.shape[1]}")
+    layer.fp8 = ops.quantize_fp8_weight(w)
+    layer.weight = None
+
+
+def _linear_fp8(x: torch.Tensor, fp8, bias) -> torch.Tensor:
+    return ops.linear_fp8(x, fp8[0], fp8[1], bias).to(x.dtype)
+
+
 class Linear(nn.Module):
     """Replicated linear layer ``y = act(x W^T + b) (+ residual)``."""
 
@@ -112,6 +126,7 @@ class MergedColumnParallelLinear(nn.Module):
         self.inter_local = self.inter_padded // tp
         self.weight = _param(2 * self.inter_local, in_features, device=device, dtype=dtype)
         self.bias = _param(2 * self.inter_local, device=device, dtype=dtype, std=None) if bias else None
+        self.fp8 = None
         self._zero_padding()
 
     def _shard_range(self) -> tuple[int, int]:
@@ -129,6 +144,8 @@ class MergedColumnParallelLinear(nn.Module):
                 self.bias.data[self.inter_local + n:].zero_()
 
     def forward(self, x, act: str = "silu"):
+        if self.fp8 is not None:
+            return ops.act_mul(_linear_fp8(x, self.fp8, self.bias), act)
         return ops.swiglu_linear(x, self.weight, self.bias, act=act)
 
     def load(self, which: str, weight: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
@@ -158,6 +175,7 @@ class RowParallelLinear(nn.Module):
         self.in_local = self.in_padded // tp
         self.weight = _param(out_features, self.in_local, device=device, dtype=dtype)
         self.bias = _param(out_features, device=device, dtype=dtype, std=None) if bias else None
+        self.fp8 = None
         self._zero_padding()
 
     def _shard_range(self) -> tuple[int, int]:
@@ -172,8 +190,15 @@ class RowParallelLinear(nn.Module):
 
     def forward(self, x, residual=None, act=None, reduce: bool = True):
         first = self.group.is_first
-        y = ops.linear(x, self.weight, self.bias if first else None, act=act if self.group.size == 1 else None,
-                       residual=residual if first else None)
+        if self.fp8 is not None:
+            if act is not None:
+                raise ValueError("the fp8 row-parallel projection has no activation epilogue")
+            y = _linear_fp8(x, self.fp8, self.bias if first else None)
+            if residual is not None and first:
+                y = y + residual
+        else:
+            y = ops.linear(x, self.weight, self.bias if first else None, act=act if self.group.size == 1 else None,
+                           residual=residual if first else None)
         if self.group.size > 1 and reduce:
             y = self.group.all_reduce(y)
         return y
@@ -216,8 +241,11 @@ class QKVParallelLinear(nn.Module):
         self.kv_size = self.kv_heads_local * head_dim
         self.weight = _param(self.q_size + 2 * self.kv_size, hidden, device=device, dtype=dtype)
         self.bias = _param(self.q_size + 2 * self.kv_size, device=device, dtype=dtype, std=None) if bias else None
+        self.fp8 = None
 
     def forward(self, x):
+        if self.fp8 is not None:
+            return _linear_fp8(x, self.fp8, self.bias)
         return ops.linear(x, self.weight, self.bias)
 
     def _rows(self, which: str) -> tuple[int, int, int]:

@@ -233,6 +233,28 @@ def row_parallel_tail(x: torch.Tensor, proj: RowParallelLinear, residual: torch.
     return normed, new_res
 
 
+def dequantize_fp8_checkpoint(weights: Iterable[tuple[str, torch.Tensor]]) -> Iterable[tuple[str, torch.Tensor]]:
+    """Pass checkpoint tensors through; an e4m3 ``X.weight`` is paired with its ``X.weight_scale_inv`` (one fp32 scale
+    per 128 x 128 block, in whichever order the two arrive) and leaves as bf16 ``X.weight``."""
+    pending: dict[str, torch.Tensor] = {}
+    for name, t in weights:
+        is_scale = name.endswith(".weight_scale_inv")
+        if not is_scale and t.dtype != torch.float8_e4m3fn:
+            yield name, t
+            continue
+        base = name[: -len("_scale_inv")] if is_scale else name
+        other = pending.pop(base, None)
+        if other is None:
+            pending[base] = t
+            continue
+        q, sc = (other, t) if is_scale else (t, other)
+        N, K = q.shape
+        full = sc.float().repeat_interleave(128, dim=0)[:N].repeat_interleave(128, dim=1)[:, :K]
+        yield base, (q.float() * full).to(torch.bfloat16)
+    if pending:
+        raise ValueError(f"fp8 checkpoint tensors without their partner: {sorted(pending)[:4]}")
+
+
 class QwenLLM(nn.Module):
     def __init__(self, cfg: LLMConfig, group: ParallelGroup | None = None, device="cpu",
                  ep_group: ParallelGroup | None = None):
@@ -305,6 +327,8 @@ class QwenLLM(nn.Module):
 
     def _fused_tail(self):
         """Lazily built fused GEMM + all-reduce + residual + RMSNorm kernel context (needs the fabric)."""
+        if getattr(self, "quantization", None) is not None:
+            return None
         if getattr(self, "_fused", None) is None and self.group.fabric is not None:
             from ..parallel.fused import FusedRowParallel
 
@@ -331,10 +355,29 @@ class QwenLLM(nn.Module):
         return tok, (h if return_hidden else None)
 
     # -- checkpoint loading -------------------------------------------------------------------------
+    def quantize_fp8_(self) -> "QwenLLM":
+        """Store the attention and dense-MLP projections as e4m3 with 128 x 128 block scales (half the weight memory);
+        their GEMMs then run the block-scaled tcgen05 kernel with activations quantised per row and 128 columns.
+        Embeddings, lm_head, norms, the router and the stacked expert weights stay bf16; the fused tensor-parallel
+        tail (which streams bf16 weights) is switched off in favour of the library reduction."""
+        from .layers import quantize_fp8_
+
+        for layer in self.layers:
+            quantize_fp8_(layer.self_attn.qkv)
+            quantize_fp8_(layer.self_attn.o_proj)
+            mlps = [layer.mlp] if isinstance(layer.mlp, MLP) else ([layer.mlp.shared] if layer.mlp.shared is not None else [])
+            for mlp in mlps:
+                quantize_fp8_(mlp.gate_up)
+                quantize_fp8_(mlp.down)
+        self.quantization = "fp8"
+        return self
+
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
-        """Accepts HF names with or without the ``model.`` / ``model.language_model.`` prefixes."""
+        """Accepts HF names with or without the ``model.`` / ``model.language_model.`` prefixes.  Block-scaled fp8
+        checkpoints (``*.weight`` in e4m3 with ``*.weight_scale_inv``) are widened to bf16 on the way in; call
+        :meth:`quantize_fp8_` afterwards to serve them in fp8."""
         loaded: set[str] = set()
-        for name, t in weights:
+        for name, t in dequantize_fp8_checkpoint(weights):
             n = name
             for pre in ("model.language_model.", "language_model.model.", "language_model.", "model.", "thinker.model."):
                 if n.startswith(pre):

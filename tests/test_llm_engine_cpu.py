@@ -2,6 +2,7 @@
 injection must reproduce a plain full-sequence forward (same model, fp32)."""
 
 import numpy as np
+import pytest
 import torch
 
 from cornserve_b200.executors.llm.block_manager import BlockManager, OutOfPages
@@ -140,6 +141,41 @@ def test_sampler_restatement_respects_cutoffs():
     want = (probs * torch.from_numpy(keep)) / (probs * torch.from_numpy(keep)).sum()
     freq = torch.bincount(toks.long(), minlength=V).float() / rows
     assert (freq - want).abs().max() < 0.06
+
+
+def test_fp8_projections_track_the_full_precision_model():
+    """Attention and MLP projections in block-scaled e4m3: hidden states stay close to the fp32 model, the bf16 weights
+    are gone, generation still runs; an fp8 checkpoint (weights + ``weight_scale_inv``) is widened on the way in."""
+    from cornserve_b200 import ops
+    from cornserve_b200.models.qwen_llm import dequantize_fp8_checkpoint
+
+    model = _model()
+    prompt = np.arange(3, 60, dtype=np.int32)
+
+    def hidden(m):
+        eng = LLMEngine(m, EngineConfig(num_pages=16, max_batched_tokens=64, decode_burst=3, max_model_len=256))
+        eng.add_request(Sequence("a", prompt, SamplingParams(1, True), return_hidden=True))
+        outs = []
+        while eng.has_work():
+            outs += eng.step()
+        return outs[-1].hidden.float().flatten()
+
+    want = hidden(model)
+    model.quantize_fp8_()
+    got = hidden(model)
+    assert torch.nn.functional.cosine_similarity(want, got, dim=0).item() > 0.98
+    lay = model.layers[0]
+    assert lay.self_attn.qkv.weight is None and lay.mlp.down.fp8[0].dtype == torch.float8_e4m3fn
+    eng = LLMEngine(model, EngineConfig(num_pages=16, max_batched_tokens=64, decode_burst=3, max_model_len=256))
+    assert len(eng.generate([Sequence("g", prompt, SamplingParams(6, True))])["g"]) == 6
+
+    w = torch.randn(200, 256)
+    q, sc = ops.quantize_fp8_weight(w)
+    out = dict(dequantize_fp8_checkpoint([("l.q_proj.weight_scale_inv", sc), ("l.q_proj.weight", q), ("l.norm.weight", torch.ones(3))]))
+    assert sorted(out) == ["l.norm.weight", "l.q_proj.weight"] and out["l.q_proj.weight"].dtype == torch.bfloat16
+    assert (out["l.q_proj.weight"].float() - w).abs().max().item() < 0.3
+    with pytest.raises(ValueError):
+        list(dequantize_fp8_checkpoint([("l.q_proj.weight", q)]))
 
 
 def test_block_manager():

@@ -109,6 +109,42 @@ def test_llm_engine_gpu_sampling_in_graph_matches_eager():
     assert other["s1"] != graph["s1"] and other["s0"] == graph["s0"]
 
 
+def test_llm_fp8_projections_on_gpu():
+    """The block-scaled e4m3 GEMM path inside the decoder (prefill, then CUDA-graph decode bursts) against the same
+    weights in bf16."""
+    torch.manual_seed(5)
+    cfg = _llm_cfg()
+    g = QwenLLM(cfg, device="cuda")
+    for p in g.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.05)
+    prompts = [np.arange(5, 300, dtype=np.int32), np.arange(900, 917, dtype=np.int32)]
+
+    def run(model, n_new=1):
+        eng = LLMEngine(model, EngineConfig(num_pages=32, max_batched_tokens=256, decode_burst=5, max_model_len=1024))
+        seqs = [Sequence(f"s{i}", p, SamplingParams(n_new, True), return_hidden=n_new == 1) for i, p in enumerate(prompts)]
+        for s in seqs:
+            eng.add_request(s)
+        hid, toks = {}, {}
+        while eng.has_work():
+            for o in eng.step():
+                toks.setdefault(o.seq_id, []).extend(o.new_token_ids)
+                if o.hidden is not None:
+                    hid[o.seq_id] = o.hidden
+        return hid, toks
+
+    h0, t0 = run(g)
+    g.quantize_fp8_()
+    h1, _ = run(g)
+    _, t1 = run(g, n_new=12)
+    torch.cuda.synchronize()
+    ops.check_error("fp8 llm")
+    assert g.layers[0].self_attn.o_proj.weight is None
+    for k in h0:
+        assert h0[k].shape == h1[k].shape and _cos(h0[k], h1[k]) > 0.97, k
+    assert all(len(v) == 12 for v in t1.values())
+
+
 def test_mllm_pipeline_end_to_end():
     torch.manual_seed(2)
     vcfg = Qwen25VisionConfig(depth=2, hidden_size=256, num_heads=4, intermediate_size=512, out_hidden_size=512,
