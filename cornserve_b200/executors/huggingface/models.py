@@ -31,7 +31,7 @@ def _build_llm(model_id: str, device: torch.device, pages: int = 256) -> tuple[L
     llm = QwenLLM(cfg, device=device)
     if device.type == "cpu":  # the CUDA kernels are bf16
         llm = llm.float()
-    load_model_weights(llm, model_id, ["model.language_model.", "language_model.", "thinker.model.", "model.", "lm_head.", ""],
+    load_model_weights(llm, model_id, ["model.language_model.", "language_model.", "thinker.model.", "model.", ""],
                        strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower.", "audio_tower."])
     llm.eval()
     engine = LLMEngine(llm, EngineConfig(num_pages=pages, decode_burst=4, max_model_len=8192, use_cuda_graph=device.type == "cuda"))

@@ -33,7 +33,9 @@ import io
 import json
 import os
 import pickle
+import random
 import re
+import sys
 import socket
 import threading
 import time
@@ -80,6 +82,8 @@ def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
     ap.add_argument("--num-kv-pages", type=int, default=0, help="0 = size the cache from free memory")
     ap.add_argument("--decode-burst", type=int, default=4)
     ap.add_argument("--kv-transfer-config", default=None)
+    ap.add_argument("--tp-rank", type=int, default=0, help="set by the executor itself for its follower ranks")
+    ap.add_argument("--tp-port", type=int, default=0, help="rendezvous port of the tensor-parallel ranks")
     ap.add_argument("--run-talker", action="store_true")
     ap.add_argument("--run-vocoder", action="store_true")
     for flag in ("--trust-remote-code", "--enforce-eager", "--no-enable-prefix-caching", "--disable-mm-preprocessor-cache",
@@ -105,8 +109,9 @@ class _Pending:
 class AsyncLLM:
     """Runs the synchronous engine on its own thread and fans step outputs out to per-request queues."""
 
-    def __init__(self, engine: LLMEngine):
+    def __init__(self, engine: LLMEngine, tp=None):
         self.engine = engine
+        self.tp = tp   # tensor-parallel control channel: every step is announced to the follower ranks first
         self.pending: dict[str, _Pending] = {}
         self.inbox: list[Sequence] = []
         self.calls: list[tuple[Any, concurrent.futures.Future]] = []
@@ -158,6 +163,13 @@ class AsyncLLM:
                 if self.engine.held:
                     for sid in self.engine.expire_held(float(os.environ.get("CORNSERVE_KV_HOLD_SECONDS", "600"))):
                         logger.warning("Freed the KV pages of %s: nobody fetched them", sid)
+                if self.tp is not None:
+                    if not new and not self.engine.has_work():
+                        continue   # nothing to run: the followers are not woken either
+                    for s in new:
+                        if s.params.samples and s.params.seed is None:
+                            s.params.seed = random.getrandbits(62)   # drawn here so that every rank gets the same stream
+                    self.tp.publish(new)
                 for s in new:
                     try:
                         self.engine.add_request(s)
@@ -169,6 +181,11 @@ class AsyncLLM:
             logger.exception("LLM engine thread died")
         finally:
             self.alive = False
+            if self.tp is not None:
+                try:
+                    self.tp.publish([], stop=True)
+                except Exception:  # noqa: BLE001
+                    logger.exception("could not tell the follower ranks to stop")
             for sid in list(self.pending):
                 self._deliver(StepOutput(sid, [], True, "error: engine stopped"))
 
@@ -190,7 +207,7 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
     model = QwenLLM(cfg, group=group, device=device)
     if device.type == "cpu":
         model = model.float()  # the CUDA kernels are bf16; fp32 is the CPU restatement's precision
-    load_model_weights(model, args.model, ["thinker.model.", "thinker.", "model.language_model.", "language_model.", "model.", "lm_head.", ""],
+    load_model_weights(model, args.model, ["thinker.model.", "thinker.", "model.language_model.", "language_model.", "model.", ""],
                        strict=False, ignored_prefixes=["visual.", "model.visual.", "vision_tower.", "thinker.visual.", "thinker.audio_tower.",
                                                        "talker.", "code2wav."])
     model.eval()
@@ -206,6 +223,10 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
             pages = max(64, budget // model.kv_bytes_per_page())
         else:
             pages = 64
+    if group is not None and group.size > 1:
+        from .tp import agree_on_min
+
+        pages = agree_on_min(int(pages), group)
     ecfg = EngineConfig(num_pages=int(pages), max_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
                         decode_burst=args.decode_burst, max_model_len=args.max_model_len,
                         use_cuda_graph=device.type == "cuda")
@@ -215,8 +236,22 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
 class LLMServer:
     def __init__(self, args: argparse.Namespace):
         self.args = args
-        self.engine, self.hf_cfg = build_engine(args)
-        self.llm = AsyncLLM(self.engine)
+        self.followers: list = []
+        tp = int(args.tensor_parallel_size)
+        if tp > 1:
+            from . import tp as tpmod
+
+            if args.kv_transfer_config:
+                raise ValueError("prefill/decode disaggregation is not available with --tensor-parallel-size > 1")
+            port = tpmod.free_port()
+            self.followers = tpmod.spawn_followers(getattr(args, "argv", None) or sys.argv[1:], tp, port)
+            group = tpmod.join_group(0, tp, port)
+            self.engine, self.hf_cfg = build_engine(args, group)
+            control = tpmod.TPControl(group, next(self.engine.model.parameters()).dtype)
+            self.llm = AsyncLLM(self.engine, tp=control)
+        else:
+            self.engine, self.hf_cfg = build_engine(args)
+            self.llm = AsyncLLM(self.engine)
         self.cfg = self.engine.mcfg
         self.tokenizer = load_tokenizer(args.model, {**(self.hf_cfg.get("thinker_config") or {}), **self.hf_cfg}, self.cfg.vocab_size)
         self.omni_cfg = self.hf_cfg if "talker_config" in self.hf_cfg else None
@@ -657,12 +692,33 @@ class LLMServer:
 
     def shutdown(self) -> None:
         self.llm.shutdown()
+        for p in self.followers:
+            try:
+                p.wait(timeout=10)
+            except Exception:  # noqa: BLE001
+                p.kill()
         if self.sidecar is not None:
             self.sidecar.shutdown_sync()
 
 
+def follower_main(args: argparse.Namespace) -> None:
+    """A further tensor-parallel rank: no HTTP server, no sidecar; it mirrors rank 0's engine steps."""
+    from . import tp as tpmod
+
+    group = tpmod.join_group(args.tp_rank, int(args.tensor_parallel_size), args.tp_port)
+    engine, _ = build_engine(args, group)
+    ops.bind_thread(engine.device)
+    control = tpmod.TPControl(group, next(engine.model.parameters()).dtype)
+    logger.info("tensor-parallel rank %d of %d is ready", args.tp_rank, group.size)
+    tpmod.follower_loop(engine, control)
+
+
 def main(argv: list[str] | None = None) -> None:
     args = parse_args(argv)
+    args.argv = list(argv) if argv is not None else sys.argv[1:]
+    if args.tp_rank > 0:
+        follower_main(args)
+        return
     configure_otel("llm")
     if args.run_talker:
         from .talker_server import TalkerServer

@@ -1,0 +1,116 @@
+"""The LLM executor with ``--tensor-parallel-size 2`` as real processes (gloo ranks on the CPU): the leader serves HTTP,
+the follower mirrors its engine steps, and the answers equal those of a one-rank executor on the same checkpoint."""
+
+import json
+import os
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+CONFIG = {"model_type": "qwen2", "architectures": ["Qwen2ForCausalLM"], "hidden_size": 64, "num_hidden_layers": 2,
+          "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 128, "vocab_size": 512,
+          "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512, "tie_word_embeddings": False,
+          "eos_token_id": 511, "torch_dtype": "float32"}
+
+
+def _checkpoint(tmp: Path) -> Path:
+    from safetensors.torch import save_file
+
+    d = tmp / "tiny-llm"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(CONFIG))
+    g = torch.Generator().manual_seed(0)
+    H, dh, hq, hkv, inter, V = 64, 16, 4, 2, 128, 512
+    r = lambda *s, std=0.08: torch.randn(*s, generator=g) * std  # noqa: E731
+    w = {"model.embed_tokens.weight": r(V, H, std=0.5), "model.norm.weight": 1 + r(H), "lm_head.weight": r(V, H, std=0.3)}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        w.update({p + "input_layernorm.weight": 1 + r(H), p + "post_attention_layernorm.weight": 1 + r(H),
+                  p + "self_attn.q_proj.weight": r(hq * dh, H), p + "self_attn.q_proj.bias": r(hq * dh),
+                  p + "self_attn.k_proj.weight": r(hkv * dh, H), p + "self_attn.k_proj.bias": r(hkv * dh),
+                  p + "self_attn.v_proj.weight": r(hkv * dh, H), p + "self_attn.v_proj.bias": r(hkv * dh),
+                  p + "self_attn.o_proj.weight": r(H, hq * dh), p + "mlp.gate_proj.weight": r(inter, H),
+                  p + "mlp.up_proj.weight": r(inter, H), p + "mlp.down_proj.weight": r(H, inter)})
+    save_file({k: v.contiguous() for k, v in w.items()}, str(d / "model.safetensors"))
+    return d
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return int(s.getsockname()[1])
+
+
+def _serve(model_dir: Path, tp: int):
+    port = _free_port()
+    env = dict(os.environ, CORNSERVE_DEVICE="cpu", PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.Popen([sys.executable, "-m", "cornserve_b200.executors.llm.server", str(model_dir), "--port", str(port),
+                             "--tensor-parallel-size", str(tp), "--num-kv-pages", "16", "--max-model-len", "512",
+                             "--max-num-batched-tokens", "64", "--decode-burst", "3"], env=env, cwd=ROOT)
+    deadline = time.time() + 180
+    while time.time() < deadline:
+        if proc.poll() is not None:
+            raise RuntimeError(f"the executor exited with {proc.returncode}")
+        try:
+            with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                if r.status == 200:
+                    return proc, port
+        except Exception:  # noqa: BLE001
+            time.sleep(0.5)
+    proc.kill()
+    raise RuntimeError("the executor did not become healthy")
+
+
+def _chat(port: int, text: str, **extra) -> str:
+    body = {"model": "tiny-llm", "messages": [{"role": "user", "content": text}], "max_completion_tokens": 12, "ignore_eos": True, **extra}
+    req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=120) as r:
+        return json.loads(r.read())["choices"][0]["message"]["content"]
+
+
+@pytest.mark.timeout(600)
+def test_two_rank_executor_answers_like_one_rank(tmp_path):
+    ckpt = _checkpoint(tmp_path)
+    prompts = ["hello there", "a much longer question about tensor parallel serving of decoders", "x"]
+    answers = {}
+    for tp in (1, 2):
+        proc, port = _serve(ckpt, tp)
+        try:
+            got = [_chat(port, p) for p in prompts]
+            got.append(_chat(port, prompts[1], temperature=1.1, top_p=0.9, seed=7))
+            got.append(_chat(port, prompts[1], temperature=1.1, top_p=0.9, seed=7))
+            answers[tp] = got
+        finally:
+            proc.terminate()
+            try:
+                proc.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                proc.kill()
+    assert answers[2][:3] == answers[1][:3]
+    assert answers[2][3] == answers[2][4]          # a seeded sampled request repeats on the two-rank executor
+    assert answers[2][3] == answers[1][3]          # and draws the same stream as on one rank
+
+
+def test_untied_lm_head_of_a_checkpoint_is_loaded(tmp_path, monkeypatch):
+    """``lm_head.weight`` sits at the top level of the checkpoint, beside ``model.*``; it must reach the model."""
+    from safetensors import safe_open
+
+    from cornserve_b200.executors.llm.server import build_engine, parse_args
+
+    monkeypatch.setenv("CORNSERVE_DEVICE", "cpu")
+    ckpt = _checkpoint(tmp_path)
+    eng, _ = build_engine(parse_args([str(ckpt), "--num-kv-pages", "16", "--max-model-len", "512"]))
+    with safe_open(str(ckpt / "model.safetensors"), framework="pt") as f:
+        want = f.get_tensor("lm_head.weight")
+        emb = f.get_tensor("model.embed_tokens.weight")
+    assert torch.allclose(eng.model.lm_head.weight.float(), want.float(), atol=1e-2)
+    assert torch.allclose(eng.model.embed_tokens.weight.float(), emb.float(), atol=1e-2)
