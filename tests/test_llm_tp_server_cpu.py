@@ -7,6 +7,7 @@ import socket
 import subprocess
 import sys
 import time
+import urllib.error
 import urllib.request
 from pathlib import Path
 
@@ -114,3 +115,41 @@ def test_untied_lm_head_of_a_checkpoint_is_loaded(tmp_path, monkeypatch):
         emb = f.get_tensor("model.embed_tokens.weight")
     assert torch.allclose(eng.model.lm_head.weight.float(), want.float(), atol=1e-2)
     assert torch.allclose(eng.model.embed_tokens.weight.float(), emb.float(), atol=1e-2)
+
+
+@pytest.mark.timeout(300)
+def test_leader_turns_unhealthy_when_a_follower_rank_exits(tmp_path):
+    """Host-side failure: the follower process is ended between requests; the leader's next step fails on the control
+    channel, the request gets an error instead of hanging, and ``/health`` reports 503 so that the executor is replaced."""
+    import psutil
+
+    ckpt = _checkpoint(tmp_path)
+    proc, port = _serve(ckpt, 2)
+    try:
+        assert _chat(port, "before")                      # both ranks work
+        followers = [c for c in psutil.Process(proc.pid).children(recursive=True) if "--tp-rank" in " ".join(c.cmdline())]
+        assert len(followers) == 1
+        followers[0].kill()
+        gone = time.time() + 20     # the leader is its parent, so it lingers as a zombie until the leader reaps it
+        while time.time() < gone and followers[0].is_running() and followers[0].status() != psutil.STATUS_ZOMBIE:
+            time.sleep(0.1)
+        try:
+            answer = _chat(port, "after")
+        except Exception as e:  # noqa: BLE001  (an HTTP error status is as good as an error body)
+            answer = f"error: {e}"
+        assert "error" in answer.lower() or answer == ""
+        deadline, status = time.time() + 30, 200
+        while time.time() < deadline and status == 200:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                    status = r.status
+            except urllib.error.HTTPError as e:
+                status = e.code
+            time.sleep(0.3)
+        assert status == 503
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            proc.kill()
