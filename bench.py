@@ -112,11 +112,11 @@ def main() -> None:
     import torch.distributed as dist
 
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-    from cornserve_b200 import ops
-    from cornserve_b200.executors.llm.engine import EngineConfig
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
-    from cornserve_b200.models.qwen_llm import LLMConfig, QwenLLM
-    from cornserve_b200.pipelines import MLLMPipeline, MLLMRequest
+    from cornserve import ops
+    from cornserve.task_executors.llm.engine import EngineConfig
+    from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.pipelines import MLLMPipeline, MLLMRequest
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
@@ -223,7 +223,7 @@ def main() -> None:
                     # whole job, like `value`: every rank copies its own batch (the ranks' batches have the same shape)
                     "h2d_bytes_per_step": world * pipe.h2d_bytes // args.steps,
                     "d2h_bytes_per_step": world * pipe.d2h_bytes // args.steps,
-                    "api": "cornserve_b200.pipelines.MLLMPipeline.generate"},
+                    "api": "cornserve.pipelines.MLLMPipeline.generate"},
             "gpu_launches": launches * world,
             "output_tokens_per_second": total_req * out_tok / (dev_ms / 1e3),
         }

@@ -57,15 +57,15 @@ def _max_over_ranks(seconds: float, world: int) -> float:
 
 
 def time_ours(model: str, pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float:
-    from cornserve_b200 import ops
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
-    from cornserve_b200.parallel.state import init_distributed
+    from cornserve import ops
+    from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve.parallel.state import init_distributed
 
     group = init_distributed(rank, world, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
                              master_port=int(os.environ.get("MASTER_PORT", "29511")), local_device=int(os.environ.get("LOCAL_RANK", rank)))
     torch.manual_seed(0)
     if model == "qwen2_vl":
-        from cornserve_b200.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
+        from cornserve.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
 
         tower = Qwen2VisionTransformer(Qwen2VisionConfig(), group=group, device=group.device)
     else:

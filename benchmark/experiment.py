@@ -82,10 +82,10 @@ class ExperimentConfig:
 def app_source(cfg: ExperimentConfig) -> str:
     """Source of the app that realises ``cfg.backend`` (one streaming ``serve`` over the matching composite task)."""
     head = '''from collections.abc import AsyncIterator
-from cornserve_b200.app.base import AppConfig, AppRequest, AppResponse
-from cornserve_b200.tasklib import (DisaggregatedMLLMTask, MLLMTask, Modality, OpenAIChatCompletionChunk,
+from cornserve.app.base import AppConfig, AppRequest, AppResponse
+from cornserve_tasklib import (DisaggregatedMLLMTask, MLLMTask, Modality, OpenAIChatCompletionChunk,
                                     OpenAIChatCompletionRequest)
-from cornserve_b200.tasklib.task.unit.encoder import DummyEncoderTask, EncoderInput
+from cornserve_tasklib.task.unit.encoder import DummyEncoderTask, EncoderInput
 
 class Request(AppRequest):
     prompt: str

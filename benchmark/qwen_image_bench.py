@@ -36,10 +36,10 @@ def main(argv: list[str] | None = None) -> None:
     ap.add_argument("--tiny", action="store_true", help="small architecture (CPU smoke run)")
     a = ap.parse_args(argv)
 
-    from cornserve_b200 import ops
-    from cornserve_b200.models.qwen_image import QwenImageDiTConfig, QwenImageModel, QwenImagePipelineConfig
-    from cornserve_b200.models.qwen_image_vae import QwenImageVAEConfig
-    from cornserve_b200.parallel.state import init_distributed, single_group
+    from cornserve import ops
+    from cornserve.models.qwen_image import QwenImageDiTConfig, QwenImageModel, QwenImagePipelineConfig
+    from cornserve.models.qwen_image_vae import QwenImageVAEConfig
+    from cornserve.parallel.state import init_distributed, single_group
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     cuda = torch.cuda.is_available()

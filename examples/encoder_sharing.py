@@ -9,8 +9,8 @@ from __future__ import annotations
 
 import asyncio
 
-from cornserve_b200.app.base import AppConfig, AppRequest, AppResponse
-from cornserve_b200.tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest
+from cornserve.app.base import AppConfig, AppRequest, AppResponse
+from cornserve_tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest
 
 MODELS = ["google/gemma-3-4b-it", "google/gemma-3-12b-it"]
 

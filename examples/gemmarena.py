@@ -10,8 +10,8 @@ from __future__ import annotations
 import asyncio
 from collections.abc import AsyncIterator
 
-from cornserve_b200.app.base import AppConfig, AppRequest, AppResponse
-from cornserve_b200.tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest
+from cornserve.app.base import AppConfig, AppRequest, AppResponse
+from cornserve_tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest
 
 MODELS = {"4b": "google/gemma-3-4b-it", "12b": "google/gemma-3-12b-it", "27b": "google/gemma-3-27b-it"}
 

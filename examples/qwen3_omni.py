@@ -9,8 +9,8 @@ from __future__ import annotations
 
 from collections.abc import AsyncIterator
 
-from cornserve_b200.app.base import AppConfig, AppRequest
-from cornserve_b200.tasklib import Modality, OmniInput, OmniTask, OpenAIChatCompletionChunk
+from cornserve.app.base import AppConfig, AppRequest
+from cornserve_tasklib import Modality, OmniInput, OmniTask, OpenAIChatCompletionChunk
 
 MODEL = "Qwen/Qwen3-Omni-30B-A3B-Instruct"
 

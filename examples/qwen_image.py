@@ -8,9 +8,9 @@ its hidden states to the diffusion generator, which skips the system-prompt rows
 
 from __future__ import annotations
 
-from cornserve_b200.app.base import AppConfig
-from cornserve_b200.task.base import Task, TaskInput, TaskOutput
-from cornserve_b200.tasklib import ImageGeneratorInput, ImageGeneratorTask, LLMEmbeddingUnitTask, OpenAIChatCompletionRequest
+from cornserve.app.base import AppConfig
+from cornserve.task.base import Task, TaskInput, TaskOutput
+from cornserve_tasklib import ImageGeneratorInput, ImageGeneratorTask, LLMEmbeddingUnitTask, OpenAIChatCompletionRequest
 
 TEXT_ENCODER = "Qwen/Qwen2.5-VL-7B-Instruct"
 # the generator was trained with this instruction in front of every prompt; its 34 tokens are not part of the conditioning

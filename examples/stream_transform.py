@@ -9,8 +9,8 @@ from __future__ import annotations
 
 from collections.abc import AsyncIterator
 
-from cornserve_b200.app.base import AppConfig, AppRequest, AppResponse
-from cornserve_b200.tasklib import MLLMTask, OpenAIChatCompletionChunk, OpenAIChatCompletionRequest
+from cornserve.app.base import AppConfig, AppRequest, AppResponse
+from cornserve_tasklib import MLLMTask, OpenAIChatCompletionChunk, OpenAIChatCompletionRequest
 
 MODEL = "Qwen/Qwen2.5-VL-7B-Instruct"
 

@@ -13,10 +13,10 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
 
-from cornserve_b200 import ops  # noqa: E402
-from cornserve_b200.ops import reference as ref  # noqa: E402
-from cornserve_b200.parallel.fused import FusedRowParallel  # noqa: E402
-from cornserve_b200.parallel.state import init_distributed  # noqa: E402
+from cornserve import ops  # noqa: E402
+from cornserve.ops import reference as ref  # noqa: E402
+from cornserve.parallel.fused import FusedRowParallel  # noqa: E402
+from cornserve.parallel.state import init_distributed  # noqa: E402
 
 
 def check(name, got, want, atol=3e-2, rtol=3e-2):
@@ -67,9 +67,9 @@ def tp_moe_llm_matches_single_gpu(g):
 def _tp_llm(g, extra):
     import numpy as np
 
-    from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
-    from cornserve_b200.models.qwen_llm import LLMConfig, QwenLLM
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.parallel.state import single_group
 
     cfg = LLMConfig(hidden_size=512, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
                     intermediate_size=1024, vocab_size=2048, eos_token_id=2047, **extra)
@@ -131,8 +131,8 @@ def tp_vision_tower(g):
     operand, chunk-wise waiting GEMM) against the same weights on one GPU, and timed against the NCCL path."""
     import numpy as np
 
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve.parallel.state import single_group
 
     rank = g.rank
     cfg = Qwen25VisionConfig(depth=4, fullatt_block_indexes=[1, 3])
@@ -243,8 +243,8 @@ def tp_vision_tower(g):
 def sp_diffusion_transformer(g):
     """Sequence-parallel MMDiT: the kernel-driven exchanges (q|k|v projection that stores head tiles at their owners,
     peer-store return of the attention output) against one GPU and against the library all-to-all path; timed."""
-    from cornserve_b200.models.qwen_image import QwenImageDiT, QwenImageDiTConfig
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.models.qwen_image import QwenImageDiT, QwenImageDiTConfig
+    from cornserve.parallel.state import single_group
 
     rank, P = g.rank, g.size
     dev = g.device
@@ -330,8 +330,8 @@ def ep_mixture_of_experts(g):
     """Expert parallelism over peer memory: every rank routes its own tokens (or a slice of replicated tokens), rows
     land in the owner's expert segments by peer stores, the down projection's epilogue returns them; against the
     single-GPU layer on all experts, and timed against the library all-to-all path."""
-    from cornserve_b200.parallel import moe
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.parallel import moe
+    from cornserve.parallel.state import single_group
 
     rank, W, dev = g.rank, g.size, g.device
     E, k, H, I = 128, 8, 2048, 768
@@ -459,8 +459,8 @@ def tp_layernorm_towers(g):
     LayerNorm variant of the reduce kernel against one GPU, and timed against the library-collective path."""
     import numpy as np
 
-    from cornserve_b200.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
+    from cornserve.parallel.state import single_group
 
     dev, rank = g.device, g.rank
 
@@ -519,7 +519,7 @@ def flag_protocol_stress(g):
     apart) and the results must stay bit-identical to the first iteration's on every rank."""
     import random
 
-    from cornserve_b200.parallel import moe
+    from cornserve.parallel import moe
 
     rank, W, dev = g.rank, g.size, g.device
     rng = random.Random(1000 + rank)

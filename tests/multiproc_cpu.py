@@ -11,7 +11,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
 
-from cornserve_b200.parallel.state import init_distributed, single_group  # noqa: E402
+from cornserve.parallel.state import init_distributed, single_group  # noqa: E402
 
 
 def cos(a, b):
@@ -21,7 +21,7 @@ def cos(a, b):
 def sp_dit(g):
     from test_geri_models import dit_weights
 
-    from cornserve_b200.models.qwen_image import QwenImageDiT, QwenImageDiTConfig
+    from cornserve.models.qwen_image import QwenImageDiT, QwenImageDiTConfig
 
     cfg = QwenImageDiTConfig(in_channels=16, out_channels=4, num_layers=2, attention_head_dim=64, num_attention_heads=4,
                              joint_attention_dim=64, axes_dims_rope=(8, 28, 28))
@@ -49,8 +49,8 @@ def sp_dit(g):
 def tp_llm(g):
     from multigpu_fused import hf_style_weights
 
-    from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
-    from cornserve_b200.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
 
     cfg = LLMConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
                     intermediate_size=256, vocab_size=512, eos_token_id=511)
@@ -78,7 +78,7 @@ def tp_llm(g):
 def tp_vit(g):
     from multigpu_fused import vit_weights
 
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
 
     cfg = Qwen25VisionConfig(depth=2, hidden_size=128, num_heads=4, intermediate_size=256, out_hidden_size=64,
                              fullatt_block_indexes=[1], window_size=56)
@@ -116,7 +116,7 @@ def tp_encoder_families(g):
     from transformers.models.qwen2_vl import modeling_qwen2_vl as hf2
     from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
 
-    from cornserve_b200.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
+    from cornserve.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
 
     hc = Qwen2VLVisionConfig(depth=2, embed_dim=128, num_heads=4, hidden_size=192, mlp_ratio=4)
     ref: nn.Module = hf2.Qwen2VisionTransformerPretrainedModel(hc).float()
@@ -130,7 +130,7 @@ def tp_encoder_families(g):
     from transformers.models.qwen3_vl import modeling_qwen3_vl as hf3
     from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig
 
-    from cornserve_b200.models.qwen3_vl import Qwen3VisionConfig, Qwen3VisionTransformer
+    from cornserve.models.qwen3_vl import Qwen3VisionConfig, Qwen3VisionTransformer
 
     hc = Qwen3VLVisionConfig(depth=3, hidden_size=128, num_heads=4, intermediate_size=256, out_hidden_size=160,
                              num_position_embeddings=36, deepstack_visual_indexes=[0, 2], patch_size=16)
@@ -144,7 +144,7 @@ def tp_encoder_families(g):
     from transformers.models.qwen2_5_omni import modeling_qwen2_5_omni as hfo
     from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniAudioEncoderConfig
 
-    from cornserve_b200.models.omni_audio import AudioEncoder, AudioEncoderConfig
+    from cornserve.models.omni_audio import AudioEncoder, AudioEncoderConfig
 
     ac = Qwen2_5OmniAudioEncoderConfig(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4,
                                        encoder_ffn_dim=128, max_source_positions=100, n_window=10, output_dim=48)
@@ -159,7 +159,7 @@ def tp_encoder_families(g):
     from transformers.models.gemma3.configuration_gemma3 import Gemma3Config
     from transformers.models.siglip.modeling_siglip import SiglipVisionModel
 
-    from cornserve_b200.models.siglip import Gemma3VisionConfig, Gemma3VisionEncoder
+    from cornserve.models.siglip import Gemma3VisionConfig, Gemma3VisionEncoder
 
     vis = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2, image_size=112, patch_size=14,
                vision_use_head=False)
@@ -176,7 +176,7 @@ def tp_encoder_families(g):
     compare("gemma3", lambda grp: Gemma3VisionEncoder(gcfg, group=grp, model_id="google/gemma-3-4b-it"), sd,
             lambda m: m("image", "google/gemma-3-4b-it", {"pixel_values": gpix, "num_crops": [torch.tensor([0]), torch.tensor([1])]}))
     # InternVL (layer scale, q/k norm over all heads)
-    from cornserve_b200.models.internvl import InternVLEncoder, InternVLVisionConfig
+    from cornserve.models.internvl import InternVLEncoder, InternVLVisionConfig
 
     icfg = InternVLVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=56,
                                 patch_size=14, qk_normalization=True, norm_type="rms_norm", llm_hidden_size=96, select_layer=-1)

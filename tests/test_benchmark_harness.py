@@ -37,7 +37,7 @@ def test_experiment_configurations_and_app_sources():
     import pytest
 
     from benchmark.experiment import BACKENDS, PARTS, ExperimentConfig, Workload, app_source, part_of
-    from cornserve_b200.services.gateway.app_manager import load_module_from_source, validate_app_module
+    from cornserve.services.gateway.app_manager import load_module_from_source, validate_app_module
 
     with pytest.raises(ValueError):
         ExperimentConfig("EV", gpus={"llm": 2})
@@ -51,7 +51,7 @@ def test_experiment_configurations_and_app_sources():
         cfg = ExperimentConfig(backend, "cornserve-b200/tiny-vlm", {p: 1 for p in PARTS[backend]})
         module = load_module_from_source(app_source(cfg), f"bench_app_{backend}")
         classes = validate_app_module(module)
-        from cornserve_b200.task.base import discover_unit_tasks
+        from cornserve.task.base import discover_unit_tasks
 
         parts = {part_of(json.dumps({"class_name": type(t).__name__})) for t in discover_unit_tasks(classes.config_cls.tasks.values())}
         assert parts == set(PARTS[backend]), (backend, parts)

@@ -13,14 +13,14 @@ import wave
 
 import pytest
 
-from cornserve_b200.cli.audio_streamer import PCMStreamPlayer
-from cornserve_b200.cli.log_streamer import LogStreamer
-from cornserve_b200.cli.main import Alias, extract_nested, load_payload, save_png
+from cornserve.cli.audio_streamer import PCMStreamPlayer
+from cornserve.cli.log_streamer import LogStreamer
+from cornserve.cli.main import Alias, extract_nested, load_payload, save_png
 
 APP_SOURCE = '''
 from collections.abc import AsyncIterator
-from cornserve_b200.app.base import AppConfig, AppRequest
-from cornserve_b200.tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest, OpenAIChatCompletionChunk
+from cornserve.app.base import AppConfig, AppRequest
+from cornserve_tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest, OpenAIChatCompletionChunk
 
 class Request(AppRequest):
     prompt: str
@@ -64,7 +64,7 @@ def test_alias_store(tmp_path):
 
 
 def test_png_and_pcm_sinks(tmp_path):
-    from cornserve_b200.models.qwen_image import encode_png
+    from cornserve.models.qwen_image import encode_png
     import numpy as np
 
     b64 = base64.b64encode(encode_png(np.zeros((4, 5, 3), dtype=np.uint8))).decode()
@@ -95,11 +95,11 @@ def test_log_streamer_follows_new_executor_logs(tmp_path):
 
 
 def test_tasklib_explorer_finds_tasks_and_descriptors(tmp_path):
-    from cornserve_b200.cli.tasklib_explorer import discover_tasklib
+    from cornserve.cli.tasklib_explorer import discover_tasklib
 
     (tmp_path / "mytasks.py").write_text('''
-from cornserve_b200.task.base import UnitTask, TaskInput, TaskOutput
-from cornserve_b200.executors.descriptor.base import TaskExecutionDescriptor
+from cornserve.task.base import UnitTask, TaskInput, TaskOutput
+from cornserve.task_executors.descriptor.base import TaskExecutionDescriptor
 
 class EchoIn(TaskInput):
     text: str
@@ -132,16 +132,16 @@ def test_cli_and_notebook_client_against_local_cluster(tmp_path, monkeypatch, ca
         monkeypatch.setenv(k, v)
     import importlib
 
-    import cornserve_b200.constants as c
-    import cornserve_b200.sidecar.constants as sc
-    import cornserve_b200.services.sidecar.launch as launch
-    import cornserve_b200.cli.main as cli
-    import cornserve_b200.cli.log_streamer as ls
+    import cornserve.constants as c
+    import cornserve.sidecar.constants as sc
+    import cornserve.services.sidecar.launch as launch
+    import cornserve.cli.main as cli
+    import cornserve.cli.log_streamer as ls
 
     for m in (c, sc, launch, ls, cli):
         importlib.reload(m)
-    from cornserve_b200.services.local_cluster import LocalCluster
-    from cornserve_b200.services.process import free_port
+    from cornserve.services.local_cluster import LocalCluster
+    from cornserve.services.process import free_port
 
     loop = asyncio.new_event_loop()
     t = threading.Thread(target=loop.run_forever, daemon=True)
@@ -167,8 +167,8 @@ def test_cli_and_notebook_client_against_local_cluster(tmp_path, monkeypatch, ca
         assert len(text) > 0
 
         # the notebook client shares the already deployed unit tasks and releases only its own reference
-        from cornserve_b200.frontend import CornserveClient
-        from cornserve_b200.tasklib import MLLMTask, Modality
+        from cornserve.frontend import CornserveClient
+        from cornserve_tasklib import MLLMTask, Modality
 
         with CornserveClient(cluster.url) as client:
             assert client.is_online()

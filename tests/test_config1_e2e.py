@@ -17,8 +17,8 @@ import uvicorn
 
 APP_SOURCE = '''
 from collections.abc import AsyncIterator
-from cornserve_b200.app.base import AppConfig, AppRequest
-from cornserve_b200.tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest, OpenAIChatCompletionChunk
+from cornserve.app.base import AppConfig, AppRequest
+from cornserve_tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest, OpenAIChatCompletionChunk
 
 class Request(AppRequest):
     prompt: str
@@ -48,14 +48,14 @@ def _port_block(n):
 
 def _expected_text(prompt: str, image_url: str, n_tokens: int, device: str = "cpu") -> str:
     """The same request through the in-process pipeline with identically seeded weights."""
-    from cornserve_b200.executors.eric.processor import load_image
-    from cornserve_b200.executors.llm.engine import EngineConfig
-    from cornserve_b200.executors.llm.tokenizer import load_tokenizer
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
-    from cornserve_b200.models.qwen_llm import LLMConfig, QwenLLM
-    from cornserve_b200.pipelines import MLLMPipeline
-    from cornserve_b200.executors.llm.engine import SamplingParams, Sequence, MMItem
-    from cornserve_b200.utils.hub import load_config
+    from cornserve.task_executors.eric.processor import load_image
+    from cornserve.task_executors.llm.engine import EngineConfig
+    from cornserve.task_executors.llm.tokenizer import load_tokenizer
+    from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.pipelines import MLLMPipeline
+    from cornserve.task_executors.llm.engine import SamplingParams, Sequence, MMItem
+    from cornserve.utils.hub import load_config
 
     cfg = load_config("cornserve-b200/tiny-vlm")
     torch.manual_seed(0)
@@ -133,22 +133,22 @@ def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu", collec
         monkeypatch.setenv(k, v)
     import importlib
 
-    import cornserve_b200.constants as c
-    import cornserve_b200.sidecar.constants as sc
-    import cornserve_b200.services.sidecar.launch as launch
+    import cornserve.constants as c
+    import cornserve.sidecar.constants as sc
+    import cornserve.services.sidecar.launch as launch
 
     for m in (c, sc, launch):
         importlib.reload(m)
 
-    import cornserve_b200.tasklib  # noqa: F401
-    from cornserve_b200.services.gateway.router import create_app
-    from cornserve_b200.services.process import free_port
-    from cornserve_b200.services.resource_manager.grpc import start_server as start_rm
-    from cornserve_b200.services.resource_manager.manager import ResourceManager
-    from cornserve_b200.services.store import LocalStore
-    from cornserve_b200.services.task_dispatcher.app import create_app as create_td_app, start_grpc as start_td_grpc
-    from cornserve_b200.services.task_dispatcher.dispatcher import TaskDispatcher
-    from cornserve_b200.services.task_registry.registry import TaskRegistry
+    import cornserve_tasklib  # noqa: F401
+    from cornserve.services.gateway.router import create_app
+    from cornserve.services.process import free_port
+    from cornserve.services.resource_manager.grpc import start_server as start_rm
+    from cornserve.services.resource_manager.manager import ResourceManager
+    from cornserve.services.store import LocalStore
+    from cornserve.services.task_dispatcher.app import create_app as create_td_app, start_grpc as start_td_grpc
+    from cornserve.services.task_dispatcher.dispatcher import TaskDispatcher
+    from cornserve.services.task_registry.registry import TaskRegistry
 
     async def serve(app, port):
         server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))

@@ -11,22 +11,22 @@ import pytest
 import uvicorn
 from aiohttp import web
 
-import cornserve_b200.tasklib  # noqa: F401
-from cornserve_b200.services.process import free_port
-from cornserve_b200.services.resource import CannotColocateError, NotEnoughGPUsError, Resource
-from cornserve_b200.services.resource_manager.grpc import start_server as start_rm
-from cornserve_b200.services.resource_manager.manager import ResourceManager
-from cornserve_b200.services.store import LocalStore
-from cornserve_b200.services.task_dispatcher.app import create_app as create_td_app
-from cornserve_b200.services.task_dispatcher.app import start_grpc as start_td_grpc
-from cornserve_b200.services.task_dispatcher.dispatcher import TaskDispatcher
-from cornserve_b200.services.task_manager.manager import plan_executors
-from cornserve_b200.services.task_registry.registry import TaskRegistry
+import cornserve_tasklib  # noqa: F401
+from cornserve.services.process import free_port
+from cornserve.services.resource import CannotColocateError, NotEnoughGPUsError, Resource
+from cornserve.services.resource_manager.grpc import start_server as start_rm
+from cornserve.services.resource_manager.manager import ResourceManager
+from cornserve.services.store import LocalStore
+from cornserve.services.task_dispatcher.app import create_app as create_td_app
+from cornserve.services.task_dispatcher.app import start_grpc as start_td_grpc
+from cornserve.services.task_dispatcher.dispatcher import TaskDispatcher
+from cornserve.services.task_manager.manager import plan_executors
+from cornserve.services.task_registry.registry import TaskRegistry
 
 APP_SOURCE = '''
 from collections.abc import AsyncIterator
-from cornserve_b200.app.base import AppConfig, AppRequest, AppResponse
-from cornserve_b200.tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest, OpenAIChatCompletionChunk
+from cornserve.app.base import AppConfig, AppRequest, AppResponse
+from cornserve_tasklib import MLLMTask, Modality, OpenAIChatCompletionRequest, OpenAIChatCompletionChunk
 
 class Request(AppRequest):
     prompt: str
@@ -97,7 +97,7 @@ async def _serve_uvicorn(app, port):
 
 
 def test_resource_allocation_policies():
-    from cornserve_b200.services.resource import GPU
+    from cornserve.services.resource import GPU
 
     r = Resource([GPU(f"n{i // 4}", i, i % 4) for i in range(8)])
     a = r.allocate(2, "a")
@@ -118,7 +118,7 @@ def test_resource_allocation_policies():
 
 
 def test_plan_executors_packs_largest_first():
-    from cornserve_b200.services.resource import GPU
+    from cornserve.services.resource import GPU
 
     gpus = [GPU("n", i, i) for i in range(7)]
     groups, left = plan_executors(gpus, [1, 2, 4])
@@ -144,7 +144,7 @@ def test_gateway_to_executors_round_trip(tmp_path):
         rm_addr = f"127.0.0.1:{free_port()}"
         rm_server = await start_rm(rm, rm_addr)
         # gateway
-        from cornserve_b200.services.gateway.router import create_app
+        from cornserve.services.gateway.router import create_app
 
         gw_app = create_app(rm_addr, f"http://127.0.0.1:{td_port}", [td_grpc_addr], registry, resource_manager_local=rm)
         gw_port = free_port()

@@ -26,7 +26,7 @@ def test_qwen2_vl_vision_matches_hf():
     hf = pytest.importorskip("transformers.models.qwen2_vl.modeling_qwen2_vl")
     from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
 
-    from cornserve_b200.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
+    from cornserve.models.qwen2_vl import Qwen2VisionConfig, Qwen2VisionTransformer
 
     hf_cfg = Qwen2VLVisionConfig(depth=2, embed_dim=128, num_heads=4, hidden_size=192, mlp_ratio=4)
     hf_cfg._attn_implementation = "eager"
@@ -49,7 +49,7 @@ def test_qwen3_vl_vision_matches_hf():
     hf = pytest.importorskip("transformers.models.qwen3_vl.modeling_qwen3_vl")
     from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig
 
-    from cornserve_b200.models.qwen3_vl import Qwen3VisionConfig, Qwen3VisionTransformer
+    from cornserve.models.qwen3_vl import Qwen3VisionConfig, Qwen3VisionTransformer
 
     hf_cfg = Qwen3VLVisionConfig(depth=3, hidden_size=128, num_heads=4, intermediate_size=256, out_hidden_size=160,
                                  num_position_embeddings=36, deepstack_visual_indexes=[0, 2], patch_size=16)
@@ -75,8 +75,8 @@ def test_qwen2_5_omni_audio_and_vision_match_hf():
     from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import (Qwen2_5OmniAudioEncoderConfig,
                                                                             Qwen2_5OmniVisionEncoderConfig)
 
-    from cornserve_b200.models.omni_audio import AudioEncoder, AudioEncoderConfig
-    from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+    from cornserve.models.omni_audio import AudioEncoder, AudioEncoderConfig
+    from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
 
     torch.manual_seed(0)
     a_cfg = Qwen2_5OmniAudioEncoderConfig(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4,
@@ -117,7 +117,7 @@ def test_qwen3_omni_audio_matches_hf():
     hf = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
     from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeAudioEncoderConfig
 
-    from cornserve_b200.models.omni_audio import AudioEncoder, AudioEncoderConfig
+    from cornserve.models.omni_audio import AudioEncoder, AudioEncoderConfig
 
     torch.manual_seed(0)
     a_cfg = Qwen3OmniMoeAudioEncoderConfig(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4,
@@ -142,7 +142,7 @@ def test_qwen3_omni_audio_matches_hf():
 
 
 def test_omni_encoder_routes_modalities():
-    from cornserve_b200.models.qwen_omni import OmniEncoderConfig, Qwen3OmniEncoder
+    from cornserve.models.qwen_omni import OmniEncoderConfig, Qwen3OmniEncoder
 
     cfg = OmniEncoderConfig.from_hf({"model_type": "qwen3_omni_moe", "thinker_config": {
         "vision_config": {"depth": 1, "hidden_size": 64, "num_heads": 2, "intermediate_size": 128, "out_hidden_size": 48,
@@ -162,7 +162,7 @@ def test_gemma3_encoder_matches_hf_and_shares_the_tower():
     from transformers.models.gemma3.configuration_gemma3 import Gemma3Config
     from transformers.models.siglip.modeling_siglip import SiglipVisionModel
 
-    from cornserve_b200.models.siglip import Gemma3VisionConfig, Gemma3VisionEncoder
+    from cornserve.models.siglip import Gemma3VisionConfig, Gemma3VisionEncoder
 
     torch.manual_seed(0)
     vis = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2, image_size=112, patch_size=14,
@@ -201,7 +201,7 @@ def test_llava_onevision_encoder_matches_hf():
     hf = pytest.importorskip("transformers.models.llava_onevision.modeling_llava_onevision")
     from transformers.models.llava_onevision.configuration_llava_onevision import LlavaOnevisionConfig
 
-    from cornserve_b200.models.siglip import LlavaOnevisionEncoder, LlavaOnevisionVisionConfig
+    from cornserve.models.siglip import LlavaOnevisionEncoder, LlavaOnevisionVisionConfig
 
     torch.manual_seed(0)
     S = 56
@@ -235,7 +235,7 @@ def test_internvl_encoder_matches_restatement():
     """InternViT + pixel shuffle + projector against a plain PyTorch restatement that uses the checkpoint's names."""
     import torch.nn.functional as F
 
-    from cornserve_b200.models.internvl import InternVLEncoder, InternVLVisionConfig, pixel_shuffle
+    from cornserve.models.internvl import InternVLEncoder, InternVLVisionConfig, pixel_shuffle
 
     torch.manual_seed(0)
     cfg = InternVLVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4, image_size=56,
@@ -293,9 +293,9 @@ def test_internvl_encoder_matches_restatement():
 ])
 def test_every_registered_encoder_runs_through_the_worker(model_id, modality, adapter, width, monkeypatch, tmp_path):
     """Registry entry -> worker -> preprocessing recipe -> forward, on raw decoded inputs, for each model family."""
-    from cornserve_b200.executors.eric.config import EricConfig, ModelConfig
-    from cornserve_b200.executors.eric.schema import Batch, Modality
-    from cornserve_b200.executors.eric.worker import Worker
+    from cornserve.task_executors.eric.config import EricConfig, ModelConfig
+    from cornserve.task_executors.eric.schema import Batch, Modality
+    from cornserve.task_executors.eric.worker import Worker
 
     monkeypatch.setenv("CORNSERVE_DEVICE", "cpu")
     monkeypatch.setenv("CORNSERVE_TEST_DUMP_TENSOR_DIR", str(tmp_path))

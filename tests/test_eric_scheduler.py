@@ -2,8 +2,8 @@
 
 import torch
 
-from cornserve_b200.executors.eric.scheduler import Scheduler
-from cornserve_b200.executors.eric.schema import EngineRequest, Modality, ProcessedItem
+from cornserve.task_executors.eric.scheduler import Scheduler
+from cornserve.task_executors.eric.schema import EngineRequest, Modality, ProcessedItem
 
 
 def _req(rid, specs):

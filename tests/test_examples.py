@@ -10,9 +10,9 @@ EXAMPLES = sorted((Path(__file__).resolve().parents[1] / "examples").glob("*.py"
 
 @pytest.mark.parametrize("path", EXAMPLES, ids=lambda p: p.stem)
 def test_example_is_a_valid_app(path):
-    import cornserve_b200.tasklib  # noqa: F401
-    from cornserve_b200.services.gateway.app_manager import load_module_from_source, validate_app_module
-    from cornserve_b200.task.base import discover_unit_tasks
+    import cornserve_tasklib  # noqa: F401
+    from cornserve.services.gateway.app_manager import load_module_from_source, validate_app_module
+    from cornserve.task.base import discover_unit_tasks
 
     module = load_module_from_source(path.read_text(), f"example_{path.stem}")
     classes = validate_app_module(module)

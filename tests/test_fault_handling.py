@@ -18,10 +18,10 @@ import time
 import pytest
 import torch
 
-from cornserve_b200.services.process import free_port, spawn
-from cornserve_b200.services.resource import GPU
-from cornserve_b200.services.task_manager.manager import TaskManager
-from cornserve_b200.tasklib.task.unit.encoder import EncoderTask, Modality
+from cornserve.services.process import free_port, spawn
+from cornserve.services.resource import GPU
+from cornserve.services.task_manager.manager import TaskManager
+from cornserve_tasklib.task.unit.encoder import EncoderTask, Modality
 
 FAKE_EXECUTOR = textwrap.dedent("""
     import sys, time
@@ -140,9 +140,9 @@ def test_kernel_wait_on_a_flag_nobody_sets_returns_an_error_status():
     return, leaving the context usable."""
     import ctypes
 
-    from cornserve_b200 import ops
-    from cornserve_b200.ops import _lib
-    from cornserve_b200.parallel import fused  # noqa: F401  (declares the entry point's signature)
+    from cornserve import ops
+    from cornserve.ops import _lib
+    from cornserve.parallel import fused  # noqa: F401  (declares the entry point's signature)
 
     dev = "cuda"
     lib = _lib.load()

@@ -7,9 +7,9 @@ import json
 import pytest
 import torch
 
-from cornserve_b200.executors.geri.api import StreamGeriResponseChunk
-from cornserve_b200.executors.geri.schema import EngineRequest
-from cornserve_b200.executors.geri.scheduler import Scheduler
+from cornserve.task_executors.geri.api import StreamGeriResponseChunk
+from cornserve.task_executors.geri.schema import EngineRequest
+from cornserve.task_executors.geri.scheduler import Scheduler
 
 
 def _req(i, **params):
@@ -58,11 +58,11 @@ def mock_sidecar(tmp_path, monkeypatch):
 def _client(model_id, modality, mock_dir, dtype, dim, max_batch=2):
     from fastapi.testclient import TestClient
 
-    from cornserve_b200.executors.geri.config import GeriConfig, ModelConfig, ServerConfig, SidecarConfig as GSC
-    from cornserve_b200.executors.geri.engine import Engine
-    from cornserve_b200.executors.geri.router import create_app
-    from cornserve_b200.sidecar.api import Sidecar
-    from cornserve_b200.sidecar.schema import SidecarConfig
+    from cornserve.task_executors.geri.config import GeriConfig, ModelConfig, ServerConfig, SidecarConfig as GSC
+    from cornserve.task_executors.geri.engine import Engine
+    from cornserve.task_executors.geri.router import create_app
+    from cornserve.sidecar.api import Sidecar
+    from cornserve.sidecar.schema import SidecarConfig
 
     cfg = GeriConfig(model=ModelConfig(id=model_id, modality=modality), server=ServerConfig(max_batch_size=max_batch),
                      sidecar=GSC(ranks=[0]))

@@ -13,9 +13,9 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from cornserve_b200.models.qwen_image import (QwenImageDiT, QwenImageDiTConfig, QwenImageModel, QwenImagePipelineConfig,
+from cornserve.models.qwen_image import (QwenImageDiT, QwenImageDiTConfig, QwenImageModel, QwenImagePipelineConfig,
                                               flow_match_sigmas, pack_latents, timestep_embedding, unpack_latents)
-from cornserve_b200.models.qwen_image_vae import QwenImageVAEConfig, QwenImageVAEDecoder
+from cornserve.models.qwen_image_vae import QwenImageVAEConfig, QwenImageVAEDecoder
 
 DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
 
@@ -319,7 +319,7 @@ def _hf_code2wav(seed=0):
 
 @pytest.mark.parametrize("device", DEVICES)
 def test_code2wav_matches_hf(device):
-    from cornserve_b200.models.code2wav import Code2Wav, Code2WavConfig
+    from cornserve.models.code2wav import Code2Wav, Code2WavConfig
 
     hf, hf_cfg = _hf_code2wav()
     cfg = Code2WavConfig.from_hf(hf_cfg.to_dict())

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import test_kv_transfer_gpu as flow
-from cornserve_b200.services.process import free_port
+from cornserve.services.process import free_port
 
 
 @pytest.mark.timeout(600)
@@ -37,8 +37,8 @@ def test_decode_executor_fetches_kv_pages_over_the_network(tmp_path, monkeypatch
 
 def test_engine_level_transfer_and_page_accounting():
     """Two engines in one process: held pages are described, pulled (both source kinds), and returned to the pool."""
-    from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, PrefilledKV, SamplingParams, Sequence
-    from cornserve_b200.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, PrefilledKV, SamplingParams, Sequence
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
 
     cfg = LLMConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
                     intermediate_size=256, vocab_size=512, eos_token_id=511)

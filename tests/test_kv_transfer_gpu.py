@@ -12,7 +12,7 @@ import urllib.request
 import pytest
 import torch
 
-from cornserve_b200.services.process import free_port
+from cornserve.services.process import free_port
 
 pytestmark = pytest.mark.gpu
 
@@ -27,7 +27,7 @@ def _post(url, body, timeout=120):
 
 def _start(role, gpu, port, log):
     env = dict(os.environ, CORNSERVE_LOCAL_GPUS=str(gpu), CORNSERVE_SEED="0", OTEL_SDK_DISABLED="true", CORNSERVE_LOG_LEVEL="WARNING")
-    cmd = [sys.executable, "-m", "cornserve_b200.executors.llm.server", MODEL, "--port", str(port), "--num-kv-pages", "64",
+    cmd = [sys.executable, "-m", "cornserve.task_executors.llm.server", MODEL, "--port", str(port), "--num-kv-pages", "64",
            "--max-model-len", "2048", "--kv-transfer-config", json.dumps({"kv_connector": "P2PConnector", "kv_role": role})]
     return subprocess.Popen(cmd, env=env, stdout=log, stderr=subprocess.STDOUT)
 

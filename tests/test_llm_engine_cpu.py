@@ -5,10 +5,10 @@ import numpy as np
 import pytest
 import torch
 
-from cornserve_b200.executors.llm.block_manager import BlockManager, OutOfPages
-from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, MMItem, SamplingParams, Sequence
-from cornserve_b200.executors.llm.mrope import mrope_positions
-from cornserve_b200.models.qwen_llm import BatchMeta, LLMConfig, QwenLLM
+from cornserve.task_executors.llm.block_manager import BlockManager, OutOfPages
+from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, MMItem, SamplingParams, Sequence
+from cornserve.task_executors.llm.mrope import mrope_positions
+from cornserve.models.qwen_llm import BatchMeta, LLMConfig, QwenLLM
 
 
 def _model():
@@ -119,7 +119,7 @@ def test_sampling_params_from_request_fields():
 
 
 def test_sampler_restatement_respects_cutoffs():
-    from cornserve_b200.ops import reference as ref
+    from cornserve.ops import reference as ref
 
     torch.manual_seed(3)
     V, rows = 400, 600
@@ -146,8 +146,8 @@ def test_sampler_restatement_respects_cutoffs():
 def test_fp8_projections_track_the_full_precision_model():
     """Attention and MLP projections in block-scaled e4m3: hidden states stay close to the fp32 model, the bf16 weights
     are gone, generation still runs; an fp8 checkpoint (weights + ``weight_scale_inv``) is widened on the way in."""
-    from cornserve_b200 import ops
-    from cornserve_b200.models.qwen_llm import dequantize_fp8_checkpoint
+    from cornserve import ops
+    from cornserve.models.qwen_llm import dequantize_fp8_checkpoint
 
     model = _model()
     prompt = np.arange(3, 60, dtype=np.int32)

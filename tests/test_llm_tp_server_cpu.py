@@ -53,7 +53,7 @@ def _free_port() -> int:
 def _serve(model_dir: Path, tp: int):
     port = _free_port()
     env = dict(os.environ, CORNSERVE_DEVICE="cpu", PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
-    proc = subprocess.Popen([sys.executable, "-m", "cornserve_b200.executors.llm.server", str(model_dir), "--port", str(port),
+    proc = subprocess.Popen([sys.executable, "-m", "cornserve.task_executors.llm.server", str(model_dir), "--port", str(port),
                              "--tensor-parallel-size", str(tp), "--num-kv-pages", "16", "--max-model-len", "512",
                              "--max-num-batched-tokens", "64", "--decode-burst", "3"], env=env, cwd=ROOT)
     deadline = time.time() + 180
@@ -105,7 +105,7 @@ def test_untied_lm_head_of_a_checkpoint_is_loaded(tmp_path, monkeypatch):
     """``lm_head.weight`` sits at the top level of the checkpoint, beside ``model.*``; it must reach the model."""
     from safetensors import safe_open
 
-    from cornserve_b200.executors.llm.server import build_engine, parse_args
+    from cornserve.task_executors.llm.server import build_engine, parse_args
 
     monkeypatch.setenv("CORNSERVE_DEVICE", "cpu")
     ckpt = _checkpoint(tmp_path)

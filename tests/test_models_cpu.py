@@ -4,8 +4,8 @@ import numpy as np
 import pytest
 import torch
 
-from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer, window_index
-from cornserve_b200.models.qwen_llm import BatchMeta, LLMConfig, QwenLLM
+from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer, window_index
+from cornserve.models.qwen_llm import BatchMeta, LLMConfig, QwenLLM
 
 
 def _cos(a, b):

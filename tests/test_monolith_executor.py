@@ -15,9 +15,9 @@ def cpu(monkeypatch):
 def test_image_monolith_generates_png(cpu):
     from fastapi.testclient import TestClient
 
-    from cornserve_b200.executors.huggingface.config import HuggingFaceConfig, ModelConfig
-    from cornserve_b200.executors.huggingface.engine import Engine
-    from cornserve_b200.executors.huggingface.router import create_app
+    from cornserve.task_executors.huggingface.config import HuggingFaceConfig, ModelConfig
+    from cornserve.task_executors.huggingface.engine import Engine
+    from cornserve.task_executors.huggingface.router import create_app
 
     cfg = HuggingFaceConfig(model=ModelConfig(id="cornserve-b200/tiny-image-generator", model_type="QWEN_IMAGE",
                                               text_encoder_id="cornserve-b200/tiny-vlm"))
@@ -34,9 +34,9 @@ def test_image_monolith_generates_png(cpu):
 def test_omni_monolith_streams_text(cpu):
     from fastapi.testclient import TestClient
 
-    from cornserve_b200.executors.huggingface.config import HuggingFaceConfig, ModelConfig
-    from cornserve_b200.executors.huggingface.engine import Engine
-    from cornserve_b200.executors.huggingface.router import create_app
+    from cornserve.task_executors.huggingface.config import HuggingFaceConfig, ModelConfig
+    from cornserve.task_executors.huggingface.engine import Engine
+    from cornserve.task_executors.huggingface.router import create_app
 
     cfg = HuggingFaceConfig(model=ModelConfig(id="cornserve-b200/tiny-vlm", model_type="QWEN_OMNI"))
     client = TestClient(create_app(cfg, Engine(cfg, torch.device("cpu"))))
@@ -54,9 +54,9 @@ def test_omni_monolith_speaks(cpu):
     """Thinker, talker and vocoder in one process: text chunks first, then the spoken answer as PCM16."""
     from fastapi.testclient import TestClient
 
-    from cornserve_b200.executors.huggingface.config import HuggingFaceConfig, ModelConfig
-    from cornserve_b200.executors.huggingface.engine import Engine
-    from cornserve_b200.executors.huggingface.router import create_app
+    from cornserve.task_executors.huggingface.config import HuggingFaceConfig, ModelConfig
+    from cornserve.task_executors.huggingface.engine import Engine
+    from cornserve.task_executors.huggingface.router import create_app
 
     cfg = HuggingFaceConfig(model=ModelConfig(id="cornserve-b200/tiny-omni", model_type="QWEN_OMNI"))
     client = TestClient(create_app(cfg, Engine(cfg, torch.device("cpu"))))

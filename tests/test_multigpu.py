@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
 def test_fused_collectives_two_ranks():
-    from cornserve_b200.services.process import free_port
+    from cornserve.services.process import free_port
 
     script = os.path.join(os.path.dirname(__file__), "multigpu_fused.py")
     n = 2

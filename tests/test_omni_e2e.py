@@ -12,9 +12,9 @@ from test_config1_e2e import _serve_app
 
 APP = '''
 from collections.abc import AsyncIterator
-from cornserve_b200.app.base import AppConfig, AppRequest
-from cornserve_b200.tasklib import OpenAIChatCompletionChunk
-from cornserve_b200.tasklib.task.composite.omni import OmniInput, OmniTask
+from cornserve.app.base import AppConfig, AppRequest
+from cornserve_tasklib import OpenAIChatCompletionChunk
+from cornserve_tasklib.task.composite.omni import OmniInput, OmniTask
 
 class Request(AppRequest):
     prompt: str

@@ -11,7 +11,7 @@ import torch
 hf = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
 from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeTalkerConfig  # noqa: E402
 
-from cornserve_b200.models.omni_talker import Talker, TalkerConfig  # noqa: E402
+from cornserve.models.omni_talker import Talker, TalkerConfig  # noqa: E402
 
 SPECIAL = {"im_start": 90, "system": 91, "user": 92, "assistant": 93, "multimodal": (95, 96, 97)}
 
@@ -51,7 +51,7 @@ def test_projections_and_decoder_match_hf():
     with torch.inference_mode():
         out = ref.model(inputs_embeds=emb, use_cache=False)
         want_h, want_logits = out.last_hidden_state[0], ref.codec_head(out.last_hidden_state)[0]
-        from cornserve_b200.models.omni_talker import _embeds_meta
+        from cornserve.models.omni_talker import _embeds_meta
 
         m = _embeds_meta(11, 0, [1], torch.device("cpu"), decode=False)
         m.mm_embeds, m.mm_index = emb[0], torch.arange(11, dtype=torch.int32)
@@ -117,7 +117,7 @@ def test_greedy_generation_matches_a_loop_over_the_hf_modules():
 
 
 def test_thinker_view_round_trip_in_bf16():
-    from cornserve_b200.models.omni_talker import pack_thinker_view, unpack_thinker_view
+    from cornserve.models.omni_talker import pack_thinker_view, unpack_thinker_view
 
     ids = np.asarray([0, 255, 256, 65535, 65536, 151671, 151936 - 1], dtype=np.int64)
     emb = torch.randn(len(ids), 64).bfloat16()
@@ -133,8 +133,8 @@ def test_thinker_view_round_trip_in_bf16():
 def test_talker_on_gpu_matches_cpu():
     """The same talker (bf16 on the GPU through the paged-KV kernels and the fused expert path, fp32 on the CPU): the
     decoder's hidden states of a prefill agree, and generation yields frames of valid codes."""
-    from cornserve_b200.models.omni_talker import _embeds_meta
-    from cornserve_b200.utils.hub import load_config
+    from cornserve.models.omni_talker import _embeds_meta
+    from cornserve.utils.hub import load_config
 
     cfg = TalkerConfig.from_hf(load_config("cornserve-b200/tiny-omni")["talker_config"])
     torch.manual_seed(3)
@@ -153,7 +153,7 @@ def test_talker_on_gpu_matches_cpu():
         pre = (torch.randn(20, cfg.text.hidden_size) * 0.5).to("cuda", torch.bfloat16)
         trail = (torch.randn(5, cfg.text.hidden_size) * 0.5).to("cuda", torch.bfloat16)
         frames = list(gpu.generate(pre, trail, trail[0], max_frames=6, sample=False, min_frames=6))
-    from cornserve_b200 import ops
+    from cornserve import ops
 
     ops.check_error("talker on the GPU")
     assert len(frames) == 6 and all(f.shape == (cfg.num_code_groups,) and int(f.max()) < cfg.predictor.vocab_size for f in frames)

@@ -5,8 +5,8 @@ import math
 import pytest
 import torch
 
-from cornserve_b200 import ops
-from cornserve_b200.ops import reference as ref
+from cornserve import ops
+from cornserve.ops import reference as ref
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -461,9 +461,9 @@ def test_encoder_families_cuda_vs_cpu(model_id, modality, monkeypatch):
     """The same random weights on the CUDA kernels and on the fp32 reference path give the same embeddings."""
     import numpy as np
 
-    from cornserve_b200.executors.eric.config import EricConfig, ModelConfig
-    from cornserve_b200.executors.eric.schema import Batch, Modality
-    from cornserve_b200.executors.eric.worker import Worker
+    from cornserve.task_executors.eric.config import EricConfig, ModelConfig
+    from cornserve.task_executors.eric.schema import Batch, Modality
+    from cornserve.task_executors.eric.worker import Worker
 
     rng = np.random.default_rng(0)
     if modality == "audio":
@@ -513,8 +513,8 @@ def _moe_reference(x, logits, wgu, wd, k, norm):
 @pytest.mark.parametrize("T,E,k,H,I", [(1, 128, 8, 2048, 768), (37, 128, 8, 2048, 768), (700, 32, 4, 512, 256),
                                        (3000, 8, 2, 256, 128), (64, 16, 16, 256, 64)])
 def test_fused_moe_layer_matches_reference(T, E, k, H, I):
-    from cornserve_b200.parallel.moe import FusedMoE
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.parallel.moe import FusedMoE
+    from cornserve.parallel.state import single_group
 
     g = torch.Generator(device="cuda").manual_seed(T + E)
     x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
@@ -533,8 +533,8 @@ def test_fused_moe_layer_matches_reference(T, E, k, H, I):
 
 
 def test_fused_moe_layer_replays_from_a_cuda_graph():
-    from cornserve_b200.parallel.moe import FusedMoE
-    from cornserve_b200.parallel.state import single_group
+    from cornserve.parallel.moe import FusedMoE
+    from cornserve.parallel.state import single_group
 
     T, E, k, H, I = 48, 64, 4, 512, 256
     x = torch.randn(T, H, device="cuda").bfloat16()
@@ -614,8 +614,8 @@ def test_reduce_norm_push_kernel_single_rank(layer_norm):
     land in the operand buffer with their arrival counters."""
     import ctypes
 
-    from cornserve_b200.ops import _lib
-    from cornserve_b200.parallel import fused  # noqa: F401  (declares the entry point's signature)
+    from cornserve.ops import _lib
+    from cornserve.parallel import fused  # noqa: F401  (declares the entry point's signature)
 
     rows, H = 256, 1280
     g = torch.Generator(device="cuda").manual_seed(7)
@@ -650,7 +650,7 @@ def test_packed_attention_windows_match_unpacked():
     """Several short windows sharing one 128-row tile (per-token key bounds) against one window per tile."""
     import numpy as np
 
-    from cornserve_b200.models.qwen2_5_vl import pack_windows, window_index
+    from cornserve.models.qwen2_5_vl import pack_windows, window_index
 
     grid = np.array([[1, 52, 92], [1, 16, 24], [2, 20, 28]])
     _, cu = window_index(grid, 112, 2, 14)

@@ -5,7 +5,7 @@ import os
 import subprocess
 import sys
 
-from cornserve_b200.services.process import free_port
+from cornserve.services.process import free_port
 
 
 def test_parallel_models_two_gloo_ranks():

@@ -6,11 +6,11 @@ import numpy as np
 import pytest
 import torch
 
-from cornserve_b200 import ops
-from cornserve_b200.executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
-from cornserve_b200.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
-from cornserve_b200.models.qwen_llm import LLMConfig, QwenLLM
-from cornserve_b200.pipelines import MLLMPipeline, MLLMRequest
+from cornserve import ops
+from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
+from cornserve.models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+from cornserve.pipelines import MLLMPipeline, MLLMRequest
 
 pytestmark = pytest.mark.gpu
 

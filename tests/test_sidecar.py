@@ -12,7 +12,7 @@ import uuid
 import pytest
 import torch
 
-from cornserve_b200.services.sidecar.allocator import OutOfSlots, SlotAllocator
+from cornserve.services.sidecar.allocator import OutOfSlots, SlotAllocator
 
 
 def _free_port_base(n):
@@ -31,13 +31,13 @@ def cluster():
     os.environ["SIDECAR_NAMESPACE"] = ns
     import importlib
 
-    import cornserve_b200.constants as c
-    import cornserve_b200.sidecar.constants as sc
+    import cornserve.constants as c
+    import cornserve.sidecar.constants as sc
 
     importlib.reload(c)
     importlib.reload(sc)
-    import cornserve_b200.services.sidecar.launch as launch
-    import cornserve_b200.sidecar.api as api
+    import cornserve.services.sidecar.launch as launch
+    import cornserve.sidecar.api as api
 
     importlib.reload(launch)
     importlib.reload(api)
@@ -55,7 +55,7 @@ def cluster():
 
 
 def _client(api, rank, group=None, shape=(-1, 64), dtype=torch.bfloat16, concurrent=False):
-    from cornserve_b200.sidecar.schema import SidecarConfig
+    from cornserve.sidecar.schema import SidecarConfig
 
     return api.Sidecar(SidecarConfig(sidecar_rank=rank, group=group, send_tensor_dtype=dtype, send_tensor_shape=shape,
                                      recv_tensor_dtype=dtype, recv_tensor_shape=shape, concurrent_copy=concurrent))
@@ -177,8 +177,8 @@ def test_dtype_mismatch_is_an_error(cluster):
 def test_mock_sidecar(tmp_path, monkeypatch):
     monkeypatch.setenv("CORNSERVE_MOCK_SIDECAR", "1")
     monkeypatch.setenv("CORNSERVE_MOCK_SIDECAR_DIR", str(tmp_path))
-    from cornserve_b200.sidecar.api import Sidecar
-    from cornserve_b200.sidecar.schema import SidecarConfig
+    from cornserve.sidecar.api import Sidecar
+    from cornserve.sidecar.schema import SidecarConfig
 
     sc = Sidecar(SidecarConfig(sidecar_rank=0, send_tensor_dtype=torch.float32, send_tensor_shape=(-1, 8)))
     t = torch.arange(16.0).view(2, 8)

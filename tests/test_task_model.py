@@ -6,13 +6,13 @@ import json
 
 import pytest
 
-from cornserve_b200.task.base import (Stream, Task, TaskContext, TaskGraphDispatch, TaskInvocation, TaskOutput,
+from cornserve.task.base import (Stream, Task, TaskContext, TaskGraphDispatch, TaskInvocation, TaskOutput,
                                       UnitTaskList, discover_unit_tasks, task_context)
-from cornserve_b200.task.forward import DataForward, ForwardableType, Tensor
-from cornserve_b200.tasklib import (DisaggregatedMLLMTask, EncoderInput, EncoderTask, LLMEmbeddingUnitTask, LLMUnitTask,
+from cornserve.task.forward import DataForward, ForwardableType, Tensor
+from cornserve_tasklib import (DisaggregatedMLLMTask, EncoderInput, EncoderTask, LLMEmbeddingUnitTask, LLMUnitTask,
                                     MLLMEmbeddingTask, MLLMTask, Modality, OmniInput, OmniTask,
                                     OpenAIChatCompletionChunk, OpenAIChatCompletionRequest)
-from cornserve_b200.tasklib.task.unit.generator import AudioGeneratorTask
+from cornserve_tasklib.task.unit.generator import AudioGeneratorTask
 
 MODEL = "Qwen/Qwen2.5-VL-7B-Instruct"
 

@@ -21,7 +21,7 @@ TOO_LARGE = -20
 
 
 def _lib():
-    from cornserve_b200.ops import _lib as loader
+    from cornserve.ops import _lib as loader
 
     lib = ctypes.CDLL(str(loader.lib_path()))  # plain dlopen + dlsym, no Python-side wrapper
     fn = lib.cs_gemm_skinny_noalloc
@@ -53,8 +53,8 @@ def _close(a, b):
 
 
 def test_noalloc_gemm_matches_regular_entry_point_twice():
-    from cornserve_b200 import ops
-    from cornserve_b200.ops.reference import ACTS
+    from cornserve import ops
+    from cornserve.ops.reference import ACTS
 
     lib = _lib()
     dev = "cuda"
