@@ -117,7 +117,8 @@ def _text_of(chunks):
     return "".join((ch["choices"][0]["delta"].get("content") or "") for ch in chunks if ch.get("choices"))
 
 
-def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu", collect=_text_of):
+def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu", collect=_text_of, request_of=None,
+               extra_env=None):
     base = _port_block(16)
     ns = uuid.uuid4().hex[:8]
     monkeypatch.delenv("CORNSERVE_DEVICE", raising=False)
@@ -129,7 +130,7 @@ def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu", collec
         "CORNSERVE_LOG_DIR": str(tmp_path / "logs"), "CORNSERVE_LOG_LEVEL": "WARNING", "CORNSERVE_SEED": "0",
         "OTEL_SDK_DISABLED": "true", "SIDECAR_SHM_SIZE": str(16 << 20),
     }
-    for k, v in env.items():
+    for k, v in {**env, **(extra_env or {})}.items():
         monkeypatch.setenv(k, v)
     import importlib
 
@@ -180,7 +181,8 @@ def _serve_app(tmp_path, monkeypatch, app_source, num_gpus, device="cpu", collec
                 app_id = events[0]["event"]["app_id"]
 
                 async def ask(i):
-                    req = {"request_data": {"prompt": f"describe picture {i}", "image_url": f"synthetic:224x224:{i}"}}
+                    data = request_of(i) if request_of else {"prompt": f"describe picture {i}", "image_url": f"synthetic:224x224:{i}"}
+                    req = {"request_data": data}
                     async with http.post(f"{url}/app/invoke/{app_id}", json=req) as resp:
                         assert resp.status == 200, await resp.text()
                         chunks = [json.loads(l) async for l in resp.content if l.strip()]
