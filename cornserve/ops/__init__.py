@@ -19,6 +19,7 @@ __all__ = [
     "linear", "swiglu_linear", "rms_norm", "layer_norm", "rope_", "mrope_table", "rope_kv_write_",
     "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
     "flow_step_", "pcm16", "decode_advance_", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
+    "count_path", "path_counts",
     "head_norm_rope_", "softmax_rows", "im2col3x3", "im2col1d", "dwconv1d", "to_rgb8", "conv3x3", "conv1d_causal",
     "conv_transpose1d_causal", "bilinear_embed_add_",
 ]
@@ -39,6 +40,19 @@ def reset_launch_count() -> None:
 def _count(n: int = 1) -> None:
     global _launches
     _launches += n
+
+
+_paths: dict[str, int] = {}
+
+
+def count_path(name: str, n: int = 1) -> None:
+    """Count ``n`` launches of a named fused path (e.g. the GEMM + all-reduce + norm tail of a tensor-parallel decoder)."""
+    _paths[name] = _paths.get(name, 0) + n
+
+
+def path_counts() -> dict[str, int]:
+    """Launches per named fused path since the process started (graph replays included by their owners)."""
+    return dict(_paths)
 
 
 def bind_thread(device: torch.device | str) -> None:

@@ -8,7 +8,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 import torch
 
 from ..ops import _lib
-from ..ops import _ptr, _skinny_workspace, _stream, _count  # noqa: F401  (shared helpers)
+from ..ops import _ptr, _skinny_workspace, _stream, _count, count_path  # noqa: F401  (shared helpers)
 from .fabric import Fabric, SymmetricBuffer
 from .state import ParallelGroup
 
@@ -61,6 +61,7 @@ class FusedRowParallel:
         if rc != 0:
             raise RuntimeError(f"cs_gemm_skinny_allreduce failed with code {rc}")
         _count()
+        count_path("llm_gemm_allreduce_norm")
         return h, normed
 
 
@@ -160,6 +161,7 @@ class FusedEncoderTP:
         if rc != 0:
             raise RuntimeError(f"cs_tp_reduce_norm_push failed with code {rc}")
         _count()
+        count_path("encoder_reduce_norm_allgather")
         return x_out
 
     def gemm_gathered(self, src: int, w: torch.Tensor, bias: torch.Tensor | None, *, act: str | None = None,
@@ -179,6 +181,7 @@ class FusedEncoderTP:
         if rc != 0:
             raise RuntimeError(f"cs_gemm_bf16_tp (gathered) failed with code {rc}")
         _count()
+        count_path("encoder_allgather_gemm")
         return out
 
     def gemm_push(self, x: torch.Tensor, w: torch.Tensor) -> None:
@@ -199,6 +202,7 @@ class FusedEncoderTP:
         if rc != 0:
             raise RuntimeError(f"cs_gemm_bf16_tp (push) failed with code {rc}")
         _count()
+        count_path("encoder_gemm_reducescatter")
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -264,6 +268,7 @@ class FusedUlysses:
         if rc != 0:
             raise RuntimeError(f"cs_gemm_bf16_a2a failed with code {rc}")
         _count()
+        count_path("ulysses_qkv_alltoall")
         # every rank makes the same calls: each delivers tiles_m x (3 * own / 128) tiles to every destination
         self.qkv_expected += g.size * (-(-M // 128)) * (3 * self.own // 128)
 
@@ -287,5 +292,6 @@ class FusedUlysses:
         self.o_expected += g.size
         lib.cs_wait_flag(self.o_flag.local.data_ptr(), self.o_expected, _stream())
         _count(2)
+        count_path("ulysses_head_return")
         rows_local = rows_total // g.size
         return self.o.local[: rows_local * self.D].view(rows_local, self.D)

@@ -135,6 +135,7 @@ class FusedMoE:
                                self.epoch.data_ptr(), self.done[3:].data_ptr(), self.out_local.data_ptr(), H, gather, row0,
                                self.out_all.ptrs, self.out_flag.ptrs, st), "cs_moe_combine")
         ops._count(7)
+        ops.count_path("moe_dispatch_gemm_combine")
         if gather:
             chk(lib.cs_moe_wait(self.out_flag.local.data_ptr(), self.epoch.data_ptr(), W, 0, st), "cs_moe_wait")
             ops._count()

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import asyncio
 import os
-import pickle
+import json
 import signal
 from dataclasses import dataclass, field
 from typing import Any
@@ -92,16 +92,16 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
         numel = self.slab_bytes // dtype.itemsize
         if self.device.type == "cuda":
             self.slab = torch.empty(numel, dtype=dtype, device=self.device)
-            from torch.multiprocessing.reductions import reduce_tensor
+            from ...utils.cuda_ipc import export_tensor
 
-            _, args = reduce_tensor(self.slab)
-            blob = pickle.dumps({"kind": "cuda_ipc", "args": args, "dtype": serde.dtype_name(dtype), "numel": numel})
+            blob = json.dumps({"kind": "cuda_ipc", "handle": export_tensor(self.slab), "dtype": serde.dtype_name(dtype),
+                               "numel": numel}).encode()
         else:
             path = shm_slab_path(self.rank)
             with open(path, "wb") as f:
                 f.truncate(self.slab_bytes)
             self.slab = torch.from_file(path, shared=True, size=numel, dtype=dtype)
-            blob = pickle.dumps({"kind": "shm", "path": path, "dtype": serde.dtype_name(dtype), "numel": numel})
+            blob = json.dumps({"kind": "shm", "path": path, "dtype": serde.dtype_name(dtype), "numel": numel}).encode()
         tmp = slab_handle_path(self.rank) + ".tmp"
         with open(tmp, "wb") as f:
             f.write(blob)

@@ -16,7 +16,6 @@ from __future__ import annotations
 import asyncio
 import json
 import os
-import pickle
 import threading
 from concurrent.futures import Future, ThreadPoolExecutor
 from pathlib import Path
@@ -102,17 +101,13 @@ class Sidecar:
             cached = self._slabs.get(rank)
             if cached is not None and serde.dtype_name(cached.dtype) == dtype_name:
                 return cached
-            info = pickle.loads(Path(slab_handle_path(rank)).read_bytes())
+            info = json.loads(Path(slab_handle_path(rank)).read_bytes())
             if info["kind"] == "cuda_ipc":
-                import inspect
-
-                from torch.multiprocessing.reductions import rebuild_cuda_tensor
+                from ..utils.cuda_ipc import import_tensor
 
                 # Open the handle with THIS process's GPU current (the open enables peer access to the slab's GPU as
                 # needed): kernels of this GPU can then read the slab in place, over NVLink when it lives elsewhere.
-                args = list(info["args"])
-                args[list(inspect.signature(rebuild_cuda_tensor).parameters).index("storage_device")] = torch.cuda.current_device()
-                slab = rebuild_cuda_tensor(*args)
+                slab = import_tensor(info["handle"], torch.cuda.current_device())
             else:
                 slab = torch.from_file(info["path"], shared=True, size=info["numel"], dtype=serde.dtype_from_name(info["dtype"]))
             self._slabs[rank] = slab

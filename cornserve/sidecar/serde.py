@@ -12,7 +12,6 @@ Three payload kinds travel in the ``data`` bytes of Send / PrepareReceive / Rece
 
 from __future__ import annotations
 
-import pickle
 from typing import Any
 
 import msgpack
@@ -44,11 +43,10 @@ def encode_inline_tensor(t: torch.Tensor) -> bytes:
 
 def encode_ipc_tensor(t: torch.Tensor) -> bytes:
     """The tensor must stay alive until the receiver has rebuilt (and copied) it."""
-    from torch.multiprocessing.reductions import reduce_tensor
+    from ..utils.cuda_ipc import export_tensor
 
-    _, args = reduce_tensor(t.detach())
     return msgpack.packb({"kind": "ipc", "dtype": dtype_name(t.dtype), "shape": list(t.shape),
-                          "args": pickle.dumps(args)}, use_bin_type=True)
+                          "handle": export_tensor(t)}, use_bin_type=True)
 
 
 def encode_slab_ref(rank: int, offset: int, numel: int, dtype: torch.dtype, shape: list[int]) -> bytes:
@@ -68,6 +66,6 @@ def tensor_from_inline(msg: dict[str, Any]) -> torch.Tensor:
 
 
 def tensor_from_ipc(msg: dict[str, Any]) -> torch.Tensor:
-    from torch.multiprocessing.reductions import rebuild_cuda_tensor
+    from ..utils.cuda_ipc import import_tensor
 
-    return rebuild_cuda_tensor(*pickle.loads(msg["args"]))
+    return import_tensor(msg["handle"])

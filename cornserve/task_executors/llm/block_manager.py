@@ -24,6 +24,11 @@ class BlockManager:
     def num_free(self) -> int:
         return len(self._free)
 
+    @property
+    def capacity(self) -> int:
+        """Pages a single sequence could ever own (page 0 is the scratch page)."""
+        return self.num_pages - 1
+
     def pages_of(self, seq_id: str) -> list[int]:
         return self._owned.get(seq_id, [])
 

@@ -168,6 +168,7 @@ class _DecodeState:
         self.sampling = False
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_replay = 0
+        self.paths_per_replay: dict[str, int] = {}
 
     def sampler(self):
         return (self.temperature, self.top_p, self.top_k, self.seed, self.draws) if self.sampling else None
@@ -195,7 +196,8 @@ class LLMEngine:
         self._decode_states: dict[int, _DecodeState] = {}
         self._copy_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
         self.held: dict[str, HeldKV] = {}
-        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "kv_pages_pulled": 0}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "kv_pages_pulled": 0, "prefill_steps": 0,
+                      "decode_bursts": 0, "prefill_ms": 0.0, "decode_ms": 0.0, "decode_host_ms": 0.0}
 
     # ---------------------------------------------------------------------------------------------
     # requests
@@ -203,6 +205,12 @@ class LLMEngine:
     def add_request(self, seq: Sequence) -> None:
         if seq.params.samples and seq.params.seed is None:
             seq.params.seed = random.getrandbits(62)
+        # a sequence is admitted only when its whole lifetime fits in free pages: one that needs more pages than the
+        # pool has would wait at the head of the queue for ever and block everything behind it
+        need = -(-(seq.prompt_len + seq.params.max_tokens + 1) // PAGE_SIZE)
+        if need > self.blocks.capacity:
+            raise ValueError(f"request needs {need} KV pages (prompt {seq.prompt_len} + {seq.params.max_tokens} new tokens) "
+                             f"but the cache holds {self.blocks.capacity}")
         if seq.prefilled is not None:
             if seq.prompt_len + seq.params.max_tokens > self.cfg.max_model_len:
                 raise ValueError("request exceeds max_model_len")
@@ -245,9 +253,17 @@ class LLMEngine:
             return outs
         batch = self._schedule_prefill()
         if batch:
-            return self._run_prefill(batch)
+            t0 = time.perf_counter()
+            outs = self._run_prefill(batch)
+            self.stats["prefill_steps"] += 1
+            self.stats["prefill_ms"] += (time.perf_counter() - t0) * 1e3
+            return outs
         if self.running:
-            return self._run_decode_burst()
+            t0 = time.perf_counter()
+            outs = self._run_decode_burst()
+            self.stats["decode_bursts"] += 1
+            self.stats["decode_ms"] += (time.perf_counter() - t0) * 1e3
+            return outs
         return []
 
     def _admit_prefilled(self) -> list[StepOutput]:
@@ -264,11 +280,18 @@ class LLMEngine:
             n = -(-s.prompt_len // PAGE_SIZE)
             pages = self.blocks.ensure(s.seq_id, total)[:n]
             dst = self.kv_backing
-            if pf.raw is not None:
-                dst[:, torch.as_tensor(pages, device=self.device)] = pf.raw[:, :n].to(self.device, dst.dtype)
-            else:
-                i32 = lambda a: self._to_dev(np.asarray(a, dtype=np.int32))  # noqa: E731
-                ops.kv_copy_pages(dst, pf.src_cache, i32(pf.src_pages[:n]), i32(pages))
+            try:
+                if pf.raw is not None:
+                    dst[:, torch.as_tensor(pages, device=self.device)] = pf.raw[:, :n].to(self.device, dst.dtype)
+                else:
+                    i32 = lambda a: self._to_dev(np.asarray(a, dtype=np.int32))  # noqa: E731
+                    ops.kv_copy_pages(dst, pf.src_cache, i32(pf.src_pages[:n]), i32(pages))
+            except Exception as e:  # noqa: BLE001  (a bad transfer fails this request, not the engine)
+                self.blocks.free(s.seq_id)
+                s.prefilled = None
+                s.status = SeqStatus.FINISHED
+                outs.append(StepOutput(s.seq_id, [], True, f"error: KV transfer failed: {e}"))
+                continue
             self.stats["kv_pages_pulled"] += n
             s.prefilled = None  # drops the reference to the producer's mapping / the fetched bytes
             s.num_computed = s.prompt_len
@@ -416,6 +439,7 @@ class LLMEngine:
         seqs = [s for s in self.running if s.status is SeqStatus.RUNNING]
         if not seqs:
             return []
+        t_host = time.perf_counter()
         burst = max(1, min(self.cfg.decode_burst, min(s.params.max_tokens - len(s.output_ids) for s in seqs)))
         n = len(seqs)
         B = self._bucket(n) if (self.on_gpu and self.cfg.use_cuda_graph) else n
@@ -453,6 +477,7 @@ class LLMEngine:
         with torch.inference_mode():
             for _ in range(burst):
                 self._decode_once(st)
+        self.stats["decode_host_ms"] += (time.perf_counter() - t_host) * 1e3   # batch state + launches, before the wait
         log = st.out_log[:burst].cpu().numpy()  # one sync per burst
         self.stats["decode_tokens"] += burst * n
         outs = []
@@ -483,15 +508,19 @@ class LLMEngine:
             body()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            before = ops.kernel_launches()
+            before, paths_before = ops.kernel_launches(), ops.path_counts()
             with torch.cuda.graph(g):
                 body()
             st.launches_per_replay = ops.kernel_launches() - before
+            st.paths_per_replay = {k: v - paths_before.get(k, 0) for k, v in ops.path_counts().items()
+                                   if v != paths_before.get(k, 0)}
             st.graph = g
             for t, v in zip((st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter, st.draws), snap):
                 t.copy_(v)
         st.graph.replay()
         ops._count(st.launches_per_replay)
+        for k, v in st.paths_per_replay.items():
+            ops.count_path(k, v)
 
     # ---------------------------------------------------------------------------------------------
     # helpers

@@ -32,7 +32,6 @@ import concurrent.futures
 import io
 import json
 import os
-import pickle
 import random
 import re
 import sys
@@ -175,8 +174,15 @@ class AsyncLLM:
                         self.engine.add_request(s)
                     except Exception as e:
                         self._deliver(StepOutput(s.seq_id, [], True, f"error: {e}"))
-                for out in self.engine.step():
+                outs = self.engine.step()
+                for out in outs:
                     self._deliver(out)
+                if not outs and not new and not self.engine.running:
+                    # work is queued but nothing could be scheduled (pages held for a remote reader, say): wait for
+                    # a new request, a call or the next poll instead of spinning
+                    with self.cv:
+                        if not self.inbox and not self.calls:
+                            self.cv.wait(timeout=0.005)
         except Exception:
             logger.exception("LLM engine thread died")
         finally:
@@ -382,10 +388,9 @@ class LLMServer:
             info: dict[str, Any] = {"engine_id": self.engine_id, "base_url": f"http://{self.args.host}:{self.args.port}",
                                     "hostname": socket.gethostname(), **eng.kv_geometry()}
             if eng.on_gpu:
-                from torch.multiprocessing.reductions import reduce_tensor
+                from ...utils.cuda_ipc import export_tensor
 
-                _, ipc_args = reduce_tensor(eng.kv_backing)
-                info["ipc"] = base64.b64encode(pickle.dumps(ipc_args)).decode()
+                info["ipc"] = export_tensor(eng.kv_backing)   # plain fields: the consumer rebuilds them with type checks
                 info["gpu_uuid"] = str(torch.cuda.get_device_properties(eng.device).uuid)
             self._kv_export = info
         return self._kv_export
@@ -405,16 +410,14 @@ class LLMServer:
                        if str(torch.cuda.get_device_properties(i).uuid) == params.get("gpu_uuid")), None)
         if theirs is None or (theirs != mine and not torch.cuda.can_device_access_peer(mine, theirs)):
             return None
-        import inspect
-
-        from torch.multiprocessing.reductions import rebuild_cuda_tensor
+        from ...utils.cuda_ipc import import_tensor
 
         try:
             # The handle is opened with THIS executor's GPU current (the open then enables peer access between the two
             # GPUs as needed), so the mapping is addressable by kernels of this GPU; the tensor is labelled accordingly.
-            args = list(pickle.loads(base64.b64decode(params["ipc"])))  # from an executor of the same deployment
-            args[list(inspect.signature(rebuild_cuda_tensor).parameters).index("storage_device")] = mine
-            mapped = rebuild_cuda_tensor(*args)
+            mapped = import_tensor(params["ipc"], mine)
+            if list(mapped.shape) != [int(v) for v in params["shape"]]:
+                raise ValueError("the exported tensor does not have the advertised cache shape")
             # reach it once through the driver's copy path (which reports an error instead of faulting) before any
             # kernel reads it
             probe = torch.empty(8, dtype=mapped.dtype, device=self.engine.device)
@@ -469,7 +472,24 @@ class LLMServer:
                 recv_ids.extend(f"{hit['id']}:{i}" for i in range(k))
         return recv_ids
 
+    def _check_transfer(self, params: dict[str, Any]) -> None:
+        """The producer's cache must have this engine's geometry (layers, heads, page size, head width, dtype): the
+        copy kernel and the page assignment assume it, and a mismatch would otherwise surface inside an engine step."""
+        mine = self.engine.kv_geometry()
+        shape = [int(v) for v in params.get("shape") or []]
+        if len(shape) != len(mine["shape"]) or shape[0] != mine["shape"][0] or shape[2:] != mine["shape"][2:]:
+            raise ValueError(f"KV transfer from a cache of shape {shape}; this executor's cache is {mine['shape']}")
+        if str(params.get("dtype")) != mine["dtype"]:
+            raise ValueError(f"KV transfer of dtype {params.get('dtype')}; this executor's cache is {mine['dtype']}")
+        pages = params.get("pages")
+        if not isinstance(pages, list) or not pages or any(int(p) < 0 or int(p) >= shape[1] for p in pages):
+            raise ValueError("KV transfer names pages outside the producer's cache")
+        for k in ("first_token", "next_pos", "num_tokens", "request_id"):
+            if k not in params:
+                raise ValueError(f"KV transfer parameters lack {k!r}")
+
     async def build_prefilled_sequence(self, body: dict[str, Any], params: dict[str, Any]) -> tuple[Sequence, list[str]]:
+        self._check_transfer(params)
         src = self._map_producer_cache(params)
         raw = None if src is not None else await self._fetch_pages(params)
         pf = PrefilledKV(int(params["first_token"]), int(params["next_pos"]), [int(p) for p in params["pages"]], src_cache=src, raw=raw)

@@ -63,3 +63,45 @@ def test_engine_level_transfer_and_page_accounting():
     # pages nobody fetched are freed after the hold time
     P.generate([Sequence("s9", prompts[0], SamplingParams(1, True), hold_kv=True)])
     assert P.expire_held(3600) == [] and P.expire_held(0.0) == ["s9"] and P.blocks.num_free == free0
+
+
+def test_transfer_with_foreign_geometry_is_refused_before_the_engine_sees_it():
+    """KV-transfer parameters come from the network: a cache shape, dtype or page list that does not fit this
+    executor's cache must be a client error, never an exception inside an engine step."""
+    import types
+
+    import pytest
+
+    from cornserve.task_executors.llm.server import LLMServer
+
+    srv = LLMServer.__new__(LLMServer)
+    srv.engine = types.SimpleNamespace(kv_geometry=lambda: {"shape": [2, 16, 2, 1, 128, 32], "dtype": "float32"})
+    good = {"shape": [2, 64, 2, 1, 128, 32], "dtype": "float32", "pages": [3, 4], "first_token": 1, "next_pos": 9,
+            "num_tokens": 200, "request_id": "r"}
+    srv._check_transfer(good)   # another pool size is fine
+    for bad in ({"shape": [4, 64, 2, 1, 128, 32]}, {"shape": [2, 64, 2, 2, 128, 32]}, {"dtype": "bfloat16"},
+                {"pages": [3, 64]}, {"pages": []}, {"pages": "3"}):
+        with pytest.raises(ValueError):
+            srv._check_transfer({**good, **bad})
+    with pytest.raises(ValueError):
+        srv._check_transfer({k: v for k, v in good.items() if k != "first_token"})
+
+
+def test_ipc_description_is_plain_data_and_type_checked():
+    import json
+
+    import pytest
+
+    from cornserve.utils.cuda_ipc import import_tensor
+
+    desc = {"tensor_size": [4, 4], "tensor_stride": [4, 1], "tensor_offset": 0, "storage_cls": "UntypedStorage",
+            "dtype": "float32", "storage_device": 0, "storage_handle": "", "storage_size_bytes": 64,
+            "storage_offset_bytes": 0, "ref_counter_handle": "", "ref_counter_offset": 0, "event_handle": "",
+            "event_sync_required": False}
+    json.dumps(desc)
+    for bad in ({"dtype": "os.system"}, {"storage_cls": "Popen"}, {"tensor_size": [4, 5]}, {"tensor_stride": [4]},
+                {"tensor_offset": -1}):
+        with pytest.raises((ValueError, TypeError)):
+            import_tensor({**desc, **bad})
+    with pytest.raises(TypeError):
+        import_tensor("gASV...")

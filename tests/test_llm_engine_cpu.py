@@ -190,3 +190,20 @@ def test_block_manager():
         pass
     bm.free("a")
     assert bm.num_free == 4
+
+
+def test_request_larger_than_the_page_pool_is_refused_not_queued():
+    """A prompt that can never fit must fail at ``add_request``; queued, it would block every later request."""
+    import numpy as np
+    import pytest
+
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, SamplingParams, Sequence
+
+    cfg = LLMConfig(hidden_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=32,
+                    intermediate_size=64, vocab_size=128, mrope_section=None)
+    eng = LLMEngine(QwenLLM(cfg).float().eval(), EngineConfig(num_pages=3, use_cuda_graph=False, max_model_len=4096))
+    with pytest.raises(ValueError, match="KV pages"):
+        eng.add_request(Sequence("big", np.arange(300, dtype=np.int32) % 100, SamplingParams(max_tokens=8, ignore_eos=True)))
+    ok = Sequence("small", np.arange(20, dtype=np.int32), SamplingParams(max_tokens=4, ignore_eos=True))
+    assert len(eng.generate([ok])["small"]) == 4
