@@ -26,6 +26,7 @@ class LocalCluster:
         self.tm_kwargs = tm_manager_kwargs or {}
         self.slab = sidecar_slab_bytes
         self._closers: list = []
+        self.rm = None
         self.url = f"http://127.0.0.1:{self.gateway_port}"
 
     async def _serve(self, app, port: int):
@@ -52,7 +53,11 @@ class LocalCluster:
 
         cpu = self.cpu or not torch.cuda.is_available()
         n = self.num_gpus or (torch.cuda.device_count() if not cpu else 2)
-        store = LocalStore(self.store_path) if self.store_path else LocalStore()
+        # one store for the whole deployment: the path given, else $CORNSERVE_STORE_PATH (what default_store() opens
+        # in every other process of the deployment), else the per-user state directory
+        import os
+
+        store = LocalStore(self.store_path or os.environ.get("CORNSERVE_STORE_PATH"))
         registry = TaskRegistry(store)
         dispatcher = TaskDispatcher(registry)
         td_grpc_addr = f"127.0.0.1:{free_port()}"
@@ -64,8 +69,16 @@ class LocalCluster:
                                         dispatcher_urls=[td_grpc_addr], tm_manager_kwargs=self.tm_kwargs, **kw)
         rm_addr = f"127.0.0.1:{free_port()}"
         rm_server = await start_rm(rm, rm_addr)
-        gw_server, gw_task = await self._serve(create_app(rm_addr, f"http://127.0.0.1:{td_port}", [td_grpc_addr], registry),
-                                               self.gateway_port)
+        gw_app = create_app(rm_addr, f"http://127.0.0.1:{td_port}", [td_grpc_addr], registry)
+        self.rm = rm
+
+        @gw_app.get("/cluster/executors")
+        async def cluster_executors():
+            """What runs where: one entry per task executor with its URL, GPUs and health (a view for operators and
+            benchmarks; the reference offers ``kubectl get pods`` for this)."""
+            return self.executors()
+
+        gw_server, gw_task = await self._serve(gw_app, self.gateway_port)
         logger.info("Control plane is up: gateway %s, %d %s", self.url, n, "CPU ranks" if cpu else "GPUs")
 
         async def close():
@@ -81,6 +94,19 @@ class LocalCluster:
 
         self._closers.append(close)
         return self
+
+    def executors(self) -> list[dict]:
+        out, seen = [], set()
+        for name, st in self.rm.task_managers.items():
+            tm = getattr(getattr(st, "servicer", None), "manager", None)
+            if tm is None or id(tm) in seen:
+                continue
+            seen.add(id(tm))
+            for d in tm.executors.values():
+                out.append({"task": name, "task_class": type(st.task).__name__, "executor_id": d.executor_id, "url": d.url,
+                            "gpus": d.sidecar_ranks, "healthy": d.healthy,
+                            "pid": getattr(getattr(d.process, "popen", None), "pid", None)})
+        return out
 
     async def stop(self) -> None:
         for c in reversed(self._closers):

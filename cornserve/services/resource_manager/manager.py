@@ -131,7 +131,8 @@ class ResourceManager:
         st = TaskManagerState(tm_id, task_instance_name, task, f"127.0.0.1:{port}", gpus)
         try:
             if self.tm_in_process:
-                st.servicer = TaskManagerServicer(self.registry, self.tm_manager_kwargs)
+                # in-process task managers read profiles from the same store as this resource manager
+                st.servicer = TaskManagerServicer(self.registry, {"profile_manager": self.profiles, **self.tm_manager_kwargs})
                 st.server = await start_server(port, st.servicer)
             else:
                 st.process = spawn(tm_id, [sys.executable, "-m", "cornserve.services.task_manager.entrypoint",

@@ -8,6 +8,7 @@ from __future__ import annotations
 import asyncio
 import queue
 import threading
+import time
 import traceback
 
 from ... import ops
@@ -16,7 +17,7 @@ from ...parallel.state import ParallelGroup
 from .config import EricConfig
 from .scheduler import Scheduler
 from .schema import EngineRequest, EngineResponse, Status
-from .worker import Worker
+from .worker import Worker, broadcast_batch
 
 logger = get_logger(__name__)
 
@@ -52,6 +53,15 @@ class Engine:
     # -- engine thread ---------------------------------------------------------------------------------------
     def _call_workers(self, method: str, *args) -> None:
         if self.group is not None and self.group.size > 1:
+            if method == "execute_model":
+                # the followers get the small part of the batch as an object and the inputs by a device broadcast
+                # from this rank's staged copy (the reference pickles whole batches through a shared-memory ring)
+                t0 = time.perf_counter()
+                staged = self.worker.stage(args[0])
+                broadcast_batch(self.group, staged, self.worker.device)
+                self.worker.stats["broadcast_ms"] += (time.perf_counter() - t0) * 1e3
+                self.worker.execute_model(staged)
+                return
             self.group.broadcast_object((method, args), src=0)
         getattr(self.worker, method)(*args)
 

@@ -55,6 +55,15 @@ def create_app(config: EricConfig, engine: Engine) -> FastAPI:
             return EmbeddingResponse(status=Status.SUCCESS)
         return EmbeddingResponse(status=Status.ERROR, error_message=resp.error_message)
 
+    @app.get("/stats")
+    async def stats():
+        """Counters of this executor since it started (rank 0 of a tensor-parallel group; the other ranks launch the
+        same kernels): this library's kernel launches, launches per fused path, batches, host-to-device bytes."""
+        from ... import ops
+
+        return {"executor": "eric", "tp_size": config.model.tp_size, "kernel_launches": ops.kernel_launches(),
+                "paths": ops.path_counts(), **engine.worker.stats}
+
     @app.post("/profile/start")
     async def profile_start(out_dir: str = "/tmp/cornserve_profile"):
         engine.start_profile(out_dir)
@@ -65,5 +74,8 @@ def create_app(config: EricConfig, engine: Engine) -> FastAPI:
         engine.stop_profile()
         return {"status": "stopped"}
 
+    from ..device_timer import add_timer_routes
+
+    add_timer_routes(app, engine.worker.device)
     app.state.processor = processor
     return app

@@ -9,6 +9,7 @@ separate processes that replay the batches rank 0 broadcasts.
 from __future__ import annotations
 
 import os
+import time
 from pathlib import Path
 
 import torch
@@ -79,7 +80,36 @@ class Worker:
                 send_tensor_dtype=self.model.dtype, send_tensor_shape=(-1, *self.model.chunk_shape[1:])))
         self.dump_dir = os.environ.get("CORNSERVE_TEST_DUMP_TENSOR_DIR")
         self.profiler = None
+        # raw inputs go through one page-locked staging buffer, so the copy to the GPU is a real asynchronous DMA
+        self._stage: torch.Tensor | None = None
+        self._stage_used = 0
+        self.stats = {"batches": 0, "items": 0, "h2d_bytes": 0, "busy_ms": 0.0, "broadcast_ms": 0.0}
         logger.info("Worker %d ready on %s (%s)", tp_rank, self.device, model_type)
+
+    def _to_device(self, t: torch.Tensor) -> torch.Tensor:
+        if t.device == self.device or self.device.type != "cuda":
+            return t.to(self.device)
+        n = t.numel() * t.element_size()
+        cap = int(os.environ.get("CORNSERVE_ERIC_STAGING_BYTES", str(256 << 20)))
+        if self._stage is None:
+            self._stage = torch.empty(cap, dtype=torch.uint8, pin_memory=True)
+        self.stats["h2d_bytes"] += n
+        if self._stage_used + n > cap:
+            return t.contiguous().to(self.device)   # larger than the staging buffer: the pageable path
+        lo = -(-self._stage_used // 256) * 256
+        if lo + n > cap:
+            return t.contiguous().to(self.device)
+        view = self._stage[lo: lo + n].view(t.dtype).view(t.shape)
+        view.copy_(t)
+        self._stage_used = lo + n
+        return view.to(self.device, non_blocking=True)
+
+    def stage(self, batch: Batch) -> Batch:
+        """The batch with every host tensor copied to this worker's device (through page-locked memory)."""
+        self._stage_used = 0
+        data = {k: [self._to_device(v) if isinstance(v, torch.Tensor) else v for v in vs] for k, vs in batch.data.items()}
+        return Batch(batch.modality, batch.adapter_name, batch.request_ids, batch.data_ids, batch.receiver_ranks, data,
+                     batch.trace_carriers)
 
     def prepare(self, batch: Batch) -> dict[str, list]:
         """Decoded uint8 pixels / float waveforms -> model inputs on the device, by the model's preprocessing recipe."""
@@ -131,8 +161,9 @@ class Worker:
     @torch.inference_mode()
     def execute_model(self, batch: Batch) -> None:
         ctx = extract(batch.trace_carriers[0]) if batch.trace_carriers else None
+        t0 = time.perf_counter()
         with tracer.start_as_current_span("Worker.execute_model", context=ctx):
-            outputs = self.model(batch.modality.value, batch.adapter_name, self.prepare(batch))
+            outputs = self.model(batch.modality.value, batch.adapter_name, self.prepare(self.stage(batch)))
             if self.profiler is not None:
                 self.profiler.step()
             for out, data_id, ranks in zip(outputs, batch.data_ids, batch.receiver_ranks, strict=True):
@@ -144,6 +175,11 @@ class Worker:
             if self.sidecar is not None:
                 # outputs are shared with the sidecar by reference: they must outlive the hand-off
                 self.sidecar.flush()
+            elif self.device.type == "cuda":
+                torch.cuda.current_stream(self.device).synchronize()   # the staging buffer is reused by the next batch
+        self.stats["batches"] += 1
+        self.stats["items"] += len(batch.data_ids)
+        self.stats["busy_ms"] += (time.perf_counter() - t0) * 1e3
 
     def start_profile(self, out_dir: str) -> None:
         acts = [torch.profiler.ProfilerActivity.CPU]
@@ -165,6 +201,52 @@ class Worker:
             self.sidecar.shutdown_sync()
 
 
+_TENSOR = "__tensor__"
+
+
+def split_batch(batch: Batch) -> tuple[Batch, list[torch.Tensor]]:
+    """A copy of ``batch`` whose tensors are replaced by (marker, index, shape, dtype) plus the tensors themselves: the
+    small part travels as a pickled object, the tensors by a device broadcast."""
+    tensors: list[torch.Tensor] = []
+
+    def strip(v):
+        if isinstance(v, torch.Tensor):
+            tensors.append(v)
+            return (_TENSOR, len(tensors) - 1, tuple(v.shape), str(v.dtype).replace("torch.", ""))
+        return v
+
+    data = {k: [strip(v) for v in vs] for k, vs in batch.data.items()}
+    return Batch(batch.modality, batch.adapter_name, batch.request_ids, batch.data_ids, batch.receiver_ranks, data,
+                 batch.trace_carriers), tensors
+
+
+def join_batch(header: Batch, tensors: list[torch.Tensor]) -> Batch:
+    fill = lambda v: tensors[v[1]] if isinstance(v, tuple) and len(v) == 4 and v[0] == _TENSOR else v  # noqa: E731
+    header.data = {k: [fill(v) for v in vs] for k, vs in header.data.items()}
+    return header
+
+
+def broadcast_batch(group: ParallelGroup, batch: Batch | None, device: torch.device) -> Batch:
+    """Rank 0 passes the staged batch (tensors on its device); the others pass ``None`` and get a batch whose tensors
+    sit on their own device.  One small object broadcast + one tensor broadcast per input."""
+    import torch.distributed as dist
+
+    if group.rank == 0:
+        header, tensors = split_batch(batch)
+        group.broadcast_object(("execute_model", header), src=0)
+    else:
+        header = batch   # the follower loop already received the header
+        tensors = []
+        for vs in header.data.values():
+            for v in vs:
+                if isinstance(v, tuple) and len(v) == 4 and v[0] == _TENSOR:
+                    tensors.append(torch.empty(v[2], dtype=getattr(torch, v[3]), device=device))
+    for t in tensors:
+        dist.broadcast(t if t.is_contiguous() else t.contiguous(), src=dist.get_global_rank(group.group, 0) if group.group else 0,
+                       group=group.group)
+    return batch if group.rank == 0 else join_batch(header, tensors)
+
+
 def tp_worker_main(config_json: str, tp_rank: int, tp_size: int, master_port: int) -> None:
     """Entry of a TP worker process (rank > 0): replay what rank 0 broadcasts until told to stop."""
     config = EricConfig.model_validate_json(config_json)
@@ -177,5 +259,8 @@ def tp_worker_main(config_json: str, tp_rank: int, tp_size: int, master_port: in
         method, arg = group.broadcast_object(None, src=0)
         if method == "shutdown":
             break
+        if method == "execute_model":
+            worker.execute_model(broadcast_batch(group, arg, worker.device))
+            continue
         getattr(worker, method)(*arg)
     worker.shutdown()

@@ -492,6 +492,24 @@ class LLMEngine:
         self._reap()
         return outs
 
+    def capture_decode_graphs(self) -> int:
+        """Capture the decode graph of every batch-size bucket up to ``max_num_seqs`` now, with all rows inactive
+        (they read the scratch page), so that no request pays for a capture later.  Every rank of a tensor-parallel
+        group calls this at the same point of its start-up.  Returns the number of graphs captured."""
+        if not (self.on_gpu and self.cfg.use_cuda_graph):
+            return 0
+        n = 0
+        for B in self.cfg.graph_batch_sizes:
+            if B > self._bucket(self.cfg.max_num_seqs) or B in self._decode_states:
+                continue
+            st = self._decode_states[B] = _DecodeState(B, self.max_blocks, self.cfg.decode_burst, self.device)
+            with torch.inference_mode():
+                self._decode_once(st)
+            st.step_counter.zero_()
+            n += 1
+        torch.cuda.synchronize(self.device)
+        return n
+
     def _decode_once(self, st: _DecodeState) -> None:
         def body():
             tok, _ = self.model(st.meta(), self.kv_caches, sampler=st.sampler())

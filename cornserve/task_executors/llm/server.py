@@ -145,12 +145,15 @@ class AsyncLLM:
 
     def _run(self) -> None:
         ops.bind_thread(self.engine.device)  # a new thread starts on CUDA device 0
+        from .tp import IDLE_BEAT_S
+
+        last_beat = time.monotonic()
         try:
             while self.alive:
                 with self.cv:
                     while self.alive and not self.inbox and not self.calls and not self.engine.has_work():
                         self.cv.wait(timeout=0.5)
-                        if self.engine.held:
+                        if self.engine.held or (self.tp is not None and time.monotonic() - last_beat > IDLE_BEAT_S):
                             break
                     new, self.inbox = self.inbox, []
                     calls, self.calls = self.calls, []
@@ -164,7 +167,13 @@ class AsyncLLM:
                         logger.warning("Freed the KV pages of %s: nobody fetched them", sid)
                 if self.tp is not None:
                     if not new and not self.engine.has_work():
-                        continue   # nothing to run: the followers are not woken either
+                        # nothing to run: the followers only get a keep-alive now and then, so that their wait on the
+                        # control group can have a finite timeout
+                        if time.monotonic() - last_beat > IDLE_BEAT_S:
+                            self.tp.publish([], beat=True)
+                            last_beat = time.monotonic()
+                        continue
+                    last_beat = time.monotonic()
                     for s in new:
                         if s.params.samples and s.params.seed is None:
                             s.params.seed = random.getrandbits(62)   # drawn here so that every rank gets the same stream
@@ -236,7 +245,13 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
     ecfg = EngineConfig(num_pages=int(pages), max_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
                         decode_burst=args.decode_burst, max_model_len=args.max_model_len,
                         use_cuda_graph=device.type == "cuda")
-    return LLMEngine(model, ecfg), hf_cfg
+    engine = LLMEngine(model, ecfg)
+    if os.environ.get("CORNSERVE_LLM_PRECAPTURE", "1") == "1":
+        t0 = time.perf_counter()
+        n = engine.capture_decode_graphs()
+        if n:
+            logger.info("captured %d decode graphs in %.1f s", n, time.perf_counter() - t0)
+    return engine, hf_cfg
 
 
 class LLMServer:
@@ -644,14 +659,18 @@ class LLMServer:
 
         if body.get("stream"):
             async def sse():
-                yield chunk({"role": "assistant", "content": ""})
-                n = 0
+                # The role chunk goes out with the first generated token, so the arrival of the first chunk is the time
+                # to first token; after that one chunk per engine output (a decode burst), even when its bytes do not yet
+                # form a printable character, so clients see every step.
+                n, first = 0, True
                 async for delta, out, n in consume():
                     if out.finish_reason and out.finish_reason.startswith("error"):
                         yield f"data: {json.dumps({'error': out.finish_reason})}\n\n"
                         break
-                    if delta or out.finished:
-                        yield chunk({"content": delta} if delta else {}, out.finish_reason if out.finished else None)
+                    if first:
+                        first = False
+                        yield chunk({"role": "assistant", "content": ""})
+                    yield chunk({"content": delta}, out.finish_reason if out.finished else None)
                 if include_usage:
                     yield chunk({}, usage={"prompt_tokens": seq.prompt_len, "completion_tokens": n,
                                            "total_tokens": seq.prompt_len + n})
@@ -679,6 +698,17 @@ class LLMServer:
         async def health():
             return Response(status_code=200 if self.llm.alive else 503)
 
+        @app.get("/stats")
+        async def stats():
+            """Counters of this executor since it started (rank 0 of a tensor-parallel group; the other ranks launch
+            the same kernels): this library's kernel launches, launches per fused path, engine steps and their time."""
+            eng = self.engine
+            return {"executor": "llm", "tp_size": int(self.args.tensor_parallel_size), "kernel_launches": ops.kernel_launches(),
+                    "paths": ops.path_counts(), **eng.stats, "running": len(eng.running), "waiting": len(eng.waiting),
+                    "kv_pages": eng.cfg.num_pages, "kv_pages_free": eng.blocks.num_free,
+                    "d2h_bytes": 4 * (eng.stats["decode_tokens"] + eng.stats["prefill_steps"]),
+                    "tp_publish_ms": getattr(self.llm.tp, "publish_ms", 0.0) if self.llm.tp is not None else 0.0}
+
         @app.get("/v1/models")
         async def models():
             return {"object": "list", "data": [{"id": self.args.model, "object": "model"}]}
@@ -686,6 +716,10 @@ class LLMServer:
         @app.post("/v1/chat/completions")
         async def chat(raw: Request):
             return await self.chat(await raw.json())
+
+        from ..device_timer import add_timer_routes
+
+        add_timer_routes(app, self.engine.device)
 
         @app.post("/kv/release")
         async def kv_release(raw: Request):

@@ -21,6 +21,7 @@ import os
 import socket
 import subprocess
 import sys
+import time
 from typing import Any
 
 import numpy as np
@@ -32,6 +33,9 @@ from ...parallel.state import ParallelGroup, init_distributed
 from .engine import LLMEngine, MMItem, SamplingParams, Sequence
 
 logger = get_logger(__name__)
+
+IDLE_BEAT_S = 5.0          # the leader's keep-alive period while it has nothing to run
+CONTROL_TIMEOUT_S = 120.0  # a follower gives up when the leader stays silent this long
 
 
 def free_port() -> int:
@@ -72,23 +76,32 @@ class TPControl:
 
     def __init__(self, group: ParallelGroup, dtype: torch.dtype):
         self.group, self.dtype = group, dtype
-        self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(days=30))
+        # An idle executor publishes nothing, so a follower may wait here for as long as no request comes: the leader
+        # sends an empty "keep-alive" step every IDLE_BEAT_S seconds, which lets this wait carry a finite timeout.  A
+        # leader that died is then noticed after CONTROL_TIMEOUT_S instead of never.
+        self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=CONTROL_TIMEOUT_S))
+        self.publish_ms = 0.0
 
     # -- rank 0 -------------------------------------------------------------------------------------------
-    def publish(self, seqs: list[Sequence], stop: bool = False) -> None:
-        dist.broadcast_object_list([{"stop": stop, "seqs": [_pack(s) for s in seqs]}], src=0, group=self.ctl)
+    def publish(self, seqs: list[Sequence], stop: bool = False, beat: bool = False) -> None:
+        t0 = time.perf_counter()
+        dist.broadcast_object_list([{"stop": stop, "beat": beat, "seqs": [_pack(s) for s in seqs]}], src=0, group=self.ctl)
         for s in seqs:
             for it in s.mm_items:
                 # a buffer of this GPU's own memory: the rows may sit in another process's slab
                 own = torch.empty(tuple(it.embeds.shape), device=self.group.device, dtype=self.dtype)
                 own.copy_(it.embeds)
                 dist.broadcast(own, src=0)
+        self.publish_ms += (time.perf_counter() - t0) * 1e3
 
     # -- other ranks -----------------------------------------------------------------------------------------
-    def receive(self) -> tuple[bool, list[Sequence]]:
+    def receive(self) -> tuple[bool, list[Sequence]] | None:
+        """``(stop, new sequences)`` of the next engine step, or ``None`` for a keep-alive (no step)."""
         box: list[Any] = [None]
         dist.broadcast_object_list(box, src=0, group=self.ctl)
         msg = box[0]
+        if msg.get("beat"):
+            return None
         seqs = []
         for d in msg["seqs"]:
             items = []
@@ -105,7 +118,10 @@ class TPControl:
 def follower_loop(engine: LLMEngine, ctl: TPControl) -> None:
     """Mirror the leader: add what it added, step when it steps, until it says stop."""
     while True:
-        stop, seqs = ctl.receive()
+        got = ctl.receive()
+        if got is None:
+            continue
+        stop, seqs = got
         if stop:
             return
         for s in seqs:
