@@ -170,7 +170,7 @@ def stop_group(proc: subprocess.Popen, grace_s: float = 30.0) -> None:
 
 def profiles_for(model: str, layout: dict, small: bool) -> list[dict]:
     """Deployment profiles: the executor size (= tensor-parallel degree) of each unit task and its launch arguments."""
-    llm_args = ["--max-num-seqs", "128", "--decode-burst", "8", "--max-model-len", "8192" if not small else "2048"]
+    llm_args = ["--max-num-seqs", "256", "--decode-burst", "8", "--max-model-len", "8192" if not small else "2048"]
     if small:
         llm_args += ["--num-kv-pages", "64", "--max-num-batched-tokens", "512"]
     out = [{"task": {"__class__": "LLMUnitTask", "model_id": model, "receive_embeddings": layout["backend"] == "EV",

@@ -1,0 +1,75 @@
+"""The rate-sweep harness behind ``bench.py``: schedule, step split, latency arithmetic, and the whole benchmark as a
+plumbing run (tiny model, CPU ranks) through ``cornserve up`` -> gateway -> dispatcher -> Eric -> sidecar -> LLM."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_poisson_schedule_is_a_function_of_the_seed_and_has_the_rate():
+    from benchmark.serving_sweep import poisson_schedule
+
+    a, b = poisson_schedule(20.0, 50.0, 7), poisson_schedule(20.0, 50.0, 7)
+    assert np.array_equal(a, b) and not np.array_equal(a, poisson_schedule(20.0, 50.0, 8))
+    assert a[0] > 0 and a[-1] < 50.0 and np.all(np.diff(a) > 0)
+    assert abs(len(a) / 50.0 - 20.0) < 2.0                      # about rate * span arrivals
+    gaps = np.diff(a)
+    assert abs(gaps.std() / gaps.mean() - 1.0) < 0.15           # exponential gaps: coefficient of variation 1
+
+
+def test_steps_are_split_over_rates_without_losing_any():
+    from benchmark.serving_sweep import split_steps
+
+    assert split_steps(20, 5) == [4, 4, 4, 4, 4]
+    assert split_steps(7, 3) == [2, 2, 3]
+    assert split_steps(2, 5) == [1, 1]
+    assert sum(split_steps(13, 4)) == 13
+
+
+def test_segment_summary_and_bound():
+    from benchmark.load_generator import RequestRecord
+    from benchmark.serving_sweep import Segment, SweepConfig, _summarise, best_segment
+
+    cfg = SweepConfig(rates=[1.0], output_tokens=11, slo_e2el_s=2.0)
+    recs = []
+    for i in range(10):
+        r = RequestRecord(send_time=float(i))
+        r.chunk_times = [i + 0.5, i + 1.5]       # first token after 0.5 s, done after 1.5 s
+        r.ok = True
+        recs.append(r)
+    seg = Segment(rate=1.0, steps=1)
+    _summarise(seg, recs, 0.0, cfg)
+    assert seg.completed == 10 and seg.failed == 0 and abs(seg.duration_s - 10.5) < 1e-9
+    assert abs(seg.request_throughput - 10 / 10.5) < 1e-9
+    assert seg.ttft_ms["p99"] == 500.0 and seg.e2el_ms["median"] == 1500.0 and seg.tpot_ms["mean"] == 100.0
+    assert seg.slo_ok
+    slow = Segment(rate=2.0, steps=1)
+    recs[3].chunk_times[-1] += 5.0              # one straggler breaks the p99 bound
+    _summarise(slow, recs, 0.0, cfg)
+    assert not slow.slo_ok
+    failed = Segment(rate=3.0, steps=1)
+    recs[3].ok = False
+    _summarise(failed, recs, 0.0, cfg)
+    assert failed.failed == 1 and not failed.slo_ok
+    assert best_segment([seg, slow, failed]) is seg and best_segment([slow]) is None
+
+
+@pytest.mark.timeout(900)
+def test_bench_runs_end_to_end_on_cpu_ranks():
+    out = subprocess.run([sys.executable, "bench.py", "--small", "--cpu", "--gpus", "2", "--steps", "2", "--warmup", "1",
+                          "--window-s", "2", "--rates", "1,2", "--offline-steps", "0", "--output-tokens", "8"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=800)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["metric"] == "requests_per_second_at_p99_e2el_slo" and line["n_gpus"] == 2 and line["steps"] == 2
+    assert line["config"]["parallelism"] == "eric tp1 x1 + llm tp1 x1"
+    assert len(line["sweep"]) == 2 and all(s["failed"] == 0 and s["completed"] == s["sent"] > 0 for s in line["sweep"])
+    assert line["value"] > 0 and line["e2e"]["value"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0
+    assert abs(line["ms_per_step"] * 2 / 1e3 - sum(s["duration_s"] for s in line["sweep"])) < 3.0
+    assert {e["executor"] for e in line["executors"]} == {"eric", "llm"}
