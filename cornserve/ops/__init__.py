@@ -19,7 +19,7 @@ __all__ = [
     "linear", "swiglu_linear", "rms_norm", "layer_norm", "rope_", "mrope_table", "rope_kv_write_",
     "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
     "flow_step_", "pcm16", "decode_advance_", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
-    "count_path", "path_counts",
+    "count_path", "path_counts", "push_bytes_",
     "head_norm_rope_", "softmax_rows", "im2col3x3", "im2col1d", "dwconv1d", "to_rgb8", "conv3x3", "conv1d_causal",
     "conv_transpose1d_causal", "bilinear_embed_add_",
 ]
@@ -489,6 +489,25 @@ def scatter_rows_(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> to
     _chk(lib.cs_gather_rows(src.data_ptr(), src.stride(0) * src.element_size(), dst.data_ptr(),
                             dst.stride(0) * dst.element_size(), idx.data_ptr(), n, row_bytes, 1, _stream()),
          "cs_gather_rows(scatter)")
+    _count()
+    return dst
+
+
+def push_bytes_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """Copy the bytes of contiguous ``src`` into contiguous ``dst`` (same byte count) with this library's copy
+    kernel, launched on ``src``'s GPU.  ``dst`` may be memory of another GPU mapped into this process (CUDA IPC): the
+    kernel then stores over NVLink, which is how the sidecar places encoder rows in the consumer's slab."""
+    nbytes = src.numel() * src.element_size()
+    if dst.numel() * dst.element_size() != nbytes:
+        raise ValueError("push_bytes_: size mismatch")
+    if not (src.is_contiguous() and dst.is_contiguous()):
+        raise ValueError("push_bytes_: both tensors must be contiguous")
+    if not src.is_cuda:
+        dst.view(torch.uint8).reshape(-1).copy_(src.view(torch.uint8).reshape(-1))
+        return dst
+    _on_current_device(src)
+    lib = _lib.load()
+    _chk(lib.cs_push_bytes(src.data_ptr(), dst.data_ptr(), nbytes, _stream()), "cs_push_bytes")
     _count()
     return dst
 

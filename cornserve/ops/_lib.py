@@ -42,6 +42,7 @@ _SIGNATURES = {
     "cs_rope_kv_write": ([P, L, I, I, I, I, P, P, P, I, P], I),
     "cs_act_mul": ([P, L, P, L, I, I, I, P], I),
     "cs_gather_rows": ([P, L, P, L, P, I, L, I, P], I),
+    "cs_push_bytes": ([P, P, L, P], I),
     "cs_argmax": ([P, L, I, I, I, P, P, P], I),
     "cs_flow_step": ([P, P, P, I, I, F, F, I, P], I),
     "cs_pcm16": ([P, P, L, P], I),

@@ -5,19 +5,27 @@ Behaviour follows the reference's sidecar (python/cornserve/services/sidecar/{se
 ``Send`` stages a tensor into producer-owned slots and tells the leader of every destination group with
 ``PrepareReceive``; ``Receive`` blocks until the chunk (or the end of the stream) is known; ``MarkDone``
 from every member of the consumer group triggers ``Unlink`` at the producer, which frees the slots once
-all destination groups are done.  What differs is where the bytes live: the reference copies GPU -> host
-shared memory -> GPU; here the slab is *GPU memory* of the producer's device, published to the other
-processes of the box as a CUDA-IPC mapping, and consumers read the region in place over NVLink with a
-copy kernel that writes straight into their destination buffer (no host staging, no NCCL).  Without CUDA
-the slab is a ``/dev/shm`` file and tensors travel inline, which serves CPU-only deployments and tests.
+all destination groups are done.  What differs is where the bytes live and who moves them: the reference copies
+GPU -> host shared memory -> GPU; here every sidecar owns a slab of *GPU memory* on its device, allocated once when the
+server starts and published to the other processes of the box as a CUDA-IPC mapping, and a producer **pushes**: its
+sidecar writes the tensor straight into the slab of the consuming executor's GPU with a copy kernel that stores over
+NVLink, then tells the consumer's sidecar where the rows are.  The consumer reads its own GPU's memory.  No host
+staging, no NCCL, one pass over the data.
+
+A push needs space at the destination without asking for it first: each slab is cut into ``world_size`` equal
+regions and region ``p`` of every slab is managed by sidecar ``p`` (the only one that writes there), so a producer
+allocates in its own ledger, writes, and frees when the consumer's ``MarkDone`` comes back as ``Unlink``.  Without CUDA
+the slabs are ``/dev/shm`` files and the same protocol runs on the CPU, which serves CPU-only deployments and tests.
 """
 
 from __future__ import annotations
 
 import asyncio
-import os
 import json
+import os
 import signal
+import time
+import uuid
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -38,9 +46,10 @@ MEMORY_PRESSURE_THRESHOLD = 500
 
 @dataclass
 class _Sent:
-    """A staged chunk waiting for its consumers."""
+    """A pushed chunk waiting for its consumers: where it was placed (destination sidecar -> offset in this
+    sidecar's region of that slab) and how many destination groups still hold it."""
 
-    offset: int
+    placed: dict[int, int]
     pending_groups: int
 
 
@@ -66,8 +75,13 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
         self.dtype = torch.bfloat16
         self.slot_numel = 1
         self.concurrent_copy = False
-        self.slab: torch.Tensor | None = None
-        self.allocator: SlotAllocator | None = None
+        self.slab: torch.Tensor | None = None          # uint8, allocated once in serve(), never replaced
+        self.generation = uuid.uuid4().hex             # names this allocation: a restarted sidecar has a new one
+        self.region_bytes = (slab_bytes // max(world_size, 1)) // 256 * 256
+        self.remote: dict[int, SlotAllocator] = {}     # destination sidecar -> allocator of this sidecar's region there
+        self._peer_slabs: dict[int, tuple[str, torch.Tensor]] = {}
+        self.send_dtype: torch.dtype | None = None
+        self.push_stats = {"pushes": 0, "bytes": 0, "copy_ms": 0.0, "send_ms": 0.0}
         self._space = asyncio.Condition()
         self.mem_pressure_count = 0
         self.sent: dict[tuple[str, int], _Sent] = {}
@@ -77,6 +91,7 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
         self._copy_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self._registered_cfg: tuple | None = None
         self._concurrent: dict[tuple[str, int], dict[str, Any]] = {}
+        self._placed: dict[tuple[str, int], dict[int, int]] = {}
 
     # -- plumbing -----------------------------------------------------------------------------------------
     def stub(self, rank: int) -> sidecar_pb2_grpc.SidecarStub:
@@ -87,130 +102,191 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
             self._stubs[rank] = sidecar_pb2_grpc.SidecarStub(ch)
         return self._stubs[rank]
 
-    def _build_slab(self, dtype: torch.dtype) -> None:
-        """(Re)create the slab for ``dtype`` and publish how other processes can map it."""
-        numel = self.slab_bytes // dtype.itemsize
+    def build_slab(self) -> None:
+        """Allocate the slab (once) and publish how other processes can map it."""
         if self.device.type == "cuda":
-            self.slab = torch.empty(numel, dtype=dtype, device=self.device)
+            self.slab = torch.empty(self.slab_bytes, dtype=torch.uint8, device=self.device)
             from ...utils.cuda_ipc import export_tensor
 
-            blob = json.dumps({"kind": "cuda_ipc", "handle": export_tensor(self.slab), "dtype": serde.dtype_name(dtype),
-                               "numel": numel}).encode()
+            info = {"kind": "cuda_ipc", "handle": export_tensor(self.slab)}
         else:
             path = shm_slab_path(self.rank)
             with open(path, "wb") as f:
                 f.truncate(self.slab_bytes)
-            self.slab = torch.from_file(path, shared=True, size=numel, dtype=dtype)
-            blob = json.dumps({"kind": "shm", "path": path, "dtype": serde.dtype_name(dtype), "numel": numel}).encode()
+            self.slab = torch.from_file(path, shared=True, size=self.slab_bytes, dtype=torch.uint8)
+            info = {"kind": "shm", "path": path}
+        info.update(nbytes=self.slab_bytes, generation=self.generation, region_bytes=self.region_bytes,
+                    world_size=self.world_size)
         tmp = slab_handle_path(self.rank) + ".tmp"
-        with open(tmp, "wb") as f:
-            f.write(blob)
+        with open(tmp, "w") as f:
+            json.dump(info, f)
         os.replace(tmp, slab_handle_path(self.rank))
-        self.dtype = dtype
+
+    def peer_slab(self, rank: int) -> torch.Tensor:
+        """Sidecar ``rank``'s slab as a tensor of this process (own slab: the tensor itself).  Mapped once per
+        allocation: when the peer restarted (new generation in its handle file) it is mapped again."""
+        if rank == self.rank:
+            return self.slab
+        info = json.loads(open(slab_handle_path(rank)).read())
+        cached = self._peer_slabs.get(rank)
+        if cached is not None and cached[0] == info["generation"]:
+            return cached[1]
+        if info["kind"] == "cuda_ipc":
+            from ...utils.cuda_ipc import import_tensor
+
+            # opened with this sidecar's GPU current, so its copy kernel can store there over NVLink
+            slab = import_tensor(info["handle"], self.device.index if self.device.type == "cuda" else None)
+        else:
+            slab = torch.from_file(info["path"], shared=True, size=info["nbytes"], dtype=torch.uint8)
+        self._peer_slabs[rank] = (info["generation"], slab)
+        self.remote.pop(rank, None)   # a new allocation starts empty
+        return slab
 
     # -- RPCs ------------------------------------------------------------------------------------------------
     async def Register(self, request, context):
+        """Records the client's group and dtypes.  The slab is not touched: it was allocated when the server started,
+        and every process that mapped it keeps a valid mapping whatever registers later."""
         cfg = (tuple(request.group), request.send_slot_numel, request.recv_slot_numel, request.concurrent_copy,
                request.send_dtype, request.recv_dtype)
         if cfg != self._registered_cfg:
-            if self.sent:
-                self.log.warning("Re-registering with %d staged chunks outstanding; dropping them", len(self.sent))
-            dtype = serde.dtype_from_name(request.send_dtype or request.recv_dtype or "bfloat16")
             self.group = sorted(request.group) or [self.rank]
             self.slot_numel = max(1, request.send_slot_numel or request.recv_slot_numel)
             self.concurrent_copy = request.concurrent_copy
-            self._build_slab(dtype)
-            self.allocator = SlotAllocator(self.slab.numel(), self.slot_numel)
-            self.sent.clear()
+            self.send_dtype = serde.dtype_from_name(request.send_dtype) if request.send_dtype else None
+            self.dtype = serde.dtype_from_name(request.send_dtype or request.recv_dtype or "bfloat16")
             self._registered_cfg = cfg
-            self.log.info("Registered group=%s slot=%d dtype=%s slab=%d elems", self.group, self.slot_numel, dtype,
-                          self.slab.numel())
+            self.log.info("Registered group=%s slot=%d dtype=%s", self.group, self.slot_numel, self.dtype)
         self.online = True
         local_rank = self.device.index if self.device.type == "cuda" and self.device.index is not None else self.rank
-        return sidecar_pb2.RegisterResponse(status=OK, shm_size=self.slab.numel(), local_rank=local_rank,
+        return sidecar_pb2.RegisterResponse(status=OK, shm_size=self.slab_bytes // self.dtype.itemsize, local_rank=local_rank,
                                             num_local_sidecars=self.world_size)
 
-    async def _allocate(self, numel: int) -> int:
-        assert self.allocator is not None
+    def _allocator(self, dst: int) -> SlotAllocator:
+        if dst not in self.remote:
+            self.remote[dst] = SlotAllocator(self.region_bytes, 1, align=256)
+        return self.remote[dst]
+
+    async def _allocate(self, dst: int, nbytes: int) -> int:
+        """Byte offset (inside this sidecar's region of ``dst``'s slab) of ``nbytes`` free bytes; waits for space."""
+        alloc = self._allocator(dst)
+        if nbytes > alloc.total:
+            raise OutOfSlots(f"{nbytes} bytes do not fit a region of {alloc.total} bytes (raise {SHM_SIZE_ENV})")
         async with self._space:
             while True:
                 try:
-                    return self.allocator.allocate(numel)
+                    return alloc.allocate(nbytes)
                 except OutOfSlots:
                     self.mem_pressure_count += 1
-                    if numel > self.allocator.total:
-                        raise
                     await self._space.wait()
 
-    async def _release(self, offset: int) -> None:
+    async def _release(self, placed: dict[int, int]) -> None:
         async with self._space:
-            self.allocator.free(offset)
+            for dst, off in placed.items():
+                alloc = self.remote.get(dst)
+                if alloc is not None:
+                    try:
+                        alloc.free(off)
+                    except KeyError:
+                        pass   # the peer restarted in between: its region started over
             self._space.notify_all()
 
-    async def _stage(self, src: torch.Tensor, shard_rank: int, key: tuple[str, int]) -> tuple[int, int] | None:
-        """Copy ``src`` into freshly allocated slots.  Returns ``(offset, numel)`` for the shard that owns
-        the notification, ``None`` for shards whose call is absorbed."""
+    def _region(self, dst: int, off: int, nbytes: int) -> tuple[torch.Tensor, int]:
+        """The destination bytes and their absolute offset in ``dst``'s slab."""
+        base = self.rank * self.region_bytes + off
+        return self.peer_slab(dst)[base: base + nbytes], base
+
+    async def _push(self, src: torch.Tensor, shard_rank: int, key: tuple[str, int], leaders: list[int]) -> dict[int, int] | None:
+        """Write ``src`` into this sidecar's region of every destination leader's slab.  Returns where it was placed
+        (destination -> absolute byte offset) for the shard that owns the notification, ``None`` for shards whose
+        call is absorbed."""
         flat = src.reshape(-1)
-        n = flat.numel()
+        nbytes = flat.numel() * flat.element_size()
         if not self.concurrent_copy:
             if shard_rank != 0:
-                return None  # every shard holds the same tensor; shard 0 stages it
-            off = await self._allocate(n)
-            await self._copy(self.slab[off: off + n], flat)
-            return off, n
-        # concurrent copy: the first shard to arrive allocates, every shard copies its 1/TP of the data,
-        # the last one to finish reports
-        st = self._concurrent.setdefault(key, {"off": None, "done": 0, "lock": asyncio.Lock()})
+                return None   # every shard holds the same tensor; shard 0 pushes it
+            placed, absolute = {}, {}
+            for dst in leaders:
+                self.peer_slab(dst)   # map (or re-map after the peer restarted) before allocating in its region
+                off = await self._allocate(dst, nbytes)
+                placed[dst] = off
+                view, absolute[dst] = self._region(dst, off, nbytes)
+                await self._copy(view, flat)
+            self._placed[key] = placed
+            return absolute
+        # concurrent copy: the first shard to arrive allocates, every shard copies its 1/TP of the bytes, the last one
+        # to finish reports
+        st = self._concurrent.setdefault(key, {"placed": None, "done": 0, "lock": asyncio.Lock()})
         async with st["lock"]:
-            if st["off"] is None:
-                st["off"] = await self._allocate(n)
+            if st["placed"] is None:
+                for dst in leaders:
+                    self.peer_slab(dst)
+                st["placed"] = {dst: await self._allocate(dst, nbytes) for dst in leaders}
         tp = len(self.group)
+        n = flat.numel()
         per = -(-n // tp)
         lo, hi = min(shard_rank * per, n), min((shard_rank + 1) * per, n)
-        if hi > lo:
-            await self._copy(self.slab[st["off"] + lo: st["off"] + hi], flat[lo:hi])
+        absolute = {}
+        for dst, off in st["placed"].items():
+            view, absolute[dst] = self._region(dst, off, nbytes)
+            if hi > lo:
+                es = flat.element_size()
+                await self._copy(view[lo * es: hi * es], flat[lo:hi])
         st["done"] += 1
         if st["done"] == tp:
             self._concurrent.pop(key, None)
-            return st["off"], n
+            self._placed[key] = st["placed"]
+            return absolute
         return None
 
-    async def _copy(self, dst: torch.Tensor, src: torch.Tensor) -> None:
-        if self._copy_stream is None:
-            dst.copy_(src.to(dst.dtype))
+    async def _copy(self, dst_bytes: torch.Tensor, src: torch.Tensor) -> None:
+        """``src`` -> ``dst_bytes`` (uint8 view of a slab, possibly on another GPU)."""
+        if self._copy_stream is None or not src.is_cuda:
+            dst_bytes.copy_(src.contiguous().view(torch.uint8).reshape(-1).to(dst_bytes.device))
             return
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(self._copy_stream):
-            dst.copy_(src.to(device=dst.device, dtype=dst.dtype, non_blocking=True), non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-        await asyncio.to_thread(ev.synchronize)
+            t0.record()
+            if src.device == self.device:
+                from ... import ops
+
+                ops.push_bytes_(dst_bytes, src.contiguous())   # this library's copy kernel: plain stores over NVLink
+            else:
+                # a shard that lives on another GPU of the group (concurrent copy): the driver's peer copy
+                dst_bytes.copy_(src.contiguous().view(torch.uint8).reshape(-1), non_blocking=True)
+            t1.record()
+        await asyncio.to_thread(t1.synchronize)
+        self.push_stats["copy_ms"] += t0.elapsed_time(t1)
+        self.push_stats["bytes"] += dst_bytes.numel()
+        self.push_stats["pushes"] += 1
 
     async def Send(self, request, context):
         if not self.online:
             return sidecar_pb2.SendResponse(status=ERROR)
+        t_begin = time.perf_counter()
         msg = serde.decode(request.data)
         key = (request.id, request.chunk_id)
+        groups = [sorted(g.ranks) for g in request.dst_ranks if g.ranks]
         try:
             if msg["kind"] == "obj":
                 if request.shard_rank != 0:
                     return sidecar_pb2.SendResponse(status=OK)
-                payload, staged = request.data, None
+                payloads = {g[0]: request.data for g in groups}
             else:
                 src = serde.tensor_from_ipc(msg) if msg["kind"] == "ipc" else serde.tensor_from_inline(msg)
-                if src.dtype != self.dtype:
-                    self.log.error("dtype mismatch: got %s, slab holds %s", src.dtype, self.dtype)
+                if self.send_dtype is not None and src.dtype != self.send_dtype:
+                    self.log.error("dtype mismatch: got %s, registered to send %s", src.dtype, self.send_dtype)
                     return sidecar_pb2.SendResponse(status=ERROR)
-                staged = await self._stage(src, request.shard_rank, key)
+                placed = await self._push(src, request.shard_rank, key, [g[0] for g in groups])
+                nbytes, dtype = src.numel() * src.element_size(), src.dtype
                 del src
-                if staged is None:
+                if placed is None:
                     return sidecar_pb2.SendResponse(status=OK)
-                payload = serde.encode_slab_ref(self.rank, staged[0], staged[1], self.dtype, msg["shape"])
-            groups = [sorted(g.ranks) for g in request.dst_ranks if g.ranks]
-            if staged is not None:
-                self.sent[key] = _Sent(staged[0], max(1, len(groups)))
+                self.sent[key] = _Sent(self._placed.pop(key), max(1, len(groups)))
+                payloads = {dst: serde.encode_slab_ref(dst, off, nbytes, dtype, msg["shape"]) for dst, off in placed.items()}
             await asyncio.gather(*(self.stub(g[0]).PrepareReceive(sidecar_pb2.PrepareReceiveRequest(
-                id=request.id, data=payload, src_rank=self.rank, chunk_id=request.chunk_id,
+                id=request.id, data=payloads[g[0]], src_rank=self.rank, chunk_id=request.chunk_id,
                 num_chunks=request.num_chunks)) for g in groups))
+            self.push_stats["send_ms"] += (time.perf_counter() - t_begin) * 1e3
             return sidecar_pb2.SendResponse(status=OK)
         except Exception:
             self.log.exception("Send failed for %s", key)
@@ -280,7 +356,7 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
         s.pending_groups -= 1
         if s.pending_groups <= 0:
             self.sent.pop(key)
-            await self._release(s.offset)
+            await self._release(s.placed)
         return sidecar_pb2.UnlinkResponse(status=OK)
 
     async def CheckHealth(self, request, context):
@@ -321,9 +397,8 @@ async def serve(rank: int, world_size: int, slab_bytes: int, device: torch.devic
     sidecar_pb2_grpc.add_SidecarServicer_to_server(servicer, server)
     server.add_insecure_port(f"0.0.0.0:{grpc_port(rank)}")
     await server.start()
-    # the slab exists (with the default dtype) before any client registers, so health checks can pass
-    servicer._build_slab(torch.bfloat16)
-    servicer.allocator = SlotAllocator(servicer.slab.numel(), 1)
+    # the slab is allocated here, once, before any client registers; nothing ever replaces it
+    servicer.build_slab()
     servicer.online = True
     servicer.log.info("Sidecar server up on port %d (%s, %d MiB slab)", grpc_port(rank), device, slab_bytes >> 20)
     if ready is not None:

@@ -63,7 +63,7 @@ class Sidecar:
         self._stubs: dict[int, Any] = {}
         self._aio_stubs: dict[int, Any] = {}
         self._channels: list[Any] = []
-        self._slabs: dict[int, torch.Tensor] = {}
+        self._slabs: dict[int, tuple[int, torch.Tensor]] = {}
         self._lock = threading.Lock()
         self._pending: list[Future] = []
         self.local_rank = config.sidecar_rank
@@ -95,13 +95,16 @@ class Sidecar:
             self._aio_stubs[rank] = sidecar_pb2_grpc.SidecarStub(ch)
         return self._aio_stubs[rank]
 
-    def _slab_of(self, rank: int, dtype_name: str) -> torch.Tensor:
-        """Map (once) the slab that sidecar ``rank`` published."""
+    def _slab_of(self, rank: int) -> torch.Tensor:
+        """Sidecar ``rank``'s slab (bytes), mapped once per allocation: the handle file changes only when that sidecar
+        was restarted, and then the mapping is renewed."""
+        path = slab_handle_path(rank)
+        stamp = os.stat(path).st_mtime_ns
         with self._lock:
             cached = self._slabs.get(rank)
-            if cached is not None and serde.dtype_name(cached.dtype) == dtype_name:
-                return cached
-            info = json.loads(Path(slab_handle_path(rank)).read_bytes())
+            if cached is not None and cached[0] == stamp:
+                return cached[1]
+            info = json.loads(Path(path).read_bytes())
             if info["kind"] == "cuda_ipc":
                 from ..utils.cuda_ipc import import_tensor
 
@@ -109,8 +112,8 @@ class Sidecar:
                 # needed): kernels of this GPU can then read the slab in place, over NVLink when it lives elsewhere.
                 slab = import_tensor(info["handle"], torch.cuda.current_device())
             else:
-                slab = torch.from_file(info["path"], shared=True, size=info["numel"], dtype=serde.dtype_from_name(info["dtype"]))
-            self._slabs[rank] = slab
+                slab = torch.from_file(info["path"], shared=True, size=info["nbytes"], dtype=torch.uint8)
+            self._slabs[rank] = (stamp, slab)
             return slab
 
     # -- send -------------------------------------------------------------------------------------------------
@@ -200,9 +203,10 @@ class Sidecar:
         if msg["kind"] == "obj":
             return msg["obj"]
         if msg["kind"] == "slab":
-            slab = self._slab_of(msg["rank"], msg["dtype"])
+            # the producer pushed the tensor into the slab of this group's leader: a view of those bytes
+            slab = self._slab_of(msg["rank"])
             shape = msg["shape"] if -1 not in msg["shape"] else list(self.config.get_recv_tensor_shape())
-            return slab[msg["offset"]: msg["offset"] + msg["numel"]].view(shape)
+            return slab[msg["offset"]: msg["offset"] + msg["nbytes"]].view(serde.dtype_from_name(msg["dtype"])).view(shape)
         if msg["kind"] == "inline":
             return serde.tensor_from_inline(msg)
         raise ValueError(f"unknown payload kind {msg['kind']}")

@@ -49,8 +49,9 @@ def encode_ipc_tensor(t: torch.Tensor) -> bytes:
                           "handle": export_tensor(t)}, use_bin_type=True)
 
 
-def encode_slab_ref(rank: int, offset: int, numel: int, dtype: torch.dtype, shape: list[int]) -> bytes:
-    return msgpack.packb({"kind": "slab", "rank": rank, "offset": offset, "numel": numel,
+def encode_slab_ref(rank: int, offset: int, nbytes: int, dtype: torch.dtype, shape: list[int]) -> bytes:
+    """``nbytes`` bytes at byte ``offset`` of sidecar ``rank``'s slab hold a tensor of ``dtype`` and ``shape``."""
+    return msgpack.packb({"kind": "slab", "rank": rank, "offset": offset, "nbytes": nbytes,
                           "dtype": dtype_name(dtype), "shape": list(shape)}, use_bin_type=True)
 
 

@@ -367,6 +367,32 @@ __global__ void gather_rows_kernel(const uint4* src, long long src_ld16, uint4* 
 }
 
 // ---------------------------------------------------------------------------------------
+// Flat copy whose destination may be another GPU's memory (the sidecar's push of encoder rows into the
+// consumer's slab): plain 16-byte loads of local memory and plain stores over NVLink, four vectors in
+// flight per thread.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) push_bytes_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                         long long n16, const unsigned char* src_tail,
+                                                         unsigned char* dst_tail, int tail) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+    dst[i] = a;
+    dst[i + stride] = b;
+    dst[i + 2 * stride] = c;
+    dst[i + 3 * stride] = d;
+  }
+  for (; i < n16; i += stride) dst[i] = src[i];
+  if (blockIdx.x == 0 && (int)threadIdx.x < tail) dst_tail[threadIdx.x] = src_tail[threadIdx.x];
+}
+
+__global__ void push_bytes_unaligned_kernel(const unsigned char* src, unsigned char* dst, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------------------
 // Greedy sampling: arg-max over a [rows, V] logits matrix (bf16 or fp32).  One CTA per row.
 // ---------------------------------------------------------------------------------------
 // Two-stage so that few rows still fill the GPU: stage 1 scans a slice of the vocabulary per CTA and
@@ -574,6 +600,26 @@ CS_API int cs_gather_rows(const void* src, long long src_ld_bytes, void* dst, lo
   long long total = (long long)n * vpr;
   gather_rows_kernel<<<ceil_div_ll(total, 256), 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src, src_ld_bytes >> 4, (uint4*)dst, dst_ld_bytes >> 4, (const int*)idx, n, vpr, scatter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+// Copies nbytes from src (memory of the launching GPU) to dst (any memory the GPU can address, e.g. a peer's).
+CS_API int cs_push_bytes(const void* src, void* dst, long long nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  const auto s = reinterpret_cast<unsigned long long>(src), d = reinterpret_cast<unsigned long long>(dst);
+  if ((s & 15) || (d & 15)) {
+    long long blocks = ceil_div_ll(nbytes, 256 * 16);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    push_bytes_unaligned_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const unsigned char*)src,
+                                                                                  (unsigned char*)dst, nbytes);
+    return cudaGetLastError() == cudaSuccess ? 0 : -10;
+  }
+  const long long n16 = nbytes >> 4;
+  const int tail = static_cast<int>(nbytes & 15);
+  long long blocks = ceil_div_ll(n16 > 0 ? n16 : 1, 256 * 4);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  push_bytes_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)src, (uint4*)dst, n16, (const unsigned char*)src + (n16 << 4), (unsigned char*)dst + (n16 << 4), tail);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 

@@ -131,6 +131,43 @@ def test_tp_groups_and_broadcast(cluster, concurrent):
             c.shutdown_sync()
 
 
+def test_rows_are_pushed_into_the_consumers_slab_and_survive_new_registrations(cluster):
+    """The producer's sidecar writes into the slab of the consumer's sidecar (a view of rank 1's slab comes back, not of
+    rank 0's), and the slab is never re-allocated: a client that registers later with another dtype and slot size does
+    not invalidate what a consumer has mapped or what is still in flight."""
+    api = cluster
+    from cornserve.sidecar import serde
+    from cornserve.services.pb import sidecar_pb2
+
+    prod, cons = _client(api, 0), _client(api, 1)
+    try:
+        first, second = uuid.uuid4().hex, uuid.uuid4().hex
+        a = torch.randn(40, 64).bfloat16()
+        prod.send(a, first, [[1]])
+        prod.flush()
+        raw = cons._stub(1).Receive(sidecar_pb2.ReceiveRequest(id=first, chunk_id=0)).data
+        ref = serde.decode(raw)
+        assert ref["kind"] == "slab" and ref["rank"] == 1 and ref["nbytes"] == a.numel() * 2
+        got_a = cons.recv_sync(first)
+        mapped_before = cons._slab_of(1)
+        # another executor shows up on the producer's GPU with a different dtype and slot size
+        other = _client(api, 0, shape=(-1, 7), dtype=torch.float32)
+        b = torch.randn(9, 7)
+        other.send(b, second, [[1]])
+        other.flush()
+        late = _client(api, 1, shape=(-1, 7), dtype=torch.float32)
+        assert torch.equal(late.recv_sync(second), b)
+        assert torch.equal(got_a, a)                                 # still the same bytes through the old mapping
+        assert cons._slab_of(1) is mapped_before                     # and the mapping was not renewed
+        cons.mark_done_sync(first)
+        late.mark_done_sync(second)
+        other.shutdown_sync()
+        late.shutdown_sync()
+    finally:
+        prod.shutdown_sync()
+        cons.shutdown_sync()
+
+
 def test_streaming_out_of_order_and_close(cluster):
     api = cluster
     prod, cons = _client(api, 0), _client(api, 2)
