@@ -292,6 +292,11 @@ def create_app(resource_manager_grpc_url: str = RESOURCE_MANAGER_GRPC_URL,
         await registry.shutdown()
 
     app = FastAPI(title="cornserve-b200 gateway", lifespan=lifespan)
+
+    from ...tracing import instrument_fastapi
+
+
+    instrument_fastapi(app, "cornserve.gateway")
     app.include_router(router)
     app.state.task_registry = registry
     app.state.profile_manager = UnitTaskProfileManager(registry.store)

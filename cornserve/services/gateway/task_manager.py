@@ -23,8 +23,15 @@ from ...logging import get_logger
 from ...task.base import TaskGraphDispatch, UnitTask
 from ..pb import resource_manager_pb2, resource_manager_pb2_grpc
 from ..task_registry.registry import TaskRegistry
+from ...tracing import grpc_client_interceptors
 
 logger = get_logger(__name__)
+
+
+def _trace_configs():
+    from ...tracing import aiohttp_trace_configs
+
+    return aiohttp_trace_configs()
 
 
 class TaskState(enum.StrEnum):
@@ -43,14 +50,14 @@ class TaskManager:
         self.task_usage: dict[str, int] = defaultdict(int)
         self.invocation_tasks: dict[str, list[asyncio.Task]] = defaultdict(list)
         self.dispatcher_url = task_dispatcher_http_url
-        self._rm_channel = grpc.aio.insecure_channel(resource_manager_grpc_url)
+        self._rm_channel = grpc.aio.insecure_channel(resource_manager_grpc_url, interceptors=grpc_client_interceptors())
         self.resource_manager = resource_manager_pb2_grpc.ResourceManagerStub(self._rm_channel)
         self._client: aiohttp.ClientSession | None = None
 
     @property
     def client(self) -> aiohttp.ClientSession:
         if self._client is None or self._client.closed:
-            self._client = aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=TASK_TIMEOUT_S),
+            self._client = aiohttp.ClientSession(trace_configs=_trace_configs(), timeout=aiohttp.ClientTimeout(total=TASK_TIMEOUT_S),
                                                  connector=aiohttp.TCPConnector(limit=0))
         return self._client
 

@@ -7,6 +7,7 @@ import grpc
 from ...logging import get_logger
 from ..pb import common_pb2, resource_manager_pb2, resource_manager_pb2_grpc
 from .manager import ResourceManager
+from ...tracing import grpc_server_interceptors
 
 logger = get_logger(__name__)
 OK, ERROR = common_pb2.STATUS_OK, common_pb2.STATUS_ERROR
@@ -63,7 +64,7 @@ class ResourceManagerServicer(resource_manager_pb2_grpc.ResourceManagerServicer)
 
 
 async def start_server(manager: ResourceManager, address: str) -> grpc.aio.Server:
-    server = grpc.aio.server()
+    server = grpc.aio.server(interceptors=grpc_server_interceptors())
     resource_manager_pb2_grpc.add_ResourceManagerServicer_to_server(ResourceManagerServicer(manager), server)
     server.add_insecure_port(address)
     await server.start()

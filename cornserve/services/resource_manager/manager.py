@@ -30,6 +30,7 @@ from ..resource import GPU, Resource
 from ..sidecar import launch as sidecar_launch
 from ..task_manager.grpc import TaskManagerServicer, start_server
 from ..task_registry.registry import TaskRegistry
+from ...tracing import grpc_client_interceptors
 
 logger = get_logger(__name__)
 
@@ -137,7 +138,7 @@ class ResourceManager:
             else:
                 st.process = spawn(tm_id, [sys.executable, "-m", "cornserve.services.task_manager.entrypoint",
                                            "--port", str(port)], port=port)
-            st.channel = grpc.aio.insecure_channel(st.url)
+            st.channel = grpc.aio.insecure_channel(st.url, interceptors=grpc_client_interceptors())
             st.stub = task_manager_pb2_grpc.TaskManagerStub(st.channel)
             await asyncio.wait_for(st.channel.channel_ready(), timeout=60)
             await st.stub.SyncTaskRegistry(common_pb2.SyncTaskRegistryRequest())
@@ -268,7 +269,7 @@ class ResourceManager:
         async def one(addr: str) -> None:
             ch = self._dispatcher_channels.get(addr)
             if ch is None:
-                ch = self._dispatcher_channels[addr] = grpc.aio.insecure_channel(addr)
+                ch = self._dispatcher_channels[addr] = grpc.aio.insecure_channel(addr, interceptors=grpc_client_interceptors())
             stub = task_dispatcher_pb2_grpc.TaskDispatcherStub(ch)
             await stub.SyncTaskRegistry(common_pb2.SyncTaskRegistryRequest(), timeout=60)
             if deployed:

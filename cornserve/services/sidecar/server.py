@@ -38,6 +38,7 @@ from ...sidecar.constants import (DEVICE_ENV, RANK_ENV, SHM_SIZE_ENV, WORLD_SIZE
                                   shm_slab_path, slab_handle_path)
 from ..pb import common_pb2, sidecar_pb2, sidecar_pb2_grpc
 from .allocator import OutOfSlots, SlotAllocator
+from ...tracing import grpc_server_interceptors
 
 OK = common_pb2.STATUS_OK
 ERROR = common_pb2.STATUS_ERROR
@@ -258,6 +259,16 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
         self.push_stats["copy_ms"] += t0.elapsed_time(t1)
         self.push_stats["bytes"] += dst_bytes.numel()
         self.push_stats["pushes"] += 1
+        if self.push_stats["pushes"] % 16 == 0:
+            self.write_stats()
+
+    def write_stats(self) -> None:
+        """Counters of the push path (device time of the copy kernels, time inside ``Send``) beside the handle file."""
+        try:
+            with open(slab_handle_path(self.rank) + ".stats", "w") as f:
+                json.dump(self.push_stats, f)
+        except OSError:
+            pass
 
     async def Send(self, request, context):
         if not self.online:
@@ -371,7 +382,11 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
     async def shutdown(self) -> None:
         for ch in self._channels.values():
             await ch.close()
-        for p in (slab_handle_path(self.rank), shm_slab_path(self.rank)):
+        if self.push_stats["pushes"]:
+            ps = self.push_stats
+            self.log.info("pushed %d tensors, %.1f MB, %.2f ms in copy kernels (%.0f GB/s), %.1f ms in Send", ps["pushes"],
+                          ps["bytes"] / 1e6, ps["copy_ms"], ps["bytes"] / 1e6 / max(ps["copy_ms"], 1e-9), ps["send_ms"])
+        for p in (slab_handle_path(self.rank), slab_handle_path(self.rank) + ".stats", shm_slab_path(self.rank)):
             try:
                 os.unlink(p)
             except OSError:
@@ -393,7 +408,7 @@ async def serve(rank: int, world_size: int, slab_bytes: int, device: torch.devic
     if device.type == "cuda":
         torch.cuda.set_device(device)
     servicer = SidecarServicer(rank, world_size, slab_bytes, device)
-    server = grpc.aio.server(options=[("grpc.max_send_message_length", -1), ("grpc.max_receive_message_length", -1)])
+    server = grpc.aio.server(interceptors=grpc_server_interceptors(), options=[("grpc.max_send_message_length", -1), ("grpc.max_receive_message_length", -1)])
     sidecar_pb2_grpc.add_SidecarServicer_to_server(servicer, server)
     server.add_insecure_port(f"0.0.0.0:{grpc_port(rank)}")
     await server.start()

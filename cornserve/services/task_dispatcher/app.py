@@ -15,6 +15,7 @@ from ...logging import get_logger
 from ...task.base import Stream, TaskGraphDispatch, TaskOutput
 from ..pb import common_pb2, task_dispatcher_pb2, task_dispatcher_pb2_grpc
 from .dispatcher import TaskDispatcher
+from ...tracing import grpc_server_interceptors
 
 logger = get_logger(__name__)
 OK, ERROR = common_pb2.STATUS_OK, common_pb2.STATUS_ERROR
@@ -22,6 +23,9 @@ OK, ERROR = common_pb2.STATUS_OK, common_pb2.STATUS_ERROR
 
 def create_app(dispatcher: TaskDispatcher) -> FastAPI:
     app = FastAPI(title="cornserve-b200 task dispatcher")
+    from ...tracing import instrument_fastapi
+
+    instrument_fastapi(app, "cornserve.task-dispatcher")
     app.state.dispatcher = dispatcher
 
     @app.post("/task")
@@ -82,7 +86,7 @@ class TaskDispatcherServicer(task_dispatcher_pb2_grpc.TaskDispatcherServicer):
 
 
 async def start_grpc(dispatcher: TaskDispatcher, address: str) -> grpc.aio.Server:
-    server = grpc.aio.server()
+    server = grpc.aio.server(interceptors=grpc_server_interceptors())
     task_dispatcher_pb2_grpc.add_TaskDispatcherServicer_to_server(TaskDispatcherServicer(dispatcher), server)
     server.add_insecure_port(address)
     await server.start()

@@ -27,8 +27,15 @@ from ...task.forward import DataForward
 from ...tracing import get_tracer
 from ..pb import task_manager_pb2, task_manager_pb2_grpc
 from ..task_registry.registry import TaskRegistry
+from ...tracing import grpc_client_interceptors
 
 logger = get_logger(__name__)
+
+
+def _trace_configs():
+    from ...tracing import aiohttp_trace_configs
+
+    return aiohttp_trace_configs()
 tracer = get_tracer(__name__)
 
 
@@ -103,14 +110,14 @@ class TaskDispatcher:
     @property
     def client(self) -> aiohttp.ClientSession:
         if self._client is None or self._client.closed:
-            self._client = aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=TASK_TIMEOUT_S),
+            self._client = aiohttp.ClientSession(trace_configs=_trace_configs(), timeout=aiohttp.ClientTimeout(total=TASK_TIMEOUT_S),
                                                  connector=aiohttp.TCPConnector(limit=0))
         return self._client
 
     # -- deployment notifications ---------------------------------------------------------------------------
     async def notify_task_deployment(self, instance_name: str, task_manager_url: str) -> None:
         task = await self.registry.get_task_instance(instance_name)
-        channel = grpc.aio.insecure_channel(task_manager_url)
+        channel = grpc.aio.insecure_channel(task_manager_url, interceptors=grpc_client_interceptors())
         info = TaskInfo(task, instance_name, task_manager_url, channel, task_manager_pb2_grpc.TaskManagerStub(channel))
         async with self.task_lock:
             old = self.task_infos.pop(instance_name, None)

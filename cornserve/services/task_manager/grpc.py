@@ -10,6 +10,7 @@ from ..pb import common_pb2, task_manager_pb2, task_manager_pb2_grpc
 from ..resource import GPU
 from ..task_registry.registry import TaskRegistry
 from .manager import TaskManager
+from ...tracing import grpc_server_interceptors
 
 logger = get_logger(__name__)
 OK, ERROR = common_pb2.STATUS_OK, common_pb2.STATUS_ERROR
@@ -105,7 +106,7 @@ class TaskManagerServicer(task_manager_pb2_grpc.TaskManagerServicer):
 
 
 async def start_server(port: int, servicer: TaskManagerServicer) -> grpc.aio.Server:
-    server = grpc.aio.server()
+    server = grpc.aio.server(interceptors=grpc_server_interceptors())
     task_manager_pb2_grpc.add_TaskManagerServicer_to_server(servicer, server)
     server.add_insecure_port(f"127.0.0.1:{port}")
     await server.start()

@@ -30,6 +30,12 @@ from ..resource import GPU
 logger = get_logger(__name__)
 
 
+def _trace_configs():
+    from ...tracing import aiohttp_trace_configs
+
+    return aiohttp_trace_configs()
+
+
 @dataclass
 class ExecutorDeployment:
     executor_id: str
@@ -90,7 +96,7 @@ class TaskManager:
 
     async def _client(self) -> aiohttp.ClientSession:
         if self._http is None or self._http.closed:
-            self._http = aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=5))
+            self._http = aiohttp.ClientSession(trace_configs=_trace_configs(), timeout=aiohttp.ClientTimeout(total=5))
         return self._http
 
     async def shutdown(self) -> None:

@@ -33,6 +33,12 @@ if TYPE_CHECKING:  # pragma: no cover
     import aiohttp
 
 logger = get_logger(__name__)
+
+
+def _trace_configs():
+    from ..tracing import aiohttp_trace_configs
+
+    return aiohttp_trace_configs()
 tracer = get_tracer(__name__)
 
 TASK_TIMEOUT = TASK_TIMEOUT_S
@@ -46,7 +52,7 @@ def get_client() -> "aiohttp.ClientSession":
 
     global _http_client
     if _http_client is None or _http_client.closed:
-        _http_client = aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=TASK_TIMEOUT),
+        _http_client = aiohttp.ClientSession(trace_configs=_trace_configs(), timeout=aiohttp.ClientTimeout(total=TASK_TIMEOUT),
                                              connector=aiohttp.TCPConnector(limit=0))
     return _http_client
 

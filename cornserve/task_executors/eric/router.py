@@ -20,6 +20,9 @@ logger = get_logger(__name__)
 
 def create_app(config: EricConfig, engine: Engine) -> FastAPI:
     app = FastAPI(title="cornserve-b200 encoder executor")
+    from ...tracing import instrument_fastapi
+
+    instrument_fastapi(app, "cornserve.eric")
     processor = Processor(engine.worker.entry.processor, config.modality)
     model_ids = set(config.model.all_model_ids)
 

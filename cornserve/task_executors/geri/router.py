@@ -43,6 +43,9 @@ async def receive_all_chunks(sidecar: Sidecar | None, data_id: str, skip_tokens:
 
 def create_app(config: GeriConfig, engine: Engine, sidecar: Sidecar | None) -> FastAPI:
     app = FastAPI(title="cornserve-b200 generator executor")
+    from ...tracing import instrument_fastapi
+
+    instrument_fastapi(app, "cornserve.geri")
 
     @app.get("/health")
     async def health():

@@ -13,6 +13,9 @@ from .engine import Engine
 
 def create_app(config: HuggingFaceConfig, engine: Engine) -> FastAPI:
     app = FastAPI(title="cornserve-b200 monolithic baseline executor")
+    from ...tracing import instrument_fastapi
+
+    instrument_fastapi(app, "cornserve.huggingface")
 
     @app.get("/health")
     async def health():

@@ -693,6 +693,9 @@ class LLMServer:
 
     def create_app(self) -> FastAPI:
         app = FastAPI(title="cornserve-b200 LLM executor")
+        from ...tracing import instrument_fastapi
+
+        instrument_fastapi(app, "cornserve.llm")
 
         @app.get("/health")
         async def health():

@@ -199,6 +199,9 @@ class TalkerServer:
 
     def create_app(self) -> FastAPI:
         app = FastAPI(title="cornserve-b200 LLM executor (talker)")
+        from ...tracing import instrument_fastapi
+
+        instrument_fastapi(app, "cornserve.llm-talker")
 
         @app.get("/health")
         async def health():
