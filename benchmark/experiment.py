@@ -120,7 +120,7 @@ class Config(AppConfig):
     tasks = {{"mllm": task}}
 
 async def serve(request: Request) -> AsyncIterator[OpenAIChatCompletionChunk]:
-    return await task(OpenAIChatCompletionRequest(model="{m}", messages=_messages(request), ignore_eos=True,
+    return await task(OpenAIChatCompletionRequest(model="{m}", messages=_messages(request), ignore_eos=True, temperature=0.0,
                                                   max_completion_tokens=request.max_completion_tokens))
 '''
 

@@ -344,14 +344,22 @@ class QwenLLM(nn.Module):
         return logits[:, : self.cfg.vocab_size]
 
     def forward(self, m: BatchMeta, kv_caches: list[torch.Tensor], return_hidden: bool = False,
-                capture: dict[int, torch.Tensor] | None = None, sampler: tuple | None = None):
+                capture: dict[int, torch.Tensor] | None = None, sampler: tuple | None = None,
+                penalties: tuple | None = None):
         """Returns ``(next_token_ids [B] int32, hidden [T, H] or None)``.  Greedy unless ``sampler`` gives the per-row
         ``(temperature, top_p, top_k, seed, draws)`` tensors of :func:`ops.sample_rows` (every tensor-parallel rank
         holds the same gathered logits and the same streams, so all ranks draw the same token)."""
         h = self.forward_hidden(m, kv_caches, capture)
         h_last = ops.gather_rows(h, m.logits_idx)
         logits = self.compute_logits(h_last)
+        if penalties is not None:
+            # (counts [B, V] int32, frequency [B], presence [B], active [B] or None): repetition control on the logits,
+            # then the chosen token is added to its row's counts
+            counts, freq, pres, active = penalties
+            ops.apply_penalties_(logits, counts, freq, pres)
         tok = ops.argmax(logits) if sampler is None else ops.sample_rows(logits, *sampler)
+        if penalties is not None:
+            ops.count_tokens_(counts, tok, active)
         return tok, (h if return_hidden else None)
 
     # -- checkpoint loading -------------------------------------------------------------------------

@@ -19,7 +19,7 @@ __all__ = [
     "linear", "swiglu_linear", "rms_norm", "layer_norm", "rope_", "mrope_table", "rope_kv_write_",
     "attention_varlen", "attention_paged", "act_mul", "gather_rows", "scatter_rows_", "argmax",
     "flow_step_", "pcm16", "decode_advance_", "l2_flush", "check_error", "kernel_launches", "reset_launch_count",
-    "count_path", "path_counts", "push_bytes_",
+    "count_path", "path_counts", "push_bytes_", "apply_penalties_", "count_tokens_",
     "head_norm_rope_", "softmax_rows", "im2col3x3", "im2col1d", "dwconv1d", "to_rgb8", "conv3x3", "conv1d_causal",
     "conv_transpose1d_causal", "bilinear_embed_add_",
 ]
@@ -548,6 +548,39 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
                             top_k.data_ptr(), seed.data_ptr(), draws.data_ptr(), out.data_ptr(), _stream()), "cs_sample_rows")
     _count()
     return out
+
+
+def apply_penalties_(logits: torch.Tensor, counts: torch.Tensor, frequency: torch.Tensor, presence: torch.Tensor) -> torch.Tensor:
+    """OpenAI ``frequency_penalty`` / ``presence_penalty`` in place on fp32 ``logits [rows, V]``: every token a row has
+    generated ``c > 0`` times (``counts [rows, V]`` int32) loses ``frequency[row] * c + presence[row]``."""
+    if not logits.is_cuda:
+        c = counts[: logits.shape[0], : logits.shape[1]].to(logits.dtype)
+        logits -= frequency[: logits.shape[0], None] * c + presence[: logits.shape[0], None] * (c > 0)
+        return logits
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and counts.dtype == torch.int32 and counts.shape[1] >= V and counts.shape[0] >= rows
+    assert frequency.dtype == torch.float32 and presence.dtype == torch.float32
+    lib = _lib.load()
+    _chk(lib.cs_apply_penalties(logits.data_ptr(), logits.stride(0), counts.data_ptr(), counts.stride(0), frequency.data_ptr(),
+                                presence.data_ptr(), rows, V, _stream()), "cs_apply_penalties")
+    _count()
+    return logits
+
+
+def count_tokens_(counts: torch.Tensor, tokens: torch.Tensor, active: torch.Tensor | None = None) -> torch.Tensor:
+    """``counts[r, tokens[r]] += 1`` for every row (rows whose ``active`` flag is 0 are skipped)."""
+    rows = tokens.shape[0]
+    if not counts.is_cuda:
+        for r in range(rows):
+            if active is None or int(active[r]) != 0:
+                counts[r, int(tokens[r])] += 1
+        return counts
+    assert counts.dtype == torch.int32 and tokens.dtype == torch.int32 and (active is None or active.dtype == torch.int32)
+    lib = _lib.load()
+    _chk(lib.cs_count_tokens(counts.data_ptr(), counts.stride(0), tokens.data_ptr(), _ptr(active), rows, counts.shape[1], _stream()),
+         "cs_count_tokens")
+    _count()
+    return counts
 
 
 def flow_step_(x: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor | None, cfg: float, dt: float,

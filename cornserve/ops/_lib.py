@@ -43,6 +43,8 @@ _SIGNATURES = {
     "cs_act_mul": ([P, L, P, L, I, I, I, P], I),
     "cs_gather_rows": ([P, L, P, L, P, I, L, I, P], I),
     "cs_push_bytes": ([P, P, L, P], I),
+    "cs_apply_penalties": ([P, L, P, L, P, P, I, I, P], I),
+    "cs_count_tokens": ([P, L, P, P, I, I, P], I),
     "cs_argmax": ([P, L, I, I, I, P, P, P], I),
     "cs_flow_step": ([P, P, P, I, I, F, F, I, P], I),
     "cs_pcm16": ([P, P, L, P], I),

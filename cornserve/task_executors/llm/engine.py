@@ -42,21 +42,30 @@ class SamplingParams:
     top_p: float = 1.0            # nucleus: smallest set of most likely tokens whose mass reaches top_p
     top_k: int = 0                # <= 0: off
     seed: int | None = None       # names the request's random stream; None = drawn once when the request is added
+    frequency_penalty: float = 0.0   # OpenAI semantics: a token generated c times loses frequency_penalty * c ...
+    presence_penalty: float = 0.0    # ... and presence_penalty once it was generated at all
 
     @classmethod
-    def from_request(cls, body: dict, **kw) -> "SamplingParams":
-        """OpenAI-style request fields.  Without ``temperature`` the request decodes greedily."""
+    def from_request(cls, body: dict, default_temperature: float = 1.0, **kw) -> "SamplingParams":
+        """OpenAI-style request fields.  A request without ``temperature`` samples at ``default_temperature`` (1.0 as
+        in the OpenAI API unless the model's ``generation_config.json`` says otherwise); ``temperature: 0`` is greedy."""
         t = body.get("temperature")
         k = body.get("top_k")
         seed = body.get("seed")
-        return cls(temperature=float(t) if t is not None else 0.0,
+        return cls(temperature=float(t) if t is not None else float(default_temperature),
                    top_p=float(body["top_p"]) if body.get("top_p") is not None else 1.0,
                    top_k=int(k) if k is not None and int(k) > 0 else 0,
-                   seed=int(seed) if seed is not None else None, **kw)
+                   seed=int(seed) if seed is not None else None,
+                   frequency_penalty=float(body.get("frequency_penalty") or 0.0),
+                   presence_penalty=float(body.get("presence_penalty") or 0.0), **kw)
 
     @property
     def samples(self) -> bool:
         return self.temperature > 0.0
+
+    @property
+    def penalized(self) -> bool:
+        return self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
 
 
 @dataclass
@@ -166,12 +175,19 @@ class _DecodeState:
         self.seed = torch.zeros(B, dtype=torch.int64, device=device)
         self.draws = torch.zeros(B, **i32)
         self.sampling = False
+        # repetition control (buckets whose graph applies penalties): how often each row generated each token
+        self.frequency = torch.zeros(B, dtype=torch.float32, device=device)
+        self.presence = torch.zeros(B, dtype=torch.float32, device=device)
+        self.counts: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_replay = 0
         self.paths_per_replay: dict[str, int] = {}
 
     def sampler(self):
         return (self.temperature, self.top_p, self.top_k, self.seed, self.draws) if self.sampling else None
+
+    def penalties(self):
+        return (self.counts, self.frequency, self.presence, self.active) if self.counts is not None else None
 
     def meta(self) -> BatchMeta:
         return BatchMeta(self.input_ids, self.positions, self.slot, self.cu_q, self.kv_len, self.block_table,
@@ -443,12 +459,16 @@ class LLMEngine:
         burst = max(1, min(self.cfg.decode_burst, min(s.params.max_tokens - len(s.output_ids) for s in seqs)))
         n = len(seqs)
         B = self._bucket(n) if (self.on_gpu and self.cfg.use_cuda_graph) else n
-        sampling = any(s.params.samples for s in seqs)
-        key = (B, "sample") if sampling else B   # a bucket's graph ends either in the arg-max or in the sampling kernel
+        penalized = any(s.params.penalized for s in seqs)
+        sampling = penalized or any(s.params.samples for s in seqs)
+        # a bucket's graph ends in the arg-max, in the sampling kernel, or in penalties + the sampling kernel
+        key = (B, "penalty") if penalized else ((B, "sample") if sampling else B)
         st = self._decode_states.get(key)
         if st is None:
             st = self._decode_states[key] = _DecodeState(B, self.max_blocks, self.cfg.decode_burst, self.device)
             st.sampling = sampling
+            if penalized:
+                st.counts = torch.zeros(B, self.mcfg.vocab_size, dtype=torch.int32, device=self.device)
         # host-side batch state
         ids = np.zeros(B, np.int32); pos = np.zeros((3, B), np.int32); slot = np.zeros(B, np.int32)
         kvl = np.ones(B, np.int32); act = np.zeros(B, np.int32)
@@ -473,6 +493,22 @@ class LLMEngine:
                 sd[b], dr[b] = s.params.seed or 0, len(s.output_ids)
             for t, a in ((st.temperature, temp), (st.top_p, tp), (st.top_k, tk), (st.seed, sd), (st.draws, dr)):
                 t.copy_(self._pin(a), non_blocking=True)
+        if penalized:
+            # rows are re-assigned every burst: rebuild each row's counts from what its sequence generated so far
+            fr = np.zeros(B, np.float32); pr = np.zeros(B, np.float32)
+            rows_idx, tok_idx = [], []
+            for b, s in enumerate(seqs):
+                fr[b], pr[b] = s.params.frequency_penalty, s.params.presence_penalty
+                if s.params.penalized:
+                    rows_idx.extend([b] * len(s.output_ids))
+                    tok_idx.extend(s.output_ids)
+            st.frequency.copy_(self._pin(fr), non_blocking=True)
+            st.presence.copy_(self._pin(pr), non_blocking=True)
+            st.counts.zero_()
+            if rows_idx:
+                r = self._to_dev(np.asarray(rows_idx, dtype=np.int64))
+                t = self._to_dev(np.asarray(tok_idx, dtype=np.int64))
+                st.counts.index_put_((r, t), torch.ones(len(rows_idx), dtype=torch.int32, device=self.device), accumulate=True)
         st.step_counter.zero_()
         with torch.inference_mode():
             for _ in range(burst):
@@ -512,7 +548,7 @@ class LLMEngine:
 
     def _decode_once(self, st: _DecodeState) -> None:
         def body():
-            tok, _ = self.model(st.meta(), self.kv_caches, sampler=st.sampler())
+            tok, _ = self.model(st.meta(), self.kv_caches, sampler=st.sampler(), penalties=st.penalties())
             ops.decode_advance_(tok, st.input_ids, st.positions, st.kv_len, st.slot, st.block_table, st.active,
                                 st.out_log, st.step_counter)
 
@@ -522,7 +558,10 @@ class LLMEngine:
         if st.graph is None:
             # warm-up run outside the graph (sets kernel attributes, fills allocator pools), then capture;
             # the state is restored afterwards so the warm-up leaves no trace
-            snap = [t.clone() for t in (st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter, st.draws)]
+            keep = [st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter, st.draws]
+            if st.counts is not None:
+                keep.append(st.counts)
+            snap = [t.clone() for t in keep]
             body()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -533,7 +572,7 @@ class LLMEngine:
             st.paths_per_replay = {k: v - paths_before.get(k, 0) for k, v in ops.path_counts().items()
                                    if v != paths_before.get(k, 0)}
             st.graph = g
-            for t, v in zip((st.input_ids, st.positions, st.slot, st.kv_len, st.step_counter, st.draws), snap):
+            for t, v in zip(keep, snap):
                 t.copy_(v)
         st.graph.replay()
         ops._count(st.launches_per_replay)

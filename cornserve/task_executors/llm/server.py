@@ -113,6 +113,7 @@ class AsyncLLM:
         self.tp = tp   # tensor-parallel control channel: every step is announced to the follower ranks first
         self.pending: dict[str, _Pending] = {}
         self.inbox: list[Sequence] = []
+        self.aborts: list[str] = []
         self.calls: list[tuple[Any, concurrent.futures.Future]] = []
         self.cv = threading.Condition()
         self.alive = True
@@ -126,6 +127,14 @@ class AsyncLLM:
             self.inbox.append(seq)
             self.cv.notify()
         return q
+
+    def abort(self, seq_id: str) -> None:
+        """Take a sequence out of the engine (a stop string matched, the client disconnected).  Runs on the engine
+        thread, and on every follower rank of a tensor-parallel executor at the same point of the step sequence."""
+        self.pending.pop(seq_id, None)
+        with self.cv:
+            self.aborts.append(seq_id)
+            self.cv.notify()
 
     def call(self, fn) -> concurrent.futures.Future:
         """Run ``fn()`` on the engine thread (the engine's state is not shared between threads)."""
@@ -151,12 +160,13 @@ class AsyncLLM:
         try:
             while self.alive:
                 with self.cv:
-                    while self.alive and not self.inbox and not self.calls and not self.engine.has_work():
+                    while self.alive and not self.inbox and not self.calls and not self.aborts and not self.engine.has_work():
                         self.cv.wait(timeout=0.5)
                         if self.engine.held or (self.tp is not None and time.monotonic() - last_beat > IDLE_BEAT_S):
                             break
                     new, self.inbox = self.inbox, []
                     calls, self.calls = self.calls, []
+                    aborts, self.aborts = self.aborts, []
                 for fn, fut in calls:
                     try:
                         fut.set_result(fn())
@@ -177,7 +187,9 @@ class AsyncLLM:
                     for s in new:
                         if s.params.samples and s.params.seed is None:
                             s.params.seed = random.getrandbits(62)   # drawn here so that every rank gets the same stream
-                    self.tp.publish(new)
+                    self.tp.publish(new, aborts=aborts)
+                for sid in aborts:
+                    self.engine.abort(sid)
                 for s in new:
                     try:
                         self.engine.add_request(s)
@@ -276,6 +288,7 @@ class LLMServer:
         self.cfg = self.engine.mcfg
         self.tokenizer = load_tokenizer(args.model, {**(self.hf_cfg.get("thinker_config") or {}), **self.hf_cfg}, self.cfg.vocab_size)
         self.omni_cfg = self.hf_cfg if "talker_config" in self.hf_cfg else None
+        self.default_temperature = self._default_temperature()
         self.receive_embeddings = os.environ.get("CORNSERVE_VLLM_DISABLE_MULTIMODAL") == "1"
         self.sidecar = None
         if args.cornserve_sidecar_ranks:
@@ -293,6 +306,30 @@ class LLMServer:
         self.engine_id = uuid.uuid4().hex
         self._kv_export: dict[str, Any] | None = None
         self._kv_maps: dict[str, torch.Tensor] = {}   # producer engine id -> its cache mapped into this process
+
+    def _default_temperature(self) -> float:
+        """What a request without ``temperature`` gets: the model's ``generation_config.json`` when it names one
+        (greedy when it says ``do_sample: false``), else the OpenAI default 1.0."""
+        from ...utils.hub import resolve_model_dir
+
+        d = resolve_model_dir(self.args.model)
+        try:
+            if d is not None and (d / "generation_config.json").is_file():
+                g = json.loads((d / "generation_config.json").read_text())
+                if g.get("do_sample") is False:
+                    return 0.0
+                if g.get("temperature") is not None:
+                    return float(g["temperature"])
+        except (OSError, ValueError):
+            pass
+        return 1.0
+
+    @staticmethod
+    def _stops(body: dict[str, Any]) -> list[str]:
+        stop = body.get("stop")
+        if stop is None:
+            return []
+        return [stop] if isinstance(stop, str) else [str(x) for x in stop if x]
 
     # -- multimodal inputs ----------------------------------------------------------------------------------
     def _grid_of(self, modality: str, url: str, n_rows: int) -> tuple[int, int, int] | None:
@@ -375,7 +412,8 @@ class LLMServer:
             out += [ids[pos]] * rows.shape[0]
             prev = pos + 1
         out += ids[prev:]
-        params = SamplingParams.from_request(body, max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
+        params = SamplingParams.from_request(body, self.default_temperature,
+                                             max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
                                              ignore_eos=bool(body.get("ignore_eos", False)))
         # without grids M-RoPE degrades to sequential positions (text-only layout)
         if any(it.grid_thw is None for it in items):
@@ -508,7 +546,8 @@ class LLMServer:
         src = self._map_producer_cache(params)
         raw = None if src is not None else await self._fetch_pages(params)
         pf = PrefilledKV(int(params["first_token"]), int(params["next_pos"]), [int(p) for p in params["pages"]], src_cache=src, raw=raw)
-        sp = SamplingParams.from_request(body, max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
+        sp = SamplingParams.from_request(body, self.default_temperature,
+                                         max_tokens=int(body.get("max_completion_tokens") or body.get("max_tokens") or 256),
                                          ignore_eos=bool(body.get("ignore_eos", False)))
         seq = Sequence(body.get("request_id") or uuid.uuid4().hex, np.zeros(int(params["num_tokens"]), dtype=np.int32), sp,
                        prefilled=pf)
@@ -600,28 +639,49 @@ class LLMServer:
                 payload["usage"] = usage
             return f"data: {json.dumps(payload)}\n\n"
 
+        stops = self._stops(body)
+        hold = max((len(x) for x in stops), default=1) - 1   # characters that may still turn out to start a stop string
+
         async def consume():
-            """Yields (text_delta, finished, finish_reason, hidden) per engine output."""
+            """Yields (text_delta, engine output, tokens so far) per engine output.  With ``stop`` strings the text is cut
+            before the first match, the request ends with reason ``stop`` and the sequence is taken out of the engine; the
+            last ``hold`` characters are kept back until it is clear that they do not begin a stop string."""
             all_ids: list[int] = []
             emitted = ""
             first = True
-            while True:
-                out: StepOutput = await queue.get()
-                if first:
-                    first = False
-                    if recv_ids:
-                        await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
-                    if kv_in is not None:
-                        await self._release_at_producer(kv_in)  # the pages were pulled before the first output
-                all_ids.extend(out.new_token_ids)
-                text = self.tokenizer.decode(all_ids)
-                if text.endswith("�") and not out.finished:
-                    delta = ""  # an incomplete multi-byte character: wait for the next token
-                else:
-                    delta, emitted = text[len(emitted):], text
-                yield delta, out, len(all_ids)
-                if out.finished:
-                    return
+            finished = False
+            try:
+                while True:
+                    out: StepOutput = await queue.get()
+                    if first:
+                        first = False
+                        if recv_ids:
+                            await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
+                        if kv_in is not None:
+                            await self._release_at_producer(kv_in)  # the pages were pulled before the first output
+                    all_ids.extend(out.new_token_ids)
+                    text = self.tokenizer.decode(all_ids)
+                    if stops:
+                        cut = min((i for i in (text.find(x, max(0, len(emitted) - hold)) for x in stops) if i >= 0), default=-1)
+                        if cut >= 0:
+                            finished = True
+                            self.llm.abort(seq.seq_id)
+                            yield text[len(emitted):cut], StepOutput(out.seq_id, out.new_token_ids, True, "stop"), len(all_ids)
+                            return
+                    if text.endswith("�") and not out.finished:
+                        delta = ""  # an incomplete multi-byte character: wait for the next token
+                    elif stops and not out.finished:
+                        safe = max(len(emitted), len(text) - hold)
+                        delta, emitted = text[len(emitted):safe], text[:safe]
+                    else:
+                        delta, emitted = text[len(emitted):], text
+                    yield delta, out, len(all_ids)
+                    if out.finished:
+                        finished = True
+                        return
+            finally:
+                if not finished:
+                    self.llm.abort(seq.seq_id)   # the client went away: free the sequence's pages
 
         if "cornserve_hidden_states_forward_id" in xargs:
             hidden = None

@@ -83,9 +83,10 @@ class TPControl:
         self.publish_ms = 0.0
 
     # -- rank 0 -------------------------------------------------------------------------------------------
-    def publish(self, seqs: list[Sequence], stop: bool = False, beat: bool = False) -> None:
+    def publish(self, seqs: list[Sequence], stop: bool = False, beat: bool = False, aborts: list[str] | None = None) -> None:
         t0 = time.perf_counter()
-        dist.broadcast_object_list([{"stop": stop, "beat": beat, "seqs": [_pack(s) for s in seqs]}], src=0, group=self.ctl)
+        dist.broadcast_object_list([{"stop": stop, "beat": beat, "aborts": list(aborts or []), "seqs": [_pack(s) for s in seqs]}],
+                                   src=0, group=self.ctl)
         for s in seqs:
             for it in s.mm_items:
                 # a buffer of this GPU's own memory: the rows may sit in another process's slab
@@ -95,8 +96,8 @@ class TPControl:
         self.publish_ms += (time.perf_counter() - t0) * 1e3
 
     # -- other ranks -----------------------------------------------------------------------------------------
-    def receive(self) -> tuple[bool, list[Sequence]] | None:
-        """``(stop, new sequences)`` of the next engine step, or ``None`` for a keep-alive (no step)."""
+    def receive(self) -> tuple[bool, list[Sequence], list[str]] | None:
+        """``(stop, new sequences, aborted sequence ids)`` of the next engine step, or ``None`` for a keep-alive."""
         box: list[Any] = [None]
         dist.broadcast_object_list(box, src=0, group=self.ctl)
         msg = box[0]
@@ -112,7 +113,7 @@ class TPControl:
             s = Sequence(d["seq_id"], d["prompt_ids"], SamplingParams(**d["params"]), mm_items=items)
             s.positions, s.next_pos = d["positions"], d["next_pos"]
             seqs.append(s)
-        return bool(msg["stop"]), seqs
+        return bool(msg["stop"]), seqs, list(msg.get("aborts") or [])
 
 
 def follower_loop(engine: LLMEngine, ctl: TPControl) -> None:
@@ -121,9 +122,11 @@ def follower_loop(engine: LLMEngine, ctl: TPControl) -> None:
         got = ctl.receive()
         if got is None:
             continue
-        stop, seqs = got
+        stop, seqs, aborts = got
         if stop:
             return
+        for sid in aborts:
+            engine.abort(sid)
         for s in seqs:
             try:
                 engine.add_request(s)

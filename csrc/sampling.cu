@@ -266,3 +266,51 @@ CS_API int cs_sample_rows(const void* logits, long long ld, int rows, int V, con
       (const long long*)seed, (int*)draws, (int*)out);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
+
+// ---------------------------------------------------------------------------------------
+// OpenAI-style repetition control: logits[r][t] -= frequency[r] * count[r][t] + presence[r] * (count[r][t] > 0),
+// where count[r][t] is how often row r has generated token t so far.  Applied before the sampling kernel; the
+// counts are advanced by cs_count_tokens after it, both inside the decode graph.
+// ---------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) apply_penalties_kernel(float* logits, long long ld, const int* counts, long long ldc,
+                                                              const float* freq, const float* pres, int V) {
+  const int r = blockIdx.y;
+  const float f = freq[r], p = pres[r];
+  if (f == 0.f && p == 0.f) return;
+  float* row = logits + r * ld;
+  const int* crow = counts + r * ldc;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < V; t += gridDim.x * blockDim.x) {
+    const int c = crow[t];
+    if (c > 0) row[t] -= f * static_cast<float>(c) + p;
+  }
+}
+
+__global__ void count_tokens_kernel(int* counts, long long ldc, const int* tokens, const int* active, int rows, int V) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  if (active != nullptr && active[r] == 0) return;
+  const int t = tokens[r];
+  if (t >= 0 && t < V) counts[r * ldc + t] += 1;
+}
+}  // namespace
+
+CS_API int cs_apply_penalties(void* logits, long long ld, const void* counts, long long ldc, const void* freq,
+                              const void* pres, int rows, int V, void* stream) {
+  if (rows <= 0 || V <= 0) return 0;
+  if (logits == nullptr || counts == nullptr || freq == nullptr || pres == nullptr) return -1;
+  int bx = (V + 256 * 8 - 1) / (256 * 8);
+  if (bx < 1) bx = 1;
+  apply_penalties_kernel<<<dim3(bx, rows), 256, 0, (cudaStream_t)stream>>>((float*)logits, ld, (const int*)counts, ldc,
+                                                                           (const float*)freq, (const float*)pres, V);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}
+
+CS_API int cs_count_tokens(void* counts, long long ldc, const void* tokens, const void* active, int rows, int V,
+                           void* stream) {
+  if (rows <= 0) return 0;
+  if (counts == nullptr || tokens == nullptr) return -1;
+  count_tokens_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>((int*)counts, ldc, (const int*)tokens,
+                                                                          (const int*)active, rows, V);
+  return cudaGetLastError() == cudaSuccess ? 0 : -10;
+}

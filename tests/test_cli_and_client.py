@@ -33,7 +33,7 @@ class Config(AppConfig):
 
 async def serve(request: Request) -> AsyncIterator[OpenAIChatCompletionChunk]:
     content = [{"type": "image_url", "image_url": {"url": request.image_url}}, {"type": "text", "text": request.prompt}]
-    return await mllm(OpenAIChatCompletionRequest(model="cornserve-b200/tiny-vlm", ignore_eos=True, max_completion_tokens=6,
+    return await mllm(OpenAIChatCompletionRequest(model="cornserve-b200/tiny-vlm", ignore_eos=True, temperature=0.0, max_completion_tokens=6,
                                                   messages=[{"role": "user", "content": content}]))
 '''
 

@@ -32,7 +32,7 @@ class Config(AppConfig):
 
 async def serve(request: Request) -> AsyncIterator[OpenAIChatCompletionChunk]:
     content = [{"type": "image_url", "image_url": {"url": request.image_url}}, {"type": "text", "text": request.prompt}]
-    return await mllm(OpenAIChatCompletionRequest(model="cornserve-b200/tiny-vlm", ignore_eos=True,
+    return await mllm(OpenAIChatCompletionRequest(model="cornserve-b200/tiny-vlm", ignore_eos=True, temperature=0.0,
                                                   max_completion_tokens=request.max_completion_tokens,
                                                   messages=[{"role": "user", "content": content}]))
 '''

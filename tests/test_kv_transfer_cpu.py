@@ -19,7 +19,7 @@ def test_decode_executor_fetches_kv_pages_over_the_network(tmp_path, monkeypatch
         flow._wait_healthy(pp, procs[0])
         flow._wait_healthy(dp, procs[1])
         body = {"model": flow.MODEL, "messages": [{"role": "user", "content": " ".join(f"w{j}" for j in range(150))}],
-                "max_completion_tokens": 8, "ignore_eos": True, "request_id": "r0"}
+                "max_completion_tokens": 8, "ignore_eos": True, "temperature": 0, "request_id": "r0"}
         alone = flow._post(f"http://127.0.0.1:{dp}/v1/chat/completions", body)
         first = flow._post(f"http://127.0.0.1:{pp}/v1/chat/completions", body)
         rest = flow._post(f"http://127.0.0.1:{dp}/v1/chat/completions", {**body, "kv_transfer_params": first["kv_transfer_params"]})

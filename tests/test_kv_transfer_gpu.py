@@ -59,7 +59,7 @@ def test_decode_executor_pulls_kv_pages_from_prefill_executor(tmp_path, consumer
         _wait_healthy(dp, procs[1])
         for i, n_words in enumerate((5, 300)):   # one page, several pages
             body = {"model": MODEL, "messages": [{"role": "user", "content": " ".join(f"w{i}{j}" for j in range(n_words))}],
-                    "max_completion_tokens": 12, "ignore_eos": True, "request_id": f"req{i}"}
+                    "max_completion_tokens": 12, "ignore_eos": True, "temperature": 0, "request_id": f"req{i}"}
             alone = _post(f"http://127.0.0.1:{dp}/v1/chat/completions", body)
             first = _post(f"http://127.0.0.1:{pp}/v1/chat/completions", body)
             params = first["kv_transfer_params"]

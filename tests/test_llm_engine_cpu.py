@@ -114,7 +114,7 @@ def test_sampling_streams_are_reproducible_and_leave_greedy_requests_alone():
 def test_sampling_params_from_request_fields():
     p = SamplingParams.from_request({"temperature": 0.7, "top_p": 0.8, "top_k": 40, "seed": 3}, max_tokens=5)
     assert (p.temperature, p.top_p, p.top_k, p.seed, p.max_tokens, p.samples) == (0.7, 0.8, 40, 3, 5, True)
-    q = SamplingParams.from_request({"top_k": -1}, max_tokens=2)
+    q = SamplingParams.from_request({"top_k": -1, "temperature": 0}, max_tokens=2)
     assert (q.temperature, q.top_p, q.top_k, q.seed, q.samples) == (0.0, 1.0, 0, None, False)
 
 
@@ -207,3 +207,78 @@ def test_request_larger_than_the_page_pool_is_refused_not_queued():
         eng.add_request(Sequence("big", np.arange(300, dtype=np.int32) % 100, SamplingParams(max_tokens=8, ignore_eos=True)))
     ok = Sequence("small", np.arange(20, dtype=np.int32), SamplingParams(max_tokens=4, ignore_eos=True))
     assert len(eng.generate([ok])["small"]) == 4
+
+
+def _tiny_engine(**kw):
+    import torch
+
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine
+
+    torch.manual_seed(3)
+    cfg = LLMConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1, head_dim=32,
+                    intermediate_size=64, vocab_size=96, mrope_section=None)
+    return LLMEngine(QwenLLM(cfg).float().eval(), EngineConfig(num_pages=8, use_cuda_graph=False, max_model_len=1024, **kw))
+
+
+def test_frequency_and_presence_penalties_change_greedy_decoding_as_specified():
+    """With penalties the engine must produce exactly what a step-by-step restatement produces: greedy over
+    ``logits - frequency * count - presence * (count > 0)`` with counts over the tokens generated so far."""
+    import numpy as np
+    import torch
+
+    from cornserve.task_executors.llm.engine import SamplingParams, Sequence
+
+    prompt = np.arange(5, 25, dtype=np.int32)
+    eng = _tiny_engine(decode_burst=3)
+    plain = eng.generate([Sequence("a", prompt, SamplingParams(max_tokens=12, ignore_eos=True))])["a"]
+    pen = eng.generate([Sequence("b", prompt, SamplingParams(max_tokens=12, ignore_eos=True, frequency_penalty=1.5,
+                                                               presence_penalty=4.0))])["b"]
+    assert plain != pen, "random tiny models repeat themselves: penalties have to change the continuation"
+    # restatement: feed the prefix again for every token, apply the penalties on the host
+    ref_eng = _tiny_engine()
+    out: list[int] = []
+    for _ in range(12):
+        ids = np.concatenate([prompt, np.asarray(out, dtype=np.int32)])
+        seq = Sequence(f"r{len(out)}", ids, SamplingParams(max_tokens=1, ignore_eos=True))
+        ref_eng.add_request(seq)
+        batch = ref_eng._schedule_prefill()
+        logits = _last_logits(ref_eng, batch)
+        counts = torch.bincount(torch.as_tensor(out, dtype=torch.long), minlength=logits.numel()).float() if out else torch.zeros_like(logits)
+        out.append(int((logits - 1.5 * counts - 4.0 * (counts > 0)).argmax()) if len(out) else int(logits.argmax()))
+        ref_eng.blocks.free(seq.seq_id)   # scheduled by hand, so never in the running list: give the pages back
+    assert pen == out
+    # a batch that mixes penalised and plain requests keeps the plain ones unchanged
+    both = eng.generate([Sequence("c", prompt, SamplingParams(max_tokens=12, ignore_eos=True)),
+                         Sequence("d", prompt, SamplingParams(max_tokens=12, ignore_eos=True, frequency_penalty=1.5, presence_penalty=4.0))])
+    assert both["c"] == plain and both["d"] == pen
+
+
+def _last_logits(eng, batch):
+    """Logits of the last prompt token of a one-sequence prefill batch, computed through the model's own layers."""
+    import numpy as np
+    import torch
+
+    from cornserve import ops
+    from cornserve.models.qwen_llm import PAGE_SIZE, BatchMeta
+
+    (s, n), = batch
+    pages = eng.blocks.ensure(s.seq_id, n + 1)
+    ar = np.arange(n)
+    t = lambda a, dt=np.int32: torch.from_numpy(np.ascontiguousarray(np.asarray(a).astype(dt)))  # noqa: E731
+    bt = np.zeros((1, eng.max_blocks), np.int32)
+    bt[0, : len(pages)] = pages
+    m = BatchMeta(t(s.prompt_ids), t(s.positions), t(np.asarray(pages)[ar // PAGE_SIZE] * PAGE_SIZE + ar % PAGE_SIZE), t([0, n]), t([n]),
+                  t(bt[:, : n // PAGE_SIZE + 2]), t([n - 1]), n, False)
+    with torch.inference_mode():
+        h = eng.model.forward_hidden(m, eng.kv_caches, None)
+        return eng.model.compute_logits(ops.gather_rows(h, m.logits_idx))[0].float()
+
+
+def test_sampling_params_follow_the_openai_defaults():
+    from cornserve.task_executors.llm.engine import SamplingParams
+
+    assert SamplingParams.from_request({}).temperature == 1.0            # OpenAI: temperature defaults to 1
+    assert SamplingParams.from_request({}, 0.0).temperature == 0.0         # the model's generation config may say greedy
+    p = SamplingParams.from_request({"temperature": 0, "frequency_penalty": 0.5, "presence_penalty": None})
+    assert p.temperature == 0.0 and not p.samples and p.frequency_penalty == 0.5 and p.presence_penalty == 0.0 and p.penalized

@@ -71,7 +71,7 @@ def _serve(model_dir: Path, tp: int):
 
 
 def _chat(port: int, text: str, **extra) -> str:
-    body = {"model": "tiny-llm", "messages": [{"role": "user", "content": text}], "max_completion_tokens": 12, "ignore_eos": True, **extra}
+    body = {"model": "tiny-llm", "messages": [{"role": "user", "content": text}], "max_completion_tokens": 12, "ignore_eos": True, "temperature": 0, **extra}
     req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=json.dumps(body).encode(),
                                  headers={"Content-Type": "application/json"})
     with urllib.request.urlopen(req, timeout=120) as r:
@@ -99,6 +99,45 @@ def test_two_rank_executor_answers_like_one_rank(tmp_path):
     assert answers[2][:3] == answers[1][:3]
     assert answers[2][3] == answers[2][4]          # a seeded sampled request repeats on the two-rank executor
     assert answers[2][3] == answers[1][3]          # and draws the same stream as on one rank
+
+
+def _chat_full(port: int, text: str, **extra) -> dict:
+    # sampled with a fixed seed: a random tiny model decodes greedily into one repeated token, which is poor text
+    body = {"model": "tiny-llm", "messages": [{"role": "user", "content": text}], "max_completion_tokens": 48, "ignore_eos": True,
+            "temperature": 1.5, "seed": 11, **extra}
+    req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=120) as r:
+        return json.loads(r.read())
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("tp", [1, 2])
+def test_stop_strings_cut_the_answer_and_free_the_sequence(tmp_path, tp):
+    """A ``stop`` string ends the answer before its first occurrence with reason ``stop``; the sequence leaves the engine
+    on every rank (the follower of a two-rank executor included: the next requests still answer alike)."""
+    ckpt = _checkpoint(tmp_path)
+    proc, port = _serve(ckpt, tp)
+    try:
+        full = _chat_full(port, "tell me something")["choices"][0]
+        text = full["message"]["content"]
+        assert full["finish_reason"] == "length" and len(text) >= 6
+        stop = text[len(text) // 2: len(text) // 2 + 2]
+        cut = _chat_full(port, "tell me something", stop=[stop, "\x00never"])["choices"][0]
+        assert cut["finish_reason"] == "stop" and cut["message"]["content"] == text[: text.find(stop)]
+        again = _chat_full(port, "tell me something")["choices"][0]
+        assert again["message"]["content"] == text                    # the engine (all ranks) is in step after the abort
+        pen = _chat_full(port, "tell me something", frequency_penalty=1.5, presence_penalty=2.0)["choices"][0]
+        assert pen["finish_reason"] == "length"
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/stats", timeout=10) as r:
+            st = json.loads(r.read())
+        assert st["running"] == 0 and st["waiting"] == 0 and st["kv_pages_free"] == st["kv_pages"] - 1
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            proc.kill()
 
 
 def test_untied_lm_head_of_a_checkpoint_is_loaded(tmp_path, monkeypatch):

@@ -26,7 +26,7 @@ class Config(AppConfig):
     tasks = {"omni": omni}
 
 async def serve(request: Request) -> AsyncIterator[OpenAIChatCompletionChunk]:
-    return await omni(OmniInput(model="cornserve-b200/tiny-omni", ignore_eos=True, max_completion_tokens=6, return_audio=True,
+    return await omni(OmniInput(model="cornserve-b200/tiny-omni", ignore_eos=True, temperature=0.0, max_completion_tokens=6, return_audio=True,
                                 messages=[{"role": "user", "content": request.prompt}]))
 '''
 
