@@ -32,3 +32,7 @@ KIND_EXECUTION_DESCRIPTOR = "ExecutionDescriptor"
 KIND_UNIT_TASK_INSTANCE = "UnitTaskInstance"
 KIND_UNIT_TASK_PROFILE = "UnitTaskProfile"
 KIND_LATEST_TASKLIB_RV = "LatestTasklibRV"
+# what is running where, so that a restarted control plane can take its processes over again
+KIND_TASK_MANAGER_RECORD = "TaskManagerRecord"
+KIND_EXECUTOR_RECORD = "ExecutorRecord"
+KIND_SIDECAR_RECORD = "SidecarRecord"

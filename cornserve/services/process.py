@@ -59,6 +59,41 @@ class ManagedProcess:
             return ""
 
 
+class _AdoptedPopen:
+    """The part of ``subprocess.Popen`` that :class:`ManagedProcess` uses, for a process this one did not start (an
+    executor that outlived the control plane that launched it)."""
+
+    def __init__(self, pid: int):
+        import psutil
+
+        self.pid = pid
+        try:
+            self._ps = psutil.Process(pid)
+            self._created = self._ps.create_time()
+        except psutil.Error:
+            self._ps = None
+        self.returncode: int | None = None
+
+    def poll(self) -> int | None:
+        import psutil
+
+        if self._ps is None:
+            self.returncode = self.returncode if self.returncode is not None else -1
+            return self.returncode
+        try:
+            if self._ps.is_running() and self._ps.status() != psutil.STATUS_ZOMBIE:
+                return None
+        except psutil.Error:
+            pass
+        self.returncode = self.returncode if self.returncode is not None else -1
+        return self.returncode
+
+
+def adopt(name: str, pid: int, port: int = 0, log_path: str = "") -> ManagedProcess:
+    """A :class:`ManagedProcess` around an already running process (same process-group conventions as :func:`spawn`)."""
+    return ManagedProcess(name, _AdoptedPopen(pid), Path(log_path or "/dev/null"), port)  # type: ignore[arg-type]
+
+
 def spawn(name: str, argv: list[str], env: dict[str, str] | None = None, port: int = 0,
           log_dir: str | None = None) -> ManagedProcess:
     """Start ``argv`` in its own process group with stdout/stderr going to a per-process log file."""

@@ -19,7 +19,8 @@ from dataclasses import dataclass, field
 
 import grpc
 
-from ...constants import SIDECAR_HEALTHY_TIMEOUT_S, TASK_DISPATCHER_GRPC_URL
+from ...constants import (KIND_EXECUTOR_RECORD, KIND_SIDECAR_RECORD, KIND_TASK_MANAGER_RECORD, SIDECAR_HEALTHY_TIMEOUT_S,
+                          TASK_DISPATCHER_GRPC_URL)
 from ...task_executors.profile import UnitTaskProfileManager
 from ...logging import get_logger
 from ...task.base import UnitTask
@@ -79,7 +80,7 @@ class ResourceManager:
     # -- start-up ----------------------------------------------------------------------------------------------
     @classmethod
     async def init(cls, num_gpus: int | None = None, spawn_sidecars: bool = True, sidecar_slab_bytes: int | None = None,
-                   sidecar_device: str | None = None, **kw) -> "ResourceManager":
+                   sidecar_device: str | None = None, adopt: bool = False, **kw) -> "ResourceManager":
         """Enumerate the GPUs of this box, start one sidecar per GPU (ranks 0..n-1) and wait until every
         sidecar reports ``ALL_GOOD``."""
         n = num_gpus if num_gpus is not None else detect_num_gpus()
@@ -87,10 +88,27 @@ class ResourceManager:
             raise RuntimeError("No GPUs found (set CORNSERVE_NUM_GPUS to run a CPU-only deployment)")
         resource = Resource.single_node(n)
         procs = []
+        store = (kw.get("registry") or TaskRegistry()).store if adopt else None
+        if kw.get("registry") is None and adopt:
+            kw["registry"] = TaskRegistry(store)
+        adopted_pids: list[int] = []
         if spawn_sidecars:
             slab = sidecar_slab_bytes or int(os.environ.get("SIDECAR_SHM_SIZE", str(1 << 30)))
             for r in range(n):
-                procs.append(sidecar_launch.spawn_sidecar(r, n, slab, device=sidecar_device))
+                # a sidecar left running by a previous control plane (same rank, same ports) is taken over as it is:
+                # executors that are adopted below have its slab mapped
+                if adopt and await asyncio.to_thread(sidecar_launch.check_health, r, 1.0) == 0:   # HEALTH_ALL_GOOD
+                    try:
+                        adopted_pids.append(int(store.get(KIND_SIDECAR_RECORD, f"sidecar-{r}").spec["pid"]))
+                        logger.info("Adopted sidecar %d (pid %d)", r, adopted_pids[-1])
+                        continue
+                    except Exception:  # noqa: BLE001  (answers but is not ours to manage: start none, it holds the port)
+                        logger.warning("Sidecar %d answers but has no record; using it without managing it", r)
+                        continue
+                p = sidecar_launch.spawn_sidecar(r, n, slab, device=sidecar_device)
+                procs.append(p)
+                if store is not None:
+                    store.update(KIND_SIDECAR_RECORD, f"sidecar-{r}", {"pid": p.pid, "rank": r}, True)
             ok = await asyncio.to_thread(sidecar_launch.wait_all_good, list(range(n)), SIDECAR_HEALTHY_TIMEOUT_S)
             if not ok:
                 for p in procs:
@@ -98,8 +116,66 @@ class ResourceManager:
                 raise RuntimeError("Sidecars did not become healthy")
             logger.info("All %d sidecars are healthy", n)
         rm = cls(resource, sidecar_processes=procs, **kw)
+        rm.adopted_sidecar_pids = adopted_pids
+        rm.persist = adopt
+        if adopt:
+            await rm.adopt_running()
         logger.info("Cluster:\n%s", resource.render())
         return rm
+
+    # -- taking over what a previous control plane left running ---------------------------------------------------------
+    async def adopt_running(self) -> list[str]:
+        """Rebuild the task managers of unit tasks whose executors are still running (the control plane was restarted,
+        its executors and sidecars were not): the recorded GPUs are marked as owned again, every executor that answers
+        ``/health`` is taken over, the task dispatchers are told.  Returns the adopted task instance names.  The
+        reference leaves this as a TODO (python/cornserve/services/resource_manager/grpc.py:44-46)."""
+        store = self.registry.store
+        records = await asyncio.to_thread(store.list, KIND_TASK_MANAGER_RECORD)
+        executors = await asyncio.to_thread(store.list, KIND_EXECUTOR_RECORD)
+        adopted = []
+        for rec in records:
+            name, spec = rec.name, rec.spec
+            try:
+                task = await self.registry.get_task_instance(name)
+                gpus = [g for g in self.resource.gpus if g.global_rank in set(spec["gpus"])]
+                if len(gpus) != len(spec["gpus"]) or any(not g.is_free for g in gpus):
+                    raise RuntimeError("its GPUs are not available")
+                mine = {e.name: e.spec for e in executors if e.spec.get("task_manager_id") == spec["tm_id"]}
+                for g in gpus:
+                    g.allocate_to(spec["tm_id"])
+                port = free_port()
+                st = TaskManagerState(spec["tm_id"], name, task, f"127.0.0.1:{port}", gpus)
+                st.servicer = TaskManagerServicer(self.registry, {"profile_manager": self.profiles, **self.tm_manager_kwargs})
+                from ..task_manager.manager import TaskManager
+
+                st.servicer.manager = await TaskManager.adopt(spec["tm_id"], task, gpus, mine,
+                                                              **{"profile_manager": self.profiles, **self.tm_manager_kwargs})
+                st.server = await start_server(port, st.servicer)
+                st.channel = grpc.aio.insecure_channel(st.url, interceptors=grpc_client_interceptors())
+                st.stub = task_manager_pb2_grpc.TaskManagerStub(st.channel)
+                await asyncio.wait_for(st.channel.channel_ready(), timeout=60)
+                self.task_managers[name] = st
+                await self._notify_dispatchers(deployed=True, name=name, url=st.url)
+                adopted.append(name)
+                logger.info("Adopted unit task %s with %d executors", name, len(st.servicer.manager.executors))
+            except Exception as e:  # noqa: BLE001
+                logger.warning("Could not adopt unit task %s: %s; dropping its record", name, e)
+                for g in self.resource.gpus:
+                    if g.owner == spec.get("tm_id"):
+                        g.free()
+                await asyncio.to_thread(self._drop_record, name)
+        return adopted
+
+    def _drop_record(self, name: str) -> None:
+        try:
+            self.registry.store.delete(KIND_TASK_MANAGER_RECORD, name)
+        except Exception:  # noqa: BLE001
+            pass
+
+    def _save_record(self, st: "TaskManagerState") -> None:
+        if getattr(self, "persist", False):
+            self.registry.store.update(KIND_TASK_MANAGER_RECORD, st.task_instance_name,
+                                       {"tm_id": st.id, "gpus": [g.global_rank for g in st.gpus]}, True)
 
     # -- deploy / teardown ----------------------------------------------------------------------------------------
     async def deploy_unit_task(self, task_instance_name: str, task: UnitTask) -> None:
@@ -149,6 +225,7 @@ class ResourceManager:
             resp = await st.stub.RegisterTask(req)
             if resp.status != common_pb2.STATUS_OK:
                 raise RuntimeError("RegisterTask returned an error status")
+            await asyncio.to_thread(self._save_record, st)
             return st
         except Exception:
             logger.exception("Failed to start task manager %s; releasing its GPUs", tm_id)
@@ -156,6 +233,7 @@ class ResourceManager:
             raise
 
     async def _stop_task_manager(self, st: TaskManagerState) -> None:
+        await asyncio.to_thread(self._drop_record, st.task_instance_name)
         try:
             if st.stub is not None:
                 await asyncio.wait_for(st.stub.Shutdown(task_manager_pb2.ShutdownRequest()), timeout=60)
@@ -232,6 +310,7 @@ class ResourceManager:
                 await st.stub.UpdateResources(req)
                 st.gpus = st.gpus[:-count]
                 self.resource.release(removed)
+        await asyncio.to_thread(self._save_record, st)
         logger.info("Scaled %s by %+d GPUs\n%s", task_instance_name, num_gpus, self.resource.render())
 
     async def reconcile(self, task_instance_name: str, target_load: float) -> str:
@@ -291,11 +370,17 @@ class ResourceManager:
             self.task_managers.clear()
         for ch in self._dispatcher_channels.values():
             await ch.close()
-        for p in self.sidecars:
+        for pid in [p.pid for p in self.sidecars] + list(getattr(self, "adopted_sidecar_pids", [])):
             try:
-                os.killpg(p.pid, 15)
+                os.killpg(pid, 15)
             except (ProcessLookupError, PermissionError):
                 pass
+        if getattr(self, "persist", False):
+            for r in range(len(self.resource.gpus)):
+                try:
+                    self.registry.store.delete(KIND_SIDECAR_RECORD, f"sidecar-{r}")
+                except Exception:  # noqa: BLE001
+                    pass
         for p in self.sidecars:
             try:
                 p.wait(timeout=10)

@@ -20,11 +20,11 @@ from dataclasses import dataclass, field
 
 import aiohttp
 
-from ...constants import EXECUTOR_HEALTH_POLL_S, EXECUTOR_HEALTHY_TIMEOUT_S
+from ...constants import EXECUTOR_HEALTH_POLL_S, EXECUTOR_HEALTHY_TIMEOUT_S, KIND_EXECUTOR_RECORD
 from ...task_executors.profile import UnitTaskProfile, UnitTaskProfileManager
 from ...logging import get_logger
 from ...task.base import UnitTask
-from ..process import ManagedProcess, free_port, spawn, terminate, to_strict_name
+from ..process import ManagedProcess, adopt, free_port, spawn, terminate, to_strict_name
 from ..resource import GPU
 
 logger = get_logger(__name__)
@@ -94,6 +94,54 @@ class TaskManager:
         await tm.update_resources(add_gpus=gpus)
         return tm
 
+    # -- records: what a restarted control plane needs to find this task's executors again ---------------------------
+    def _record(self, dep: ExecutorDeployment) -> None:
+        if dep.process is None:
+            return
+        try:
+            self.profiles.store.update(KIND_EXECUTOR_RECORD, dep.executor_id, {
+                "task_manager_id": self.id, "url": dep.url, "pid": dep.process.pid, "log_path": str(dep.process.log_path),
+                "gpus": [[g.node, g.global_rank, g.local_rank] for g in dep.gpus]}, True)
+        except Exception as e:  # noqa: BLE001
+            logger.warning("could not record executor %s: %s", dep.executor_id, e)
+
+    def _forget(self, executor_id: str) -> None:
+        try:
+            self.profiles.store.delete(KIND_EXECUTOR_RECORD, executor_id)
+        except Exception:  # noqa: BLE001
+            pass
+
+    @classmethod
+    async def adopt(cls, task_manager_id: str, task: UnitTask, gpus: list[GPU], records: dict[str, dict], **kw) -> "TaskManager":
+        """A task manager around executors that are already running (their control plane was restarted): every recorded
+        executor that still answers ``/health`` is taken over as it is, the others are forgotten and their GPUs get new
+        executors."""
+        tm = cls(task_manager_id, task, **kw)
+        client = await tm._client()
+        by_rank = {g.global_rank: g for g in gpus}
+        for eid, rec in records.items():
+            mine = [by_rank[r[1]] for r in rec.get("gpus", []) if r[1] in by_rank]
+            ok = False
+            if len(mine) == len(rec.get("gpus", [])) and mine:
+                try:
+                    async with client.get(f"{rec['url']}/health", timeout=aiohttp.ClientTimeout(total=2)) as r:
+                        ok = r.status == 200
+                except (aiohttp.ClientError, asyncio.TimeoutError):
+                    ok = False
+            if ok:
+                proc = adopt(eid, int(rec["pid"]), log_path=rec.get("log_path", ""))
+                tm.executors[eid] = ExecutorDeployment(eid, rec["url"], mine, proc)
+                logger.info("Adopted task executor %s at %s (pid %s)", eid, rec["url"], rec["pid"])
+            else:
+                logger.warning("Recorded task executor %s is gone; its GPUs will get a new one", eid)
+                try:
+                    os.killpg(int(rec["pid"]), 15)   # whatever is left of it
+                except (ProcessLookupError, PermissionError, KeyError, ValueError):
+                    pass
+                tm._forget(eid)
+        await tm.update_resources(add_gpus=gpus)   # GPUs without a live executor are filled as on a first start
+        return tm
+
     async def _client(self) -> aiohttp.ClientSession:
         if self._http is None or self._http.closed:
             self._http = aiohttp.ClientSession(trace_configs=_trace_configs(), timeout=aiohttp.ClientTimeout(total=5))
@@ -159,6 +207,7 @@ class TaskManager:
                 await terminate(proc, 2.0)
             raise
         self.executors[executor_id] = dep
+        self._record(dep)
         logger.info("Task executor %s is healthy at %s", executor_id, url)
         return dep
 
@@ -182,6 +231,7 @@ class TaskManager:
         dep = self.executors.pop(executor_id, None)
         if dep is None:
             return
+        self._forget(executor_id)
         if dep.process is not None:
             await terminate(dep.process)
             logger.info("Task executor %s stopped (log kept at %s)", executor_id, dep.process.log_path)
