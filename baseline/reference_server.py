@@ -125,6 +125,7 @@ def encoder_main(a: argparse.Namespace) -> None:
                 return
             forward(*box[0])
 
+    print(f"encoder replica {a.replica} rank {a.rank}: tower on {torch.cuda.get_device_name()}", flush=True)
     processor = ref.ModalityProcessor(str(Path(a.workdir) / "encoder_model"))
     slab = torch.from_file(a.slab, shared=True, size=a.slab_bytes, dtype=torch.uint8)
     copy_stream = torch.cuda.Stream()
@@ -241,6 +242,7 @@ def llm_main(a: argparse.Namespace) -> None:
         gpu_memory_utilization=a.gpu_util, max_num_seqs=256, load_format="dummy", enable_prompt_embeds=True,
         skip_tokenizer_init=True, trust_remote_code=True, dtype="bfloat16", generation_config="vllm",
         max_model_len=8192, disable_log_stats=True))
+    print(f"llm replica {a.replica}: engine ready", flush=True)
     conn = Client(("127.0.0.1", a.front_port), authkey=AUTH)
     send_lock = threading.Lock()
     stats = {"h2d_bytes": 0, "d2h_bytes": 0, "requests": 0}
@@ -380,13 +382,16 @@ class Front:
                 init_port = s.getsockname()[1]
             gpus = "0" if a.share_gpu else ",".join(str(r * et + i) for i in range(et))
             for k in range(et):
-                env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus)
+                env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus, GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo")
                 log = open(work / f"encoder_{r}_{k}.log", "w")
                 self.procs.append(subprocess.Popen(base + ["--role", "encoder", "--replica", str(r), "--rank", str(k), "--world", str(et),
                                                            "--init-port", str(init_port), "--slab", slabs[r]], env=env, stdout=log, stderr=subprocess.STDOUT))
         for r in range(R):
             gpus = "0" if a.share_gpu else ",".join(str(R * et + r * lt + i) for i in range(lt))
-            env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus)
+            # no network here: vLLM must not look for its address through a route to the outside or a host name that
+            # does not resolve (its torch.distributed rendezvous then waits for ever)
+            env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus, VLLM_HOST_IP="127.0.0.1", GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo",
+                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1")
             log = open(work / f"llm_{r}.log", "w")
             util = 0.80 if a.share_gpu else 0.93
             self.procs.append(subprocess.Popen(base + ["--role", "llm", "--replica", str(r), "--world", str(lt), "--slab", ",".join(slabs),

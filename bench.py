@@ -139,6 +139,7 @@ class ClockSampler:
 # the deployment under test (this repository's arm)
 # ----------------------------------------------------------------------------------------------------------------------
 def wait_http(url: str, proc: subprocess.Popen, timeout_s: float, what: str) -> None:
+    import urllib.error
     import urllib.request
 
     deadline = time.time() + timeout_s
@@ -149,6 +150,10 @@ def wait_http(url: str, proc: subprocess.Popen, timeout_s: float, what: str) -> 
             with urllib.request.urlopen(url, timeout=2) as r:
                 if r.status == 200:
                     return
+        except urllib.error.HTTPError as e:
+            if e.code == 500:   # the service says that it cannot become healthy (a worker of it died)
+                raise RuntimeError(f"{what} reports a failure: {e.read().decode(errors='replace')[:300]}") from None
+            time.sleep(0.5)
         except Exception:  # noqa: BLE001
             time.sleep(0.5)
     raise TimeoutError(f"{what} did not answer {url} within {timeout_s:.0f} s")
@@ -299,7 +304,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
 
     layout = LAYOUTS[max(k for k in LAYOUTS if k <= world)]
     model = TINY if args.small else MODEL
-    tmp = Path(args.keep_logs or tempfile.mkdtemp(prefix="cornserve-bench-"))
+    tmp = Path(args.keep_logs or tempfile.mkdtemp(prefix="cornserve-bench-")).resolve()
     (tmp / "logs").mkdir(parents=True, exist_ok=True)
     port = free_port()
     env = dict(os.environ, CORNSERVE_LOG_DIR=str(tmp / "logs"), CORNSERVE_STORE_PATH=str(tmp / "store.sqlite"),
@@ -317,7 +322,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
     gateway = f"http://127.0.0.1:{port}"
     sampler = ClockSampler()
     try:
-        wait_http(f"{gateway}/health", cluster, 300, "the control plane")
+        wait_http(f"{gateway}/health", cluster, 240, "the control plane")
         t0 = time.time()
         app_id, executors = asyncio.run(deploy_ours(gateway, model, layout, args.small))
         deploy_s = time.time() - t0
@@ -461,7 +466,7 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
     if not (ref_root / "cornserve").is_dir():
         return {"impl": "reference", "unavailable": "the reference package is not installed under baseline/_ref"}
     layout = LAYOUTS[max(k for k in LAYOUTS if k <= world)]
-    tmp = Path(args.keep_logs or tempfile.mkdtemp(prefix="cornserve-refbench-"))
+    tmp = Path(args.keep_logs or tempfile.mkdtemp(prefix="cornserve-refbench-")).resolve()
     tmp.mkdir(parents=True, exist_ok=True)
     port = free_port()
     # the server's import path holds the reference package and never this repository (both packages are called cornserve)
@@ -481,14 +486,18 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
     sampler = ClockSampler()
 
     def tail() -> str:
-        try:
-            return " | ".join((tmp / "reference_server.log").read_text(errors="replace").splitlines()[-6:])[-900:]
-        except OSError:
-            return ""
+        out = []
+        for p in [tmp / "reference_server.log", *sorted(tmp.glob("llm_*.log")), *sorted(tmp.glob("encoder_*.log"))]:
+            try:
+                lines = [ln for ln in p.read_text(errors="replace").splitlines() if ln.strip()]
+                out.append(f"{p.name}: " + " | ".join(lines[-4:])[-400:])
+            except OSError:
+                pass
+        return " || ".join(out)[-1500:]
 
     try:
         try:
-            wait_http(f"{base}/health", proc, 600, "the reference server")
+            wait_http(f"{base}/health", proc, 420, "the reference server")
         except Exception as e:  # noqa: BLE001
             return {"impl": "reference", "unavailable": f"the reference arm did not start: {e}; log tail: {tail()}"}
         probe = ExecutorProbe([base])

@@ -67,7 +67,7 @@ class LocalCluster:
         kw = {"sidecar_slab_bytes": self.slab} if self.slab else {}
         # adopt=True: sidecars and executors that a previous control plane over the same store left running are taken
         # over instead of being started again
-        rm = await ResourceManager.init(num_gpus=n, sidecar_device="cpu" if cpu else "cuda", registry=registry, adopt=True,
+        rm = await ResourceManager.init(num_gpus=n, sidecar_device="cpu" if cpu else None, registry=registry, adopt=True,
                                         dispatcher_urls=[td_grpc_addr], tm_manager_kwargs=self.tm_kwargs, **kw)
         rm_addr = f"127.0.0.1:{free_port()}"
         rm_server = await start_rm(rm, rm_addr)

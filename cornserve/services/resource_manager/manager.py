@@ -105,15 +105,24 @@ class ResourceManager:
                     except Exception:  # noqa: BLE001  (answers but is not ours to manage: start none, it holds the port)
                         logger.warning("Sidecar %d answers but has no record; using it without managing it", r)
                         continue
-                p = sidecar_launch.spawn_sidecar(r, n, slab, device=sidecar_device)
+                from ...constants import LOG_DIR
+
+                os.makedirs(LOG_DIR, exist_ok=True)
+                p = sidecar_launch.spawn_sidecar(r, n, slab, device=sidecar_device, log_path=os.path.join(LOG_DIR, f"sidecar-{r}.log"))
                 procs.append(p)
                 if store is not None:
                     store.update(KIND_SIDECAR_RECORD, f"sidecar-{r}", {"pid": p.pid, "rank": r}, True)
-            ok = await asyncio.to_thread(sidecar_launch.wait_all_good, list(range(n)), SIDECAR_HEALTHY_TIMEOUT_S)
+            ok = await asyncio.to_thread(sidecar_launch.wait_all_good, list(range(n)), SIDECAR_HEALTHY_TIMEOUT_S, procs)
             if not ok:
                 for p in procs:
                     p.terminate()
-                raise RuntimeError("Sidecars did not become healthy")
+                tails = []
+                for r in range(n):
+                    try:
+                        tails.append(f"sidecar-{r}: " + " | ".join(open(os.path.join(LOG_DIR, f"sidecar-{r}.log"), errors="replace").read().splitlines()[-5:]))
+                    except OSError:
+                        pass
+                raise RuntimeError("Sidecars did not become healthy\n" + "\n".join(tails))
             logger.info("All %d sidecars are healthy", n)
         rm = cls(resource, sidecar_processes=procs, **kw)
         rm.adopted_sidecar_pids = adopted_pids

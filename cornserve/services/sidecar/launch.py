@@ -35,13 +35,17 @@ def check_health(rank: int, timeout_s: float = 1.0) -> int | None:
         return None
 
 
-def wait_all_good(ranks: list[int], timeout_s: float = 300.0) -> bool:
+def wait_all_good(ranks: list[int], timeout_s: float = 300.0, procs: list | None = None) -> bool:
+    """Wait until every listed sidecar reports ``ALL_GOOD``.  With ``procs`` (the ``Popen`` objects of sidecars started
+    for this wait) the wait ends at once when one of them has exited: a sidecar that died will never answer."""
     deadline = time.monotonic() + timeout_s
     pending = set(ranks)
     while pending and time.monotonic() < deadline:
         for r in list(pending):
             if check_health(r) == sidecar_pb2.HealthStatus.HEALTH_ALL_GOOD:
                 pending.discard(r)
+        if pending and procs and any(p.poll() is not None for p in procs):
+            return False
         if pending:
             time.sleep(0.2)
     return not pending

@@ -396,7 +396,10 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
 def pick_device(rank: int) -> torch.device:
     want = os.environ.get(DEVICE_ENV)
     if want:
-        return torch.device(want)
+        dev = torch.device(want)
+        if dev.type == "cuda" and dev.index is None:   # "cuda" alone means this sidecar's own GPU
+            dev = torch.device("cuda", rank % max(torch.cuda.device_count(), 1))
+        return dev
     if torch.cuda.is_available():
         return torch.device("cuda", rank % torch.cuda.device_count())
     return torch.device("cpu")

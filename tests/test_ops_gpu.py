@@ -676,3 +676,38 @@ def test_packed_attention_windows_match_unpacked():
     one = torch.tensor([0, Tn], dtype=torch.int32)
     bounded = ops.attention_varlen(qc[:Tn], kc[:Tn], vc[:Tn], one, one, Tn, row_bounds=(torch.from_numpy(lo[:Tn]), torch.from_numpy(hi[:Tn])))
     assert torch.allclose(plain, bounded, atol=1e-4)
+
+
+@pytest.mark.parametrize("nbytes,src_off,dst_off", [(1196 * 3584 * 2, 0, 0), (4096 + 5, 0, 0), (777, 16, 32), (100_003, 3, 0),
+                                                    (64 << 20, 0, 256), (15, 0, 0)])
+def test_push_bytes_is_an_exact_copy(nbytes, src_off, dst_off):
+    """The sidecar's copy kernel: vector path, ragged tail and misaligned pointers, bit for bit; bytes around the
+    destination stay untouched."""
+    g = torch.Generator(device=DEV).manual_seed(nbytes)
+    src_buf = torch.randint(0, 256, (nbytes + src_off + 64,), device=DEV, dtype=torch.uint8, generator=g)
+    dst_buf = torch.full((nbytes + dst_off + 64,), 0xAB, device=DEV, dtype=torch.uint8)
+    src, dst = src_buf[src_off: src_off + nbytes], dst_buf[dst_off: dst_off + nbytes]
+    ops.push_bytes_(dst, src)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src)
+    assert bool((dst_buf[:dst_off] == 0xAB).all()) and bool((dst_buf[dst_off + nbytes:] == 0xAB).all())
+
+
+def test_penalties_and_token_counts_match_the_restatement():
+    torch.manual_seed(5)
+    rows, V = 37, 152064
+    logits = torch.randn(rows, V + 64, device=DEV)[:, :V]            # a strided view, as the padded lm_head gives
+    counts = torch.zeros(rows, V, device=DEV, dtype=torch.int32)
+    idx = torch.randint(0, V, (rows, 50), device=DEV)
+    counts.scatter_add_(1, idx, torch.ones_like(idx, dtype=torch.int32))
+    freq = torch.rand(rows, device=DEV) * 2
+    pres = torch.rand(rows, device=DEV) * 3
+    freq[3] = pres[3] = 0.0
+    want = ops.apply_penalties_(logits.cpu().clone(), counts.cpu(), freq.cpu(), pres.cpu())
+    got = ops.apply_penalties_(logits, counts, freq, pres)
+    torch.testing.assert_close(got.cpu(), want, rtol=1e-6, atol=1e-6)
+    toks = torch.randint(0, V, (rows,), device=DEV, dtype=torch.int32)
+    active = (torch.arange(rows, device=DEV) % 3 != 0).to(torch.int32)
+    want_c = ops.count_tokens_(counts.cpu().clone(), toks.cpu(), active.cpu())
+    ops.count_tokens_(counts, toks, active)
+    assert torch.equal(counts.cpu(), want_c)
