@@ -56,6 +56,7 @@ class LLMConfig:
     vision_start_token_id: int = 151652
     eos_token_id: int = 151645
     spatial_merge_size: int = 2
+    tokens_per_second: float | None = None   # Qwen2.5-VL: temporal positions of videos are in units of 1 / this; None = per frame
 
     def __post_init__(self):
         if self.head_dim is None:
@@ -76,6 +77,8 @@ class LLMConfig:
         if "rope_theta" in rs:
             kw["rope_theta"] = rs["rope_theta"]
         mt = t.get("model_type", cfg.get("model_type", ""))
+        if "qwen2_5_vl" in cfg.get("model_type", "") or "qwen2_5_vl" in mt or "qwen2_5_omni" in cfg.get("model_type", ""):
+            kw.setdefault("tokens_per_second", float((cfg.get("vision_config") or {}).get("tokens_per_second", 2.0)))
         if "qwen3" in mt:
             kw.setdefault("qk_norm", True)
             kw.setdefault("attention_bias", t.get("attention_bias", False))

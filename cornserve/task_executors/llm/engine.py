@@ -76,6 +76,7 @@ class MMItem:
     embeds: torch.Tensor
     offset: int
     grid_thw: tuple[int, int, int] | None = None
+    second_per_grid: float | None = None   # videos: seconds between two temporal grid steps (Qwen2.5-VL scales time by it)
 
 
 @dataclass
@@ -238,9 +239,15 @@ class LLMEngine:
         if seq.positions is None:
             grids = [it.grid_thw for it in seq.mm_items if it.grid_thw is not None]
             if grids:
+                # videos of Qwen2.5-VL advance the temporal index by seconds_per_grid * tokens_per_second per grid
+                # step (1.0 s and 2 tokens/s unless the processor says otherwise); images are unaffected
+                spg = [it.second_per_grid for it in seq.mm_items if it.grid_thw is not None]
+                timed = self.mcfg.tokens_per_second is not None
                 seq.positions, seq.next_pos = mrope_positions(
                     seq.prompt_ids, grids, self.mcfg.image_token_id, self.mcfg.video_token_id,
-                    self.mcfg.spatial_merge_size)
+                    self.mcfg.spatial_merge_size,
+                    second_per_grid=[1.0 if v is None else float(v) for v in spg] if timed else None,
+                    tokens_per_second=float(self.mcfg.tokens_per_second or 2.0))
             else:
                 T = seq.prompt_len
                 seq.positions = np.broadcast_to(np.arange(T, dtype=np.int32)[None], (3, T)).copy()

@@ -406,9 +406,14 @@ class LLMServer:
         out: list[int] = []
         items: list[MMItem] = []
         prev = 0
-        for (pos, _), (rows, grid) in zip(marks, embeds):
+        for (pos, modality), (rows, grid), part in zip(marks, embeds, parts):
             out += ids[prev:pos]
-            items.append(MMItem(rows, len(out), grid))
+            spg = None
+            if modality == "video":
+                # seconds per temporal grid step = frames merged per step / sampling rate (Hugging Face: fps 2 -> 1.0 s)
+                fps = float((part.get(part["type"]) or {}).get("fps") or body.get("video_fps") or 2.0)
+                spg = float((self.hf_cfg.get("vision_config") or {}).get("temporal_patch_size", 2)) / fps
+            items.append(MMItem(rows, len(out), grid, spg))
             out += [ids[pos]] * rows.shape[0]
             prev = pos + 1
         out += ids[prev:]

@@ -68,7 +68,7 @@ def agree_on_min(value: int, group: ParallelGroup) -> int:
 def _pack(seq: Sequence) -> dict[str, Any]:
     return {"seq_id": seq.seq_id, "prompt_ids": np.asarray(seq.prompt_ids), "params": dataclasses.asdict(seq.params),
             "positions": seq.positions, "next_pos": seq.next_pos,
-            "mm": [(it.offset, it.grid_thw, tuple(it.embeds.shape)) for it in seq.mm_items]}
+            "mm": [(it.offset, it.grid_thw, tuple(it.embeds.shape), it.second_per_grid) for it in seq.mm_items]}
 
 
 class TPControl:
@@ -106,10 +106,10 @@ class TPControl:
         seqs = []
         for d in msg["seqs"]:
             items = []
-            for offset, grid, shape in d["mm"]:
+            for offset, grid, shape, spg in d["mm"]:
                 rows = torch.empty(shape, device=self.group.device, dtype=self.dtype)
                 dist.broadcast(rows, src=0)
-                items.append(MMItem(rows, offset, grid))
+                items.append(MMItem(rows, offset, grid, spg))
             s = Sequence(d["seq_id"], d["prompt_ids"], SamplingParams(**d["params"]), mm_items=items)
             s.positions, s.next_pos = d["positions"], d["next_pos"]
             seqs.append(s)

@@ -175,18 +175,39 @@ def iter_safetensors(model_id: str, required_prefixes: list[str] | None = None, 
                 yield out, f.get_tensor(name)
 
 
+_BUFFER_SUFFIXES = ("inv_freq", "rotary_emb.inv_freq", "position_ids", "num_batches_tracked")
+
+
 def load_model_weights(model: torch.nn.Module, model_id: str, required_prefixes: list[str], strict: bool = True,
                        ignored_prefixes: list[str] | None = None, strip_prefixes: bool = True) -> bool:
     """Load checkpoint tensors through ``model.load_weights``.  Returns ``False`` (leaving the random
     initialisation in place) when the model has no weights on disk and random init is allowed."""
     if not has_weights(model_id):
-        if os.environ.get("CORNSERVE_ALLOW_RANDOM_INIT", "1") != "1":
-            raise FileNotFoundError(f"No safetensors found for {model_id}")
+        # serving random weights is for benchmarks and tests, which ask for it; a mistyped model id must not do it
+        if os.environ.get("CORNSERVE_ALLOW_RANDOM_INIT", "0") != "1":
+            raise FileNotFoundError(f"No safetensors found for {model_id} (set CORNSERVE_ALLOW_RANDOM_INIT=1 to serve "
+                                    "randomly initialised weights of its architecture)")
         logger.warning("No checkpoint for %s on this machine: keeping randomly initialised weights", model_id)
         return False
-    loaded = model.load_weights(iter_safetensors(model_id, required_prefixes, strip_prefixes, ignored_prefixes))
+    seen: list[str] = []
+
+    def counted():
+        for name, t in iter_safetensors(model_id, required_prefixes, strip_prefixes, ignored_prefixes):
+            seen.append(name)
+            yield name, t
+
+    loaded = set(model.load_weights(counted()))
     expected = {n for n, _ in model.named_parameters()}
     logger.info("Loaded %d checkpoint tensors into %d parameters of %s", len(loaded), len(expected), model_id)
     if strict and not loaded:
         raise RuntimeError(f"No tensor of {model_id} matched prefixes {required_prefixes}")
+    # checkpoint tensors under the model's prefixes that the model did not take: a layout it does not know (stacked
+    # experts, renamed projections) would otherwise leave those parameters at their random initialisation in silence
+    skipped = [n for n in dict.fromkeys(seen) if n not in loaded and not n.endswith(_BUFFER_SUFFIXES)]
+    if skipped:
+        msg = (f"{len(skipped)} of {len(set(seen))} checkpoint tensors of {model_id} were not recognised by "
+               f"{type(model).__name__}: {skipped[:12]}{' ...' if len(skipped) > 12 else ''}")
+        if strict and os.environ.get("CORNSERVE_STRICT_WEIGHTS", "1") == "1":
+            raise RuntimeError(msg)
+        logger.error(msg)
     return True

@@ -9,6 +9,7 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 os.environ.setdefault("OTEL_SDK_DISABLED", "true")
+os.environ.setdefault("CORNSERVE_ALLOW_RANDOM_INIT", "1")   # tests serve tiny architectures without checkpoints
 
 
 def pytest_configure(config):

@@ -282,3 +282,39 @@ def test_sampling_params_follow_the_openai_defaults():
     assert SamplingParams.from_request({}, 0.0).temperature == 0.0         # the model's generation config may say greedy
     p = SamplingParams.from_request({"temperature": 0, "frequency_penalty": 0.5, "presence_penalty": None})
     assert p.temperature == 0.0 and not p.samples and p.frequency_penalty == 0.5 and p.presence_penalty == 0.0 and p.penalized
+
+
+def test_video_positions_scale_time_by_seconds_per_grid():
+    """Qwen2.5-VL (Hugging Face ``get_rope_index``): the temporal index of a video's tokens is
+    ``floor(frame_index * second_per_grid_t * tokens_per_second)``, height / width indices count merged cells, all three
+    offset by the running position; text resumes at ``max + 1``.  Images keep a temporal index of zero."""
+    import numpy as np
+
+    IMG, VID = 900, 901
+    # text a | video of 2 temporal steps x (2 x 4 patches -> 1 x 2 merged cells) | text b | image 4 x 4 -> 2 x 2 | text c
+    ids = np.asarray([5, VID, VID, VID, VID, 6, IMG, IMG, IMG, IMG, 7], dtype=np.int32)
+    got, nxt = mrope_positions(ids, [(2, 2, 4), (1, 4, 4)], IMG, VID, 2, second_per_grid=[1.5, 1.0], tokens_per_second=2.0)
+    want = np.asarray([[0, 1, 1, 4, 4, 5, 6, 6, 6, 6, 8],      # time: frames at 0 and floor(1 * 1.5 * 2) = 3, offset 1
+                       [0, 1, 1, 1, 1, 5, 6, 6, 7, 7, 8],      # height
+                       [0, 1, 2, 1, 2, 5, 6, 7, 6, 7, 8]])     # width
+    assert np.array_equal(got, want) and nxt == 9
+    # without timing information a video is indexed per frame (Qwen2-VL)
+    plain, _ = mrope_positions(ids, [(2, 2, 4), (1, 4, 4)], IMG, VID, 2)
+    assert plain[0].tolist() == [0, 1, 1, 2, 2, 3, 4, 4, 4, 4, 6]
+
+
+def test_engine_passes_video_timing_to_the_positions():
+    import numpy as np
+    import torch
+
+    from cornserve.models.qwen_llm import LLMConfig, QwenLLM
+    from cornserve.task_executors.llm.engine import EngineConfig, LLMEngine, MMItem, SamplingParams, Sequence
+
+    cfg = LLMConfig(hidden_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=32, intermediate_size=64,
+                    vocab_size=1024, mrope_section=[4, 6, 6], image_token_id=900, video_token_id=901, tokens_per_second=2.0)
+    eng = LLMEngine(QwenLLM(cfg).float().eval(), EngineConfig(num_pages=4, use_cuda_graph=False, max_model_len=256))
+    ids = np.asarray([5, 901, 901, 901, 901, 6], dtype=np.int32)
+    seq = Sequence("v", ids, SamplingParams(max_tokens=1, ignore_eos=True),
+                   mm_items=[MMItem(torch.zeros(4, 64), 1, (2, 2, 4), second_per_grid=1.5)])
+    eng.add_request(seq)
+    assert seq.positions[0].tolist() == [0, 1, 1, 4, 4, 5] and seq.next_pos == 6
