@@ -125,9 +125,12 @@ class Attention(nn.Module):
 
     def attend(self, h: torch.Tensor, cs: torch.Tensor, cache: torch.Tensor, m: BatchMeta) -> torch.Tensor:
         """Attention context ``[T, heads_local * d]`` (before the output projection)."""
+        return self.attend_qkv(self.qkv(h), cs, cache, m)
+
+    def attend_qkv(self, qkv: torch.Tensor, cs: torch.Tensor, cache: torch.Tensor, m: BatchMeta) -> torch.Tensor:
+        """The same from an already projected ``q | k | v`` (``[T, (heads_local + 2 kv_heads_local) * d]``, changed in place)."""
         d = self.cfg.head_dim
-        T = h.shape[0]
-        qkv = self.qkv(h)
+        T = qkv.shape[0]
         if self.cfg.qk_norm:
             qk = qkv[:, : (self.hq + self.hkv) * d]
             normed_q = self.q_norm(qkv[:, : self.hq * d].reshape(-1, d)).view(T, self.hq * d)
@@ -267,6 +270,10 @@ class QwenLLM(nn.Module):
         self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size, device=device)
         self.layers = nn.ModuleList([DecoderLayer(cfg, self.group, device, ep_group) for _ in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+        # tensor-parallel prefill through the peer-memory chain (GEMM -> reduce-scatter -> norm -> all-gather -> GEMM);
+        # the engine raises the hint to its token budget so that the buffers are allocated once
+        self.prefill_chain = True
+        self.prefill_rows_hint = 2048
         if cfg.tie_word_embeddings:
             self.lm_head = None
         else:
@@ -317,6 +324,10 @@ class QwenLLM(nn.Module):
         half = cfg.head_dim // 2
         sections = cfg.mrope_section or [half, 0, 0]
         cs = ops.mrope_table(m.positions, half, cfg.rope_theta, sections)
+        if capture is None and not m.is_decode and x.shape[0] > 256:
+            chain = self._fused_chain(x.shape[0])
+            if chain is not None:
+                return self._forward_hidden_chain(chain, x, cs, kv_caches, m)
         residual = x
         h = self.layers[0].input_layernorm(x)
         fused = self._fused_tail() if (self.group.size > 1 and x.is_cuda) else None
@@ -327,6 +338,58 @@ class QwenLLM(nn.Module):
             if capture is not None and i + 1 in capture:
                 capture[i + 1] = residual.clone()
         return h
+
+    def _fused_chain(self, rows: int):
+        """Peer-memory context of the tensor-parallel prefill chain, or ``None`` when it does not apply (one rank, no
+        fabric, experts, quantised projections).  Every rank sees the same sequence of row counts, so the buffers are
+        (re)allocated by all ranks at the same step."""
+        if (self.group.size == 1 or self.group.fabric is None or self.cfg.num_experts > 0 or self.device.type != "cuda"
+                or getattr(self, "quantization", None) is not None or not self.prefill_chain):
+            return None
+        ctx = getattr(self, "_chain", None)
+        if ctx is None or ctx.S_cap < rows:
+            from ..parallel.fused import FusedEncoderTP
+
+            ctx = self._chain = FusedEncoderTP(self.group, self.cfg.hidden_size, max(rows, self.prefill_rows_hint))
+        return ctx
+
+    def _forward_hidden_chain(self, tp, x: torch.Tensor, cs: torch.Tensor, kv_caches: list[torch.Tensor], m: BatchMeta) -> torch.Tensor:
+        """Prefill with the residual stream sharded by rows over the tensor-parallel ranks and no library collective
+        inside the layers: each row-parallel projection (o_proj, down_proj) pushes its partial tiles from the GEMM
+        epilogue to the rank that owns the rows (the reduce-scatter is the store), one kernel per owned row reduces them,
+        adds the residual, applies the next RMSNorm and stores the normalised row into every rank's operand buffer (the
+        all-gather is that store), and the following column-parallel GEMM (q|k|v, gate/up) starts on each 128-row chunk
+        as soon as it has landed.  Attention runs between them on all tokens of this rank's heads, as without the chain.
+        One library all-gather of the residual shards at the end gives every rank the full rows for the final norm."""
+        import torch.distributed as dist
+
+        T = x.shape[0]
+        tp.begin(T)
+        lo, hi = tp.row_range
+        xs = x[lo:hi].contiguous()
+        layers = self.layers
+        n = len(layers)
+        tp.reduce_norm_push(bias=None, residual=xs, dst=0, reduce=False, norm_w=layers[0].input_layernorm.weight,
+                            eps=layers[0].input_layernorm.eps)
+        for i, (layer, cache) in enumerate(zip(layers, kv_caches)):
+            at, mlp = layer.self_attn, layer.mlp
+            qkv = tp.gemm_gathered(0, at.qkv.weight, at.qkv.bias)
+            o = at.attend_qkv(qkv, cs, cache, m)
+            tp.gemm_push(o, at.o_proj.weight)
+            pn = layer.post_attention_layernorm
+            xs = tp.reduce_norm_push(bias=at.o_proj.bias, residual=xs, dst=1, norm_w=pn.weight, eps=pn.eps)
+            act = tp.gemm_gathered(1, mlp.gate_up.weight, mlp.gate_up.bias, act="silu", swiglu=True)
+            tp.gemm_push(act, mlp.down.weight)
+            if i + 1 < n:
+                nn_ = layers[i + 1].input_layernorm
+                xs = tp.reduce_norm_push(bias=mlp.down.bias, residual=xs, dst=0, norm_w=nn_.weight, eps=nn_.eps)
+            else:
+                xs = tp.reduce_norm_push(bias=mlp.down.bias, residual=xs, norm_w=None, eps=0.0, dst=None)
+        full = torch.zeros((tp.group.size * tp.R, x.shape[1]), device=x.device, dtype=x.dtype)
+        mine = full[lo: lo + tp.R]
+        mine[: xs.shape[0]] = xs
+        dist.all_gather_into_tensor(full, mine.clone(), group=tp.group.group)
+        return self.norm(full[:T])
 
     def _fused_tail(self):
         """Lazily built fused GEMM + all-reduce + residual + RMSNorm kernel context (needs the fabric)."""

@@ -106,18 +106,39 @@ class FusedEncoderTP:
         self.S_cap = self.R_cap * T
         fab: Fabric = group.fabric
         self.gather = [fab.alloc(self.S_cap * hidden, torch.bfloat16, zero=False) for _ in range(3)]
-        self.gflags = [fab.alloc(self.S_cap // 128 + 1, torch.int32) for _ in range(3)]
         self.recv = fab.alloc(T * self.R_cap * hidden, torch.bfloat16, zero=False)
-        self.rflags = fab.alloc(self.R_cap // 128 + 1, torch.int32)
+        # Two sets of arrival counters, used by alternate passes.  A pass starts by clearing the set of the NEXT pass
+        # on its own stream, so no rank ever has to wait for the others before it pushes: a peer can only be one pass
+        # ahead, and it reaches that pass only after this rank's pushes of the current one, which are ordered behind
+        # the clear.  (Every push of a pass is awaited by a kernel of the same pass on the receiving rank, so the set
+        # of the previous pass is quiet by the time it is cleared.)  The allocation itself is collective and zeroed.
+        self._gflag_sets = [[fab.alloc(self.S_cap // 128 + 1, torch.int32) for _ in range(3)] for _ in range(2)]
+        self._rflag_sets = [fab.alloc(self.R_cap // 128 + 1, torch.int32) for _ in range(2)]
         self._gptr = [b.ptr_array() for b in self.gather]
-        self._gfptr = [b.ptr_array() for b in self.gflags]
+        self._gfptr_sets = [[b.ptr_array() for b in fs] for fs in self._gflag_sets]
         self._rptr = self.recv.ptr_array()
-        self._rfptr = self.rflags.ptr_array()
-        self._sync = torch.zeros(1, device=group.device, dtype=torch.float32)
+        self._rfptr_sets = [b.ptr_array() for b in self._rflag_sets]
+        self.cur = 1
         self.S = self.R = self.rows_local = 0
         self.g_epoch = [0, 0, 0]
         self.r_epoch = 0
         self._last_push_tiles_n = 0
+
+    @property
+    def gflags(self):
+        return self._gflag_sets[self.cur]
+
+    @property
+    def rflags(self):
+        return self._rflag_sets[self.cur]
+
+    @property
+    def _gfptr(self):
+        return self._gfptr_sets[self.cur]
+
+    @property
+    def _rfptr(self):
+        return self._rfptr_sets[self.cur]
 
     def begin(self, S: int) -> None:
         T, r = self.group.size, self.group.rank
@@ -126,9 +147,10 @@ class FusedEncoderTP:
             raise ValueError(f"{S} rows exceed the capacity of this fused context ({self.S_cap})")
         self.S, self.R = S, R
         self.rows_local = max(0, min(R, S - r * R))
-        for f in (*self.gflags, self.rflags):
+        self.cur ^= 1
+        nxt = self.cur ^ 1
+        for f in (*self._gflag_sets[nxt], self._rflag_sets[nxt]):   # the counters of the pass after this one
             f.local.zero_()
-        dist.all_reduce(self._sync, group=self.group.group)  # nobody pushes before everyone has cleared
         self.g_epoch = [0, 0, 0]
         self.r_epoch = 0
 
@@ -237,22 +259,20 @@ class FusedUlysses:
         self.cap = max_local_rows
         fab: Fabric = group.fabric
         self.qkv = fab.alloc(Pn * max_local_rows * 3 * self.own, torch.bfloat16, zero=False)
-        self.qkv_flag = fab.alloc(4, torch.int32)
         self.o = fab.alloc(max_local_rows * hidden, torch.bfloat16, zero=False)
+        # The arrival counters only ever grow (every rank makes the same calls, so every rank knows the value a counter
+        # must reach): nothing is cleared between passes and no rank waits for the others before it pushes.  32 bits
+        # last for 2^32 tiles, i.e. months of continuous denoising.
+        self.qkv_flag = fab.alloc(4, torch.int32)
         self.o_flag = fab.alloc(4, torch.int32)
         self._qkv_ptr, self._qkv_fptr = self.qkv.ptr_array(), self.qkv_flag.ptr_array()
         self._o_ptr, self._o_fptr = self.o.ptr_array(), self.o_flag.ptr_array()
         self.done = torch.zeros(1, device=group.device, dtype=torch.int32)
-        self._sync = torch.zeros(1, device=group.device, dtype=torch.float32)
         self.qkv_expected = 0
         self.o_expected = 0
 
     def begin_pass(self) -> None:
-        self.qkv_flag.local.zero_()
-        self.o_flag.local.zero_()
-        dist.all_reduce(self._sync, group=self.group.group)
-        self.qkv_expected = 0
-        self.o_expected = 0
+        """Start of a denoiser forward.  Nothing to do on the device: the counters are cumulative."""
 
     def qkv_scatter(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, row0: int, run: int, stride: int,
                     seg: int) -> None:
@@ -270,7 +290,7 @@ class FusedUlysses:
         _count()
         count_path("ulysses_qkv_alltoall")
         # every rank makes the same calls: each delivers tiles_m x (3 * own / 128) tiles to every destination
-        self.qkv_expected += g.size * (-(-M // 128)) * (3 * self.own // 128)
+        self.qkv_expected = (self.qkv_expected + g.size * (-(-M // 128)) * (3 * self.own // 128)) & 0xFFFFFFFF
 
     def gathered_qkv(self, rows_total: int) -> torch.Tensor:
         """Waits for all ranks' tiles, then returns ``[rows_total, 3 * own]`` (this rank's heads, every token)."""
@@ -289,7 +309,7 @@ class FusedUlysses:
                                    self.done.data_ptr(), _stream())
         if rc != 0:
             raise RuntimeError(f"cs_a2a_push_heads failed with code {rc}")
-        self.o_expected += g.size
+        self.o_expected = (self.o_expected + g.size) & 0xFFFFFFFF
         lib.cs_wait_flag(self.o_flag.local.data_ptr(), self.o_expected, _stream())
         _count(2)
         count_path("ulysses_head_return")

@@ -204,6 +204,7 @@ class LLMEngine:
         self.cfg = cfg or EngineConfig()
         self.device = model.device
         self.on_gpu = self.device.type == "cuda"
+        model.prefill_rows_hint = max(getattr(model, "prefill_rows_hint", 0), self.cfg.max_batched_tokens)
         self.blocks = BlockManager(self.cfg.num_pages)
         self.kv_caches = model.alloc_kv_cache(self.cfg.num_pages)
         self.kv_backing: torch.Tensor = model.kv_backing  # [layers, pages, 2, heads, 128, d]; kv_caches are its views

@@ -252,7 +252,7 @@ __global__ void wait_flag_kernel(const unsigned* flag, unsigned target, int* err
   for (uint32_t spin = 0;; ++spin) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v >= target) return;
+    if (static_cast<int>(v - target) >= 0) return;   // the counters are cumulative and may wrap: compare the difference
     if ((spin & 0x3f) == 0x3f) {
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
