@@ -237,11 +237,27 @@ def llm_main(a: argparse.Namespace) -> None:
     hidden = 256 if a.small else HIDDEN
     slabs = {i: torch.from_file(p, shared=True, size=a.slab_bytes, dtype=torch.uint8) for i, p in enumerate(a.slab.split(","))}
     text_rows = (torch.randn(4096, hidden, generator=torch.Generator().manual_seed(1)) * 0.02).to(torch.bfloat16)
-    engine = AsyncLLM.from_engine_args(AsyncEngineArgs(
-        model=str(Path(a.workdir) / "decoder_model"), tensor_parallel_size=a.world, enforce_eager=True, enable_prefix_caching=False,
-        gpu_memory_utilization=a.gpu_util, max_num_seqs=256, load_format="dummy", enable_prompt_embeds=True,
-        skip_tokenizer_init=True, trust_remote_code=True, dtype="bfloat16", generation_config="vllm",
-        max_model_len=8192, disable_log_stats=True))
+    # Attention backend: on sm_100 vLLM's first choice is FlashInfer, whose helper kernels are compiled with nvcc at the
+    # first start; on a fresh box without FlashInfer's cache that takes longer than this arm is given.  The next entry
+    # of vLLM's own priority list, FLASH_ATTN, ships precompiled in the wheel; Triton attention is the one after.
+    # REF_VLLM_ATTENTION_BACKEND=auto restores vLLM's own choice.
+    wanted = os.environ.get("REF_VLLM_ATTENTION_BACKEND", "FLASH_ATTN,TRITON_ATTN,auto").split(",")
+    engine, last = None, None
+    for backend in wanted:
+        kw = {} if backend == "auto" else {"attention_backend": backend}
+        try:
+            engine = AsyncLLM.from_engine_args(AsyncEngineArgs(
+                model=str(Path(a.workdir) / "decoder_model"), tensor_parallel_size=a.world, enforce_eager=True,
+                enable_prefix_caching=False, gpu_memory_utilization=a.gpu_util, max_num_seqs=256, load_format="dummy",
+                enable_prompt_embeds=True, skip_tokenizer_init=True, trust_remote_code=True, dtype="bfloat16",
+                generation_config="vllm", max_model_len=8192, disable_log_stats=True, enable_flashinfer_autotune=False, **kw))
+            print(f"llm replica {a.replica}: vLLM started with attention backend {backend}", flush=True)
+            break
+        except Exception as e:  # noqa: BLE001
+            last = e
+            print(f"llm replica {a.replica}: attention backend {backend} did not start: {type(e).__name__}: {e}", flush=True)
+    if engine is None:
+        raise RuntimeError(f"vLLM did not start with any of {wanted}: {last}")
     print(f"llm replica {a.replica}: engine ready", flush=True)
     conn = Client(("127.0.0.1", a.front_port), authkey=AUTH)
     send_lock = threading.Lock()
@@ -391,7 +407,7 @@ class Front:
             # no network here: vLLM must not look for its address through a route to the outside or a host name that
             # does not resolve (its torch.distributed rendezvous then waits for ever)
             env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus, VLLM_HOST_IP="127.0.0.1", GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo",
-                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1")
+                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1", VLLM_USE_FLASHINFER_SAMPLER="0")
             log = open(work / f"llm_{r}.log", "w")
             util = 0.80 if a.share_gpu else 0.93
             self.procs.append(subprocess.Popen(base + ["--role", "llm", "--replica", str(r), "--world", str(lt), "--slab", ",".join(slabs),

@@ -78,10 +78,8 @@ def time_ours(model: str, pixels: list[torch.Tensor], grids: list[list[int]], it
 
 
 def time_reference(model: str, pixels: list[torch.Tensor], grids: list[list[int]], iters: int, warmup: int, rank: int, world: int) -> float | str:
-    root = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
-    if not (root / "cornserve").is_dir():
-        return "the reference package is not installed under baseline/_ref"
-    sys.path.insert(0, str(root))
+    """Runs in a process of its own whose import path holds the reference package and not this repository (both are
+    called ``cornserve``); see :func:`reference_in_subprocess`."""
     try:
         from cornserve.task_executors.eric.distributed import parallel
 
@@ -98,10 +96,8 @@ def time_reference(model: str, pixels: list[torch.Tensor], grids: list[list[int]
         Modality = ref_mod.Modality
     except Exception as e:  # noqa: BLE001
         return f"the reference encoder does not import here: {type(e).__name__}: {e}"
-    finally:
-        sys.path.remove(str(root))
     parallel.init_distributed(world_size=world, rank=rank, init_method=f"tcp://{os.environ.get('MASTER_ADDR', '127.0.0.1')}:"
-                                                                       f"{os.environ.get('MASTER_PORT', '29511')}")
+                                                                       f"{int(os.environ.get('MASTER_PORT', '29511')) + 7}")
     torch.manual_seed(0)
     tower = build().to(device="cuda", dtype=torch.bfloat16).eval()
     batch = {"pixel_values": pixels, "image_grid_thw": [torch.tensor([g]) for g in grids]}
@@ -110,12 +106,32 @@ def time_reference(model: str, pixels: list[torch.Tensor], grids: list[list[int]
     return _max_over_ranks(secs, world)
 
 
+def reference_in_subprocess(a: argparse.Namespace) -> float | str:
+    """The reference arm, one child process per rank: started with ``-P`` and a ``PYTHONPATH`` that holds
+    ``baseline/_ref`` (the unmodified reference) and not this repository."""
+    import subprocess
+
+    repo = Path(__file__).resolve().parents[1]
+    root = repo / "baseline" / "_ref"
+    if not (root / "cornserve").is_dir():
+        return "the reference package is not installed under baseline/_ref"
+    keep = [p for p in os.environ.get("PYTHONPATH", "").split(os.pathsep) if p and Path(p).resolve() != repo]
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(root), *keep]))
+    r = subprocess.run([sys.executable, "-P", str(Path(__file__).resolve()), "--arm", "reference", "--model", a.model, "--images", str(a.images),
+                        "--iters", str(a.iters), "--warmup", str(a.warmup)], env=env, cwd="/", capture_output=True, text=True, timeout=900)
+    if r.returncode != 0:
+        return f"the reference arm failed: {r.stderr.strip().splitlines()[-1] if r.stderr.strip() else r.returncode}"
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    return out.get("unavailable") or float(out["seconds_per_pass"])
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--model", default="qwen2_5_vl", choices=["qwen2_5_vl", "qwen2_vl"], help="which 7B vision tower")
     ap.add_argument("--images", type=int, default=7, help="1280x720 images per forward pass")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--arm", default="both", choices=["both", "reference"], help="reference: only that arm, for the child process")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("encoder_compare needs a CUDA device")
@@ -125,8 +141,11 @@ def main() -> None:
     grid = [1, 52, 92]   # 1280x720 -> 728 x 1288 after rounding to 28-pixel cells: 52 x 92 patches
     pixels = [torch.randn(grid[1] * grid[2], 3 * 2 * 14 * 14, device="cuda", generator=gen).bfloat16() for _ in range(a.images)]
     grids = [grid] * a.images
-    # the reference first: it creates the process group (this package joins an existing one, the reference does not)
-    ref = time_reference(a.model, pixels, grids, a.iters, a.warmup, rank, world)
+    if a.arm == "reference":
+        ref = time_reference(a.model, pixels, grids, a.iters, a.warmup, rank, world)
+        print(json.dumps({"unavailable": ref} if isinstance(ref, str) else {"seconds_per_pass": ref}))
+        return
+    ref = reference_in_subprocess(a)   # first, and finished before this package touches the GPU
     ours = time_ours(a.model, pixels, grids, a.iters, a.warmup, rank, world)
     out = {"metric": "encoder_images_per_second", "model": a.model, "n_gpus": world, "parallelism": f"tp{world}", "dtype": "bf16",
            "images_per_pass": a.images, "data": "synthetic (random patches, random-init weights)",

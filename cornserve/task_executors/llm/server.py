@@ -29,6 +29,7 @@ import ast
 import asyncio
 import base64
 import concurrent.futures
+import contextlib
 import io
 import json
 import os
@@ -266,6 +267,98 @@ def build_engine(args: argparse.Namespace, group: ParallelGroup | None = None) -
     return engine, hf_cfg
 
 
+class LocalEncoder:
+    """The vision tower inside the LLM executor (the monolithic, no-fission deployment).
+
+    Images of waiting requests are encoded by a thread of their own on a high-priority CUDA stream, in batches of up to
+    ``MAX_PATCHES`` patches, so that the tower's kernels run beside the decode graphs of the engine thread instead of
+    queueing behind them, and so that the event loop never waits for the GPU.  Raw pixels go to the GPU through one
+    page-locked staging buffer."""
+
+    MAX_PATCHES = 34000      # seven 1280x720 images: whole tile waves on 148 SMs for the tower's GEMMs
+    STAGING_BYTES = 128 << 20
+
+    def __init__(self, server: "LLMServer"):
+        import queue
+
+        from ...models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
+
+        self.device = server.engine.device
+        v = Qwen25VisionTransformer(Qwen25VisionConfig.from_hf(server.hf_cfg), device=self.device)
+        if next(server.engine.model.parameters()).dtype == torch.float32:
+            v = v.float()
+        load_model_weights(v, server.args.model, ["visual.", "model.visual."], strict=False)
+        self.vision = v.eval()
+        self.inbox: queue.Queue = queue.Queue()
+        self.h2d_bytes = 0
+        self.images = 0
+        self.batches = 0
+        self.stream = torch.cuda.Stream(device=self.device, priority=-1) if self.device.type == "cuda" else None
+        self.stage = torch.empty(self.STAGING_BYTES, dtype=torch.uint8, pin_memory=True) if self.stream is not None else None
+        self.thread = threading.Thread(target=self._run, name="llm-local-encoder", daemon=True)
+        self.thread.start()
+
+    async def encode(self, url: str) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        from ..eric.processor import load_image
+
+        pixels = torch.from_numpy(await asyncio.to_thread(load_image, url))
+        loop = asyncio.get_running_loop()
+        fut: asyncio.Future = loop.create_future()
+        self.inbox.put((pixels, loop, fut))
+        return await fut
+
+    def _run(self) -> None:
+        import queue
+
+        from ..eric.preprocess import patchify_frames
+
+        ops.bind_thread(self.device)
+        vc = self.vision.cfg
+        per_image_guess = 0
+        while True:
+            batch = [self.inbox.get()]
+            while True:   # whatever else is waiting, up to the patch budget
+                if per_image_guess and (len(batch) + 1) * per_image_guess > self.MAX_PATCHES:
+                    break
+                try:
+                    batch.append(self.inbox.get_nowait())
+                except queue.Empty:
+                    break
+            try:
+                ctx = torch.cuda.stream(self.stream) if self.stream is not None else contextlib.nullcontext()
+                with torch.inference_mode(), ctx:
+                    pix, grids, used = [], [], 0
+                    for img, _, _ in batch:
+                        n = img.numel()
+                        if self.stage is not None and used + n <= self.stage.numel():
+                            view = self.stage[used: used + n].view(img.shape)
+                            view.copy_(img)
+                            used += -(-n // 256) * 256
+                            dev_img = view.to(self.device, non_blocking=True)
+                        else:
+                            dev_img = img.to(self.device)
+                        self.h2d_bytes += n
+                        pv, grid = patchify_frames(dev_img, vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size,
+                                                   out_dtype=self.vision.dtype)
+                        pix.append(pv)
+                        grids.append(grid)
+                    per_image_guess = max(per_image_guess, max(p.shape[0] for p in pix))
+                    embs = self.vision("image", None, {"pixel_values": pix, "image_grid_thw": [list(g) for g in grids]})
+                    embs = [e.contiguous() for e in embs]
+                    if self.stream is not None:
+                        for e in embs:   # consumed later by the engine thread's kernels on the default stream
+                            e.record_stream(torch.cuda.default_stream(self.device))
+                        self.stream.synchronize()
+                self.images += len(batch)
+                self.batches += 1
+                for (_, loop, fut), emb, grid in zip(batch, embs, grids):
+                    loop.call_soon_threadsafe(lambda f=fut, r=(emb, grid): f.done() or f.set_result(r))
+            except Exception as e:  # noqa: BLE001
+                logger.exception("local encoding failed")
+                for _, loop, fut in batch:
+                    loop.call_soon_threadsafe(lambda f=fut, err=e: f.done() or f.set_exception(err))
+
+
 class LLMServer:
     def __init__(self, args: argparse.Namespace):
         self.args = args
@@ -300,7 +393,7 @@ class LLMServer:
                                                  group=list(args.cornserve_sidecar_ranks),
                                                  send_tensor_dtype=dtype, send_tensor_shape=(-1, self.cfg.hidden_size),
                                                  recv_tensor_dtype=dtype, recv_tensor_shape=(-1, self.cfg.hidden_size)))
-        self.vision = None  # built lazily for requests that carry raw URLs
+        self.local_encoder: LocalEncoder | None = None  # built lazily for requests that carry raw URLs (no fission)
         kv_cfg = json.loads(args.kv_transfer_config) if args.kv_transfer_config else {}
         self.kv_role = kv_cfg.get("kv_role")
         self.engine_id = uuid.uuid4().hex
@@ -354,24 +447,9 @@ class LLMServer:
         return None
 
     async def _local_encode(self, modality: str, url: str) -> tuple[torch.Tensor, tuple[int, int, int]]:
-        if self.vision is None:
-            from ...models.qwen2_5_vl import Qwen25VisionConfig, Qwen25VisionTransformer
-
-            v = Qwen25VisionTransformer(Qwen25VisionConfig.from_hf(self.hf_cfg), device=self.engine.device)
-            if next(self.engine.model.parameters()).dtype == torch.float32:
-                v = v.float()
-            load_model_weights(v, self.args.model, ["visual.", "model.visual."], strict=False)
-            self.vision = v.eval()
-        from ..eric.preprocess import patchify_frames
-        from ..eric.processor import load_image
-
-        img = torch.from_numpy(await asyncio.to_thread(load_image, url)).to(self.engine.device)
-        vc = self.vision.cfg
-        with torch.inference_mode():
-            pv, grid = patchify_frames(img, vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size,
-                                       out_dtype=self.vision.dtype)
-            (emb,) = self.vision("image", None, {"pixel_values": [pv], "image_grid_thw": [list(grid)]})
-        return emb, grid
+        if self.local_encoder is None:
+            self.local_encoder = LocalEncoder(self)
+        return await self.local_encoder.encode(url)
 
     async def build_sequence(self, body: dict[str, Any]) -> tuple[Sequence, list[str]]:
         messages = body["messages"]
@@ -775,7 +853,10 @@ class LLMServer:
                     "paths": ops.path_counts(), **eng.stats, "running": len(eng.running), "waiting": len(eng.waiting),
                     "kv_pages": eng.cfg.num_pages, "kv_pages_free": eng.blocks.num_free,
                     "d2h_bytes": 4 * (eng.stats["decode_tokens"] + eng.stats["prefill_steps"]),
-                    "tp_publish_ms": getattr(self.llm.tp, "publish_ms", 0.0) if self.llm.tp is not None else 0.0}
+                    "tp_publish_ms": getattr(self.llm.tp, "publish_ms", 0.0) if self.llm.tp is not None else 0.0,
+                    "h2d_bytes": self.local_encoder.h2d_bytes if self.local_encoder is not None else 0,
+                    "local_encoder_images": self.local_encoder.images if self.local_encoder is not None else 0,
+                    "local_encoder_batches": self.local_encoder.batches if self.local_encoder is not None else 0}
 
         @app.get("/v1/models")
         async def models():
