@@ -12,6 +12,9 @@
   python -m cornserve.ops.microbench sample 128 152064 50     # rows, vocabulary, top-k (temperature 1, top-p 0.9)
   python -m cornserve.ops.microbench gemm-fp8 16384 3584 3584 # e4m3 with 1x128 / 128x128 block scales
   python -m cornserve.ops.microbench moe 128 128 8 2048 768   # tokens, experts, top-k, hidden, expert FFN width
+  python -m cornserve.ops.microbench push 8573952             # the sidecar's copy kernel, bytes
+  python -m cornserve.ops.microbench tp-chain 19136 1280 3424 # fused TP half-block on one rank (loopback fabric)
+  python -m cornserve.ops.microbench ulysses-qkv 4352 3072 24 # q|k|v GEMM with the all-to-all epilogue (loopback)
 
 Each line printed gives the time per launch, the achieved rate and the fraction of the measured peak
 (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).  The same
@@ -186,6 +189,58 @@ def main() -> None:
         touched = min(E, T * kk)  # experts whose weights must be read (upper bound when tokens collide)
         report(f"moe layer T={T} E={E} top{kk} H={H} I={I} (row tile {layer.tile_rows_for(T)})", secs, 6.0 * T * kk * H * I,
                2.0 * (touched * 3 * H * I + 2 * T * kk * (H + I) + 2 * T * H))
+    elif k == "push":
+        nbytes = (a.args[0] if a.args else 1196 * 3584 * 2)
+        src = torch.randint(0, 255, (nbytes,), device=dev, dtype=torch.uint8)
+        dst = torch.empty_like(src)
+        secs = t(lambda: ops.push_bytes_(dst, src))
+        report(f"sidecar push kernel {nbytes} bytes (same GPU)", secs, 0.0, 2.0 * nbytes)
+    elif k == "tp-chain":
+        # the tensor-parallel MLP half-block (norm -> all-gather -> gate/up GEMM -> down GEMM -> reduce-scatter ->
+        # residual + norm) with one rank: every push, counter and wait of the fused kernels runs, against this GPU's memory
+        from cornserve.parallel.fabric import Fabric
+        from cornserve.parallel.fused import FusedEncoderTP
+
+        S, H, I = (a.args + [19136, 1280, 3424][len(a.args):])[:3]
+        fab = Fabric.loopback(dev)
+        tp = FusedEncoderTP(fab.group, H, S)
+        xs, nw = rnd(S, H), rnd(H)
+        wgu, wdn = rnd(2 * I, H, std=H ** -0.5), rnd(H, I, std=I ** -0.5)
+        state = {}
+
+        def stage(name):
+            def run():
+                tp.begin(S)
+                if name in ("all", "norm+push"):
+                    tp.reduce_norm_push(bias=None, residual=xs, dst=1, reduce=False, norm_w=nw, eps=1e-6)
+                if name in ("all", "gathered gemm"):
+                    state["h"] = tp.gemm_gathered(1, wgu, None, act="silu", swiglu=True)
+                if name in ("all", "push gemm"):
+                    tp.gemm_push(state["h"], wdn)
+                if name in ("all", "reduce+norm+push"):
+                    tp.reduce_norm_push(bias=None, residual=xs, dst=0, norm_w=nw, eps=1e-6)
+            return run
+
+        stage("all")()
+        torch.cuda.synchronize()
+        report(f"tp-chain (one rank, loopback) S={S} H={H} I={I}: whole half-block", t(stage("all")), 6.0 * S * H * I,
+               2.0 * (3 * I * H + 6 * S * H + 2 * S * I))
+        # a stage alone starts a pass with fresh counters, so its waits pass at once: this is its own time
+        report("  norm + push (all-gather store)", t(stage("norm+push")), 0.0, 2.0 * 2 * S * H)
+        report("  gate/up GEMM on the gathered operand (SwiGLU epilogue)", t(stage("gathered gemm")), 4.0 * S * H * I)
+        report("  down GEMM with the reduce-scatter in its epilogue", t(stage("push gemm")), 2.0 * S * H * I)
+        report("  reduce + residual + norm + push", t(stage("reduce+norm+push")), 0.0, 2.0 * 4 * S * H)
+    elif k == "ulysses-qkv":
+        from cornserve.parallel.fabric import Fabric
+        from cornserve.parallel.fused import FusedUlysses
+
+        rows, D, heads = (a.args + [4352, 3072, 24][len(a.args):])[:3]
+        fab = Fabric.loopback(dev)
+        fu = FusedUlysses(fab.group, D, heads, D // heads, rows)
+        x, w, b = rnd(rows, D), rnd(3 * D, D, std=D ** -0.5), rnd(3 * D)
+        secs = t(lambda: fu.qkv_scatter(x, w, b, 0, rows, rows, rows))
+        report(f"ulysses q|k|v projection with the all-to-all in its epilogue (one rank, loopback) {rows}x{3 * D}x{D}", secs,
+               6.0 * rows * D * D, 2.0 * (rows * D + 3 * D * D + 3 * rows * D))
     else:
         raise SystemExit(f"unknown kernel {k}")
 

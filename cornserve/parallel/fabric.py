@@ -45,8 +45,26 @@ class Fabric:
             raise RuntimeError("the peer-memory fabric needs CUDA devices")
         return cls(group)
 
+    @classmethod
+    def loopback(cls, device: torch.device | str) -> "Fabric":
+        """A one-rank fabric whose "peer" buffers are this GPU's own memory.  The fused kernels then run their whole
+        communication path (pushes, arrival counters, waits) against themselves on a single GPU, which is how they are
+        timed and profiled in isolation (a profiler that replays a kernel cannot be pointed at one rank of a group:
+        the replays would break the counters the other ranks wait on)."""
+        from .state import ParallelGroup
+
+        f = cls(ParallelGroup(0, 1, None, None, torch.device(device)))
+        f._loopback = True
+        f.group.fabric = f
+        return f
+
     def alloc(self, numel: int, dtype: torch.dtype, zero: bool = True) -> SymmetricBuffer:
         """Collective: every rank of the group must call with the same arguments, in the same order."""
+        if getattr(self, "_loopback", False):
+            t = torch.zeros(numel, dtype=dtype, device=self.device) if zero else torch.empty(numel, dtype=dtype, device=self.device)
+            buf = SymmetricBuffer(t, [t.data_ptr()], 0, None)
+            self._buffers.append(buf)
+            return buf
         import torch.distributed._symmetric_memory as symm
 
         t = symm.empty(numel, dtype=dtype, device=self.device)

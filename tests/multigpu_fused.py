@@ -370,15 +370,53 @@ def ep_mixture_of_experts(g):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item() * 1000
 
+    def library_twin(x, lg, cap):
+        """The same layer from library pieces with no host round trip: capacity-padded buckets (``cap`` rows per
+        (rank, expert) pair, what the dropless kernel path needs no padding for), NCCL equal-split all-to-all both
+        ways, batched cuBLAS GEMMs over this rank's experts, index-add combine.  Tokens beyond a bucket's capacity
+        are dropped, so this twin is a timing partner, not an oracle."""
+        T = x.shape[0]
+        w, idx = moe.route(lg, k, True)
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        sorted_e = flat_e[order]
+        first = torch.searchsorted(sorted_e, torch.arange(E, device=dev))
+        slot = torch.arange(T * k, device=dev) - first[sorted_e]            # position inside the expert's bucket
+        keep = slot < cap
+        dest = (sorted_e * cap + slot)[keep]
+        tok = torch.div(order, k, rounding_mode="floor")[keep]
+        send = torch.zeros(E * cap, H, device=dev, dtype=x.dtype)
+        send[dest] = x[tok]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=g.group)                    # [W (source), El, cap, H]
+        xe = recv.view(W, El, cap, H).transpose(0, 1).reshape(El, W * cap, H)
+        gu = torch.bmm(xe, wgu_l.transpose(1, 2))
+        h = torch.nn.functional.silu(gu[..., :I]) * gu[..., I:]
+        ye = torch.bmm(h, wd_l.transpose(1, 2)).view(El, W, cap, H).transpose(0, 1).contiguous()
+        back = torch.empty_like(send)
+        dist.all_to_all_single(back, ye.view(E * cap, H), group=g.group)
+        out = torch.zeros(T, H, device=dev, dtype=torch.float32)
+        out.index_add_(0, tok, back[dest].float() * w.reshape(-1)[order][keep].unsqueeze(1))
+        return out.to(x.dtype)
+
     for T in (64, 2048):
         x = torch.randn(T, H, device=dev).bfloat16()
         lg = torch.randn(T, E, device=dev)
+        cap = max(8, -(-int(1.25 * T * k / E) // 8) * 8)
         t_f = timed(lambda: ep.forward(x, lg, wgu_l, wd_l))
-        t_l = timed(lambda: moe.moe_forward(x, lg, wgu_l, wd_l, k, True, g), n=3)
+        t_l = timed(lambda: library_twin(x, lg, cap), n=10)
+        t_loop = timed(lambda: moe.moe_forward(x, lg, wgu_l, wd_l, k, True, g), n=3)
         ops.check_error("expert-parallel timing")
+        # roofline of one layer on one rank: expert FLOPs at the measured GEMM peak against the rows that must cross
+        # NVLink (dispatch + return, the (W-1)/W share that leaves the GPU) at the measured peer bandwidth
+        flops = 2.0 * T * k * 3 * I * H
+        wire = 2.0 * T * k * H * 2 * (W - 1) / W
+        weights = El * 3 * I * H * 2
+        bound = max(flops / 1657e12, wire / 770e9, weights / 6539e9) * 1e6
         if rank == 0:
-            print(f"MoE layer E={E} top{k} H={H} I={I}, {T} tokens per rank, EP={W}: peer-memory kernels {t_f:.0f} us   "
-                  f"library all-to-all + per-expert GEMMs {t_l:.0f} us", flush=True)
+            print(f"MoE layer E={E} top{k} H={H} I={I}, {T} tokens per rank, EP={W}: peer-memory kernels {t_f:.0f} us "
+                  f"({bound / t_f:.2f} of its roofline {bound:.0f} us)   library twin (padded all-to-all + batched cuBLAS, no host sync) "
+                  f"{t_l:.0f} us   per-expert loop with host syncs {t_loop:.0f} us", flush=True)
 
 
 def decode_allreduce_tail(g):
