@@ -242,18 +242,41 @@ def llm_main(a: argparse.Namespace) -> None:
     # of vLLM's own priority list, FLASH_ATTN, ships precompiled in the wheel; Triton attention is the one after.
     # REF_VLLM_ATTENTION_BACKEND=auto restores vLLM's own choice.
     wanted = os.environ.get("REF_VLLM_ATTENTION_BACKEND", "FLASH_ATTN,TRITON_ATTN,auto").split(",")
+    start_limit = float(os.environ.get("REF_VLLM_START_TIMEOUT_S", "240"))
     engine, last = None, None
+
+    def give_up_on_children(done: threading.Event, backend: str) -> None:
+        """An engine process that has not come up in time is asked to abort (with PYTHONFAULTHANDLER set it leaves the
+        stacks of its threads in this log), so that the next backend can be tried."""
+        if done.wait(start_limit):
+            return
+        import signal
+
+        import psutil
+
+        print(f"llm replica {a.replica}: vLLM with attention backend {backend} is not up after {start_limit:.0f} s; aborting its processes",
+              flush=True)
+        for child in psutil.Process().children(recursive=True):
+            try:
+                child.send_signal(signal.SIGABRT)
+            except psutil.Error:
+                pass
+
     for backend in wanted:
         kw = {} if backend == "auto" else {"attention_backend": backend}
+        done = threading.Event()
+        threading.Thread(target=give_up_on_children, args=(done, backend), daemon=True).start()
         try:
             engine = AsyncLLM.from_engine_args(AsyncEngineArgs(
                 model=str(Path(a.workdir) / "decoder_model"), tensor_parallel_size=a.world, enforce_eager=True,
                 enable_prefix_caching=False, gpu_memory_utilization=a.gpu_util, max_num_seqs=256, load_format="dummy",
                 enable_prompt_embeds=True, skip_tokenizer_init=True, trust_remote_code=True, dtype="bfloat16",
                 generation_config="vllm", max_model_len=8192, disable_log_stats=True, enable_flashinfer_autotune=False, **kw))
+            done.set()
             print(f"llm replica {a.replica}: vLLM started with attention backend {backend}", flush=True)
             break
-        except Exception as e:  # noqa: BLE001
+        except BaseException as e:  # noqa: BLE001
+            done.set()
             last = e
             print(f"llm replica {a.replica}: attention backend {backend} did not start: {type(e).__name__}: {e}", flush=True)
     if engine is None:
@@ -407,7 +430,7 @@ class Front:
             # no network here: vLLM must not look for its address through a route to the outside or a host name that
             # does not resolve (its torch.distributed rendezvous then waits for ever)
             env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus, VLLM_HOST_IP="127.0.0.1", GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo",
-                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1", VLLM_USE_FLASHINFER_SAMPLER="0")
+                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1", VLLM_USE_FLASHINFER_SAMPLER="0", PYTHONFAULTHANDLER="1")
             log = open(work / f"llm_{r}.log", "w")
             util = 0.80 if a.share_gpu else 0.93
             self.procs.append(subprocess.Popen(base + ["--role", "llm", "--replica", str(r), "--world", str(lt), "--slab", ",".join(slabs),

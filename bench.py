@@ -497,7 +497,7 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
 
     try:
         try:
-            wait_http(f"{base}/health", proc, 420, "the reference server")
+            wait_http(f"{base}/health", proc, float(os.environ.get("REF_START_WAIT_S", "600")), "the reference server")
         except Exception as e:  # noqa: BLE001
             return {"impl": "reference", "unavailable": f"the reference arm did not start: {e}; log tail: {tail()}"}
         probe = ExecutorProbe([base])
