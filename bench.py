@@ -278,9 +278,13 @@ def diff_stats(before: list[dict], after: list[dict]) -> dict:
         out["d2h_bytes"] += a.get("d2h_bytes", 0) - b.get("d2h_bytes", 0)
         e = {"executor": a.get("executor"), "tp_size": tp, "gpu_launches": launches}
         for k in ("prefill_steps", "decode_bursts", "prefill_ms", "decode_ms", "decode_host_ms", "prefill_tokens",
-                  "decode_tokens", "batches", "items", "busy_ms", "broadcast_ms", "tp_publish_ms"):
+                  "decode_tokens", "batches", "items", "busy_ms", "broadcast_ms", "tp_publish_ms", "requests", "inputs_ms",
+                  "first_token_ms", "local_encoder_images", "local_encoder_batches", "local_encoder_ms"):
             if k in a:
                 e[k] = round(a[k] - b.get(k, 0), 1)
+        if e.get("requests") and "inputs_ms" in e:
+            e["ms_per_request_waiting_for_inputs"] = round(e["inputs_ms"] / e["requests"], 1)
+            e["ms_per_request_queue_and_prefill"] = round(e["first_token_ms"] / e["requests"], 1)
         if e.get("decode_bursts"):
             e["host_ms_per_decode_burst"] = round(e["decode_host_ms"] / e["decode_bursts"], 3)
             e["ms_per_decode_burst"] = round(e["decode_ms"] / e["decode_bursts"], 3)

@@ -293,6 +293,7 @@ class LocalEncoder:
         self.h2d_bytes = 0
         self.images = 0
         self.batches = 0
+        self.busy_ms = 0.0
         self.stream = torch.cuda.Stream(device=self.device, priority=-1) if self.device.type == "cuda" else None
         self.stage = torch.empty(self.STAGING_BYTES, dtype=torch.uint8, pin_memory=True) if self.stream is not None else None
         self.thread = threading.Thread(target=self._run, name="llm-local-encoder", daemon=True)
@@ -324,6 +325,7 @@ class LocalEncoder:
                     batch.append(self.inbox.get_nowait())
                 except queue.Empty:
                     break
+            t0 = time.perf_counter()
             try:
                 ctx = torch.cuda.stream(self.stream) if self.stream is not None else contextlib.nullcontext()
                 with torch.inference_mode(), ctx:
@@ -351,6 +353,7 @@ class LocalEncoder:
                         self.stream.synchronize()
                 self.images += len(batch)
                 self.batches += 1
+                self.busy_ms += (time.perf_counter() - t0) * 1e3
                 for (_, loop, fut), emb, grid in zip(batch, embs, grids):
                     loop.call_soon_threadsafe(lambda f=fut, r=(emb, grid): f.done() or f.set_result(r))
             except Exception as e:  # noqa: BLE001
@@ -394,6 +397,7 @@ class LLMServer:
                                                  send_tensor_dtype=dtype, send_tensor_shape=(-1, self.cfg.hidden_size),
                                                  recv_tensor_dtype=dtype, recv_tensor_shape=(-1, self.cfg.hidden_size)))
         self.local_encoder: LocalEncoder | None = None  # built lazily for requests that carry raw URLs (no fission)
+        self.timing = {"requests": 0, "inputs_ms": 0.0, "first_token_ms": 0.0}
         kv_cfg = json.loads(args.kv_transfer_config) if args.kv_transfer_config else {}
         self.kv_role = kv_cfg.get("kv_role")
         self.engine_id = uuid.uuid4().hex
@@ -681,6 +685,7 @@ class LLMServer:
     async def chat(self, body: dict[str, Any]):
         xargs = body.get("vllm_xargs") or {}
         kv_in: dict[str, Any] | None = None
+        t_arrival = time.perf_counter()
         try:
             recv_kv = xargs.get("cornserve_kv_transfer_params_recv_id")
             if recv_kv is not None:
@@ -707,6 +712,9 @@ class LLMServer:
         if omni_view:
             seq.return_hidden = False   # the answer is generated first; the talker's view is captured in a second pass
             held_ids, recv_ids = recv_ids, []   # the encoder rows are needed again by that pass: release them afterwards
+        t_built = time.perf_counter()
+        self.timing["requests"] += 1
+        self.timing["inputs_ms"] += (t_built - t_arrival) * 1e3   # tokenising + encoding or receiving the embeddings
         queue = self.llm.submit(seq)
         if omni_view:
             try:
@@ -738,6 +746,7 @@ class LLMServer:
                     out: StepOutput = await queue.get()
                     if first:
                         first = False
+                        self.timing["first_token_ms"] += (time.perf_counter() - t_built) * 1e3   # queue + prefill
                         if recv_ids:
                             await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
                         if kv_in is not None:
@@ -854,7 +863,9 @@ class LLMServer:
                     "kv_pages": eng.cfg.num_pages, "kv_pages_free": eng.blocks.num_free,
                     "d2h_bytes": 4 * (eng.stats["decode_tokens"] + eng.stats["prefill_steps"]),
                     "tp_publish_ms": getattr(self.llm.tp, "publish_ms", 0.0) if self.llm.tp is not None else 0.0,
+                    **self.timing,
                     "h2d_bytes": self.local_encoder.h2d_bytes if self.local_encoder is not None else 0,
+                    "local_encoder_ms": self.local_encoder.busy_ms if self.local_encoder is not None else 0.0,
                     "local_encoder_images": self.local_encoder.images if self.local_encoder is not None else 0,
                     "local_encoder_batches": self.local_encoder.batches if self.local_encoder is not None else 0}
 
