@@ -235,13 +235,10 @@ def llm_main(a: argparse.Namespace) -> None:
     from vllm.v1.engine.async_llm import AsyncLLM
 
     hidden = 256 if a.small else HIDDEN
-    slabs = {i: torch.from_file(p, shared=True, size=a.slab_bytes, dtype=torch.uint8) for i, p in enumerate(a.slab.split(","))}
-    text_rows = (torch.randn(4096, hidden, generator=torch.Generator().manual_seed(1)) * 0.02).to(torch.bfloat16)
-    # Attention backend: on sm_100 vLLM's first choice is FlashInfer, whose helper kernels are compiled with nvcc at the
-    # first start; on a fresh box without FlashInfer's cache that takes longer than this arm is given.  The next entry
-    # of vLLM's own priority list, FLASH_ATTN, ships precompiled in the wheel; Triton attention is the one after.
-    # REF_VLLM_ATTENTION_BACKEND=auto restores vLLM's own choice.
-    wanted = os.environ.get("REF_VLLM_ATTENTION_BACKEND", "FLASH_ATTN,TRITON_ATTN,auto").split(",")
+    # Attention backend: vLLM's own choice first ("auto": FlashInfer on sm_100).  FlashInfer compiles helper kernels
+    # with nvcc at the first start; if that takes longer than REF_VLLM_START_TIMEOUT_S on a box without its cache, the
+    # next entries of vLLM's own priority list are tried: FLASH_ATTN (precompiled in the wheel), then Triton attention.
+    wanted = os.environ.get("REF_VLLM_ATTENTION_BACKEND", "auto,FLASH_ATTN,TRITON_ATTN").split(",")
     start_limit = float(os.environ.get("REF_VLLM_START_TIMEOUT_S", "240"))
     engine, last = None, None
 
@@ -281,6 +278,10 @@ def llm_main(a: argparse.Namespace) -> None:
             print(f"llm replica {a.replica}: attention backend {backend} did not start: {type(e).__name__}: {e}", flush=True)
     if engine is None:
         raise RuntimeError(f"vLLM did not start with any of {wanted}: {last}")
+    # (after the engine: vLLM may fork its engine process, and a forked child of a process that has already run
+    # multi-threaded CPU kernels of torch deadlocks in its first one)
+    slabs = {i: torch.from_file(p, shared=True, size=a.slab_bytes, dtype=torch.uint8) for i, p in enumerate(a.slab.split(","))}
+    text_rows = (torch.randn(4096, hidden, generator=torch.Generator().manual_seed(1)) * 0.02).to(torch.bfloat16)
     print(f"llm replica {a.replica}: engine ready", flush=True)
     conn = Client(("127.0.0.1", a.front_port), authkey=AUTH)
     send_lock = threading.Lock()
@@ -430,7 +431,8 @@ class Front:
             # no network here: vLLM must not look for its address through a route to the outside or a host name that
             # does not resolve (its torch.distributed rendezvous then waits for ever)
             env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus, VLLM_HOST_IP="127.0.0.1", GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo",
-                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1", VLLM_USE_FLASHINFER_SAMPLER="0", PYTHONFAULTHANDLER="1")
+                       VLLM_LOGGING_LEVEL="INFO", MASTER_ADDR="127.0.0.1", VLLM_USE_FLASHINFER_SAMPLER="0", PYTHONFAULTHANDLER="1",
+                       VLLM_WORKER_MULTIPROC_METHOD="spawn")
             log = open(work / f"llm_{r}.log", "w")
             util = 0.80 if a.share_gpu else 0.93
             self.procs.append(subprocess.Popen(base + ["--role", "llm", "--replica", str(r), "--world", str(lt), "--slab", ",".join(slabs),
