@@ -61,6 +61,20 @@ def test_segment_summary_and_bound():
 
 
 @pytest.mark.timeout(900)
+def test_bench_monolithic_layout_encodes_inside_the_llm_executor():
+    """One rank: no encoder executor; the LLM executor's own vision tower thread encodes the images (and counts them)."""
+    out = subprocess.run([sys.executable, "bench.py", "--small", "--cpu", "--gpus", "1", "--steps", "2", "--warmup", "1",
+                          "--window-s", "2", "--rates", "1,2", "--offline-steps", "0", "--output-tokens", "8"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=800)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["config"]["parallelism"].startswith("1 x monolithic")
+    (llm,) = line["executors"]
+    assert llm["executor"] == "llm" and llm["local_encoder_images"] > 0 and llm["requests"] == sum(s["sent"] for s in line["sweep"])
+    assert all(s["failed"] == 0 for s in line["sweep"]) and line["e2e"]["h2d_bytes_per_step"] > 0
+
+
+@pytest.mark.timeout(900)
 def test_bench_runs_end_to_end_on_cpu_ranks():
     out = subprocess.run([sys.executable, "bench.py", "--small", "--cpu", "--gpus", "2", "--steps", "2", "--warmup", "1",
                           "--window-s", "2", "--rates", "1,2", "--offline-steps", "0", "--output-tokens", "8"],
