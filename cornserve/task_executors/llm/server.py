@@ -462,28 +462,30 @@ class LLMServer:
                  if p.get("type", "text") != "text"]
         if len(parts) != len(marks):
             raise ValueError("placeholder count does not match the multimodal parts")
-        embeds: list[tuple[torch.Tensor, tuple[int, int, int] | None]] = []
-        recv_ids: list[str] = []
-        for p in parts:
+        async def one(p) -> tuple[torch.Tensor, tuple[int, int, int] | None, list[str]]:
             modality = p["type"].split("_")[0]
             url = p[p["type"]]["url"]
             m = _SIDECAR_URI.match(url)
-            if m is not None:
-                if self.sidecar is None:
-                    raise ValueError("request refers to forwarded embeddings but this executor has no sidecar")
-                chunks, k = [], 0
-                while True:
-                    t = await self.sidecar.recv(m["id"], k)
-                    if t is None:
-                        break
-                    chunks.append(t)
-                    k += 1
-                rows = chunks[0] if len(chunks) == 1 else torch.cat(chunks, dim=0)
-                recv_ids.extend(f"{m['id']}:{i}" for i in range(k))
-                embeds.append((rows, self._grid_of(modality, m["url"], rows.shape[0])))
-            else:
+            if m is None:
                 emb, grid = await self._local_encode(modality, url)
-                embeds.append((emb, grid))
+                return emb, grid, []
+            if self.sidecar is None:
+                raise ValueError("request refers to forwarded embeddings but this executor has no sidecar")
+            chunks, k = [], 0
+            while True:
+                t = await self.sidecar.recv(m["id"], k)
+                if t is None:
+                    break
+                chunks.append(t)
+                k += 1
+            rows = chunks[0] if len(chunks) == 1 else torch.cat(chunks, dim=0)
+            return rows, self._grid_of(modality, m["url"], rows.shape[0]), [f"{m['id']}:{i}" for i in range(k)]
+
+        # all parts of a request at once: forwarded embeddings arrive in any order, and locally encoded images of one
+        # request share a tower pass
+        got = await asyncio.gather(*(one(p) for p in parts))
+        embeds = [(rows, grid) for rows, grid, _ in got]
+        recv_ids = [r for _, _, ids_ in got for r in ids_]
         # expand each single placeholder into as many pad tokens as there are embedding rows
         out: list[int] = []
         items: list[MMItem] = []
