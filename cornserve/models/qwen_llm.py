@@ -344,7 +344,8 @@ class QwenLLM(nn.Module):
         fabric, experts, quantised projections).  Every rank sees the same sequence of row counts, so the buffers are
         (re)allocated by all ranks at the same step."""
         if (self.group.size == 1 or self.group.fabric is None or self.cfg.num_experts > 0 or self.device.type != "cuda"
-                or getattr(self, "quantization", None) is not None or not self.prefill_chain):
+                or getattr(self, "quantization", None) is not None or not self.prefill_chain
+                or self.cfg.hidden_size > 4096):   # the reduce + norm kernel keeps a row in registers: up to 4096 wide
             return None
         ctx = getattr(self, "_chain", None)
         if ctx is None or ctx.S_cap < rows:

@@ -14,7 +14,7 @@
 namespace {
 
 constexpr int TP_MAX_WORLD = 8;
-constexpr int TP_MAXV = 8;  // uint4 per lane: H <= 32 * 8 * 8 = 2048
+constexpr int TP_MAXV = 16;  // 16-byte vectors per lane: H <= 32 * 8 * 16 = 4096
 
 struct ReduceNormPushParams {
   int rows;                    // rows owned by this rank in this call
@@ -49,6 +49,10 @@ __device__ __forceinline__ uint4 pack8t(const float (&f)[8]) {
 
 constexpr int TP_ROWS_PER_CTA = 32;  // 8 warps x 4 rows; divides every flag chunk (multiples of 128 rows)
 
+// NV = 16-byte vectors per lane (H <= 256 * NV).  Per row a warp first issues every load of a source (all NV vectors
+// are independent, so they are all in flight together), accumulates in fp32, and only then stores: loads never wait
+// behind the stores of the same row (x_out may alias residual), which is what bounded the first version of this kernel.
+template <int NV>
 __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNormPushParams p) {
   __shared__ int wait_ok;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -77,32 +81,57 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNo
   }
   for (int r = r_first + warp; r < r_end; r += 8) {
     // ---- sum partials + bias + residual ----
-    float acc[TP_MAXV][8];
-    float ss = 0.f, sm = 0.f;
+    float acc[NV][8];
+    uint4 raw[NV];
 #pragma unroll
-    for (int i = 0; i < TP_MAXV; ++i) {
-      const int v = lane + 32 * i;
-      if (v < nvec) {
+    for (int i = 0; i < NV; ++i) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-        if (p.recv != nullptr) {
-          for (int s = 0; s < p.world; ++s) {
+      for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    }
+    if (p.recv != nullptr) {
+      for (int s = 0; s < p.world; ++s) {
+        const __nv_bfloat16* src = p.recv + (static_cast<long long>(s) * p.rows_per_rank + r) * p.ldp;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int v = lane + 32 * i;
+          if (v < nvec) raw[i] = __ldcg(reinterpret_cast<const uint4*>(src + v * 8));
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          if (lane + 32 * i < nvec) {
             float f[8];
-            const __nv_bfloat16* src = p.recv + (static_cast<long long>(s) * p.rows_per_rank + r) * p.ldp + v * 8;
-            unpack8t(__ldcg(reinterpret_cast<const uint4*>(src)), f);
+            unpack8t(raw[i], f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
           }
         }
-        if (p.bias != nullptr) {
+      }
+    }
+    if (p.residual != nullptr) {
+      const __nv_bfloat16* src = p.residual + static_cast<long long>(r) * p.ldr;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) raw[i] = *reinterpret_cast<const uint4*>(src + v * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        if (lane + 32 * i < nvec) {
           float f[8];
-          unpack8t(__ldg(reinterpret_cast<const uint4*>(p.bias + v * 8)), f);
+          unpack8t(raw[i], f);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
         }
-        if (p.residual != nullptr) {
+      }
+    }
+    float ss = 0.f, sm = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        if (p.bias != nullptr) {
           float f[8];
-          unpack8t(*reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(r) * p.ldr + v * 8), f);
+          unpack8t(__ldg(reinterpret_cast<const uint4*>(p.bias + v * 8)), f);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[i][j] += f[j];
         }
@@ -133,7 +162,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_push_kernel(const ReduceNo
     // ---- normalise and write the row into every rank's operand buffer ----
     const long long g = static_cast<long long>(p.rank) * p.rows_per_rank + r;  // row in the gathered operand
 #pragma unroll
-    for (int i = 0; i < TP_MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
       if (v < nvec) {
         float y[8];
@@ -198,7 +227,9 @@ CS_API int cs_tp_reduce_norm_push(int rows, int H, int world, int rank, int rows
   }
   p.err = cs_error_word();
   if (p.gather_chunk % TP_ROWS_PER_CTA != 0 || rows_per_rank % TP_ROWS_PER_CTA != 0) return -1;
-  tp_reduce_norm_push_kernel<<<(rows + TP_ROWS_PER_CTA - 1) / TP_ROWS_PER_CTA, 256, 0, (cudaStream_t)stream>>>(p);
+  const unsigned grid = (rows + TP_ROWS_PER_CTA - 1) / TP_ROWS_PER_CTA;
+  if (H <= 256 * 8) tp_reduce_norm_push_kernel<8><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  else tp_reduce_norm_push_kernel<16><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 
