@@ -279,7 +279,8 @@ def diff_stats(before: list[dict], after: list[dict]) -> dict:
         e = {"executor": a.get("executor"), "tp_size": tp, "gpu_launches": launches}
         for k in ("prefill_steps", "decode_bursts", "prefill_ms", "decode_ms", "decode_host_ms", "prefill_tokens",
                   "decode_tokens", "batches", "items", "busy_ms", "broadcast_ms", "tp_publish_ms", "requests", "inputs_ms",
-                  "first_token_ms", "local_encoder_images", "local_encoder_batches", "local_encoder_ms"):
+                  "first_token_ms", "local_encoder_images", "local_encoder_batches", "local_encoder_ms", "local_encoder_host_ms",
+                  "local_encoder_wait_ms", "alloc_retries", "device_allocs"):
             if k in a:
                 e[k] = round(a[k] - b.get(k, 0), 1)
         if e.get("requests") and "inputs_ms" in e:

@@ -294,6 +294,8 @@ class LocalEncoder:
         self.images = 0
         self.batches = 0
         self.busy_ms = 0.0
+        self.host_ms = 0.0
+        self.wait_ms = 0.0
         self.stream = torch.cuda.Stream(device=self.device, priority=-1) if self.device.type == "cuda" else None
         self.stage = torch.empty(self.STAGING_BYTES, dtype=torch.uint8, pin_memory=True) if self.stream is not None else None
         self.thread = threading.Thread(target=self._run, name="llm-local-encoder", daemon=True)
@@ -350,7 +352,10 @@ class LocalEncoder:
                     if self.stream is not None:
                         for e in embs:   # consumed later by the engine thread's kernels on the default stream
                             e.record_stream(torch.cuda.default_stream(self.device))
+                        t_issued = time.perf_counter()
                         self.stream.synchronize()
+                        self.host_ms += (t_issued - t0) * 1e3   # staging, preprocessing and launching the tower
+                        self.wait_ms += (time.perf_counter() - t_issued) * 1e3   # the GPU finishing it
                 self.images += len(batch)
                 self.batches += 1
                 self.busy_ms += (time.perf_counter() - t0) * 1e3
@@ -868,6 +873,10 @@ class LLMServer:
                     **self.timing,
                     "h2d_bytes": self.local_encoder.h2d_bytes if self.local_encoder is not None else 0,
                     "local_encoder_ms": self.local_encoder.busy_ms if self.local_encoder is not None else 0.0,
+                    "local_encoder_host_ms": self.local_encoder.host_ms if self.local_encoder is not None else 0.0,
+                    "local_encoder_wait_ms": self.local_encoder.wait_ms if self.local_encoder is not None else 0.0,
+                    "alloc_retries": int(torch.cuda.memory_stats(eng.device).get("num_alloc_retries", 0)) if eng.on_gpu else 0,
+                    "device_allocs": int(torch.cuda.memory_stats(eng.device).get("num_device_alloc", 0)) if eng.on_gpu else 0,
                     "local_encoder_images": self.local_encoder.images if self.local_encoder is not None else 0,
                     "local_encoder_batches": self.local_encoder.batches if self.local_encoder is not None else 0}
 
