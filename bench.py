@@ -58,9 +58,10 @@ LAYOUTS = {
     4: {"backend": "EV", "encoder_tp": 2, "llm_tp": 2, "replicas": 1, "name": "eric tp2 x1 + llm tp2 x1"},
     8: {"backend": "EV", "encoder_tp": 2, "llm_tp": 2, "replicas": 2, "name": "eric tp2 x2 + llm tp2 x2"},
 }
-# arrival rates (requests/s) swept at each N, the same for both arms
-RATES = {1: [2.0, 3.5, 5.0, 6.5, 8.0], 2: [3.0, 5.0, 7.0, 9.0, 11.0], 4: [4.0, 7.0, 10.0, 13.0, 16.0],
-         8: [8.0, 14.0, 20.0, 26.0, 32.0]}
+# arrival rates (requests/s) swept at each N, the same for both arms: geometric ladders that start below what either
+# arm sustains and end above what both do, so that each arm's best passing rate lies inside its ladder
+RATES = {1: [3.0, 4.5, 6.5, 9.0, 12.0], 2: [4.0, 6.0, 9.0, 13.0, 18.0], 4: [6.0, 10.0, 16.0, 23.0, 30.0],
+         8: [12.0, 20.0, 32.0, 46.0, 60.0]}
 
 
 def parse_args() -> argparse.Namespace:
@@ -289,6 +290,8 @@ def diff_stats(before: list[dict], after: list[dict]) -> dict:
         if e.get("decode_bursts"):
             e["host_ms_per_decode_burst"] = round(e["decode_host_ms"] / e["decode_bursts"], 3)
             e["ms_per_decode_burst"] = round(e["decode_ms"] / e["decode_bursts"], 3)
+        if a.get("stack_samples"):
+            e["stack_samples"] = a["stack_samples"]
         if e.get("batches"):
             e["ms_per_encoder_batch"] = round(e["busy_ms"] / e["batches"], 3)
             e["broadcast_ms_per_encoder_batch"] = round(e.get("broadcast_ms", 0.0) / e["batches"], 3)

@@ -412,10 +412,15 @@ class QwenLLM(nn.Module):
 
     def forward(self, m: BatchMeta, kv_caches: list[torch.Tensor], return_hidden: bool = False,
                 capture: dict[int, torch.Tensor] | None = None, sampler: tuple | None = None,
-                penalties: tuple | None = None):
+                penalties: tuple | None = None, logprobs: tuple | None = None):
         """Returns ``(next_token_ids [B] int32, hidden [T, H] or None)``.  Greedy unless ``sampler`` gives the per-row
         ``(temperature, top_p, top_k, seed, draws)`` tensors of :func:`ops.sample_rows` (every tensor-parallel rank
-        holds the same gathered logits and the same streams, so all ranks draw the same token)."""
+        holds the same gathered logits and the same streams, so all ranks draw the same token).
+
+        ``logprobs`` = ``(chosen [S, B] f32, top_values [S, B, K] f32, top_ids [S, B, K] i32, step [1] i32)``: the log
+        probability of the chosen token and the ``K`` most likely ones (of the distribution after penalties, before
+        temperature) are written at index ``step`` -- a device value, so the same launches serve every step of a
+        captured decode burst."""
         h = self.forward_hidden(m, kv_caches, capture)
         h_last = ops.gather_rows(h, m.logits_idx)
         logits = self.compute_logits(h_last)
@@ -424,9 +429,17 @@ class QwenLLM(nn.Module):
             # then the chosen token is added to its row's counts
             counts, freq, pres, active = penalties
             ops.apply_penalties_(logits, counts, freq, pres)
+        lsm = torch.log_softmax(logits, dim=-1) if logprobs is not None else None   # before the sampler touches the logits
         tok = ops.argmax(logits) if sampler is None else ops.sample_rows(logits, *sampler)
         if penalties is not None:
             ops.count_tokens_(counts, tok, active)
+        if logprobs is not None:
+            chosen, top_v, top_i, step = logprobs
+            at = step.long()
+            chosen.index_copy_(0, at, lsm.gather(1, tok.long().unsqueeze(1)).view(1, -1))
+            tv, ti = lsm.topk(top_v.shape[-1], dim=-1)
+            top_v.index_copy_(0, at, tv.unsqueeze(0))
+            top_i.index_copy_(0, at, ti.to(torch.int32).unsqueeze(0))
         return tok, (h if return_hidden else None)
 
     # -- checkpoint loading -------------------------------------------------------------------------

@@ -13,7 +13,7 @@ from pathlib import Path
 
 _LIB_PATH = Path(__file__).resolve().parent / "libcornserve.so"
 _lock = threading.Lock()
-_lib: ctypes.CDLL | None = None
+_lib: ctypes.PyDLL | None = None
 
 ERROR_NAMES = {
     0: "ok",
@@ -76,8 +76,12 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
-def load() -> ctypes.CDLL:
-    """Load the kernel library (once) and declare the argument types of every entry point."""
+def load() -> ctypes.PyDLL:
+    """Load the kernel library (once) and declare the argument types of every entry point.
+
+    Every entry point only enqueues work on a stream, a few microseconds, so calls keep the interpreter lock
+    (``PyDLL``): giving it up around each launch would let a busy thread of the same process take it for a whole
+    switch interval, once per kernel."""
     global _lib
     if _lib is not None:
         return _lib
@@ -89,7 +93,7 @@ def load() -> ctypes.CDLL:
                 f"{_LIB_PATH} is missing: build it with `python -m cornserve.ops.build` "
                 "(the CUDA path never falls back to PyTorch kernels)"
             )
-        lib = ctypes.CDLL(str(_LIB_PATH))
+        lib = ctypes.PyDLL(str(_LIB_PATH))
         for name, (argtypes, restype) in _SIGNATURES.items():
             if not hasattr(lib, name):
                 continue

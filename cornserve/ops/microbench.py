@@ -16,6 +16,9 @@
   python -m cornserve.ops.microbench tp-chain 19136 1280 3424 # fused TP half-block on one rank (loopback fabric)
   python -m cornserve.ops.microbench ulysses-qkv 4352 3072 24 # q|k|v GEMM with the all-to-all epilogue (loopback)
 
+``--graph`` (gemm / skinny / swiglu) times the launches inside one CUDA graph over rotating weight copies, which is how
+the decode path runs them; without it a kernel of a few microseconds is dominated by the host's launch path.
+
 Each line printed gives the time per launch, the achieved rate and the fraction of the measured peak
 (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).  The same
 commands, with ``--iters 1 --warmup 1``, are what the ncu summaries under ``profiles/`` were captured on.
@@ -65,6 +68,33 @@ class Timer:
         return total / self.iters * 1e-3
 
 
+def graph_time(launch, weights: list[torch.Tensor], replays: int = 5) -> float:
+    """Device time per launch with the host out of the picture: one CUDA graph of ``len(weights)`` launches, each on
+    its own copy of the weight (together larger than L2, so every launch streams its weight from HBM as a decode step
+    does), replayed ``replays`` times between two events."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for w in weights[:2]:
+            launch(w)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for w in weights:
+            launch(w)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_error("microbench")
+    return e0.elapsed_time(e1) * 1e-3 / (replays * len(weights))
+
+
 def report(name: str, secs: float, flops: float = 0.0, nbytes: float = 0.0) -> None:
     bw, fl, tag = peaks()
     parts = [f"{name}: {secs * 1e6:.1f} us"]
@@ -84,13 +114,41 @@ def main() -> None:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0, help="K splits of the weight-streaming kernel (0 = its own choice)")
+    ap.add_argument("--graph", action="store_true",
+                    help="gemm / skinny / swiglu: time inside a CUDA graph over rotating weight copies (no host time)")
+    ap.add_argument("--cublas", action="store_true", help="with --graph: the same shape through torch's cuBLAS call")
     a = ap.parse_args()
     t = Timer(a.iters, a.warmup, not a.no_flush)
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *s, std=1.0: (torch.randn(*s, device=dev, generator=g) * std).bfloat16()  # noqa: E731
     k = a.kernel
-    if k in ("gemm", "swiglu", "skinny"):
+    if k in ("gemm", "swiglu", "skinny") and a.graph:
+        M, N, K = a.args[:3]
+        x = rnd(M, K)
+        rows = 2 * N if k == "swiglu" else N
+        copies = max(2, min(64, -(-(300 << 20) // (rows * K * 2))))
+        weights = [rnd(rows, K, std=K ** -0.5) for _ in range(copies)]
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        if a.cublas:
+            if k == "swiglu":
+                def launch(w):
+                    y = torch.nn.functional.linear(x, w)
+                    torch.mul(torch.nn.functional.silu(y[:, :N]), y[:, N:], out=out)
+            else:
+                def launch(w):
+                    torch.matmul(x, w.t(), out=out)
+        elif k == "swiglu":
+            def launch(w):
+                ops.swiglu_linear(x, w, bn=a.bn, skinny=True if a.splits else None, splits=a.splits)
+        else:
+            def launch(w):
+                ops.linear(x, w, out=out, bn=a.bn, skinny=(k == "skinny"), splits=a.splits)
+        secs = graph_time(launch, weights)
+        mult = 2.0 if k == "swiglu" else 1.0
+        report(f"{'cublas ' if a.cublas else ''}{k} {M}x{N}x{K} (graph of {copies} launches, splits={a.splits}, bn={a.bn})", secs,
+               2.0 * mult * M * N * K, 2.0 * (M * K + rows * K + M * N))
+    elif k in ("gemm", "swiglu", "skinny"):
         M, N, K = a.args[:3]
         x = rnd(M, K)
         if k == "swiglu":

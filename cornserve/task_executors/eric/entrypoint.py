@@ -13,6 +13,7 @@ from ...logging import get_logger
 from ...parallel.state import init_distributed
 from ...services.process import free_port
 from ...tracing import configure_otel
+from ...utils.threads import maybe_start_sampler, tune_interpreter
 from .config import EricConfig
 from .engine import Engine
 from .router import create_app
@@ -23,7 +24,9 @@ logger = get_logger(__name__)
 
 def main(argv: list[str] | None = None) -> None:
     config = tyro.cli(EricConfig, args=argv)
+    tune_interpreter()
     configure_otel("eric")
+    maybe_start_sampler()
     tp = config.model.tp_size
     group = None
     children: list[subprocess.Popen] = []

@@ -33,6 +33,9 @@ from .block_manager import BlockManager
 from .mrope import mrope_positions
 
 
+MAX_TOP_LOGPROBS = 20   # as the OpenAI API allows
+
+
 @dataclass
 class SamplingParams:
     max_tokens: int = 256
@@ -44,6 +47,7 @@ class SamplingParams:
     seed: int | None = None       # names the request's random stream; None = drawn once when the request is added
     frequency_penalty: float = 0.0   # OpenAI semantics: a token generated c times loses frequency_penalty * c ...
     presence_penalty: float = 0.0    # ... and presence_penalty once it was generated at all
+    logprobs: int = -1               # -1: off; k >= 0: report the chosen token's log probability and the k most likely tokens
 
     @classmethod
     def from_request(cls, body: dict, default_temperature: float = 1.0, **kw) -> "SamplingParams":
@@ -52,6 +56,11 @@ class SamplingParams:
         t = body.get("temperature")
         k = body.get("top_k")
         seed = body.get("seed")
+        lp = body.get("logprobs")
+        if lp is True:      # chat completions: a switch plus ``top_logprobs``
+            kw.setdefault("logprobs", max(0, min(MAX_TOP_LOGPROBS, int(body.get("top_logprobs") or 0))))
+        elif lp is not None and lp is not False:   # completions: a count
+            kw.setdefault("logprobs", max(0, min(MAX_TOP_LOGPROBS, int(lp))))
         return cls(temperature=float(t) if t is not None else float(default_temperature),
                    top_p=float(body["top_p"]) if body.get("top_p") is not None else 1.0,
                    top_k=int(k) if k is not None and int(k) > 0 else 0,
@@ -151,6 +160,13 @@ class StepOutput:
     finished: bool
     finish_reason: str | None = None
     hidden: torch.Tensor | None = None
+    # per new token, for requests that asked: (log probability of the token, [(token id, log probability), ...] most likely)
+    logprobs: list[tuple[float, list[tuple[int, float]]]] | None = None
+
+
+def _logprob_entry(lp: list[np.ndarray], step: int, row: int, k: int) -> tuple[float, list[tuple[int, float]]]:
+    chosen, top_v, top_i = lp
+    return float(chosen[step, row]), [(int(top_i[step, row, j]), float(top_v[step, row, j])) for j in range(k)]
 
 
 class _DecodeState:
@@ -180,6 +196,10 @@ class _DecodeState:
         self.frequency = torch.zeros(B, dtype=torch.float32, device=device)
         self.presence = torch.zeros(B, dtype=torch.float32, device=device)
         self.counts: torch.Tensor | None = None
+        # log probabilities (buckets whose graph reports them): per step of a burst, chosen token and the most likely ones
+        self.lp_chosen: torch.Tensor | None = None
+        self.lp_top_v: torch.Tensor | None = None
+        self.lp_top_i: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_replay = 0
         self.paths_per_replay: dict[str, int] = {}
@@ -189,6 +209,14 @@ class _DecodeState:
 
     def penalties(self):
         return (self.counts, self.frequency, self.presence, self.active) if self.counts is not None else None
+
+    def enable_logprobs(self, burst: int, device: torch.device) -> None:
+        self.lp_chosen = torch.zeros(max(burst, 1), self.B, dtype=torch.float32, device=device)
+        self.lp_top_v = torch.zeros(max(burst, 1), self.B, MAX_TOP_LOGPROBS, dtype=torch.float32, device=device)
+        self.lp_top_i = torch.zeros(max(burst, 1), self.B, MAX_TOP_LOGPROBS, dtype=torch.int32, device=device)
+
+    def logprobs(self):
+        return (self.lp_chosen, self.lp_top_v, self.lp_top_i, self.step_counter) if self.lp_chosen is not None else None
 
     def meta(self) -> BatchMeta:
         return BatchMeta(self.input_ids, self.positions, self.slot, self.cu_q, self.kv_len, self.block_table,
@@ -427,9 +455,18 @@ class LLMEngine:
             sampler = (f([s.params.temperature for s, _ in batch], np.float32), f([s.params.top_p for s, _ in batch], np.float32),
                        f([s.params.top_k for s, _ in batch]), f([s.params.seed or 0 for s, _ in batch], np.int64),
                        f([len(s.output_ids) for s, _ in batch]))
+        lp_dev = None
+        if any(s.params.logprobs >= 0 for s, _ in batch):
+            nb = len(batch)
+            lp_dev = (torch.zeros(1, nb, dtype=torch.float32, device=dev),
+                      torch.zeros(1, nb, MAX_TOP_LOGPROBS, dtype=torch.float32, device=dev),
+                      torch.zeros(1, nb, MAX_TOP_LOGPROBS, dtype=torch.int32, device=dev),
+                      torch.zeros(1, dtype=torch.int32, device=dev))
         with torch.inference_mode():
-            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden, capture=capture, sampler=sampler)
+            next_tok, hidden = self.model(m, self.kv_caches, return_hidden=want_hidden, capture=capture, sampler=sampler,
+                                          logprobs=lp_dev)
         toks = next_tok.tolist()
+        lp = [t.cpu().numpy() for t in lp_dev[:3]] if lp_dev is not None else None
         self.stats["prefill_tokens"] += tok
         outs: list[StepOutput] = []
         now = time.monotonic()
@@ -446,7 +483,10 @@ class LLMEngine:
             s.status = SeqStatus.RUNNING
             s.first_token_time = now
             s.output_ids.append(int(toks[b]))
-            outs.append(self._emit(s, [int(toks[b])]))
+            out = self._emit(s, [int(toks[b])])
+            if lp is not None and s.params.logprobs >= 0:
+                out.logprobs = [_logprob_entry(lp, 0, b, s.params.logprobs)]
+            outs.append(out)
         self._reap()
         return outs
 
@@ -471,10 +511,15 @@ class LLMEngine:
         sampling = penalized or any(s.params.samples for s in seqs)
         # a bucket's graph ends in the arg-max, in the sampling kernel, or in penalties + the sampling kernel
         key = (B, "penalty") if penalized else ((B, "sample") if sampling else B)
+        want_lp = any(s.params.logprobs >= 0 for s in seqs)
+        if want_lp:
+            key = (key if isinstance(key, tuple) else (key, "greedy")) + ("logprobs",)
         st = self._decode_states.get(key)
         if st is None:
             st = self._decode_states[key] = _DecodeState(B, self.max_blocks, self.cfg.decode_burst, self.device)
             st.sampling = sampling
+            if want_lp:
+                st.enable_logprobs(self.cfg.decode_burst, self.device)
             if penalized:
                 st.counts = torch.zeros(B, self.mcfg.vocab_size, dtype=torch.int32, device=self.device)
         # host-side batch state
@@ -523,6 +568,7 @@ class LLMEngine:
                 self._decode_once(st)
         self.stats["decode_host_ms"] += (time.perf_counter() - t_host) * 1e3   # batch state + launches, before the wait
         log = st.out_log[:burst].cpu().numpy()  # one sync per burst
+        lp = [t[:burst].cpu().numpy() for t in (st.lp_chosen, st.lp_top_v, st.lp_top_i)] if want_lp else None
         self.stats["decode_tokens"] += burst * n
         outs = []
         for b, s in enumerate(seqs):
@@ -532,7 +578,10 @@ class LLMEngine:
                 new.append(int(t))
                 if self._should_stop(s):
                     break
-            outs.append(self._emit(s, new))
+            out = self._emit(s, new)
+            if lp is not None and s.params.logprobs >= 0:
+                out.logprobs = [_logprob_entry(lp, i, b, s.params.logprobs) for i in range(len(new))]
+            outs.append(out)
         self._reap()
         return outs
 
@@ -556,7 +605,8 @@ class LLMEngine:
 
     def _decode_once(self, st: _DecodeState) -> None:
         def body():
-            tok, _ = self.model(st.meta(), self.kv_caches, sampler=st.sampler(), penalties=st.penalties())
+            tok, _ = self.model(st.meta(), self.kv_caches, sampler=st.sampler(), penalties=st.penalties(),
+                                logprobs=st.logprobs())
             ops.decode_advance_(tok, st.input_ids, st.positions, st.kv_len, st.slot, st.block_table, st.active,
                                 st.out_log, st.step_counter)
 

@@ -30,6 +30,7 @@ import asyncio
 import base64
 import concurrent.futures
 import contextlib
+import dataclasses
 import io
 import json
 import os
@@ -55,6 +56,7 @@ from ...models.qwen_llm import LLMConfig, QwenLLM
 from ...parallel.state import ParallelGroup
 from ...tracing import configure_otel
 from ...utils.hub import load_config, load_model_weights
+from ...utils.threads import maybe_start_sampler, sampler_report, tune_interpreter
 from ..eric.preprocess import smart_resize
 from ..eric.processor import fetch_bytes
 from .engine import EngineConfig, LLMEngine, MMItem, PrefilledKV, SamplingParams, Sequence, StepOutput
@@ -719,55 +721,92 @@ class LLMServer:
         if omni_view:
             seq.return_hidden = False   # the answer is generated first; the talker's view is captured in a second pass
             held_ids, recv_ids = recv_ids, []   # the encoder rows are needed again by that pass: release them afterwards
+        n_choices = max(1, int(body.get("n") or 1))
+        if n_choices > 1 and (omni_view or producer or kv_in is not None or "cornserve_hidden_states_forward_id" in xargs):
+            await self._release(recv_ids)
+            return JSONResponse({"error": {"message": "n > 1 is available for plain chat completions only",
+                                           "type": "invalid_request_error"}}, status_code=400)
         t_built = time.perf_counter()
         self.timing["requests"] += 1
         self.timing["inputs_ms"] += (t_built - t_arrival) * 1e3   # tokenising + encoding or receiving the embeddings
-        queue = self.llm.submit(seq)
+        # ``n`` choices are n sequences over the same prompt (and the same encoder rows), each with its own random stream
+        seqs = [seq] + [Sequence(f"{seq.seq_id}-{i}", seq.prompt_ids,
+                                 dataclasses.replace(seq.params, seed=None if seq.params.seed is None else seq.params.seed + i),
+                                 mm_items=seq.mm_items) for i in range(1, n_choices)]
+        queues = [self.llm.submit(s) for s in seqs]
+        queue = queues[0]
         if omni_view:
             try:
                 return await self._omni_thinker_forward(seq, queue, xargs, rid, created, model)
             finally:
                 await self._release(held_ids)
         include_usage = bool((body.get("stream_options") or {}).get("include_usage", False))
+        want_logprobs = seq.params.logprobs >= 0
 
-        def chunk(delta: dict[str, Any], finish: str | None = None, usage: dict | None = None) -> str:
+        def chunk(delta: dict[str, Any], finish: str | None = None, usage: dict | None = None, index: int = 0,
+                  logprobs: dict | None = None) -> str:
+            choice = {"index": index, "delta": delta, "finish_reason": finish}
+            if logprobs is not None:
+                choice["logprobs"] = logprobs
             payload = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
-                       "choices": [{"index": 0, "delta": delta, "finish_reason": finish}] if usage is None else []}
+                       "choices": [choice] if usage is None else []}
             if usage is not None:
                 payload["usage"] = usage
             return f"data: {json.dumps(payload)}\n\n"
 
+        def logprob_content(out: StepOutput) -> list[dict]:
+            """OpenAI's ``logprobs.content`` entries of the tokens of one engine output."""
+            def entry(tid: int, lp: float) -> dict:
+                t = self.tokenizer.decode([tid])
+                return {"token": t, "logprob": lp, "bytes": list(t.encode("utf-8"))}
+            return [{**entry(tid, lp), "top_logprobs": [entry(i, v) for i, v in top]}
+                    for tid, (lp, top) in zip(out.new_token_ids, out.logprobs or [])]
+
         stops = self._stops(body)
         hold = max((len(x) for x in stops), default=1) - 1   # characters that may still turn out to start a stop string
+        first_left = [n_choices]   # choices that have not produced their first token yet (they all read the encoder rows)
 
-        async def consume():
-            """Yields (text_delta, engine output, tokens so far) per engine output.  With ``stop`` strings the text is cut
-            before the first match, the request ends with reason ``stop`` and the sequence is taken out of the engine; the
-            last ``hold`` characters are kept back until it is clear that they do not begin a stop string."""
+        async def consume(idx: int = 0):
+            """Yields (text_delta, engine output, tokens so far) per engine output of choice ``idx``.  With ``stop`` strings
+            the text is cut before the first match, the request ends with reason ``stop`` and the sequence is taken out of
+            the engine; the last ``hold`` characters are kept back until it is clear that they do not begin a stop string."""
             all_ids: list[int] = []
             emitted = ""
+            stable_text, stable_ids = "", 0
             first = True
             finished = False
+            my_seq, my_queue = seqs[idx], queues[idx]
             try:
                 while True:
-                    out: StepOutput = await queue.get()
+                    out: StepOutput = await my_queue.get()
                     if first:
                         first = False
-                        self.timing["first_token_ms"] += (time.perf_counter() - t_built) * 1e3   # queue + prefill
-                        if recv_ids:
-                            await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
-                        if kv_in is not None:
-                            await self._release_at_producer(kv_in)  # the pages were pulled before the first output
+                        first_left[0] -= 1
+                        if idx == 0:
+                            self.timing["first_token_ms"] += (time.perf_counter() - t_built) * 1e3   # queue + prefill
+                        if first_left[0] == 0:
+                            if recv_ids:
+                                await self._release(recv_ids)  # the prompt embeddings were consumed by the prefill
+                            if kv_in is not None:
+                                await self._release_at_producer(kv_in)  # the pages were pulled before the first output
                     all_ids.extend(out.new_token_ids)
-                    text = self.tokenizer.decode(all_ids)
+                    # detokenise only the tail: the text of ids[:stable_ids] is final; a few tokens before it give the
+                    # tokenizer the context it needs (leading spaces, merges across the boundary)
+                    ctx = max(0, stable_ids - 6)
+                    lead = self.tokenizer.decode(all_ids[ctx:stable_ids]) if stable_ids else ""
+                    tail = self.tokenizer.decode(all_ids[ctx:])[len(lead):]
+                    text = stable_text + tail
+                    if not tail.endswith("\ufffd"):
+                        stable_text, stable_ids = text, len(all_ids)
                     if stops:
                         cut = min((i for i in (text.find(x, max(0, len(emitted) - hold)) for x in stops) if i >= 0), default=-1)
                         if cut >= 0:
                             finished = True
-                            self.llm.abort(seq.seq_id)
-                            yield text[len(emitted):cut], StepOutput(out.seq_id, out.new_token_ids, True, "stop"), len(all_ids)
+                            self.llm.abort(my_seq.seq_id)
+                            yield text[len(emitted):cut], StepOutput(out.seq_id, out.new_token_ids, True, "stop",
+                                                                     logprobs=out.logprobs), len(all_ids)
                             return
-                    if text.endswith("�") and not out.finished:
+                    if text.endswith("\ufffd") and not out.finished:
                         delta = ""  # an incomplete multi-byte character: wait for the next token
                     elif stops and not out.finished:
                         safe = max(len(emitted), len(text) - hold)
@@ -780,7 +819,39 @@ class LLMServer:
                         return
             finally:
                 if not finished:
-                    self.llm.abort(seq.seq_id)   # the client went away: free the sequence's pages
+                    self.llm.abort(my_seq.seq_id)   # the client went away: free the sequence's pages
+                if first:   # never produced a token: it no longer holds the release of the encoder rows back
+                    first_left[0] -= 1
+                    if first_left[0] == 0 and recv_ids:
+                        await self._release(recv_ids)
+
+        async def merged():
+            """(choice index, text delta, engine output, tokens so far) of every choice, as they arrive."""
+            if n_choices == 1:
+                async for delta, out, cnt in consume(0):
+                    yield 0, delta, out, cnt
+                return
+            sink: asyncio.Queue = asyncio.Queue()
+
+            async def pump(i: int) -> None:
+                try:
+                    async for delta, out, cnt in consume(i):
+                        await sink.put((i, delta, out, cnt))
+                finally:
+                    sink.put_nowait((i, None, None, 0))
+
+            tasks = [asyncio.create_task(pump(i)) for i in range(n_choices)]
+            live = n_choices
+            try:
+                while live:
+                    i, delta, out, cnt = await sink.get()
+                    if out is None:
+                        live -= 1
+                        continue
+                    yield i, delta, out, cnt
+            finally:
+                for t in tasks:
+                    t.cancel()
 
         if "cornserve_hidden_states_forward_id" in xargs:
             hidden = None
@@ -821,33 +892,40 @@ class LLMServer:
                 # The role chunk goes out with the first generated token, so the arrival of the first chunk is the time
                 # to first token; after that one chunk per engine output (a decode burst), even when its bytes do not yet
                 # form a printable character, so clients see every step.
-                n, first = 0, True
-                async for delta, out, n in consume():
+                counts, started = [0] * n_choices, set()
+                async for i, delta, out, cnt in merged():
                     if out.finish_reason and out.finish_reason.startswith("error"):
                         yield f"data: {json.dumps({'error': out.finish_reason})}\n\n"
                         break
-                    if first:
-                        first = False
-                        yield chunk({"role": "assistant", "content": ""})
-                    yield chunk({"content": delta}, out.finish_reason if out.finished else None)
+                    counts[i] = cnt
+                    if i not in started:
+                        started.add(i)
+                        yield chunk({"role": "assistant", "content": ""}, index=i)
+                    yield chunk({"content": delta}, out.finish_reason if out.finished else None, index=i,
+                                logprobs={"content": logprob_content(out)} if want_logprobs else None)
                 if include_usage:
-                    yield chunk({}, usage={"prompt_tokens": seq.prompt_len, "completion_tokens": n,
-                                           "total_tokens": seq.prompt_len + n})
+                    yield chunk({}, usage={"prompt_tokens": seq.prompt_len, "completion_tokens": sum(counts),
+                                           "total_tokens": seq.prompt_len + sum(counts)})
                 yield "data: [DONE]\n\n"
 
             return StreamingResponse(sse(), media_type="text/event-stream")
 
-        text, reason, n = "", None, 0
-        async for delta, out, n in consume():
-            text += delta
-            reason = out.finish_reason
-        if reason and reason.startswith("error"):
-            return JSONResponse({"error": {"message": reason}}, status_code=500)
+        texts, reasons, counts = [""] * n_choices, [None] * n_choices, [0] * n_choices
+        lps: list[list[dict]] = [[] for _ in range(n_choices)]
+        async for i, delta, out, cnt in merged():
+            texts[i] += delta
+            reasons[i], counts[i] = out.finish_reason, cnt
+            if want_logprobs:
+                lps[i].extend(logprob_content(out))
+        bad = next((r for r in reasons if r and r.startswith("error")), None)
+        if bad:
+            return JSONResponse({"error": {"message": bad}}, status_code=500)
+        choices = [{"index": i, "message": {"role": "assistant", "content": texts[i]}, "finish_reason": reasons[i],
+                    **({"logprobs": {"content": lps[i]}} if want_logprobs else {})} for i in range(n_choices)]
         return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
-                             "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
-                                          "finish_reason": reason}],
-                             "usage": {"prompt_tokens": seq.prompt_len, "completion_tokens": n,
-                                       "total_tokens": seq.prompt_len + n},
+                             "choices": choices,
+                             "usage": {"prompt_tokens": seq.prompt_len, "completion_tokens": sum(counts),
+                                       "total_tokens": seq.prompt_len + sum(counts)},
                              **({"cornserve": {"kv_source": seq.kv_source}} if kv_in is not None else {})})
 
     def create_app(self) -> FastAPI:
@@ -878,7 +956,8 @@ class LLMServer:
                     "alloc_retries": int(torch.cuda.memory_stats(eng.device).get("num_alloc_retries", 0)) if eng.on_gpu else 0,
                     "device_allocs": int(torch.cuda.memory_stats(eng.device).get("num_device_alloc", 0)) if eng.on_gpu else 0,
                     "local_encoder_images": self.local_encoder.images if self.local_encoder is not None else 0,
-                    "local_encoder_batches": self.local_encoder.batches if self.local_encoder is not None else 0}
+                    "local_encoder_batches": self.local_encoder.batches if self.local_encoder is not None else 0,
+                    "stack_samples": sampler_report()}
 
         @app.get("/v1/models")
         async def models():
@@ -941,10 +1020,12 @@ def follower_main(args: argparse.Namespace) -> None:
 def main(argv: list[str] | None = None) -> None:
     args = parse_args(argv)
     args.argv = list(argv) if argv is not None else sys.argv[1:]
+    tune_interpreter()
     if args.tp_rank > 0:
         follower_main(args)
         return
     configure_otel("llm")
+    maybe_start_sampler()
     if args.run_talker:
         from .talker_server import TalkerServer
 

@@ -63,6 +63,11 @@ class OpenAIChatCompletionRequest(TaskInput):
     top_p: float | None = None
     request_id: str = Field(default_factory=lambda: uuid.uuid4().hex)
     ignore_eos: bool = False
+    # further OpenAI fields that the LLM executor honours (absent from the request unless set)
+    n: int | None = None
+    stop: str | list[str] | None = None
+    logprobs: bool | None = None
+    top_logprobs: int | None = None
     # extensions: encoder outputs and KV-transfer parameters arrive through the sidecars
     cornserve_embeddings: list[DataForward[Tensor]] = []
     cornserve_kv_transfer_params: DataForward[dict] | None = None

@@ -11,8 +11,10 @@
 //   warps 2..5         epilogue: thread r owns W row r of the tile = output column n0 + r, so for a
 //                      fixed token the 32 lanes of a warp write 32 consecutive output columns
 //
-// Scratch: `ws` holds splits x N x M_pad fp32 partials, `counters` one int per tile (zero before the
-// first call; the reducing CTA resets its counter, so back-to-back calls on one stream can share them).
+// Scratch: `ws` holds splits x tiles x M_pad x 128 fp32 partials, `counters` one int per tile (zero before the
+// first call; the CTA that leaves a tile last resets its counter, so back-to-back calls on one stream can share
+// them).  When the whole grid is resident (tiles x splits <= SMs) the splits of a tile wait for one another and each
+// reduces and finishes a share of the tile's 16-token chunks; otherwise the split that arrives last does all of it.
 #include "common.cuh"
 
 namespace {
@@ -87,6 +89,7 @@ struct SkinnyParams {
   const __nv_bfloat16* residual; long long ldr;
   int act;
   float* ws; int* counters;
+  int par_reduce;       // every split CTA of a tile reduces a share of the tile's token chunks (all CTAs resident)
   uint32_t idesc;
   uint32_t tmem_cols;
   int* err;
@@ -194,7 +197,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const bool row_valid = p.swiglu ? (n0 + (r & 63) < p.N) : (n0 + r < p.N);
     if (p.splits > 1) {
       // 1) publish this split's partial sums
-      float* wsrow = p.ws + (static_cast<long long>(split) * (p.swiglu ? 2 * p.N : p.N) + (p.swiglu ? (r < 64 ? n0 + r : p.N + n0 + r - 64) : n0 + r)) * p.m_pad;
+      // layout [split][tile][token][tile row]: the 32 lanes of a warp store (and later load) 128 contiguous bytes
+      float* wst = p.ws + (static_cast<long long>(split) * num_tiles_total + tile) * 128 * p.m_pad + r;
       for (int c = 0; c < chunks; ++c) {
         uint32_t v[16];
         if (ok && n_it > 0) { tmem_ld16(t_row + c * 16, v); tmem_wait_ld(); }
@@ -202,28 +206,44 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0;
         }
-        if (row_valid) {
-          float4* dst = reinterpret_cast<float4*>(wsrow + c * 16);
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-        }
+        for (int i = 0; i < 16; ++i) __stcg(wst + (c * 16 + i) * 128, __uint_as_float(v[i]));
       }
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
-        const int prev = atomicAdd(&p.counters[tile], 1);
-        if (prev == p.splits - 1) { p.counters[tile] = 0; is_last = 1; }
+        if (p.par_reduce) {
+          // arrivals count in the low half of the tile's word, departures in the high half; wait (bounded) until
+          // every split of this tile has published: all CTAs of the grid are resident (checked by the host)
+          atomicAdd(&p.counters[tile], 1);
+          uint64_t t0 = 0;
+          for (uint32_t spin = 0;; ++spin) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.counters + tile) : "memory");
+            if ((v & 0xffff) >= p.splits) break;
+            if ((spin & 0xff) == 0xff) {
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              if (now - t0 > CS_WAIT_LIMIT_NS) { cs_set_error(p.err, CS_ERR_TIMEOUT_EPI); ok = false; is_last = -1; break; }
+            }
+          }
+        } else {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          if (prev == p.splits - 1) { p.counters[tile] = 0; is_last = 1; }
+        }
         __threadfence();
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-    const bool reducer = (p.splits == 1) || (*reinterpret_cast<volatile int*>(&is_last) != 0);
+    const int last_word = *reinterpret_cast<volatile int*>(&is_last);
+    const bool reducer = (p.splits == 1) || (p.par_reduce ? last_word == 0 : last_word != 0);
+    // token chunks this CTA finishes: all of them, or every splits-th one when the splits share the reduction
+    const int c_first = (p.splits > 1 && p.par_reduce) ? split : 0;
+    const int c_step = (p.splits > 1 && p.par_reduce) ? p.splits : 1;
     if (reducer) {
       const float bias = (p.bias != nullptr && row_valid) ? __bfloat162float(p.bias[p.swiglu ? (r < 64 ? n0 + r : p.N + n0 + r - 64) : n0 + r]) : 0.f;
       (void)w_row;
-      for (int c = 0; c < chunks; ++c) {
+      for (int c = c_first; c < chunks; c += c_step) {
         float f[16];
         if (p.splits == 1) {
           uint32_t v[16];
@@ -237,15 +257,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) f[i] = 0.f;
-          if (row_valid) {
-            const long long rows_total = p.swiglu ? 2 * p.N : p.N;
-            const long long myrow = p.swiglu ? (r < 64 ? n0 + r : p.N + n0 + r - 64) : n0 + r;
-            for (int s = 0; s < p.splits; ++s) {
-              const float4* src = reinterpret_cast<const float4*>(p.ws + (s * rows_total + myrow) * p.m_pad + c * 16);
+          // four splits' worth of loads are in flight before the first sum (one L2 round trip per group)
+          const long long split_stride = static_cast<long long>(num_tiles_total) * 128 * p.m_pad;
+          const float* src0 = p.ws + static_cast<long long>(tile) * 128 * p.m_pad + (c * 16) * 128 + r;
+          for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float t[4][16];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float4 t = __ldcg(src + i);
-                f[4 * i] += t.x; f[4 * i + 1] += t.y; f[4 * i + 2] += t.z; f[4 * i + 3] += t.w;
+            for (int j = 0; j < 4; ++j) {
+              const float* src = src0 + min(s0 + j, p.splits - 1) * split_stride;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) t[j][i] = __ldcg(src + i * 128);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (s0 + j < p.splits) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) f[i] += t[j][i];
               }
             }
           }
@@ -301,6 +328,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             for (int i = 0; i < 16; ++i)
               if (i < mmax) op[static_cast<long long>(i) * p.ldc] = __float2bfloat16(f[i]);
           }
+        }
+      }
+      if (p.splits > 1 && p.par_reduce) {
+        // departures count in the high half of the tile's word; the last one re-arms it for the next call
+        if (threadIdx.x == 64) {
+          const int prev = atomicAdd(&p.counters[tile], 0x10000);
+          if ((prev >> 16) == p.splits - 1) p.counters[tile] = 0;
         }
       }
       if (p.ar.world > 1) {
@@ -439,7 +473,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 // Workspace sizes for cs_gemm_skinny: bytes of fp32 partials and number of int counters.
 CS_API long long cs_gemm_skinny_ws_bytes(int M, int N, int splits, int swiglu) {
   const long long m_pad = (M + 15) & ~15;
-  return splits > 1 ? static_cast<long long>(splits) * (swiglu ? 2 * N : N) * m_pad * 4 : 0;
+  const long long tiles = (N + (swiglu ? 64 : 128) - 1) / (swiglu ? 64 : 128);
+  return splits > 1 ? static_cast<long long>(splits) * tiles * 128 * m_pad * 4 : 0;
 }
 
 // Picks the split count used when `splits` is passed as 0.
@@ -489,6 +524,7 @@ CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long
       return -5;
   }
   p.splits = splits;
+  p.par_reduce = (splits > 1 && tiles * splits <= cs_num_sms()) ? 1 : 0;
   p.ws = reinterpret_cast<float*>(ws);
   p.counters = reinterpret_cast<int*>(counters);
   const int stage_bytes = KATOMS * (W_ATOM + p.m_pad * 128);
@@ -725,6 +761,7 @@ CS_API int cs_gemm_skinny_noalloc(const void* X, long long ldx, const void* W, l
   p.act = act;
   p.err = reinterpret_cast<int*>(base + CS_NOALLOC_SCRATCH_BYTES);
   p.splits = splits;
+  p.par_reduce = (splits > 1 && tiles * splits <= cs_num_sms()) ? 1 : 0;
   p.ws = reinterpret_cast<float*>(base);
   p.counters = counters;
   const int stage_bytes = KATOMS * (W_ATOM + p.m_pad * 128);

@@ -129,6 +129,19 @@ def test_stop_strings_cut_the_answer_and_free_the_sequence(tmp_path, tp):
         assert again["message"]["content"] == text                    # the engine (all ranks) is in step after the abort
         pen = _chat_full(port, "tell me something", frequency_penalty=1.5, presence_penalty=2.0)["choices"][0]
         assert pen["finish_reason"] == "length"
+        # n choices: choice 0 draws the request's own stream (the answer above), the others draw their own
+        many = _chat_full(port, "tell me something", n=3)
+        assert [c["index"] for c in many["choices"]] == [0, 1, 2] and many["choices"][0]["message"]["content"] == text
+        assert len({c["message"]["content"] for c in many["choices"]}) == 3
+        assert many["usage"]["completion_tokens"] == 3 * 48
+        # log probabilities: one entry per generated token, the chosen token's value and the most likely ones in order
+        lp = _chat_full(port, "tell me something", logprobs=True, top_logprobs=4, temperature=0)["choices"][0]
+        entries = lp["logprobs"]["content"]
+        assert len(entries) == 48
+        for e in entries:
+            tops = [t["logprob"] for t in e["top_logprobs"]]
+            assert len(tops) == 4 and tops == sorted(tops, reverse=True) and e["logprob"] <= 0
+            assert abs(e["logprob"] - tops[0]) < 1e-5 and e["token"] == e["top_logprobs"][0]["token"]   # greedy picks the top one
         with urllib.request.urlopen(f"http://127.0.0.1:{port}/stats", timeout=10) as r:
             st = json.loads(r.read())
         assert st["running"] == 0 and st["waiting"] == 0 and st["kv_pages_free"] == st["kv_pages"] - 1

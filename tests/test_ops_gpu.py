@@ -208,7 +208,7 @@ def test_misc_kernels():
 
 @pytest.mark.parametrize("M,N,K", [(1, 256, 128), (16, 3584, 3584), (64, 3584, 18944), (7, 4608, 3584), (128, 1000, 1352),
                                    (100, 152064, 512)])
-@pytest.mark.parametrize("splits", [0, 1, 3])
+@pytest.mark.parametrize("splits", [0, 1, 3, 6])   # 6: more CTAs than SMs for the wide shapes (the last split reduces alone)
 def test_gemm_skinny(M, N, K, splits):
     if N > 100000 and splits > 1:
         pytest.skip("split-K scratch is sized for decoder projections, not for a forced split of the vocabulary")
