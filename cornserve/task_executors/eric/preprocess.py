@@ -36,6 +36,20 @@ def smart_resize(height: int, width: int, factor: int = 28, min_pixels: int = 56
     return h, w
 
 
+_norm_cache: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _norm_constants(mean, std, device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(mean, std)`` of a recipe scaled to 0..255 as ``[1, 3, 1, 1]`` tensors on ``device``, made once per device:
+    building a device tensor from Python numbers is a blocking copy that drains the stream it runs on."""
+    key = (tuple(mean), tuple(std), str(device))
+    got = _norm_cache.get(key)
+    if got is None:
+        got = _norm_cache[key] = (torch.tensor(mean, device=device).view(1, 3, 1, 1) * 255.0,
+                                  torch.tensor(std, device=device).view(1, 3, 1, 1) * 255.0)
+    return got
+
+
 def patchify_frames(frames: torch.Tensor, patch: int = 14, temporal: int = 2, merge: int = 2,
                     out_dtype: torch.dtype = torch.bfloat16, min_pixels: int = 56 * 56,
                     max_pixels: int = 14 * 14 * 4 * 16384, mean=CLIP_MEAN, std=CLIP_STD) -> tuple[torch.Tensor, tuple[int, int, int]]:
@@ -51,8 +65,7 @@ def patchify_frames(frames: torch.Tensor, patch: int = 14, temporal: int = 2, me
     if (h, w) != (H, W):
         x = F.interpolate(x, size=(h, w), mode="bicubic", align_corners=False, antialias=True)
         x = x.clamp_(0.0, 255.0)
-    mean = torch.tensor(mean, device=x.device).view(1, 3, 1, 1) * 255.0
-    std = torch.tensor(std, device=x.device).view(1, 3, 1, 1) * 255.0
+    mean, std = _norm_constants(mean, std, x.device)
     x = (x - mean) / std
     if T % temporal != 0:
         x = torch.cat([x, x[-1:].expand(temporal - T % temporal, -1, -1, -1)], dim=0)
@@ -78,8 +91,7 @@ def resize_normalize(frames: torch.Tensor, size: tuple[int, int], mean=HALF, std
     x = frames.permute(0, 3, 1, 2).float()
     if tuple(x.shape[-2:]) != tuple(size):
         x = F.interpolate(x, size=size, mode=mode, align_corners=False, antialias=True).clamp_(0.0, 255.0)
-    m = torch.tensor(mean, device=x.device).view(1, 3, 1, 1) * 255.0
-    s = torch.tensor(std, device=x.device).view(1, 3, 1, 1) * 255.0
+    m, s = _norm_constants(mean, std, x.device)
     return ((x - m) / s).to(out_dtype)
 
 
@@ -114,8 +126,7 @@ def anyres_tiles(image: torch.Tensor, pinpoints: list[list[int]], tile: int, mea
     tiles = canvas.view(1, 3, bh // tile, tile, bw // tile, tile).permute(0, 2, 4, 1, 3, 5).reshape(-1, 3, tile, tile)
     base = F.interpolate(x, size=(tile, tile), mode="bicubic", align_corners=False, antialias=True).clamp_(0, 255)
     allt = torch.cat([base, tiles], dim=0)
-    m = torch.tensor(mean, device=image.device).view(1, 3, 1, 1) * 255.0
-    s = torch.tensor(std, device=image.device).view(1, 3, 1, 1) * 255.0
+    m, s = _norm_constants(mean, std, image.device)
     return ((allt - m) / s).to(out_dtype), (H, W)
 
 
@@ -138,8 +149,7 @@ def dynamic_tiles(image: torch.Tensor, size: int = 448, min_num: int = 1, max_nu
     if thumbnail and tiles.shape[0] > 1:
         thumb = F.interpolate(x, size=(size, size), mode="bicubic", align_corners=False, antialias=True).clamp_(0, 255)
         tiles = torch.cat([tiles, thumb], dim=0)
-    m = torch.tensor(IMAGENET_MEAN, device=image.device).view(1, 3, 1, 1) * 255.0
-    s = torch.tensor(IMAGENET_STD, device=image.device).view(1, 3, 1, 1) * 255.0
+    m, s = _norm_constants(IMAGENET_MEAN, IMAGENET_STD, image.device)
     return ((tiles - m) / s).to(out_dtype)
 
 
