@@ -71,6 +71,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--max-tokens", type=int, default=256)
     ap.add_argument("--prompt-tokens", type=int, default=128)
     ap.add_argument("--small", action="store_true", help="tiny decoder and tower: a plumbing run")
+    ap.add_argument("--encoder-batch", type=int, default=1,
+                    help="images per tower call at most (the reference's EncoderTask.max_batch_size; its default is 1)")
     # worker roles
     ap.add_argument("--replica", type=int, default=0)
     ap.add_argument("--rank", type=int, default=0)
@@ -113,9 +115,10 @@ def encoder_main(a: argparse.Namespace) -> None:
     tower = ref.Qwen2_5_VisionTransformer(Qwen2_5_VLConfig(vision_config=vision)).to(device="cuda", dtype=torch.bfloat16).eval()
     Modality = ref.Modality
 
-    def forward(pixel_values, grid):
+    def forward(pixel_values: list, grids: list) -> list:
+        """One call of the reference's tower on a batch of images (lists, as its scheduler hands them over)."""
         with torch.inference_mode():
-            return tower(Modality.IMAGE, "", {"pixel_values": [pixel_values], "image_grid_thw": [grid]})[0]
+            return tower(Modality.IMAGE, "", {"pixel_values": list(pixel_values), "image_grid_thw": list(grids)})
 
     if a.rank > 0:   # follower of a tensor-parallel group: replay what rank 0 broadcasts
         while True:
@@ -190,36 +193,55 @@ def encoder_main(a: argparse.Namespace) -> None:
     threading.Thread(target=reader, daemon=True).start()
     with send_lock:
         conn.send(("hello", "encoder", a.replica))
-    while True:
+    stop = False
+    while not stop:
         item = ready.get()
         if item is None:
             break
-        item_id, data = item
-        if isinstance(data, Exception):
-            with send_lock:
-                conn.send(("error", item_id, repr(data)))
+        batch = [item]
+        while len(batch) < max(1, a.encoder_batch):   # whatever else is ready, up to the batch limit (first come, first served)
+            try:
+                more = ready.get_nowait()
+            except queue.Empty:
+                break
+            if more is None:
+                stop = True
+                break
+            batch.append(more)
+        good = []
+        for item_id, data in batch:
+            if isinstance(data, Exception):
+                with send_lock:
+                    conn.send(("error", item_id, repr(data)))
+            else:
+                good.append((item_id, data))
+        if not good:
             continue
         t0 = time.perf_counter()
-        pv, grid = data["pixel_values"], data["image_grid_thw"]
-        stats["h2d_bytes"] += pv.numel() * pv.element_size()
+        pvs = [d["pixel_values"] for _, d in good]
+        grids = [d["image_grid_thw"] for _, d in good]
+        stats["h2d_bytes"] += sum(pv.numel() * pv.element_size() for pv in pvs)
         if a.world > 1:
-            torch.distributed.broadcast_object_list([(pv, grid)], src=0)
-        out = forward(pv, grid).contiguous()
-        nbytes = out.numel() * out.element_size()
-        off = allocate(nbytes)
-        while off is None:   # back-pressure: wait for the consumer to release rows
-            time.sleep(0.002)
+            torch.distributed.broadcast_object_list([(pvs, grids)], src=0)
+        outs = forward(pvs, grids)
+        for (item_id, _), out in zip(good, outs):
+            out = out.contiguous()
+            nbytes = out.numel() * out.element_size()
             off = allocate(nbytes)
-        held[item_id] = (off, nbytes)
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_stream(torch.cuda.current_stream())
-            slab[off: off + nbytes].view(torch.bfloat16).view(out.shape).copy_(out, non_blocking=True)
-        copy_stream.synchronize()
-        stats["d2h_bytes"] += nbytes
-        stats["items"] += 1
+            while off is None:   # back-pressure: wait for the consumer to release rows
+                time.sleep(0.002)
+                off = allocate(nbytes)
+            held[item_id] = (off, nbytes)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_stream(torch.cuda.current_stream())
+                slab[off: off + nbytes].view(torch.bfloat16).view(out.shape).copy_(out, non_blocking=True)
+            copy_stream.synchronize()
+            stats["d2h_bytes"] += nbytes
+            stats["items"] += 1
+            with send_lock:
+                conn.send(("done", item_id, off, int(out.shape[0])))
         stats["busy_ms"] += (time.perf_counter() - t0) * 1e3
-        with send_lock:
-            conn.send(("done", item_id, off, int(out.shape[0])))
+        stats["batches"] = stats.get("batches", 0) + 1
     if a.world > 1:
         torch.distributed.broadcast_object_list([None], src=0)
 
@@ -412,7 +434,7 @@ class Front:
             slabs.append(str(p))
         self.slab_paths = slabs
         base = [sys.executable, "-P", str(Path(__file__).resolve()), "--workdir", a.workdir, "--front-port", str(listener_port),
-                "--slab-bytes", str(slab_bytes)] + (["--small"] if a.small else [])
+                "--slab-bytes", str(slab_bytes), "--encoder-batch", str(a.encoder_batch)] + (["--small"] if a.small else [])
         et, lt, R = a.encoder_tp, a.llm_tp, a.replicas
         import socket
 

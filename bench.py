@@ -72,6 +72,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--window-s", type=float, default=8.0, help="seconds of Poisson arrivals per step")
     ap.add_argument("--slo-s", type=float, default=10.0, help="bound on the p99 end-to-end latency (both arms)")
+    ap.add_argument("--encoder-batch", type=int, default=8,
+                    help="images per call of the encoder executor at most, for both arms (the reference benchmark's "
+                         "eric_max_batch_size; waiting items are batched, nothing waits for a batch to fill)")
     ap.add_argument("--rates", default="", help="comma-separated requests/s (default: the table for N)")
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--prompt-tokens", type=int, default=128)
@@ -174,7 +177,7 @@ def stop_group(proc: subprocess.Popen, grace_s: float = 30.0) -> None:
             pass
 
 
-def profiles_for(model: str, layout: dict, small: bool) -> list[dict]:
+def profiles_for(model: str, layout: dict, small: bool, encoder_batch: int = 1) -> list[dict]:
     """Deployment profiles: the executor size (= tensor-parallel degree) of each unit task and its launch arguments."""
     llm_args = ["--max-num-seqs", "256", "--decode-burst", "8", "--max-model-len", "8192" if not small else "2048"]
     if small:
@@ -185,11 +188,12 @@ def profiles_for(model: str, layout: dict, small: bool) -> list[dict]:
     if layout["backend"] == "EV":
         out.append({"task": {"__class__": "EncoderTask", "modality": "image", "model_ids": [model], "max_batch_size": 1,
                              "execution_descriptor_name": None},
-                    "num_gpus_to_profile": {str(layout["encoder_tp"]): {"launch_args": []}}})
+                    "num_gpus_to_profile": {str(layout["encoder_tp"]): {
+                        "launch_args": ["--server.max-batch-size", str(max(1, encoder_batch))]}}})
     return out
 
 
-async def deploy_ours(gateway: str, model: str, layout: dict, small: bool) -> tuple[str, list[dict]]:
+async def deploy_ours(gateway: str, model: str, layout: dict, small: bool, encoder_batch: int = 1) -> tuple[str, list[dict]]:
     import aiohttp
 
     from benchmark.experiment import ExperimentConfig, app_source, part_of
@@ -197,7 +201,7 @@ async def deploy_ours(gateway: str, model: str, layout: dict, small: bool) -> tu
     parts = {"llm": 1} if layout["backend"] == "V" else {"encoder": 1, "llm": 1}
     cfg = ExperimentConfig(layout["backend"], model, parts)
     async with aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=1800)) as http:
-        async with http.post(f"{gateway}/deploy-profiles", json={"profiles": profiles_for(model, layout, small)}) as r:
+        async with http.post(f"{gateway}/deploy-profiles", json={"profiles": profiles_for(model, layout, small, encoder_batch)}) as r:
             if r.status != 200:
                 raise RuntimeError(f"deploying profiles failed: {await r.text()}")
         async with http.post(f"{gateway}/app/register", json={"source_code": app_source(cfg)}) as resp:
@@ -265,6 +269,20 @@ def request_payload(i: int, small: bool, prompt_tokens: int, output_tokens: int)
     return {"prompt": text, "multimodal_data": media, "max_completion_tokens": output_tokens}
 
 
+def server_env(**extra: str) -> dict[str, str]:
+    """The environment of the serving processes of either arm: this process's, without what a ``torch.distributed.run``
+    launcher added for its own ranks.  The servers form their own process groups; with the launcher's variables still set
+    (its rendezvous address, ``TORCHELASTIC_USE_AGENT_STORE``: "the agent hosts the store, connect as a client") rank 0 of
+    such a group would wait for a store that nobody hosts, and ``OMP_NUM_THREADS=1`` would pin their host-side work to one
+    thread."""
+    drop = {"RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE", "ROLE_RANK",
+            "ROLE_WORLD_SIZE", "ROLE_NAME", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS", "NCCL_ASYNC_ERROR_HANDLING",
+            "TORCH_NCCL_ASYNC_ERROR_HANDLING"}
+    env = {k: v for k, v in os.environ.items() if k not in drop and not k.startswith("TORCHELASTIC_")}
+    env.update(extra)
+    return env
+
+
 def diff_stats(before: list[dict], after: list[dict]) -> dict:
     out = {"gpu_launches": 0, "paths": {}, "h2d_bytes": 0, "d2h_bytes": 0, "executors": []}
     for b, a in zip(before, after):
@@ -315,7 +333,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
     tmp = Path(args.keep_logs or tempfile.mkdtemp(prefix="cornserve-bench-")).resolve()
     (tmp / "logs").mkdir(parents=True, exist_ok=True)
     port = free_port()
-    env = dict(os.environ, CORNSERVE_LOG_DIR=str(tmp / "logs"), CORNSERVE_STORE_PATH=str(tmp / "store.sqlite"),
+    env = server_env(CORNSERVE_LOG_DIR=str(tmp / "logs"), CORNSERVE_STORE_PATH=str(tmp / "store.sqlite"),
                CORNSERVE_LOG_LEVEL=os.environ.get("CORNSERVE_LOG_LEVEL", "WARNING"), OTEL_SDK_DISABLED="true",
                SIDECAR_SHM_SIZE=str((64 << 20) if args.small else (4 << 30)), CORNSERVE_ALLOW_RANDOM_INIT="1",
                CORNSERVE_SIDECAR_BASE_PORT=str(free_port()), SIDECAR_NAMESPACE=f"bench{os.getpid()}",
@@ -332,7 +350,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
     try:
         wait_http(f"{gateway}/health", cluster, 240, "the control plane")
         t0 = time.time()
-        app_id, executors = asyncio.run(deploy_ours(gateway, model, layout, args.small))
+        app_id, executors = asyncio.run(deploy_ours(gateway, model, layout, args.small, args.encoder_batch))
         deploy_s = time.time() - t0
         probe = ExecutorProbe([e["url"] for e in executors])
         cfg = sweep_config(args, world)
@@ -385,7 +403,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
             "seq_len": int(2.5 * (1196 + 2) + args.prompt_tokens) + args.output_tokens if not args.small else None,
             "images_per_request": "1-4 (mean 2.5) of 1280x720" if not args.small else "1-4 of 224x224",
             "prompt_tokens": args.prompt_tokens, "output_tokens": args.output_tokens, "rates_req_s": sorted(cfg.rates),
-            "window_s": cfg.window_s, "slo_p99_e2el_s": cfg.slo_e2el_s,
+            "window_s": cfg.window_s, "slo_p99_e2el_s": cfg.slo_e2el_s, "encoder_max_batch": args.encoder_batch,
             "serving_path": "client -> gateway -> task dispatcher -> Eric -> sidecar -> LLM executor (HTTP + gRPC, local processes)",
             "l2_policy": "inputs larger than L2: every decode step streams the 15 GB of decoder weights plus the KV cache",
             "timing": "value = requests of the best rate / that rate's span between CUDA events (max over executors); e2e = client clock",
@@ -479,11 +497,12 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
     port = free_port()
     # the server's import path holds the reference package and never this repository (both packages are called cornserve)
     keep = [p for p in os.environ.get("PYTHONPATH", "").split(os.pathsep) if p and Path(p).resolve() != ROOT]
-    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(ref_root), *keep]), OTEL_SDK_DISABLED="true",
+    env = server_env(PYTHONPATH=os.pathsep.join([str(ref_root), *keep]), OTEL_SDK_DISABLED="true",
                VLLM_LOGGING_LEVEL=os.environ.get("VLLM_LOGGING_LEVEL", "WARNING"), HF_HUB_OFFLINE="1", TRANSFORMERS_OFFLINE="1")
     cmd = [sys.executable, "-P", str(server), "--port", str(port), "--gpus", str(world), "--encoder-tp", str(max(1, layout["encoder_tp"])),
            "--llm-tp", str(layout["llm_tp"]), "--replicas", str(layout["replicas"]), "--workdir", str(tmp),
-           "--max-tokens", str(args.output_tokens), "--prompt-tokens", str(args.prompt_tokens)]
+           "--max-tokens", str(args.output_tokens), "--prompt-tokens", str(args.prompt_tokens),
+           "--encoder-batch", str(args.encoder_batch)]
     if layout["backend"] == "V":
         cmd.append("--share-gpu")
     if args.small:
@@ -547,7 +566,7 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
                    "parallelism": layout["name"].replace("monolithic executor (encoder inside the LLM executor)", "reference encoder + vLLM sharing the GPU"),
                    "images_per_request": "1-4 (mean 2.5) of 1280x720", "prompt_tokens": args.prompt_tokens,
                    "output_tokens": args.output_tokens, "rates_req_s": sorted(cfg.rates), "window_s": cfg.window_s,
-                   "slo_p99_e2el_s": cfg.slo_e2el_s,
+                   "slo_p99_e2el_s": cfg.slo_e2el_s, "encoder_max_batch": args.encoder_batch,
                    "reference_class": a.get("reference_class", "cornserve.task_executors.eric Qwen2_5_VisionTransformer + its ModalityProcessor -> pinned shared memory -> stock vLLM (prompt embeddings)"),
                    "vllm_flags": a.get("vllm_flags")},
         "clocks": clocks,
@@ -568,6 +587,11 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     sys.path.insert(0, str(ROOT))
+    # Standard output carries the one result line and nothing else: libraries that write there (NCCL's version banner at
+    # the first collective, for one) are pointed at standard error for the life of the process.
+    sys.stdout.flush()
+    result_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
     dist = None
     if world > 1:
@@ -608,7 +632,7 @@ def main() -> None:
                 if args.impl != "reference":
                     raise
                 line = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:600]}
-            print(json.dumps(line, default=str), flush=True)
+            print(json.dumps(line, default=str), file=result_out, flush=True)
         except BaseException as e:  # noqa: BLE001  (the other ranks are released first, then it is raised again)
             failure = e
     if dist is not None:

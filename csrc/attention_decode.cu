@@ -127,6 +127,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // barriers and TMEM were set up while the kernel ahead in the stream may still have been running; its results
+  // (queries, the cache rows of this step) are read from here on
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tmem = tmem_slot;
   const uint32_t tS0 = tmem, tO = tmem + 64;  // S^T buffers at columns 0 and 32, O^T at column 64
   volatile int* abortp = &abort_flag;
@@ -350,6 +354,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // Merge the split-KV partials of one (token, head) row: one warp per row, d = 128.
 __global__ void attn_decode_combine_kernel(const float* ws_o, const float* ws_ml, __nv_bfloat16* O, long long ldo,
                                            int rows, int Hq, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -421,11 +427,12 @@ CS_API int cs_attention_decode(const void* q, long long ldq, const void* cache, 
     attr_done[dev] = true;
   }
   const int grid = p.total_items < cs_num_sms() ? p.total_items : cs_num_sms();
-  if (p.G <= 8) attn_decode_kernel<8><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
-  else attn_decode_kernel<16><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
+  if (p.G <= 8) cs_launch_pdl(attn_decode_kernel<8>, dim3(grid), dim3(192), smem, stream, tmQ, tmKV, p);
+  else cs_launch_pdl(attn_decode_kernel<16>, dim3(grid), dim3(192), smem, stream, tmQ, tmKV, p);
   if (kv_splits > 1) {
     const int rows = B * Hq;
-    attn_decode_combine_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(p.ws_o, p.ws_ml, p.O, ldo, rows, Hq, kv_splits);
+    cs_launch_pdl(attn_decode_combine_kernel, dim3((rows + 7) / 8), dim3(256), 0, stream, p.ws_o, p.ws_ml, p.O, ldo, rows, Hq,
+                  kv_splits);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }

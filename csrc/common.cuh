@@ -265,6 +265,15 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t m, uint32_
 }
 
 // ---- misc ------------------------------------------------------------------------------
+// ---- programmatic dependent launch -------------------------------------------------------------------------
+// A kernel launched with the programmatic-serialisation attribute (cs_launch_pdl below) may start while the kernel
+// before it in the stream is still running: its CTAs take free SM resources, do whatever does not depend on that
+// kernel (barrier and TMEM set-up, prefetching weights) and then call pdl_wait(), which returns once the earlier
+// kernel has completed and its writes are visible.  The earlier kernel allows this from the moment all of its CTAs
+// have called pdl_launch_dependents() (or have exited).  Both are no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -277,4 +286,23 @@ int cs_encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer,
                       int elem_bytes, int swizzle128);
 int cs_num_sms();
+// 1 unless CORNSERVE_PDL=0: kernels that support it are launched with programmatic stream serialisation
+int cs_pdl_enabled();
+
+#ifdef __CUDACC__
+// Launch `kernel` so that it may overlap the tail of the previous kernel of `stream` (it must call pdl_wait() before
+// it touches anything an earlier kernel wrote or still reads).
+template <typename... KArgs, typename... Args>
+inline cudaError_t cs_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cs_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 int* cs_error_word();  // device-visible address of the error word

@@ -63,6 +63,8 @@ struct NormParams {
 
 __global__ void __launch_bounds__(NORM_THREADS) norm_kernel(const NormParams p) {
   __shared__ float red[NORM_THREADS / 32];
+  pdl_wait();                // launched so that its CTAs may be in place before the kernel ahead of it has ended
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const int nvec = p.H >> 3;
   float v[NORM_MAXV][8];
@@ -144,6 +146,8 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_kernel(const NormParams p) 
 // words that were loaded (or stored to `res_out`), so MAXV = 16 (4096 columns) costs 64 registers.
 template <int MAXV>
 __global__ void __launch_bounds__(256) norm_warp_kernel(const NormParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -284,6 +288,8 @@ __global__ void mrope_table_kernel(const int* pos, int T, int half, float theta,
 // qkv: [T, (Hq + 2*Hkv) * d]; cache: [pages, 2, Hkv, page, d]; slot[t] = page_id*page + offset.
 __global__ void rope_kv_write_kernel(__nv_bfloat16* qkv, long long ld, int T, int Hq, int Hkv, int d,
                                      const float* cs, __nv_bfloat16* cache, const int* slot, int page) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int half = d >> 1;
   const int chunks = half >> 2;
   const int heads = Hq + 2 * Hkv;
@@ -544,12 +550,13 @@ CS_API int cs_norm(const void* x, long long ldx, const void* residual, long long
   p.ldmod = ldmod; p.rpb = rpb > 0 ? rpb : 1;
   p.y = (__nv_bfloat16*)y; p.ldy = ldy;
   p.rows = rows; p.H = H; p.eps = eps; p.mode = mode;
+  cudaStream_t st = (cudaStream_t)stream;
   if (H <= 2048 && rows >= 64)
-    norm_warp_kernel<8><<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(p);
+    cs_launch_pdl(norm_warp_kernel<8>, dim3((rows + 7) / 8), dim3(256), 0, st, p);
   else if (H <= 4096 && rows >= 2048 && mode == 2)  // two reductions per row: a warp needs no block-wide barrier for them
-    norm_warp_kernel<16><<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(p);
+    cs_launch_pdl(norm_warp_kernel<16>, dim3((rows + 7) / 8), dim3(256), 0, st, p);
   else
-    norm_kernel<<<rows, NORM_THREADS, 0, (cudaStream_t)stream>>>(p);
+    cs_launch_pdl(norm_kernel, dim3(rows), dim3(NORM_THREADS), 0, st, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 
@@ -576,8 +583,8 @@ CS_API int cs_rope_kv_write(void* qkv, long long ld, int T, int Hq, int Hkv, int
   if (T <= 0) return 0;
   if (d & 7) return -1;
   long long total = (long long)T * (Hq + 2 * Hkv) * (d >> 3);
-  rope_kv_write_kernel<<<ceil_div_ll(total, 256), 256, 0, (cudaStream_t)stream>>>(
-      (__nv_bfloat16*)qkv, ld, T, Hq, Hkv, d, (const float*)cs, (__nv_bfloat16*)cache, (const int*)slot, page);
+  cs_launch_pdl(rope_kv_write_kernel, dim3((unsigned)ceil_div_ll(total, 256)), dim3(256), 0, (cudaStream_t)stream,
+                (__nv_bfloat16*)qkv, ld, T, Hq, Hkv, d, (const float*)cs, (__nv_bfloat16*)cache, (const int*)slot, page);
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 

@@ -125,6 +125,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
+    pdl_launch_dependents();   // the next kernel of the stream may set itself up while this one runs
   }
   if (warp == 1) { tmem_alloc(&tmem_slot, p.tmem_cols); tmem_relinquish(); }
   tc_fence_before();
@@ -135,13 +136,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0; uint32_t phase = 0;
       const uint32_t tx = static_cast<uint32_t>(stage_bytes);
-      for (int it = 0; it < n_it; ++it) {
-        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp, p.err, CS_ERR_TIMEOUT_SLOT)) break;
+      auto load_w = [&](int it, int stage) {
         uint8_t* sW = smem + stage * stage_bytes;
-        uint8_t* sX = sW + KATOMS * W_ATOM;
-        mbar_arrive_expect_tx(&full_bar[stage], tx);
         const int k0 = (it_lo + it) * BK * KATOMS;
 #pragma unroll
         for (int a = 0; a < KATOMS; ++a) {
@@ -151,8 +148,30 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           } else {
             tma_load_2d(sW + a * W_ATOM, &tmW, k0 + a * BK, n0, &full_bar[stage]);
           }
-          tma_load_2d(sX + a * x_atom, &tmX, k0 + a * BK, 0, &full_bar[stage]);
         }
+      };
+      auto load_x = [&](int it, int stage) {
+        uint8_t* sX = smem + stage * stage_bytes + KATOMS * W_ATOM;
+        const int k0 = (it_lo + it) * BK * KATOMS;
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a) tma_load_2d(sX + a * x_atom, &tmX, k0 + a * BK, 0, &full_bar[stage]);
+      };
+      // The weights do not depend on the kernel before this one: fill the ring with them first, then wait for that
+      // kernel (a no-op unless this launch may overlap it) and fetch the activations.
+      const int pre = min(n_it, p.stages);
+      for (int it = 0; it < pre; ++it) {
+        mbar_arrive_expect_tx(&full_bar[it], tx);
+        load_w(it, it);
+      }
+      pdl_wait();
+      for (int it = 0; it < pre; ++it) load_x(it, it);
+      int stage = pre == p.stages ? 0 : pre;
+      uint32_t phase = pre == p.stages ? 1 : 0;
+      for (int it = pre; it < n_it; ++it) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp, p.err, CS_ERR_TIMEOUT_SLOT)) break;
+        mbar_arrive_expect_tx(&full_bar[stage], tx);
+        load_w(it, stage);
+        load_x(it, stage);
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
     }
@@ -185,6 +204,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int r = q * 32 + lane;  // W row of the tile
     const uint32_t t_row = tmem + (static_cast<uint32_t>(q * 32) << 16);
     bool ok = true;
+    pdl_wait();   // before the first access to memory that an earlier kernel wrote or still reads
     if (n_it > 0) ok = mbar_wait(&acc_full, 0, abortp, p.err, CS_ERR_TIMEOUT_MMA);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
@@ -550,7 +570,8 @@ CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long
     cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     attr_done[dev] = true;
   }
-  gemm_skinny_kernel<<<tiles * splits, 192, smem, stream>>>(tmW, tmX, p);
+  // may start (set-up, weight prefetch) while the previous kernel of the stream is still running
+  if (cs_launch_pdl(gemm_skinny_kernel, dim3(tiles * splits), dim3(192), smem, stream, tmW, tmX, p) != cudaSuccess) return -10;
   return cudaGetLastError() == cudaSuccess ? 0 : -10;
 }
 

@@ -3,6 +3,7 @@
 #include <mutex>
 #include <stdio.h>
 
+#include <cstdlib>
 #include "common.cuh"
 
 namespace {
@@ -101,5 +102,14 @@ CS_API void cs_reset_error() {
   int* p = cs_error_word();
   if (p) *reinterpret_cast<volatile int*>(p) = 0;
 }
+int cs_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("CORNSERVE_PDL");
+    on = (v != nullptr && v[0] == '0') ? 0 : 1;
+  }
+  return on;
+}
+
 CS_API int cs_sm_count() { return cs_num_sms(); }
 CS_API int cs_abi_version() { return 1; }

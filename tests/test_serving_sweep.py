@@ -18,7 +18,7 @@ def test_poisson_schedule_is_a_function_of_the_seed_and_has_the_rate():
     a, b = poisson_schedule(20.0, 50.0, 7), poisson_schedule(20.0, 50.0, 7)
     assert np.array_equal(a, b) and not np.array_equal(a, poisson_schedule(20.0, 50.0, 8))
     assert a[0] > 0 and a[-1] < 50.0 and np.all(np.diff(a) > 0)
-    assert abs(len(a) / 50.0 - 20.0) < 2.0                      # about rate * span arrivals
+    assert len(a) == 1000                                      # rate * span arrivals exactly
     gaps = np.diff(a)
     assert abs(gaps.std() / gaps.mean() - 1.0) < 0.15           # exponential gaps: coefficient of variation 1
 
