@@ -17,9 +17,13 @@ import time
 
 
 def tune_interpreter() -> None:
-    """Set the interpreter's thread switch interval (``CORNSERVE_GIL_SWITCH_S``, default 0.5 ms)."""
+    """Set the interpreter's thread switch interval (``CORNSERVE_GIL_SWITCH_S``, default 0.1 ms).
+
+    A thread that launches a tower forward makes a few thousand short calls that give the lock up; whenever another
+    thread holds it at that moment the launcher waits up to one interval, so the interval bounds what a forward pass
+    loses to the other threads of the process (measured: 5 ms -> 480 ms per batch, 0.5 ms -> 180 ms)."""
     try:
-        sys.setswitchinterval(max(1e-5, float(os.environ.get("CORNSERVE_GIL_SWITCH_S", "0.0005"))))
+        sys.setswitchinterval(max(1e-5, float(os.environ.get("CORNSERVE_GIL_SWITCH_S", "0.0001"))))
     except ValueError:
         pass
 
