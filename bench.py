@@ -72,6 +72,10 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--window-s", type=float, default=8.0, help="seconds of Poisson arrivals per step")
     ap.add_argument("--slo-s", type=float, default=10.0, help="bound on the p99 end-to-end latency (both arms)")
+    ap.add_argument("--deadline-s", type=float, default=540.0,
+                    help="wall-clock budget of warm-up + timed steps; segments that do not fit are dropped and the line says so")
+    ap.add_argument("--slab-mib", type=int, default=0,
+                    help="size of every sidecar's slab (0: 4096, or 64 with --small); a producer owns 1/N of its consumer's slab")
     ap.add_argument("--encoder-batch", type=int, default=8,
                     help="images per call of the encoder executor at most, for both arms (the reference benchmark's "
                          "eric_max_batch_size; waiting items are batched, nothing waits for a batch to fill)")
@@ -322,7 +326,7 @@ def sweep_config(args: argparse.Namespace, world: int):
 
     rates = [float(x) for x in args.rates.split(",") if x] or RATES[max(k for k in RATES if k <= world)]
     return SweepConfig(rates=rates, steps=args.steps, warmup=args.warmup, window_s=args.window_s, slo_e2el_s=args.slo_s,
-                       output_tokens=args.output_tokens)
+                       output_tokens=args.output_tokens, deadline_s=args.deadline_s if args.deadline_s > 0 else None)
 
 
 def run_ours(args: argparse.Namespace, world: int) -> dict:
@@ -335,7 +339,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
     port = free_port()
     env = server_env(CORNSERVE_LOG_DIR=str(tmp / "logs"), CORNSERVE_STORE_PATH=str(tmp / "store.sqlite"),
                CORNSERVE_LOG_LEVEL=os.environ.get("CORNSERVE_LOG_LEVEL", "WARNING"), OTEL_SDK_DISABLED="true",
-               SIDECAR_SHM_SIZE=str((64 << 20) if args.small else (4 << 30)), CORNSERVE_ALLOW_RANDOM_INIT="1",
+               SIDECAR_SHM_SIZE=str((args.slab_mib << 20) if args.slab_mib > 0 else ((64 << 20) if args.small else (4 << 30))), CORNSERVE_ALLOW_RANDOM_INIT="1",
                CORNSERVE_SIDECAR_BASE_PORT=str(free_port()), SIDECAR_NAMESPACE=f"bench{os.getpid()}",
                PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
     if args.cpu:
@@ -374,7 +378,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
 
         res, state = asyncio.run(measure())
         clocks = sampler.stop(world)
-        counters = diff_stats(state["before"], state["after"])
+        counters = diff_stats(state.get("before", state["after"]), state["after"])
     except Exception:
         sys.stderr.write(f"--- deployment logs under {tmp} ---\n")
         for p in sorted((tmp / "logs").glob("*.log")) + [tmp / "cluster.log"]:
@@ -414,6 +418,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
                 "api": "HTTP POST {gateway}/app/invoke/{app_id} (app registered from source through /app/register)",
                 "whole_sweep_req_s": n_req / timed_s},
         "gpu_launches": counters["gpu_launches"], "fused_path_launches": counters["paths"],
+        "steps_run": res.get("steps_run", args.steps), "truncated": bool(res.get("truncated", False)),
         "best_rate_req_s": best.rate if best else None,
         "latency_at_best_rate_ms": {"ttft": best.ttft_ms, "tpot": best.tpot_ms, "e2el": best.e2el_ms} if best else None,
         "sweep": [asdict(s) for s in segs], "executors": counters["executors"], "deploy_s": round(deploy_s, 1),
@@ -556,9 +561,10 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
         log.close()
     segs = res["segments"]
     best = best_segment(segs)
-    b, a = state["before"][0], state["after"][0]
+    b, a = state.get("before", state["after"])[0], state["after"][0]
     return {
-        "impl": "reference", "metric": METRIC, "value": best.completed / (best.device_ms / 1e3) if best else 0.0, "unit": "req/s",
+        "impl": "reference", "steps_run": res.get("steps_run", args.steps), "truncated": bool(res.get("truncated", False)),
+        "metric": METRIC, "value": best.completed / (best.device_ms / 1e3) if best else 0.0, "unit": "req/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["timed_s"] * 1e3 / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (uniform-random images, random prompt tokens, random-init weights)",
@@ -575,6 +581,7 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
                 "d2h_bytes_per_step": (a.get("d2h_bytes", 0) - b.get("d2h_bytes", 0)) // args.steps,
                 "api": "HTTP POST to the reference arm's front process (the reference's own gateway needs Kubernetes)",
                 "whole_sweep_req_s": sum(s.sent for s in segs) / res["timed_s"]},
+        "steps_run": res.get("steps_run", args.steps), "truncated": bool(res.get("truncated", False)),
         "best_rate_req_s": best.rate if best else None,
         "latency_at_best_rate_ms": {"ttft": best.ttft_ms, "tpot": best.tpot_ms, "e2el": best.e2el_ms} if best else None,
         "sweep": [asdict(s) for s in segs],

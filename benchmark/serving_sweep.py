@@ -40,7 +40,8 @@ class SweepConfig:
     slo_e2el_s: float = 10.0           # bound on the 99th-percentile end-to-end latency
     output_tokens: int = 256           # tokens every request generates (ignore_eos): used for TPOT
     seed: int = 48105
-    request_timeout_s: float = 600.0
+    request_timeout_s: float = 120.0   # a request that takes longer is a failure (the latency bound is far below)
+    deadline_s: float | None = None    # wall-clock budget of warm-up + timed steps; what does not fit is cut (and says so)
 
 
 @dataclass
@@ -95,7 +96,9 @@ def _summarise(seg: Segment, records: list[RequestRecord], t_first: float, cfg: 
 
 
 async def _drive(http: aiohttp.ClientSession, url: str, payload_of: Callable[[int], dict], first_index: int,
-                 offsets: np.ndarray) -> tuple[list[RequestRecord], float]:
+                 offsets: np.ndarray, give_up_at: float | None = None) -> tuple[list[RequestRecord], float]:
+    """Send one request at every offset (open loop) and wait for all answers; requests that are still unanswered at
+    ``give_up_at`` (a ``perf_counter`` value) are cancelled and count as failures."""
     records = [RequestRecord(0.0) for _ in offsets]
     t0 = time.perf_counter()
     tasks = []
@@ -103,9 +106,20 @@ async def _drive(http: aiohttp.ClientSession, url: str, payload_of: Callable[[in
         delay = t0 + float(at) - time.perf_counter()
         if delay > 0:
             await asyncio.sleep(delay)
+        if give_up_at is not None and time.perf_counter() > give_up_at:
+            rec.ok, rec.error = False, "not sent: out of time"
+            continue
         tasks.append(asyncio.create_task(one_request(http, url, payload_of(first_index + k), rec)))
     if tasks:
-        await asyncio.gather(*tasks)
+        left = None if give_up_at is None else max(0.0, give_up_at - time.perf_counter())
+        _, pending = await asyncio.wait(tasks, timeout=left)
+        for t in pending:
+            t.cancel()
+        if pending:
+            await asyncio.gather(*pending, return_exceptions=True)
+            for rec in records:
+                if not rec.ok and not rec.error:
+                    rec.error = "no answer before the deadline"
     return records, t0
 
 
@@ -122,29 +136,35 @@ async def run_sweep(url: str, payload_of: Callable[[int], dict], cfg: SweepConfi
     timeout = aiohttp.ClientTimeout(total=cfg.request_timeout_s)
     segments: list[Segment] = []
     index = 0
+    give_up_at = None if cfg.deadline_s is None else time.perf_counter() + cfg.deadline_s
+    truncated = False
     async with aiohttp.ClientSession(timeout=timeout, connector=aiohttp.TCPConnector(limit=0)) as http:
         if cfg.warmup > 0:
             mid = rates[len(rates) // 2]
             off = poisson_schedule(mid, cfg.warmup * cfg.window_s, cfg.seed - 1)
-            recs, _ = await _drive(http, url, payload_of, index, off)
+            recs, _ = await _drive(http, url, payload_of, index, off, give_up_at)
             index += len(off)
             bad = [r.error for r in recs if not r.ok]
             if bad and len(bad) == len(recs):
                 raise RuntimeError(f"every warm-up request failed: {bad[0]}")
         t_begin = time.perf_counter()
         for i, (rate, n_steps) in enumerate(zip(rates, per_seg)):
+            if give_up_at is not None and time.perf_counter() + n_steps * cfg.window_s > give_up_at:
+                truncated = True   # this segment's arrivals alone would run past the budget
+                break
             seg = Segment(rate=rate, steps=n_steps)
             off = poisson_schedule(rate, n_steps * cfg.window_s, cfg.seed + i)
             if hook is not None:
                 await hook("begin", i)
-            recs, t0 = await _drive(http, url, payload_of, index, off)
+            recs, t0 = await _drive(http, url, payload_of, index, off, give_up_at)
             if hook is not None:
                 await hook("end", i)
             index += len(off)
             _summarise(seg, recs, t0, cfg)
             segments.append(seg)
         t_end = time.perf_counter()
-    return {"segments": segments, "timed_s": t_end - t_begin, "requests": index}
+    return {"segments": segments, "timed_s": t_end - t_begin, "requests": index, "truncated": truncated,
+            "steps_run": sum(s.steps for s in segments)}
 
 
 def best_segment(segments: list[Segment]) -> Segment | None:

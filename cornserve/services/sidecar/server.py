@@ -173,13 +173,22 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
         alloc = self._allocator(dst)
         if nbytes > alloc.total:
             raise OutOfSlots(f"{nbytes} bytes do not fit a region of {alloc.total} bytes (raise {SHM_SIZE_ENV})")
+        deadline = time.monotonic() + float(os.environ.get("SIDECAR_ALLOC_TIMEOUT_S", "120"))
         async with self._space:
             while True:
                 try:
                     return alloc.allocate(nbytes)
                 except OutOfSlots:
                     self.mem_pressure_count += 1
-                    await self._space.wait()
+                    left = deadline - time.monotonic()
+                    if left <= 0:
+                        # the consumer does not give space back (it died, or never marks its data done): fail this
+                        # send rather than hold the producer for ever
+                        raise OutOfSlots(f"no {nbytes} free bytes in the region of sidecar {dst} after waiting") from None
+                    try:
+                        await asyncio.wait_for(self._space.wait(), timeout=left)
+                    except asyncio.TimeoutError:
+                        pass
 
     async def _release(self, placed: dict[int, int]) -> None:
         async with self._space:

@@ -242,18 +242,27 @@ class Sidecar:
         """The data was consumed: once every member of this group said so the producer frees the slots."""
         if _is_mocking():
             return
-        resp = await self._aio_stub(self.config.leader).MarkDone(
-            sidecar_pb2.MarkDoneRequest(id=id, chunk_id=chunk_id, shard_rank=self.shard_rank))
-        if resp.status != common_pb2.STATUS_OK:
-            logger.error("Failed to mark %s chunk %d done", id, chunk_id)
+        for shard in self._marks():
+            resp = await self._aio_stub(self.config.leader).MarkDone(
+                sidecar_pb2.MarkDoneRequest(id=id, chunk_id=chunk_id, shard_rank=shard))
+            if resp.status != common_pb2.STATUS_OK:
+                logger.error("Failed to mark %s chunk %d done", id, chunk_id)
+                return
 
     def mark_done_sync(self, id: str, chunk_id: int = 0) -> None:
         if _is_mocking():
             return
-        resp = self._stub(self.config.leader).MarkDone(
-            sidecar_pb2.MarkDoneRequest(id=id, chunk_id=chunk_id, shard_rank=self.shard_rank))
-        if resp.status != common_pb2.STATUS_OK:
-            logger.error("Failed to mark %s chunk %d done", id, chunk_id)
+        for shard in self._marks():
+            resp = self._stub(self.config.leader).MarkDone(
+                sidecar_pb2.MarkDoneRequest(id=id, chunk_id=chunk_id, shard_rank=shard))
+            if resp.status != common_pb2.STATUS_OK:
+                logger.error("Failed to mark %s chunk %d done", id, chunk_id)
+                return
+
+    def _marks(self) -> list[int]:
+        """Shard ranks this client reports for: its own, or every member's when it stands for the whole group (the
+        producer's slots are freed once every member of the consuming group has said it is done)."""
+        return list(range(len(self.group))) if self.config.whole_group else [self.shard_rank]
 
     # -- lifecycle ---------------------------------------------------------------------------------------------------
     def check_health(self, rank: int | None = None) -> int:

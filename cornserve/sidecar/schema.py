@@ -22,6 +22,10 @@ class SidecarConfig:
     recv_tensor_dtype: torch.dtype | None = None
     recv_tensor_shape: tuple[int, ...] | int | None = None
     concurrent_copy: bool = False
+    # This client stands for every rank of ``group``: the other ranks of the executor have no sidecar client of their
+    # own (an executor whose leader alone talks to the sidecars), so it also answers for them where the protocol counts
+    # the members of a group (``mark_done``).
+    whole_group: bool = False
 
     def __post_init__(self) -> None:
         if self.group is None:

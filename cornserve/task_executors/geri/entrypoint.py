@@ -46,7 +46,7 @@ def main(argv: list[str] | None = None) -> None:
     sidecar = None
     if config.sidecar.ranks:
         entry, _ = resolve_entry(config.model.id)
-        sidecar = Sidecar(SidecarConfig(sidecar_rank=config.sidecar.ranks[0], group=list(config.sidecar.ranks),
+        sidecar = Sidecar(SidecarConfig(sidecar_rank=config.sidecar.ranks[0], group=list(config.sidecar.ranks), whole_group=True,
                                         recv_tensor_dtype=entry.embedding_dtype,
                                         recv_tensor_shape=(-1, find_embedding_dim(config.model.id))))
     try:

@@ -399,8 +399,9 @@ class LLMServer:
             from ...sidecar.schema import SidecarConfig
 
             dtype = next(self.engine.model.parameters()).dtype
+            # the leader alone talks to the sidecars: it answers for the follower ranks too
             self.sidecar = Sidecar(SidecarConfig(sidecar_rank=args.cornserve_sidecar_ranks[0],
-                                                 group=list(args.cornserve_sidecar_ranks),
+                                                 group=list(args.cornserve_sidecar_ranks), whole_group=True,
                                                  send_tensor_dtype=dtype, send_tensor_shape=(-1, self.cfg.hidden_size),
                                                  recv_tensor_dtype=dtype, recv_tensor_shape=(-1, self.cfg.hidden_size)))
         self.local_encoder: LocalEncoder | None = None  # built lazily for requests that carry raw URLs (no fission)

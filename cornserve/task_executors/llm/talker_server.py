@@ -87,7 +87,7 @@ class TalkerServer:
             from ...sidecar.schema import SidecarConfig
 
             H = self.cfg.thinker_hidden_size
-            self.sidecar = Sidecar(SidecarConfig(sidecar_rank=args.cornserve_sidecar_ranks[0], group=list(args.cornserve_sidecar_ranks),
+            self.sidecar = Sidecar(SidecarConfig(sidecar_rank=args.cornserve_sidecar_ranks[0], group=list(args.cornserve_sidecar_ranks), whole_group=True,
                                                  send_tensor_dtype=torch.int64, send_tensor_shape=(-1, self.cfg.num_code_groups),
                                                  recv_tensor_dtype=self.talker.dtype, recv_tensor_shape=(-1, H)))
         self.lock = asyncio.Lock()

@@ -60,6 +60,48 @@ def test_segment_summary_and_bound():
     assert best_segment([seg, slow, failed]) is seg and best_segment([slow]) is None
 
 
+def test_sweep_stops_at_its_deadline_instead_of_waiting_for_a_stalled_server():
+    """A server that stops answering: requests in flight at the deadline are cancelled and counted as failures, segments
+    whose arrivals no longer fit are dropped, and the result says that it was cut short."""
+    import asyncio
+
+    from aiohttp import web
+
+    from benchmark.serving_sweep import SweepConfig, run_sweep
+
+    served = {"n": 0}
+
+    async def invoke(request: web.Request) -> web.StreamResponse:
+        served["n"] += 1
+        resp = web.StreamResponse()
+        await resp.prepare(request)
+        if served["n"] > 6:
+            await asyncio.sleep(3600)          # the deployment has stalled
+        await resp.write(b'{"choices": [{"delta": {"content": "a"}}]}\n')   # the gateway streams one JSON object per line
+        await resp.write(b'{"choices": [{"delta": {"content": "b"}}]}\n')
+        return resp
+
+    async def main():
+        app = web.Application()
+        app.router.add_post("/invoke", invoke)
+        runner = web.AppRunner(app)
+        await runner.setup()
+        site = web.TCPSite(runner, "127.0.0.1", 0, shutdown_timeout=0.5)
+        await site.start()
+        port = site._server.sockets[0].getsockname()[1]
+        try:
+            cfg = SweepConfig(rates=[4.0, 6.0, 8.0], steps=3, warmup=0, window_s=1.0, output_tokens=2, deadline_s=3.0)
+            return await run_sweep(f"http://127.0.0.1:{port}/invoke", lambda i: {"i": i}, cfg)
+        finally:
+            await runner.cleanup()
+
+    res = asyncio.run(main())
+    assert res["truncated"] and 1 <= len(res["segments"]) < 3 and res["steps_run"] == len(res["segments"])
+    first, last = res["segments"][0], res["segments"][-1]
+    assert first.completed == 4 and first.failed == 0
+    assert last.failed > 0 and not last.slo_ok and "deadline" in " ".join(last.errors)
+
+
 @pytest.mark.timeout(900)
 def test_bench_monolithic_layout_encodes_inside_the_llm_executor():
     """One rank: no encoder executor; the LLM executor's own vision tower thread encodes the images (and counts them)."""

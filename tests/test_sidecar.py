@@ -131,6 +131,41 @@ def test_tp_groups_and_broadcast(cluster, concurrent):
             c.shutdown_sync()
 
 
+def test_group_leader_that_alone_has_a_client_frees_the_producers_space(cluster):
+    """A tensor-parallel executor whose leader is its only sidecar client (``whole_group``): its ``mark_done`` counts for
+    every rank of the group, so the producer's region of the leader's slab is freed and never fills up.  The region is
+    2 MiB (an 8 MiB slab shared by four sidecars); 40 tensors of 256 KiB only fit if space comes back."""
+    import concurrent.futures
+    import dataclasses
+
+    api = cluster
+    from cornserve.sidecar.schema import SidecarConfig
+
+    prod = _client(api, 0)
+    cfg = SidecarConfig(sidecar_rank=2, group=[2, 3], recv_tensor_dtype=torch.bfloat16, recv_tensor_shape=(-1, 64), whole_group=True)
+    leader = api.Sidecar(cfg)
+    try:
+        t = torch.randn(2048, 64).bfloat16()   # 256 KiB
+
+        def roundtrip(i: int) -> bool:
+            did = uuid.uuid4().hex
+            prod.send(t, did, [[2, 3]])
+            ok = torch.equal(leader.recv_sync(did), t)
+            leader.mark_done_sync(did)
+            return ok
+
+        pool = concurrent.futures.ThreadPoolExecutor(max_workers=1)
+        try:
+            for i in range(40):
+                assert pool.submit(roundtrip, i).result(timeout=20), f"tensor {i} did not come back intact"
+        finally:
+            pool.shutdown(wait=False, cancel_futures=True)
+        assert dataclasses.replace(cfg, whole_group=False).whole_group is False
+    finally:
+        prod.shutdown_sync()
+        leader.shutdown_sync()
+
+
 def test_rows_are_pushed_into_the_consumers_slab_and_survive_new_registrations(cluster):
     """The producer's sidecar writes into the slab of the consumer's sidecar (a view of rank 1's slab comes back, not of
     rank 0's), and the slab is never re-allocated: a client that registers later with another dtype and slot size does
