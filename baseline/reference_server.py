@@ -261,7 +261,7 @@ def llm_main(a: argparse.Namespace) -> None:
     # with nvcc at the first start; if that takes longer than REF_VLLM_START_TIMEOUT_S on a box without its cache, the
     # next entries of vLLM's own priority list are tried: FLASH_ATTN (precompiled in the wheel), then Triton attention.
     wanted = os.environ.get("REF_VLLM_ATTENTION_BACKEND", "auto,FLASH_ATTN,TRITON_ATTN").split(",")
-    start_limit = float(os.environ.get("REF_VLLM_START_TIMEOUT_S", "240"))
+    start_limit = float(os.environ.get("REF_VLLM_START_TIMEOUT_S", "150"))
     engine, last = None, None
 
     def give_up_on_children(done: threading.Event, backend: str) -> None:

@@ -265,17 +265,16 @@ class SidecarServicer(sidecar_pb2_grpc.SidecarServicer):
                 # a shard that lives on another GPU of the group (concurrent copy): the driver's peer copy
                 dst_bytes.copy_(src.contiguous().view(torch.uint8).reshape(-1), non_blocking=True)
             t1.record()
+            t2 = None
             if self._probe_repeat and src.device == self.device:
                 # diagnosis only (SIDECAR_PUSH_PROBE=1): the same copy once more, straight behind the first, tells the
                 # kernel's own time apart from what its launch out of an otherwise idle process costs on a shared GPU
-                from ... import ops
-
                 t2 = torch.cuda.Event(enable_timing=True)
                 ops.push_bytes_(dst_bytes, src.contiguous())
                 t2.record()
-                await asyncio.to_thread(t2.synchronize)
-                self.push_stats["repeat_ms"] = self.push_stats.get("repeat_ms", 0.0) + t1.elapsed_time(t2)
-        await asyncio.to_thread(t1.synchronize)
+        await asyncio.to_thread((t2 or t1).synchronize)
+        if t2 is not None:
+            self.push_stats["repeat_ms"] = self.push_stats.get("repeat_ms", 0.0) + t1.elapsed_time(t2)
         self.push_stats["copy_ms"] += t0.elapsed_time(t1)
         self.push_stats["bytes"] += dst_bytes.numel()
         self.push_stats["pushes"] += 1
