@@ -625,6 +625,23 @@ def _vllm_version() -> str:
         return "?"
 
 
+def exit_with_parent() -> None:
+    """REF_EXIT_WITH_PARENT=1 (set by bench.py, inherited by the workers): leave when the starting process is gone, so
+    that a run that was killed does not leave vLLM holding its GPUs."""
+    if os.environ.get("REF_EXIT_WITH_PARENT") != "1":
+        return
+    parent = os.getppid()
+
+    def watch() -> None:
+        while True:
+            time.sleep(1.0)
+            if os.getppid() != parent:
+                os._exit(113)
+
+    threading.Thread(target=watch, name="exit-with-parent", daemon=True).start()
+
+
 if __name__ == "__main__":
     args = parse_args()
+    exit_with_parent()
     {"front": front_main, "encoder": encoder_main, "llm": llm_main}[args.role](args)

@@ -343,6 +343,7 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
     port = free_port()
     env = server_env(CORNSERVE_LOG_DIR=str(tmp / "logs"), CORNSERVE_STORE_PATH=str(tmp / "store.sqlite"),
                CORNSERVE_LOG_LEVEL=os.environ.get("CORNSERVE_LOG_LEVEL", "WARNING"), OTEL_SDK_DISABLED="true",
+               CORNSERVE_EXIT_WITH_PARENT="1",
                SIDECAR_SHM_SIZE=str((args.slab_mib << 20) if args.slab_mib > 0 else ((64 << 20) if args.small else (4 << 30))), CORNSERVE_ALLOW_RANDOM_INIT="1",
                CORNSERVE_SIDECAR_BASE_PORT=str(free_port()), SIDECAR_NAMESPACE=f"bench{os.getpid()}",
                PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
@@ -508,7 +509,7 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
     port = free_port()
     # the server's import path holds the reference package and never this repository (both packages are called cornserve)
     keep = [p for p in os.environ.get("PYTHONPATH", "").split(os.pathsep) if p and Path(p).resolve() != ROOT]
-    env = server_env(PYTHONPATH=os.pathsep.join([str(ref_root), *keep]), OTEL_SDK_DISABLED="true",
+    env = server_env(PYTHONPATH=os.pathsep.join([str(ref_root), *keep]), OTEL_SDK_DISABLED="true", REF_EXIT_WITH_PARENT="1",
                VLLM_LOGGING_LEVEL=os.environ.get("VLLM_LOGGING_LEVEL", "WARNING"), HF_HUB_OFFLINE="1", TRANSFORMERS_OFFLINE="1")
     cmd = [sys.executable, "-P", str(server), "--port", str(port), "--gpus", str(world), "--encoder-tp", str(max(1, layout["encoder_tp"])),
            "--llm-tp", str(layout["llm_tp"]), "--replicas", str(layout["replicas"]), "--workdir", str(tmp),
@@ -594,8 +595,15 @@ def run_reference(args: argparse.Namespace, world: int) -> dict:
     }
 
 
+def _raise_on_signal(signum, _frame) -> None:
+    raise SystemExit(f"signal {signum}")
+
+
 def main() -> None:
     args = parse_args()
+    # a launcher that gives up sends SIGTERM: unwind (the deployment is stopped in `finally` blocks) instead of dying on the spot
+    for sig in (signal.SIGTERM, signal.SIGHUP):
+        signal.signal(sig, _raise_on_signal)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -129,3 +129,44 @@ def test_bench_runs_end_to_end_on_cpu_ranks():
     assert line["value"] > 0 and line["e2e"]["value"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0
     assert abs(line["ms_per_step"] * 2 / 1e3 - sum(s["duration_s"] for s in line["sweep"])) < 3.0
     assert {e["executor"] for e in line["executors"]} == {"eric", "llm"}
+
+
+@pytest.mark.timeout(400)
+def test_a_killed_bench_leaves_no_process_of_its_deployment_behind():
+    """The control plane, executors and sidecars run in sessions of their own; when ``bench.py`` is killed outright they
+    must not stay behind holding GPUs for the next run: every process of the tree leaves once its parent is gone."""
+    import os
+    import signal
+    import time
+
+    import psutil
+
+    def members(tag):
+        out = []
+        for p in psutil.process_iter(["pid"]):
+            try:
+                if p.environ().get("SIDECAR_NAMESPACE") == tag:
+                    out.append(p.pid)
+            except (psutil.Error, OSError):
+                pass
+        return out
+
+    b = subprocess.Popen([sys.executable, "bench.py", "--gpus", "2", "--cpu", "--small", "--steps", "4", "--warmup", "1",
+                          "--window-s", "5", "--offline-steps", "0", "--rates", "1", "--output-tokens", "8"],
+                         cwd=ROOT, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    tag = f"bench{b.pid}"
+    try:
+        deadline = time.time() + 240
+        while time.time() < deadline and len(members(tag)) < 5:   # control plane, two sidecars, two executors
+            assert b.poll() is None, "bench.py ended before its deployment was up"
+            time.sleep(1)
+        assert len(members(tag)) >= 5
+        os.kill(b.pid, signal.SIGKILL)
+        b.wait(timeout=30)
+        deadline = time.time() + 30
+        while time.time() < deadline and members(tag):
+            time.sleep(0.5)
+        assert members(tag) == []
+    finally:
+        if b.poll() is None:
+            b.kill()
