@@ -636,6 +636,13 @@ def exit_with_parent() -> None:
         while True:
             time.sleep(1.0)
             if os.getppid() != parent:
+                try:   # vLLM's engine-core and worker processes are this process's own children
+                    import psutil
+
+                    for child in psutil.Process().children(recursive=True):
+                        child.kill()
+                except Exception:  # noqa: BLE001
+                    pass
                 os._exit(113)
 
     threading.Thread(target=watch, name="exit-with-parent", daemon=True).start()

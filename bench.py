@@ -170,16 +170,16 @@ def wait_http(url: str, proc: subprocess.Popen, timeout_s: float, what: str) -> 
 
 def stop_group(proc: subprocess.Popen, grace_s: float = 30.0) -> None:
     """SIGTERM to the process group this script started, then SIGKILL if it lingers."""
-    if proc.poll() is not None:
-        return
     try:
-        os.killpg(proc.pid, signal.SIGTERM)
-        proc.wait(timeout=grace_s)
+        if proc.poll() is None:
+            os.killpg(proc.pid, signal.SIGTERM)
+            proc.wait(timeout=grace_s)
     except Exception:  # noqa: BLE001
-        try:
-            os.killpg(proc.pid, signal.SIGKILL)
-        except Exception:  # noqa: BLE001
-            pass
+        pass
+    try:
+        os.killpg(proc.pid, signal.SIGKILL)   # members of the group that outlived its leader (no-op when there are none)
+    except Exception:  # noqa: BLE001
+        pass
 
 
 def profiles_for(model: str, layout: dict, small: bool, encoder_batch: int = 1) -> list[dict]:
