@@ -170,3 +170,21 @@ def test_a_killed_bench_leaves_no_process_of_its_deployment_behind():
     finally:
         if b.poll() is None:
             b.kill()
+
+
+def test_serving_processes_do_not_inherit_the_launchers_variables(monkeypatch):
+    """``torch.distributed.run`` exports its rendezvous and ``TORCHELASTIC_USE_AGENT_STORE`` to its ranks; servers that
+    form their own process groups must not see them (rank 0 of such a group would wait for a store nobody hosts)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_under_test", ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for k, v in {"RANK": "0", "WORLD_SIZE": "4", "LOCAL_RANK": "0", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29500",
+                 "TORCHELASTIC_USE_AGENT_STORE": "True", "TORCHELASTIC_RUN_ID": "x", "OMP_NUM_THREADS": "1",
+                 "CORNSERVE_KEEP_ME": "1"}.items():
+        monkeypatch.setenv(k, v)
+    env = bench.server_env(EXTRA="yes")
+    assert env["EXTRA"] == "yes" and env["CORNSERVE_KEEP_ME"] == "1" and "PATH" in env
+    assert not any(k in env for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS"))
+    assert not any(k.startswith("TORCHELASTIC_") for k in env)
