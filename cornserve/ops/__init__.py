@@ -132,12 +132,15 @@ def _skinny_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]
 
 
 def _skinny(x2, w, bias, act, r2, out2, M, N, K, swiglu, fp32, splits):
+    # A stored weight (an ``nn.Parameter``) is fetched while the kernel before this one still runs; anything else may
+    # be that kernel's output (attention scores against keys, a slice made a moment ago) and is fetched after it.
     lib = _lib.load()
     ws, counters = _skinny_workspace(x2.device)
     rc = lib.cs_gemm_skinny(
         x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0), out2.data_ptr(), out2.stride(0),
         _ptr(bias), _ptr(r2), 0 if r2 is None else r2.stride(0), M, N, K, ACTS[act or "none"],
-        1 if swiglu else 0, 1 if fp32 else 0, splits, ws.data_ptr(), ws.numel(), counters.data_ptr(),
+        1 if swiglu else 0, (1 if fp32 else 0) | (0 if isinstance(w, torch.nn.Parameter) else 2), splits,
+        ws.data_ptr(), ws.numel(), counters.data_ptr(),
         counters.numel(), _stream(),
     )
     _chk(rc, "cs_gemm_skinny")

@@ -90,6 +90,7 @@ struct SkinnyParams {
   int act;
   float* ws; int* counters;
   int par_reduce;       // every split CTA of a tile reduces a share of the tile's token chunks (all CTAs resident)
+  int w_dynamic;        // W may have been written by the kernel before this one: no weight prefetch ahead of it
   uint32_t idesc;
   uint32_t tmem_cols;
   int* err;
@@ -159,6 +160,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       // The weights do not depend on the kernel before this one: fill the ring with them first, then wait for that
       // kernel (a no-op unless this launch may overlap it) and fetch the activations.
       const int pre = min(n_it, p.stages);
+      if (p.w_dynamic) pdl_wait();   // W is an activation here (scores against keys, say), not a stored weight
       for (int it = 0; it < pre; ++it) {
         mbar_arrive_expect_tx(&full_bar[it], tx);
         load_w(it, it);
@@ -515,6 +517,8 @@ CS_API int cs_gemm_skinny_auto_splits(int N, int K, int swiglu) {
 // C[M,N] = act(X W^T + bias) + residual   (swiglu == 0),  W: [N,K]
 // C[M,N] = act(X Wg^T + bg) * (X Wu^T + bu), W = [Wg; Wu] ([2N,K])   (swiglu == 1)
 // M <= 256.  `ws` / `counters` as described at the top of this file (`counters` needs one int per tile).
+// `out_fp32`: bit 0 = fp32 output; bit 1 = W is not a stored weight but may have been written by the kernel that
+// precedes this call on the stream (the kernel then fetches nothing before that kernel has completed).
 CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc,
                           const void* bias, const void* residual, long long ldr, int M, int N, int K, int act,
                           int swiglu, int out_fp32, int splits, void* ws, long long ws_bytes, void* counters,
@@ -527,7 +531,8 @@ CS_API int cs_gemm_skinny(const void* X, long long ldx, const void* W, long long
   p.m_pad = (M + 15) & ~15;
   p.swiglu = swiglu;
   p.up_row_offset = N;
-  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32 & 1;
+  p.w_dynamic = (out_fp32 >> 1) & 1;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
