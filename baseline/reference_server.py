@@ -120,13 +120,30 @@ def encoder_main(a: argparse.Namespace) -> None:
         with torch.inference_mode():
             return tower(Modality.IMAGE, "", {"pixel_values": list(pixel_values), "image_grid_thw": list(grids)})
 
+    def share(pixel_values: list, grids: list) -> list:
+        """Rank 0 of a tensor-parallel group: hand the batch to the other ranks.  Shapes go as a small pickled message,
+        the pixels as device tensors over NCCL (the reference moves them through a shared-memory ring; pickling 20 MB
+        per image through ``broadcast_object_list`` would make this arm slower than what it stands for)."""
+        meta = [(tuple(pv.shape), str(pv.dtype).split(".")[-1], g.tolist()) for pv, g in zip(pixel_values, grids)]
+        torch.distributed.broadcast_object_list([meta], src=0)
+        on_device = [pv.to("cuda") for pv in pixel_values]
+        for t in on_device:
+            torch.distributed.broadcast(t, src=0)
+        return on_device
+
     if a.rank > 0:   # follower of a tensor-parallel group: replay what rank 0 broadcasts
         while True:
             box = [None]
             torch.distributed.broadcast_object_list(box, src=0)
             if box[0] is None:
                 return
-            forward(*box[0])
+            pvs, grids = [], []
+            for shape, dtype, grid in box[0]:
+                t = torch.empty(shape, dtype=getattr(torch, dtype), device="cuda")
+                torch.distributed.broadcast(t, src=0)
+                pvs.append(t)
+                grids.append(torch.tensor(grid))
+            forward(pvs, grids)
 
     print(f"encoder replica {a.replica} rank {a.rank}: tower on {torch.cuda.get_device_name()}", flush=True)
     processor = ref.ModalityProcessor(str(Path(a.workdir) / "encoder_model"))
@@ -222,7 +239,7 @@ def encoder_main(a: argparse.Namespace) -> None:
         grids = [d["image_grid_thw"] for _, d in good]
         stats["h2d_bytes"] += sum(pv.numel() * pv.element_size() for pv in pvs)
         if a.world > 1:
-            torch.distributed.broadcast_object_list([(pvs, grids)], src=0)
+            pvs = share(pvs, grids)
         outs = forward(pvs, grids)
         for (item_id, _), out in zip(good, outs):
             out = out.contiguous()
