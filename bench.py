@@ -75,6 +75,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--slo-s", type=float, default=10.0, help="bound on the p99 end-to-end latency (both arms)")
     ap.add_argument("--deadline-s", type=float, default=540.0,
                     help="wall-clock budget of warm-up + timed steps; segments that do not fit are dropped and the line says so")
+    ap.add_argument("--no-fallback", action="store_true", help="do not repeat a failed tensor-parallel layout with one-GPU executors")
+    ap.add_argument("--fail-first-layout", action="store_true", help=argparse.SUPPRESS)   # tests of the fallback path
     ap.add_argument("--slab-mib", type=int, default=0,
                     help="size of every sidecar's slab (0: 4096, or 64 with --small); a producer owns 1/N of its consumer's slab")
     ap.add_argument("--encoder-batch", type=int, default=8,
@@ -333,19 +335,44 @@ def sweep_config(args: argparse.Namespace, world: int):
                        output_tokens=args.output_tokens, deadline_s=deadline)
 
 
+# If the tensor-parallel layout of an N cannot serve (its deployment does not come up, or every warm-up request fails),
+# the run is repeated once with one-GPU executors on the same GPUs, and the line says so (`fallback_from`).
+FALLBACKS = {
+    4: {"backend": "EV", "encoder_tp": 1, "llm_tp": 1, "replicas": 2, "name": "eric tp1 x2 + llm tp1 x2"},
+    8: {"backend": "EV", "encoder_tp": 1, "llm_tp": 1, "replicas": 4, "name": "eric tp1 x4 + llm tp1 x4"},
+}
+
+
 def run_ours(args: argparse.Namespace, world: int) -> dict:
+    key = max(k for k in LAYOUTS if k <= world)
+    try:
+        return run_ours_layout(args, world, LAYOUTS[key], "")
+    except Exception as e:  # noqa: BLE001
+        fallback = FALLBACKS.get(key)
+        left = 800.0 - (time.monotonic() - T_START)
+        if fallback is None or args.no_fallback or left < 330.0:
+            raise
+        sys.stderr.write(f"--- layout '{LAYOUTS[key]['name']}' failed ({type(e).__name__}: {str(e)[:300]}); "
+                         f"one more run as '{fallback['name']}' with {left:.0f} s left ---\n")
+        args.deadline_s = min(args.deadline_s if args.deadline_s > 0 else left, left - 130.0)
+        args.offline_steps = 0
+        line = run_ours_layout(args, world, fallback, "-fallback")
+        line["fallback_from"] = {"parallelism": LAYOUTS[key]["name"], "reason": f"{type(e).__name__}: {e}"[:400]}
+        return line
+
+
+def run_ours_layout(args: argparse.Namespace, world: int, layout: dict, tag: str) -> dict:
     from benchmark.serving_sweep import best_segment, run_sweep
 
-    layout = LAYOUTS[max(k for k in LAYOUTS if k <= world)]
     model = TINY if args.small else MODEL
-    tmp = Path(args.keep_logs or tempfile.mkdtemp(prefix="cornserve-bench-")).resolve()
+    tmp = Path((args.keep_logs + tag) if args.keep_logs else tempfile.mkdtemp(prefix="cornserve-bench-")).resolve()
     (tmp / "logs").mkdir(parents=True, exist_ok=True)
     port = free_port()
     env = server_env(CORNSERVE_LOG_DIR=str(tmp / "logs"), CORNSERVE_STORE_PATH=str(tmp / "store.sqlite"),
                CORNSERVE_LOG_LEVEL=os.environ.get("CORNSERVE_LOG_LEVEL", "WARNING"), OTEL_SDK_DISABLED="true",
                CORNSERVE_EXIT_WITH_PARENT="1",
                SIDECAR_SHM_SIZE=str((args.slab_mib << 20) if args.slab_mib > 0 else ((64 << 20) if args.small else (4 << 30))), CORNSERVE_ALLOW_RANDOM_INIT="1",
-               CORNSERVE_SIDECAR_BASE_PORT=str(free_port()), SIDECAR_NAMESPACE=f"bench{os.getpid()}",
+               CORNSERVE_SIDECAR_BASE_PORT=str(free_port()), SIDECAR_NAMESPACE=f"bench{os.getpid()}{tag}",
                PYTHONPATH=str(ROOT) + os.pathsep + os.environ.get("PYTHONPATH", ""))
     if args.cpu:
         env.update(CORNSERVE_DEVICE="cpu", SIDECAR_DEVICE="cpu")
@@ -361,6 +388,8 @@ def run_ours(args: argparse.Namespace, world: int) -> dict:
         t0 = time.time()
         app_id, executors = asyncio.run(deploy_ours(gateway, model, layout, args.small, args.encoder_batch))
         deploy_s = time.time() - t0
+        if args.fail_first_layout and not tag:
+            raise RuntimeError("the first layout was made to fail (--fail-first-layout)")
         probe = ExecutorProbe([e["url"] for e in executors])
         cfg = sweep_config(args, world)
         payload_of = lambda i: request_payload(i, args.small, args.prompt_tokens, args.output_tokens)  # noqa: E731
