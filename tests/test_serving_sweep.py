@@ -188,3 +188,18 @@ def test_serving_processes_do_not_inherit_the_launchers_variables(monkeypatch):
     assert env["EXTRA"] == "yes" and env["CORNSERVE_KEEP_ME"] == "1" and "PATH" in env
     assert not any(k in env for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS"))
     assert not any(k.startswith("TORCHELASTIC_") for k in env)
+
+
+@pytest.mark.timeout(1200)
+def test_bench_repeats_a_failed_tensor_parallel_layout_with_one_gpu_executors():
+    """Four ranks: the TP 2 + TP 2 layout is made to fail after its deployment; the run is repeated as two one-GPU
+    encoder executors and two one-GPU LLM executors, and the line names both layouts."""
+    out = subprocess.run([sys.executable, "bench.py", "--small", "--cpu", "--gpus", "4", "--steps", "2", "--warmup", "1",
+                          "--window-s", "3", "--rates", "2", "--offline-steps", "0", "--output-tokens", "8", "--slab-mib", "8",
+                          "--fail-first-layout"], cwd=ROOT, capture_output=True, text=True, timeout=1100)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["config"]["parallelism"] == "eric tp1 x2 + llm tp1 x2"
+    assert line["fallback_from"]["parallelism"] == "eric tp2 x1 + llm tp2 x1" and "made to fail" in line["fallback_from"]["reason"]
+    assert sorted(e["executor"] for e in line["executors"]) == ["eric", "eric", "llm", "llm"]
+    assert all(s["failed"] == 0 and s["completed"] == s["sent"] > 0 for s in line["sweep"])
