@@ -610,7 +610,9 @@ class LLMEngine:
             ops.decode_advance_(tok, st.input_ids, st.positions, st.kv_len, st.slot, st.block_table, st.active,
                                 st.out_log, st.step_counter)
 
-        if not (self.on_gpu and self.cfg.use_cuda_graph):
+        if not (self.on_gpu and self.cfg.use_cuda_graph) or st.lp_chosen is not None:
+            # buckets that report log probabilities run eagerly: their soft-max and top-k are library calls whose
+            # behaviour under stream capture is not relied upon, and such requests are rare
             body()
             return
         if st.graph is None:
