@@ -31,7 +31,9 @@ def tune_interpreter() -> None:
 class StackSampler:
     """Samples every thread's innermost frames at a fixed period; ``top()`` gives the most frequent ones per thread.
 
-    Enabled in the executors by ``CORNSERVE_SAMPLE_STACKS=1``; the result is part of their ``/stats`` answer."""
+    Enabled in the executors by ``CORNSERVE_SAMPLE_STACKS=1``; the result is part of their ``/stats`` answer.  The
+    sampler needs the interpreter lock to look, so it sees a busy thread mostly at the calls where that thread gives
+    the lock up (a copy, a wait, a library call): read the counts as "where threads yield", not as CPU time."""
 
     def __init__(self, period_s: float = 0.005, depth: int = 3):
         self.period_s, self.depth = period_s, depth
