@@ -27,6 +27,12 @@ the bytes the executors copied from page-locked host memory to the GPUs (the ima
   python bench.py --impl reference --gpus N ...            # the reference arm: its Eric modules + stock vLLM
 
 Rank 0 drives the deployment; the other ranks of the launcher join an NCCL group with it and wait.
+
+Both arms get the same rates, request mix, bound, encoder batch limit (``--encoder-batch``) and a wall-clock budget
+(``--deadline-s``): segments that no longer fit are dropped and the line says ``truncated``.  The serving processes are
+started without the launcher's environment variables and leave with this process, also when it is killed.  If a
+tensor-parallel layout (N = 4, 8) cannot serve, the run is repeated once with one-GPU executors on the same GPUs and the
+line names both layouts (``fallback_from``).
 """
 
 from __future__ import annotations
