@@ -2,6 +2,7 @@
 plumbing run (tiny model, CPU ranks) through ``cornserve up`` -> gateway -> dispatcher -> Eric -> sidecar -> LLM."""
 
 import json
+import socket
 import subprocess
 import sys
 from pathlib import Path
@@ -203,3 +204,25 @@ def test_bench_repeats_a_failed_tensor_parallel_layout_with_one_gpu_executors():
     assert line["fallback_from"]["parallelism"] == "eric tp2 x1 + llm tp2 x1" and "made to fail" in line["fallback_from"]["reason"]
     assert sorted(e["executor"] for e in line["executors"]) == ["eric", "eric", "llm", "llm"]
     assert all(s["failed"] == 0 and s["completed"] == s["sent"] > 0 for s in line["sweep"])
+
+
+@pytest.mark.timeout(1500)
+def test_bench_under_the_launcher_with_four_ranks_prints_one_line():
+    """``torch.distributed.run`` with four (gloo) ranks: rank 0 deploys the TP 2 + TP 2 layout, whose executors form their
+    own process groups although the launcher's rendezvous variables are set around them; standard output carries the one
+    result line and nothing else."""
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), "bench.py", "--gpus", "4", "--cpu", "--small",
+                          "--slab-mib", "8", "--steps", "2", "--warmup", "1", "--window-s", "3", "--offline-steps", "0",
+                          "--rates", "2", "--output-tokens", "8", "--no-fallback"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=1400)
+    assert out.returncode == 0, out.stderr[-3000:]
+    lines = out.stdout.strip().splitlines()
+    assert len(lines) == 1, lines[:5]
+    line = json.loads(lines[0])
+    assert line["n_gpus"] == 4 and line["config"]["parallelism"] == "eric tp2 x1 + llm tp2 x1" and "fallback_from" not in line
+    assert all(s["failed"] == 0 and s["completed"] == s["sent"] > 0 for s in line["sweep"])
+    assert sorted((e["executor"], e["tp_size"]) for e in line["executors"]) == [("eric", 2), ("llm", 2)]
